@@ -1,0 +1,745 @@
+// Fused block-Hadamard rotation + micro-scaled FP4 quantisation (MXFP4 / NVFP4) for sm_100a.
+//
+// One thread owns 32 contiguous elements of a row (64 B of bf16 = two 128-bit loads, one
+// 256-bit load on sm_100).  Butterfly stages with pair distance <= 16 run in registers, the
+// stages for distance 32 and 64 exchange registers with the neighbouring lanes by warp
+// shuffle.  All rotation arithmetic is IEEE fp32 add/sub/mul in a fixed order (distances
+// 1,2,4,..,g/2, then one multiply by fl32(1/sqrt(g))) so that a CPU can reproduce it bit
+// for bit.  The scale chain and the division that precedes E2M1 rounding reproduce the
+// fp32 operation sequence of the reference Quantizer (src/quantization/quantizer.py:107-168,
+// src/quantization/quant_ops.py:57-94 of IST-DASLab/FP-Quant).
+//
+// The kernel is HBM-bound: 2 B read + 0.5 B codes + 1/g B scale per element.
+
+#include "common.cuh"
+
+namespace fpq {
+namespace {
+
+enum Mode { MODE_CODES = 0, MODE_DEQUANT = 1, MODE_ROTATE = 2, MODE_ABSMAX = 3 };
+
+struct QuantParams {
+  const void* x;
+  int64_t n_chunks;     // rows * cols / 32
+  uint32_t chunks_per_row;
+  uint8_t* codes;       // [rows, cols/2]
+  uint8_t* sbytes;      // scale bytes
+  float* sf32;          // fp32 scales, row-major
+  void* y;              // dequantised / rotated output
+  const float* gs;      // NVFP4 tensor scale
+  uint32_t* absmax_bits;
+  uint32_t sf_tiles_per_row_block;  // ceil((cols/g)/4)
+  int layout;
+  int out_bf16;
+  int ste;
+};
+
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 pack2(float lo, float hi) {
+  u64 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(u64 p, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+__device__ __forceinline__ u64 add2(u64 a, u64 b) {
+  u64 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ u64 sub2(u64 a, u64 b) {
+  u64 r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ u64 mul2(u64 a, u64 b) {
+  u64 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
+  u64 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// 32 contiguous elements -> 16 packed pairs (element 2j in the low half of P[j]).
+template <bool IN_BF16>
+__device__ __forceinline__ void load_chunk(const void* base, int64_t chunk, bool active, u64 (&P)[16]) {
+  if (IN_BF16) {
+    uint32_t w[16];
+    if (active) {
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(base) + chunk * 16;
+      asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]),
+                     "=r"(w[6]), "=r"(w[7])
+                   : "l"(p));
+      asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]),
+                     "=r"(w[14]), "=r"(w[15])
+                   : "l"(p + 8));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) w[j] = 0;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      P[j] = pack2(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u));
+  } else {
+    if (active) {
+      const u64* p = reinterpret_cast<const u64*>(base) + chunk * 16;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        asm volatile("ld.global.nc.L1::no_allocate.v4.b64 {%0,%1,%2,%3}, [%4];"
+                     : "=l"(P[4 * q]), "=l"(P[4 * q + 1]), "=l"(P[4 * q + 2]), "=l"(P[4 * q + 3])
+                     : "l"(p + 4 * q));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) P[j] = 0ull;
+    }
+  }
+}
+
+// Butterfly stages with pair distance 1..min(GH,32)/2 inside the thread, then the
+// cross-lane stages for distance 32 (GH >= 64) and 64 (GH == 128), then * 1/sqrt(GH).
+template <int GH>
+__device__ __forceinline__ void rotate_chunk(u64 (&P)[16], int lane) {
+  if (GH == 0) return;
+  // distance 1: inside each packed pair
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float a, b;
+    unpack2(P[j], a, b);
+    P[j] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));
+  }
+  // distances 2, 4, 8, 16 <-> pair index distance 1, 2, 4, 8
+#pragma unroll
+  for (int d = 1; d < 16; d <<= 1) {
+    if (2 * d < (GH < 32 ? GH : 32)) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if ((j & d) == 0) {
+          u64 a = P[j], b = P[j + d];
+          P[j] = add2(a, b);
+          P[j + d] = sub2(a, b);
+        }
+      }
+    }
+  }
+  if (GH >= 64) {
+#pragma unroll
+    for (int bit = 1; bit < GH / 32; bit <<= 1) {
+      const float sgn = (lane & bit) ? -1.0f : 1.0f;
+      const u64 S = pack2(sgn, sgn);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        u64 other = __shfl_xor_sync(0xffffffffu, P[j], bit);
+        P[j] = fma2(S, P[j], other);  // bit clear: own + other, bit set: other - own
+      }
+    }
+  }
+  const float c = GH == 16 ? 0.25f : GH == 32 ? 0.17677669529663687f : GH == 64 ? 0.125f : 0.08838834764831845f;
+  const u64 C = pack2(c, c);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) P[j] = mul2(P[j], C);
+}
+
+__device__ __forceinline__ float absmax_pairs(const u64* P, int n) {
+  float m = 0.0f;
+#pragma unroll
+  for (int j = 0; j < n; ++j) {
+    float a, b;
+    unpack2(P[j], a, b);
+    m = fmaxf(m, fmaxf(fabsf(a), fabsf(b)));
+  }
+  return m;
+}
+
+// floor(fl32(log2(m))) as torch's fp32 log2 yields it: the exponent field, plus one when m is
+// so close below a power of two that the correctly rounded fp32 logarithm is that integer.
+__device__ __forceinline__ int mx_exponent(float m /* >= 2^-126, finite */) {
+  uint32_t b = __float_as_uint(m);
+  int e = (int)(b >> 23) - 127;
+  if ((b & 0x7fffffu) >= 0x7fff00u) {
+    float l = (float)log2((double)m);
+    e = (int)floorf(l);
+  }
+  return max(-127, min(127, e));
+}
+
+// MXFP4 scale of one 32-element group: returns the divisor s and the stored byte.
+__device__ __forceinline__ float mx_scale(float a, uint32_t& byte) {
+  float s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
+  float m = fmaxf(__fmul_rn(6.0f, s0), 1.17549435e-38f);
+  int e = mx_exponent(m);
+  byte = (uint32_t)(e + 127);
+  float s;
+  if (e >= -124) {
+    // fl(2^(e-2) / 0.75) = 2^(e-2) * fl(4/3): exponent field e-2+127, mantissa of fl(4/3)
+    s = __uint_as_float(((uint32_t)(e + 125) << 23) | 0x2aaaabu);
+  } else {
+    s = __fdiv_rn(ldexpf(1.0f, e - 2), 0.75f);  // subnormal power of two
+    if (s == 0.0f) s = 1.0f;
+  }
+  return s;
+}
+
+// NVFP4 scale of one 16-element group.
+__device__ __forceinline__ float nv_scale(float a, float gs, float rgs, uint32_t& byte) {
+  float s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
+  float t = fminf(fmaxf(__fmul_rn(s0, gs), -448.0f), 448.0f);
+  uint16_t u2;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(u2) : "f"(0.0f), "f"(t));
+  uint32_t u = u2 & 0xffu;
+  // decode the (non-negative) E4M3 byte exactly: (8+m) * 2^(e-10), or m * 2^-9 when e == 0
+  uint32_t ex = u >> 3, ma = u & 7u;
+  float uf = ex == 0 ? (float)ma * 0.001953125f : __uint_as_float(((ex + 120u) << 23) | (ma << 20));
+  float s = __fmul_rn(uf, rgs);
+  byte = u;
+  return s == 0.0f ? 1.0f : s;
+}
+
+// Correctly rounded y / s for the pairs P[0..n): reciprocal once per group, then the classic
+// multiply + two fused residual corrections, two elements per instruction.  Falls back to
+// per-element IEEE division when s is so small or large that the reciprocal or a residual
+// could leave the normal range.
+__device__ __forceinline__ void divide_pairs(u64* P, int n, float s) {
+  const float as = fabsf(s);
+  if (as > 7.8886e-31f /* 2^-100 */ && as < 1.2676e30f /* 2^100 */) {
+    const float r = __frcp_rn(s);
+    const u64 R = pack2(r, r), NS = pack2(-s, -s);
+#pragma unroll
+    for (int j = 0; j < n; ++j) {
+      u64 y = P[j];
+      u64 q = mul2(y, R);
+      u64 e = fma2(q, NS, y);
+      q = fma2(e, R, q);
+      e = fma2(q, NS, y);
+      P[j] = fma2(e, R, q);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < n; ++j) {
+      float a, b;
+      unpack2(P[j], a, b);
+      P[j] = pack2(__fdiv_rn(a, s), __fdiv_rn(b, s));
+    }
+  }
+}
+
+// Eight quotients (4 pairs) -> one word of eight 4-bit codes, element 0 in the lowest nibble.
+__device__ __forceinline__ uint32_t codes_word(const u64* P) {
+  uint32_t w = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float a, b;
+    unpack2(P[j], a, b);
+    uint32_t byte;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t; }"
+        : "=r"(byte)
+        : "f"(b), "f"(a));
+    w |= byte << (8 * j);
+  }
+  return patch_zero_codes(w);
+}
+
+__device__ __forceinline__ size_t swizzled_offset(uint32_t row, uint32_t sfc, uint32_t tiles_per_row_block) {
+  return ((size_t)(row >> 7) * tiles_per_row_block + (sfc >> 2)) * 512u + (row & 31u) * 16u +
+         ((row >> 5) & 3u) * 4u + (sfc & 3u);
+}
+
+template <int GH, int FMT, bool IN_BF16, int MODE>
+__global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  float gs = 0.0f, rgs = 0.0f;
+  if (FMT == FPQ_FMT_NVFP4 && (MODE == MODE_CODES || MODE == MODE_DEQUANT)) {
+    gs = *p.gs;
+    rgs = gs == 0.0f ? 0.0f : __frcp_rn(gs);
+  }
+  float running_max = 0.0f;
+
+  for (int64_t cb = warp * 32; cb < p.n_chunks; cb += nwarps * 32) {
+    const int64_t c = cb + lane;
+    const bool active = c < p.n_chunks;
+    u64 P[16];
+    load_chunk<IN_BF16>(p.x, c, active, P);
+    rotate_chunk<GH>(P, lane);
+
+    if (MODE == MODE_ABSMAX) {
+      running_max = fmaxf(running_max, absmax_pairs(P, 16));
+      continue;
+    }
+    if (MODE == MODE_ROTATE) {
+      if (active) {
+        if (p.out_bf16) {
+          uint4* o = reinterpret_cast<uint4*>(p.y) + c * 4;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float a, b;
+              unpack2(P[4 * q + j], a, b);
+              __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            o[q] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+          ulonglong2* o = reinterpret_cast<ulonglong2*>(p.y) + c * 8;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) o[q] = make_ulonglong2(P[2 * q], P[2 * q + 1]);
+        }
+      }
+      continue;
+    }
+
+    // ---- scales
+    constexpr int NG = FMT == FPQ_FMT_NVFP4 ? 2 : 1;  // groups per thread
+    constexpr int PG = 16 / NG;                       // pairs per group
+    float s[NG];
+    uint32_t sb[NG];
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      float a = absmax_pairs(P + g * PG, PG);
+      s[g] = FMT == FPQ_FMT_NVFP4 ? nv_scale(a, gs, rgs, sb[g]) : mx_scale(a, sb[g]);
+    }
+    if (MODE == MODE_CODES && active) {
+      const uint32_t row = (uint32_t)(c / p.chunks_per_row);
+      const uint32_t cir = (uint32_t)(c - (int64_t)row * p.chunks_per_row);
+      if (p.sbytes) {
+        const uint32_t sfc = cir * NG;
+        size_t off = p.layout == FPQ_SCALES_SWIZZLED
+                         ? swizzled_offset(row, sfc, p.sf_tiles_per_row_block)
+                         : (size_t)c * NG;
+        if (NG == 2)
+          *reinterpret_cast<uint16_t*>(p.sbytes + off) = (uint16_t)(sb[0] | (sb[NG - 1] << 8));
+        else
+          p.sbytes[off] = (uint8_t)sb[0];
+      }
+      if (p.sf32) {
+        if (NG == 2)
+          *reinterpret_cast<float2*>(p.sf32 + c * 2) = make_float2(s[0], s[NG - 1]);
+        else
+          p.sf32[c] = s[0];
+      }
+    }
+    if (MODE == MODE_CODES && p.codes == nullptr) continue;
+
+    // ---- keep the rotated values when the straight-through form needs them
+    u64 Y[MODE == MODE_DEQUANT ? 16 : 1];
+    if (MODE == MODE_DEQUANT) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) Y[j] = P[j];
+    }
+
+#pragma unroll
+    for (int g = 0; g < NG; ++g) divide_pairs(P + g * PG, PG, s[g]);
+
+    uint32_t cw[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) cw[q] = codes_word(P + 4 * q);
+
+    if (MODE == MODE_CODES) {
+      if (active) reinterpret_cast<uint4*>(p.codes)[c] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+    } else {  // MODE_DEQUANT
+      float out[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float sc = s[(i * NG) / 32];
+        float v = __fmul_rn(e2m1_value((cw[i / 8] >> (4 * (i % 8))) & 15u), sc);
+        if (p.ste) {
+          float a, b;
+          unpack2(Y[i / 2], a, b);
+          const float x = (i & 1) ? b : a;
+          v = __fadd_rn(x, __fsub_rn(v, x));
+        }
+        out[i] = v;
+      }
+      if (active) {
+        if (p.out_bf16) {
+          uint4* o = reinterpret_cast<uint4*>(p.y) + c * 4;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(out[8 * q + 2 * j], out[8 * q + 2 * j + 1]);
+              w[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            o[q] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+          float4* o = reinterpret_cast<float4*>(p.y) + c * 8;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            o[q] = make_float4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
+        }
+      }
+    }
+  }
+
+  if (MODE == MODE_ABSMAX) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      running_max = fmaxf(running_max, __shfl_xor_sync(0xffffffffu, running_max, o));
+    if (lane == 0) atomicMax(p.absmax_bits, __float_as_uint(running_max));
+  }
+}
+
+template <int GH, int FMT, bool IN_BF16, int MODE>
+int launch_one(const QuantParams& p, cudaStream_t stream) {
+  const int64_t warps_needed = ceil_div64(p.n_chunks, 32);
+  const int64_t blocks_needed = ceil_div64(warps_needed, 8);
+  int64_t blocks = (int64_t)sm_count() * 8;
+  if (blocks > blocks_needed) blocks = blocks_needed;
+  if (blocks < 1) blocks = 1;
+  quant_kernel<GH, FMT, IN_BF16, MODE><<<(unsigned)blocks, 256, 0, stream>>>(p);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+template <int FMT, bool IN_BF16, int MODE>
+int launch_gh(int gh, const QuantParams& p, cudaStream_t stream) {
+  switch (gh) {
+    case 0: return launch_one<0, FMT, IN_BF16, MODE>(p, stream);
+    case 16: return launch_one<16, FMT, IN_BF16, MODE>(p, stream);
+    case 32: return launch_one<32, FMT, IN_BF16, MODE>(p, stream);
+    case 64: return launch_one<64, FMT, IN_BF16, MODE>(p, stream);
+    case 128: return launch_one<128, FMT, IN_BF16, MODE>(p, stream);
+  }
+  set_error("hadamard_group must be 0, 16, 32, 64 or 128 (got %d)", gh);
+  return FPQ_ERR_INVALID_ARGUMENT;
+}
+
+template <int MODE>
+int launch_mode(int gh, int fmt, int dtype, const QuantParams& p, cudaStream_t stream) {
+  if constexpr (MODE == MODE_ROTATE || MODE == MODE_ABSMAX) {
+    return dtype == FPQ_DT_BF16 ? launch_gh<FPQ_FMT_MXFP4, true, MODE>(gh, p, stream)
+                                : launch_gh<FPQ_FMT_MXFP4, false, MODE>(gh, p, stream);
+  } else {
+    if (fmt == FPQ_FMT_MXFP4)
+      return dtype == FPQ_DT_BF16 ? launch_gh<FPQ_FMT_MXFP4, true, MODE>(gh, p, stream)
+                                  : launch_gh<FPQ_FMT_MXFP4, false, MODE>(gh, p, stream);
+    return dtype == FPQ_DT_BF16 ? launch_gh<FPQ_FMT_NVFP4, true, MODE>(gh, p, stream)
+                                : launch_gh<FPQ_FMT_NVFP4, false, MODE>(gh, p, stream);
+  }
+}
+
+int check_common(const void* x, int dtype, int64_t rows, int64_t cols, int gh) {
+  FPQ_CHECK_ARG(x != nullptr, "x is NULL");
+  FPQ_CHECK_ARG(dtype == FPQ_DT_BF16 || dtype == FPQ_DT_F32, "dtype must be FPQ_DT_BF16 or FPQ_DT_F32");
+  FPQ_CHECK_ARG(rows >= 0 && cols > 0, "bad shape [%lld, %lld]", (long long)rows, (long long)cols);
+  FPQ_CHECK_ARG(cols % 32 == 0, "cols (%lld) must be a multiple of 32", (long long)cols);
+  FPQ_CHECK_ARG(gh == 0 || gh == 16 || gh == 32 || gh == 64 || gh == 128,
+                "hadamard_group must be 0, 16, 32, 64 or 128 (got %d)", gh);
+  FPQ_CHECK_ARG(gh == 0 || cols % gh == 0, "cols (%lld) must be a multiple of the hadamard group %d",
+                (long long)cols, gh);
+  FPQ_CHECK_ARG(((uintptr_t)x & 31) == 0, "x must be 32-byte aligned");
+  FPQ_CHECK_ARG(rows * cols / 32 < (int64_t)1 << 40, "tensor too large");
+  return FPQ_OK;
+}
+
+// ------------------------------------------------------------------ auxiliary kernels
+__global__ void global_scale_update_kernel(const uint32_t* absmax_bits, float* gs, int32_t* status) {
+  float a = __uint_as_float(*absmax_bits);
+  if (a == 0.0f) {
+    if (status) *status = 1;
+    return;
+  }
+  float cur = __fmul_rn(2688.0f, __fdiv_rn(1.0f, a));
+  *gs = fminf(*gs, cur);
+  if (status) *status = 0;
+}
+
+template <bool IN_BF16>
+__global__ void __launch_bounds__(256) apply_scales_kernel(const void* x, int64_t n_words, uint32_t cols,
+                                                           const float* scales, uint32_t group, int out_kind,
+                                                           void* out) {
+  // one thread per 8 consecutive elements (one word of codes)
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words;
+       w += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t e0 = w * 8;
+    const int64_t row = e0 / cols;
+    const uint32_t col = (uint32_t)(e0 - row * cols);
+    const float s = scales[row * (cols / group) + col / group];
+    float v[8];
+    if (IN_BF16) {
+      uint4 raw = reinterpret_cast<const uint4*>(x)[w];
+      const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(r[j] << 16);
+        v[2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u);
+      }
+    } else {
+      float4 a = reinterpret_cast<const float4*>(x)[2 * w], b = reinterpret_cast<const float4*>(x)[2 * w + 1];
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    uint32_t word = 0;
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t code = e2m1_code(__fdiv_rn(v[j], s));
+      word |= code << (4 * j);
+      float g = e2m1_value(code);
+      if (out_kind == FPQ_OUT_GRID) o[j] = g;
+      else {
+        float d = __fmul_rn(g, s);
+        o[j] = out_kind == FPQ_OUT_DEQUANT_STE ? __fadd_rn(v[j], __fsub_rn(d, v[j])) : d;
+      }
+    }
+    if (out_kind == FPQ_OUT_CODES) {
+      reinterpret_cast<uint32_t*>(out)[w] = word;
+    } else if (IN_BF16) {
+      uint32_t r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(o[2 * j], o[2 * j + 1]);
+        r[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      reinterpret_cast<uint4*>(out)[w] = make_uint4(r[0], r[1], r[2], r[3]);
+    } else {
+      reinterpret_cast<float4*>(out)[2 * w] = make_float4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<float4*>(out)[2 * w + 1] = make_float4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
+template <bool IN_BF16>
+__global__ void __launch_bounds__(256) pack_grid_kernel(const void* q, int64_t n_words, uint32_t* packed) {
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words;
+       w += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    if (IN_BF16) {
+      uint4 raw = reinterpret_cast<const uint4*>(q)[w];
+      const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(r[j] << 16);
+        v[2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u);
+      }
+    } else {
+      float4 a = reinterpret_cast<const float4*>(q)[2 * w], b = reinterpret_cast<const float4*>(q)[2 * w + 1];
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) word |= e2m1_code(v[j]) << (4 * j);
+    packed[w] = word;
+  }
+}
+
+__global__ void __launch_bounds__(256) swizzle_scales_kernel(const uint8_t* __restrict__ src, uint32_t rows,
+                                                             uint32_t sf_cols, uint32_t rows_pad,
+                                                             uint32_t tiles_per_row_block,
+                                                             uint32_t* __restrict__ dst) {
+  // one thread per destination word (4 scale bytes of one row inside one tile)
+  const int64_t n_words = (int64_t)rows_pad * tiles_per_row_block;
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words;
+       w += (int64_t)gridDim.x * blockDim.x) {
+    const uint32_t tile = (uint32_t)(w >> 7), in_tile = (uint32_t)(w & 127);
+    const uint32_t rb = tile / tiles_per_row_block, kb = tile - rb * tiles_per_row_block;
+    const uint32_t row = rb * 128 + (in_tile & 3u) * 32 + (in_tile >> 2);
+    uint32_t word = 0;
+    if (row < rows) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t c = kb * 4 + j;
+        if (c < sf_cols) word |= (uint32_t)src[(size_t)row * sf_cols + c] << (8 * j);
+      }
+    }
+    dst[w] = word;
+  }
+}
+
+__global__ void __launch_bounds__(128) rotate_dense_kernel(const void* x, int in_bf16, void* y, int out_bf16,
+                                                           int64_t n_groups, int g, const float* matrix) {
+  // one warp per group; the g x g matrix lives in shared memory
+  extern __shared__ float sm[];
+  float* M = sm;                  // g * g
+  float* xs = sm + g * g;         // 4 warps * g
+  for (int i = threadIdx.x; i < g * g; i += blockDim.x) M[i] = matrix[i];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  float* xw = xs + wid * g;
+  for (int64_t grp = (int64_t)blockIdx.x * 4 + wid; grp < n_groups; grp += (int64_t)gridDim.x * 4) {
+    for (int i = lane; i < g; i += 32)
+      xw[i] = in_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[grp * g + i])
+                      : reinterpret_cast<const float*>(x)[grp * g + i];
+    __syncwarp();
+    for (int j = lane; j < g; j += 32) {
+      float acc = 0.0f;
+      for (int k = 0; k < g; ++k) acc = __fadd_rn(acc, __fmul_rn(xw[k], M[k * g + j]));
+      if (out_bf16) reinterpret_cast<__nv_bfloat16*>(y)[grp * g + j] = __float2bfloat16_rn(acc);
+      else reinterpret_cast<float*>(y)[grp * g + j] = acc;
+    }
+    __syncwarp();
+  }
+}
+
+int grid_for(int64_t work_items, int threads) {
+  int64_t b = ceil_div64(work_items, threads);
+  int64_t cap = (int64_t)sm_count() * 16;
+  if (b > cap) b = cap;
+  return (int)(b < 1 ? 1 : b);
+}
+
+}  // namespace
+}  // namespace fpq
+
+using namespace fpq;
+
+extern "C" int fpq_rotate_hadamard(const void* x, int dtype_in, void* y, int dtype_out, int64_t rows,
+                                   int64_t cols, int group, fpq_stream_t stream) {
+  if (int rc = check_common(x, dtype_in, rows, cols, group)) return rc;
+  FPQ_CHECK_ARG(group != 0, "group must be 16, 32, 64 or 128");
+  FPQ_CHECK_ARG(y != nullptr && ((uintptr_t)y & 15) == 0, "y must be non-NULL and 16-byte aligned");
+  FPQ_CHECK_ARG(dtype_out == FPQ_DT_BF16 || dtype_out == FPQ_DT_F32, "bad dtype_out");
+  FPQ_CHECK_ARG(x != y || dtype_in == dtype_out, "in-place rotation needs equal dtypes");
+  if (rows == 0) return FPQ_OK;
+  QuantParams p{};
+  p.x = x;
+  p.n_chunks = rows * cols / 32;
+  p.chunks_per_row = (uint32_t)(cols / 32);
+  p.y = y;
+  p.out_bf16 = dtype_out == FPQ_DT_BF16;
+  return launch_mode<MODE_ROTATE>(group, 0, dtype_in, p, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_rotate_dense(const void* x, int dtype_in, void* y, int dtype_out, int64_t rows,
+                                int64_t cols, int group, const float* matrix, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(x && y && matrix, "NULL pointer");
+  FPQ_CHECK_ARG(group == 16 || group == 32 || group == 64 || group == 128, "group must be 16, 32, 64 or 128");
+  FPQ_CHECK_ARG(rows >= 0 && cols > 0 && cols % group == 0, "cols must be a multiple of group");
+  FPQ_CHECK_ARG(x != y, "fpq_rotate_dense cannot run in place");
+  if (rows == 0) return FPQ_OK;
+  const int64_t n_groups = rows * cols / group;
+  const size_t smem = (size_t)(group * group + 4 * group) * sizeof(float);
+  FPQ_CHECK_CUDA(cudaFuncSetAttribute(rotate_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  rotate_dense_kernel<<<grid_for(n_groups, 4), 128, smem, (cudaStream_t)stream>>>(
+      x, dtype_in == FPQ_DT_BF16, y, dtype_out == FPQ_DT_BF16, n_groups, group, matrix);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+extern "C" int fpq_absmax(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+                          uint32_t* absmax_bits, fpq_stream_t stream) {
+  if (int rc = check_common(x, dtype, rows, cols, hadamard_group)) return rc;
+  FPQ_CHECK_ARG(absmax_bits != nullptr, "absmax_bits is NULL");
+  if (rows == 0) return FPQ_OK;
+  QuantParams p{};
+  p.x = x;
+  p.n_chunks = rows * cols / 32;
+  p.chunks_per_row = (uint32_t)(cols / 32);
+  p.absmax_bits = absmax_bits;
+  return launch_mode<MODE_ABSMAX>(hadamard_group, 0, dtype, p, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_global_scale_update(const uint32_t* absmax_bits, float* global_scale, int32_t* status,
+                                       fpq_stream_t stream) {
+  FPQ_CHECK_ARG(absmax_bits && global_scale, "NULL pointer");
+  global_scale_update_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(absmax_bits, global_scale, status);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+extern "C" int fpq_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+                            int format, const float* global_scale, uint8_t* codes, uint8_t* scale_bytes,
+                            int scale_layout, float* scales_f32, fpq_stream_t stream) {
+  if (int rc = check_common(x, dtype, rows, cols, hadamard_group)) return rc;
+  FPQ_CHECK_ARG(format == FPQ_FMT_MXFP4 || format == FPQ_FMT_NVFP4, "format must be FPQ_FMT_MXFP4 or FPQ_FMT_NVFP4");
+  FPQ_CHECK_ARG(format != FPQ_FMT_NVFP4 || global_scale != nullptr, "NVFP4 needs a global_scale pointer");
+  FPQ_CHECK_ARG(scale_layout == FPQ_SCALES_ROWMAJOR || scale_layout == FPQ_SCALES_SWIZZLED, "bad scale_layout");
+  FPQ_CHECK_ARG(codes || scale_bytes || scales_f32, "no output requested");
+  FPQ_CHECK_ARG(((uintptr_t)codes & 15) == 0 && ((uintptr_t)scale_bytes & 15) == 0 && ((uintptr_t)scales_f32 & 15) == 0,
+                "outputs must be 16-byte aligned");
+  if (rows == 0) return FPQ_OK;
+  const int g = format == FPQ_FMT_NVFP4 ? 16 : 32;
+  QuantParams p{};
+  p.x = x;
+  p.n_chunks = rows * cols / 32;
+  p.chunks_per_row = (uint32_t)(cols / 32);
+  p.codes = codes;
+  p.sbytes = scale_bytes;
+  p.sf32 = scales_f32;
+  p.gs = global_scale;
+  p.sf_tiles_per_row_block = (uint32_t)ceil_div64(cols / g, 4);
+  p.layout = scale_layout;
+  return launch_mode<MODE_CODES>(hadamard_group, format, dtype, p, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+                                 int format, const float* global_scale, void* y, int ste, fpq_stream_t stream) {
+  if (int rc = check_common(x, dtype, rows, cols, hadamard_group)) return rc;
+  FPQ_CHECK_ARG(format == FPQ_FMT_MXFP4 || format == FPQ_FMT_NVFP4, "format must be FPQ_FMT_MXFP4 or FPQ_FMT_NVFP4");
+  FPQ_CHECK_ARG(format != FPQ_FMT_NVFP4 || global_scale != nullptr, "NVFP4 needs a global_scale pointer");
+  FPQ_CHECK_ARG(y != nullptr && ((uintptr_t)y & 15) == 0, "y must be non-NULL and 16-byte aligned");
+  if (rows == 0) return FPQ_OK;
+  QuantParams p{};
+  p.x = x;
+  p.n_chunks = rows * cols / 32;
+  p.chunks_per_row = (uint32_t)(cols / 32);
+  p.y = y;
+  p.gs = global_scale;
+  p.out_bf16 = dtype == FPQ_DT_BF16;
+  p.ste = ste;
+  return launch_mode<MODE_DEQUANT>(hadamard_group, format, dtype, p, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_apply_scales(const void* x, int dtype, int64_t rows, int64_t cols, const float* scales,
+                                int group, int out_kind, void* out, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(x && scales && out, "NULL pointer");
+  FPQ_CHECK_ARG(dtype == FPQ_DT_BF16 || dtype == FPQ_DT_F32, "bad dtype");
+  FPQ_CHECK_ARG(rows >= 0 && cols > 0 && group > 0 && cols % group == 0 && group % 8 == 0,
+                "group (%d) must be a multiple of 8 dividing cols (%lld)", group, (long long)cols);
+  FPQ_CHECK_ARG(out_kind >= FPQ_OUT_CODES && out_kind <= FPQ_OUT_DEQUANT_STE, "bad out_kind");
+  FPQ_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0, "x and out must be 16-byte aligned");
+  FPQ_CHECK_ARG(cols < ((int64_t)1 << 31), "cols too large");
+  if (rows == 0) return FPQ_OK;
+  const int64_t n_words = rows * cols / 8;
+  const int grid = grid_for(n_words, 256);
+  if (dtype == FPQ_DT_BF16)
+    apply_scales_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(x, n_words, (uint32_t)cols, scales, (uint32_t)group, out_kind, out);
+  else
+    apply_scales_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(x, n_words, (uint32_t)cols, scales, (uint32_t)group, out_kind, out);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+extern "C" int fpq_pack_grid(const void* q, int dtype, int64_t rows, int64_t cols, uint8_t* packed,
+                             fpq_stream_t stream) {
+  FPQ_CHECK_ARG(q && packed, "NULL pointer");
+  FPQ_CHECK_ARG(dtype == FPQ_DT_BF16 || dtype == FPQ_DT_F32, "bad dtype");
+  FPQ_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0, "cols must be a multiple of 8");
+  FPQ_CHECK_ARG(((uintptr_t)q & 15) == 0 && ((uintptr_t)packed & 3) == 0, "bad alignment");
+  if (rows == 0) return FPQ_OK;
+  const int64_t n_words = rows * cols / 8;
+  const int grid = grid_for(n_words, 256);
+  if (dtype == FPQ_DT_BF16)
+    pack_grid_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(q, n_words, reinterpret_cast<uint32_t*>(packed));
+  else
+    pack_grid_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(q, n_words, reinterpret_cast<uint32_t*>(packed));
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+extern "C" int fpq_swizzle_scales(const uint8_t* rowmajor, int64_t rows, int64_t sf_cols, uint8_t* swizzled,
+                                  fpq_stream_t stream) {
+  FPQ_CHECK_ARG(rowmajor && swizzled, "NULL pointer");
+  FPQ_CHECK_ARG(rows > 0 && sf_cols > 0 && rows < ((int64_t)1 << 31) && sf_cols < ((int64_t)1 << 31), "bad shape");
+  FPQ_CHECK_ARG(((uintptr_t)swizzled & 3) == 0, "swizzled must be 4-byte aligned");
+  const uint32_t rows_pad = (uint32_t)(ceil_div64(rows, 128) * 128);
+  const uint32_t tprb = (uint32_t)ceil_div64(sf_cols, 4);
+  const int64_t n_words = (int64_t)rows_pad * tprb;
+  swizzle_scales_kernel<<<grid_for(n_words, 256), 256, 0, (cudaStream_t)stream>>>(
+      rowmajor, (uint32_t)rows, (uint32_t)sf_cols, rows_pad, tprb, reinterpret_cast<uint32_t*>(swizzled));
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}

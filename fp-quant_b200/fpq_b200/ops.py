@@ -1,0 +1,161 @@
+"""Tensor-level wrappers over the C ABI: allocate outputs with torch, pass raw
+pointers and the current CUDA stream, never synchronise."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi as C
+
+FORMATS = {"mxfp4": C.FMT_MXFP4, "nvfp4": C.FMT_NVFP4}
+GROUP_OF = {"mxfp4": 32, "nvfp4": 16}
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return C.DT_BF16
+    if t.dtype == torch.float32:
+        return C.DT_F32
+    raise ValueError(f"fpq_b200 kernels take bfloat16 or float32 tensors, got {t.dtype}")
+
+
+def _cuda(t: torch.Tensor, name: str = "tensor") -> torch.Tensor:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: fpq_b200 has no CPU path")
+    return t
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _2d(x: torch.Tensor) -> Tuple[torch.Tensor, int, int]:
+    x = _cuda(x, "x").contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    return x, rows, cols
+
+
+def padded_scale_shape(rows: int, sf_cols: int) -> Tuple[int, int]:
+    return ((rows + 127) // 128) * 128, ((sf_cols + 3) // 4) * 4
+
+
+def rotate_hadamard(x: torch.Tensor, group: int, out_dtype: Optional[torch.dtype] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    x, rows, cols = _2d(x)
+    if out is None:
+        out = torch.empty_like(x, dtype=out_dtype or x.dtype)
+    with torch.cuda.device(x.device):
+        C.call("fpq_rotate_hadamard", x.data_ptr(), _dt(x), out.data_ptr(), _dt(out), rows, cols, group, _stream(x))
+    return out
+
+
+def rotate_dense(x: torch.Tensor, matrix: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    x, rows, cols = _2d(x)
+    m = _cuda(matrix, "matrix").to(torch.float32).contiguous()
+    out = torch.empty_like(x, dtype=out_dtype or x.dtype)
+    with torch.cuda.device(x.device):
+        C.call("fpq_rotate_dense", x.data_ptr(), _dt(x), out.data_ptr(), _dt(out), rows, cols, m.shape[0],
+               m.data_ptr(), _stream(x))
+    return out
+
+
+def absmax_bits(x: torch.Tensor, hadamard_group: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """uint32 bit pattern (held in an int32 tensor) of max |rotate(x)|."""
+    x, rows, cols = _2d(x)
+    if out is None:
+        out = torch.zeros(1, dtype=torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        C.call("fpq_absmax", x.data_ptr(), _dt(x), rows, cols, hadamard_group, out.data_ptr(), _stream(x))
+    return out
+
+
+def global_scale_update(bits: torch.Tensor, global_scale: torch.Tensor,
+                        status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    assert global_scale.dtype == torch.float32 and global_scale.is_cuda
+    with torch.cuda.device(bits.device):
+        C.call("fpq_global_scale_update", bits.data_ptr(), global_scale.data_ptr(), _ptr(status), _stream(bits))
+    return global_scale
+
+
+def quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0, global_scale: Optional[torch.Tensor] = None,
+             codes: bool = True, scale_bytes: bool = True, swizzled: bool = False, scales_f32: bool = False):
+    """Returns (codes u8 [rows, cols/2] | None, scale bytes | None, fp32 scales | None)."""
+    x, rows, cols = _2d(x)
+    g = GROUP_OF[fmt]
+    sf_cols = cols // g
+    dev = x.device
+    q = torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev) if codes else None
+    sb = None
+    if scale_bytes:
+        if swizzled:
+            pr, pc = padded_scale_shape(rows, sf_cols)
+            alloc = torch.zeros if (pr != rows or pc != sf_cols) else torch.empty
+            sb = alloc(pr, pc, dtype=torch.uint8, device=dev)
+        else:
+            sb = torch.empty(rows, sf_cols, dtype=torch.uint8, device=dev)
+    sf = torch.empty(rows, sf_cols, dtype=torch.float32, device=dev) if scales_f32 else None
+    if fmt == "nvfp4":
+        if global_scale is None:
+            raise ValueError("nvfp4 needs a global_scale tensor")
+        global_scale = _cuda(global_scale, "global_scale").to(torch.float32)
+    with torch.cuda.device(dev):
+        C.call("fpq_quantize", x.data_ptr(), _dt(x), rows, cols, hadamard_group, FORMATS[fmt],
+               _ptr(global_scale) if fmt == "nvfp4" else None, _ptr(q), _ptr(sb),
+               C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _ptr(sf), _stream(x))
+    return q, sb, sf
+
+
+def fake_quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0,
+                  global_scale: Optional[torch.Tensor] = None, ste: bool = False) -> torch.Tensor:
+    shape = x.shape
+    x, rows, cols = _2d(x)
+    y = torch.empty_like(x)
+    if fmt == "nvfp4":
+        if global_scale is None:
+            raise ValueError("nvfp4 needs a global_scale tensor")
+        global_scale = _cuda(global_scale, "global_scale").to(torch.float32)
+    with torch.cuda.device(x.device):
+        C.call("fpq_fake_quantize", x.data_ptr(), _dt(x), rows, cols, hadamard_group, FORMATS[fmt],
+               _ptr(global_scale) if fmt == "nvfp4" else None, y.data_ptr(), int(ste), _stream(x))
+    return y.view(shape)
+
+
+def apply_scales(x: torch.Tensor, scales: torch.Tensor, group: int, out_kind: int) -> torch.Tensor:
+    x, rows, cols = _2d(x)
+    s = _cuda(scales, "scales").to(torch.float32).contiguous()
+    assert s.numel() == rows * (cols // group), "scales must be [rows, cols/group]"
+    if out_kind == C.OUT_CODES:
+        out = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    else:
+        out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        C.call("fpq_apply_scales", x.data_ptr(), _dt(x), rows, cols, s.data_ptr(), group, out_kind,
+               out.data_ptr(), _stream(x))
+    return out
+
+
+def pack_grid(q: torch.Tensor) -> torch.Tensor:
+    q, rows, cols = _2d(q)
+    out = torch.empty(rows, cols // 2, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        C.call("fpq_pack_grid", q.data_ptr(), _dt(q), rows, cols, out.data_ptr(), _stream(q))
+    return out
+
+
+def swizzle_scales(sb: torch.Tensor) -> torch.Tensor:
+    sb = _cuda(sb, "scales")
+    if sb.dtype != torch.uint8:
+        sb = sb.view(torch.uint8)
+    sb = sb.contiguous()
+    rows, sf_cols = sb.shape
+    pr, pc = padded_scale_shape(rows, sf_cols)
+    out = torch.empty(pr, pc, dtype=torch.uint8, device=sb.device)
+    with torch.cuda.device(sb.device):
+        C.call("fpq_swizzle_scales", sb.data_ptr(), rows, sf_cols, out.data_ptr(), _stream(sb))
+    return out

@@ -1,0 +1,143 @@
+/*
+ * fpq_b200 -- C ABI of the B200 (sm_100a) MR-GPTQ hot-path library.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream
+ * (cudaStream_t passed as void*), launches on that stream without synchronising,
+ * allocates nothing (the caller owns inputs, outputs and workspaces) and returns
+ * FPQ_OK or a negative status; fpq_last_error() gives the text of the calling
+ * thread's last failure.  Citations name the file and lines of IST-DASLab/FP-Quant
+ * whose behaviour the entry point replaces.
+ */
+#ifndef FPQ_B200_H_
+#define FPQ_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define FPQ_OK 0
+#define FPQ_ERR_INVALID_ARGUMENT (-1)
+#define FPQ_ERR_CUDA (-2)
+#define FPQ_ERR_UNSUPPORTED_DEVICE (-3)
+#define FPQ_ERR_DEVICE_TIMEOUT (-4)
+#define FPQ_ERR_NOT_POSITIVE_DEFINITE (-5)
+
+/* element formats */
+#define FPQ_FMT_MXFP4 0 /* E2M1 codes, one E8M0 scale per 32 elements */
+#define FPQ_FMT_NVFP4 1 /* E2M1 codes, one E4M3 scale per 16 elements + fp32 tensor scale */
+
+/* tensor dtypes */
+#define FPQ_DT_BF16 0
+#define FPQ_DT_F32 1
+
+/* layouts of the scale bytes */
+#define FPQ_SCALES_ROWMAJOR 0 /* [rows, cols/g] */
+#define FPQ_SCALES_SWIZZLED 1 /* 128x4 tiles, padded to [ceil(rows/128)*128, ceil(cols/g/4)*4] */
+
+/* what fpq_apply_scales writes */
+#define FPQ_OUT_CODES 0      /* packed E2M1 codes, uint8 [rows, cols/2] */
+#define FPQ_OUT_GRID 1       /* E2M1 grid values in the dtype of x */
+#define FPQ_OUT_DEQUANT 2    /* grid value * scale in the dtype of x */
+#define FPQ_OUT_DEQUANT_STE 3 /* fl(x + fl(grid*scale - x)), the value `Quantizer.__call__` returns */
+
+typedef void* fpq_stream_t;
+
+int fpq_version(void);
+const char* fpq_last_error(void);
+
+/* FPQ_OK when `device` is a compute-capability 10.0 GPU. */
+int fpq_check_device(int device);
+
+/*
+ * Block-Hadamard rotation of every contiguous `group` (16/32/64/128) elements of
+ * the last dim: fp32 butterfly, pair distances 1,2,..,group/2, then * fl32(1/sqrt(group)).
+ * Replaces HadamardTransform.forward (src/transforms/transforms.py:81-84) and its
+ * external `fast_hadamard_transform` kernel.  x, y: [rows, cols]; y may alias x
+ * when the dtypes match.
+ */
+int fpq_rotate_hadamard(const void* x, int dtype_in, void* y, int dtype_out, int64_t rows,
+                        int64_t cols, int group, fpq_stream_t stream);
+
+/*
+ * y = x.view(-1, g) @ matrix for an arbitrary g x g rotation (g in 16/32/64/128),
+ * fp32 sequential accumulation over k.  Covers the identity / GSR / user matrices
+ * that `forward_quantize` accepts (inference_lib/src/fp_quant/module/linear_fns.py:27-50,
+ * linear.py:37-41).  matrix: fp32 [g, g] row-major.
+ */
+int fpq_rotate_dense(const void* x, int dtype_in, void* y, int dtype_out, int64_t rows,
+                     int64_t cols, int group, const float* matrix, fpq_stream_t stream);
+
+/*
+ * Tensor-wide max |rotate(x)| folded into *absmax_bits with an unsigned atomic max on
+ * the fp32 bit pattern (the caller zeroes it first).  First half of the NVFP4 global
+ * scale (src/quantization/quantizer.py:146).  hadamard_group 0 = no rotation.
+ */
+int fpq_absmax(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+               uint32_t* absmax_bits, fpq_stream_t stream);
+
+/*
+ * *global_scale = min(*global_scale, fl(2688 * fl(1 / absmax))) -- the running-min
+ * update of Quantizer.global_scale (src/quantization/quantizer.py:10-16, :145-150).
+ * A zero absmax leaves the scale unchanged and sets *status to 1.
+ */
+int fpq_global_scale_update(const uint32_t* absmax_bits, float* global_scale, int32_t* status,
+                            fpq_stream_t stream);
+
+/*
+ * Fused rotate + micro-scaled FP4 quantise: the one memory-bound pass that replaces
+ * Quantizer.get_quantization_params + quantize + pack_fp4_to_uint8 + cast_scales_to_eXmY
+ * (src/quantization/quantizer.py:87-182, quant_ops.py:31-40, :57-71, :82-94, :111-118),
+ * qutlass.fusedQuantizeMx / fusedQuantizeNv and the `to_blocked` re-layout
+ * (inference_lib/src/fp_quant/module/qutlass_ops.py:36-105, :122-123, :334-335).
+ *   x            [rows, cols] bf16 or fp32, cols % 32 == 0 and cols % hadamard_group == 0
+ *   hadamard_group 0 (none), 16, 32, 64 or 128
+ *   global_scale device fp32[1], NVFP4 only (NULL for MXFP4)
+ *   codes        uint8 [rows, cols/2] or NULL
+ *   scale_bytes  uint8 in `scale_layout` or NULL; swizzled buffers must be zero-filled by
+ *                the caller when rows % 128 != 0 or (cols/g) % 4 != 0
+ *   scales_f32   fp32 [rows, cols/g] (the divisor actually used) or NULL
+ */
+int fpq_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+                 int format, const float* global_scale, uint8_t* codes, uint8_t* scale_bytes,
+                 int scale_layout, float* scales_f32, fpq_stream_t stream);
+
+/*
+ * Fused rotate + quantise + dequantise ("pseudo-quantisation"): y = grid(code) * scale
+ * (or the straight-through form when ste != 0), same dtype as x.  Replaces the Triton
+ * kernels mxfp4_forward_kernel / nvfp4_forward_kernel
+ * (inference_lib/src/fp_quant/module/triton/mxfp4.py:19-119, nvfp4.py:19-106) with the
+ * rounding rule of Quantizer.__call__ (src/quantization/quantizer.py:190-197).
+ */
+int fpq_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+                      int format, const float* global_scale, void* y, int ste,
+                      fpq_stream_t stream);
+
+/*
+ * Quantise with scales given by the caller: Quantizer.quantize / dequantize / __call__
+ * (src/quantization/quantizer.py:175-197).  scales: fp32 [rows, cols/group]; `group` any
+ * divisor of cols that is a multiple of 8; out_kind one of FPQ_OUT_*.
+ */
+int fpq_apply_scales(const void* x, int dtype, int64_t rows, int64_t cols, const float* scales,
+                     int group, int out_kind, void* out, fpq_stream_t stream);
+
+/*
+ * pack_fp4_to_uint8 (src/quantization/quant_ops.py:31-40): tensor of E2M1 grid values ->
+ * two 4-bit codes per byte, even element in the low nibble, zeros as 0x8.
+ */
+int fpq_pack_grid(const void* q, int dtype, int64_t rows, int64_t cols, uint8_t* packed,
+                  fpq_stream_t stream);
+
+/*
+ * Row-major scale bytes [rows, sf_cols] -> zero-padded 128x4-tile layout.  Replaces
+ * qutlass.utils.to_blocked (inference_lib/src/fp_quant/module/qutlass_ops.py:334-335).
+ */
+int fpq_swizzle_scales(const uint8_t* rowmajor, int64_t rows, int64_t sf_cols, uint8_t* swizzled,
+                       fpq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FPQ_B200_H_ */

@@ -1,0 +1,153 @@
+"""GPU parity of the fused rotate + FP4 quantise kernels against the CPU oracle (bit-exact)."""
+import pytest
+import torch
+
+from oracle import fp4
+from tests import inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_quant(y, fmt, gs=None):
+    return fp4.quantize(y, fmt, gs)
+
+
+def _global_scale(y):
+    return fp4.nvfp4_global_scale(y.abs().max())
+
+
+@pytest.mark.parametrize("group", [16, 32, 64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rotate_matches_butterfly(cuda_device, group, dtype):
+    from fpq_b200 import ops
+
+    x = inputs.normal_weight(67, 512, seed=3, std=1.0, dtype=dtype)
+    want = fp4.fwht_butterfly(x, group)
+    got = ops.rotate_hadamard(x.to(cuda_device), group, out_dtype=torch.float32).cpu()
+    assert torch.equal(got, want)
+    got_same = ops.rotate_hadamard(x.to(cuda_device), group).cpu()
+    assert torch.equal(got_same, want.to(dtype))
+
+
+@pytest.mark.parametrize("group", [16, 64])
+def test_rotate_dense_matches_sequential_sum(cuda_device, group):
+    from fpq_b200 import ops
+
+    x = inputs.normal_weight(33, 256, seed=5, std=1.0)
+    perm = fp4.gsr_permutation(group)
+    m = fp4.hadamard_matrix(group)[:, perm].bfloat16()
+    want = fp4.rotate_dense(x, m)
+    got = ops.rotate_dense(x.to(cuda_device), m.to(cuda_device), out_dtype=torch.float32).cpu()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("hgroup", [0, 16, 32, 64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(1, 128), (3, 256), (130, 384), (512, 4096)])
+def test_quantize_bit_exact(cuda_device, fmt, hgroup, dtype, shape):
+    from fpq_b200 import ops
+
+    x = inputs.outlier_activations(*shape, seed=11, dtype=dtype)
+    y = fp4.fwht_butterfly(x, hgroup) if hgroup else x.float()
+    gs = _global_scale(y) if fmt == "nvfp4" else None
+    want_codes, want_sb, want_s = _oracle_quant(y, fmt, gs)
+    q, sb, sf = ops.quantize(x.to(cuda_device), fmt, hgroup, None if gs is None else gs.to(cuda_device),
+                             scales_f32=True)
+    assert torch.equal(sf.cpu(), want_s)
+    assert torch.equal(sb.cpu(), want_sb)
+    assert torch.equal(q.cpu(), want_codes)
+    # same call writing the swizzled layout
+    q2, sbz, _ = ops.quantize(x.to(cuda_device), fmt, hgroup, None if gs is None else gs.to(cuda_device),
+                              swizzled=True)
+    assert torch.equal(q2.cpu(), want_codes)
+    assert torch.equal(sbz.cpu(), fp4.swizzle_scales(want_sb))
+    assert torch.equal(ops.swizzle_scales(sb).cpu(), fp4.swizzle_scales(want_sb))
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_quantize_edge_cases(cuda_device, fmt):
+    """Ties, signed zeros, zero groups, maxima just below powers of two, extreme magnitudes."""
+    from fpq_b200 import ops
+
+    x = inputs.edge_case_rows(128)
+    gs = torch.tensor([3.0]) if fmt == "nvfp4" else None
+    want_codes, want_sb, want_s = _oracle_quant(x, fmt, gs)
+    q, sb, sf = ops.quantize(x.to(cuda_device), fmt, 0, None if gs is None else gs.to(cuda_device), scales_f32=True)
+    assert torch.equal(sf.cpu(), want_s)
+    assert torch.equal(sb.cpu(), want_sb)
+    assert torch.equal(q.cpu(), want_codes)
+
+
+@pytest.mark.parametrize("fmt,hgroup", [("nvfp4", 128), ("mxfp4", 128), ("mxfp4", 32)])
+def test_weight_round_trip_4096(cuda_device, fmt, hgroup):
+    """The 4096 x 4096 N(0, 0.02^2) weight: codes, scales, global scale and MSE."""
+    from fpq_b200 import ops
+
+    w = inputs.normal_weight(4096, 4096, seed=0)
+    y = fp4.fwht_butterfly(w, hgroup)
+    wd = w.to(cuda_device)
+    gs_d = None
+    gs = None
+    if fmt == "nvfp4":
+        bits = ops.absmax_bits(wd, hgroup)
+        gs_d = torch.full((1,), float("inf"), device=cuda_device)
+        ops.global_scale_update(bits, gs_d)
+        gs = _global_scale(y)
+        assert torch.equal(gs_d.cpu(), gs)
+    want_codes, want_sb, want_s = _oracle_quant(y, fmt, gs)
+    q, sb, sf = ops.quantize(wd, fmt, hgroup, gs_d, scales_f32=True)
+    assert torch.equal(sb.cpu(), want_sb)
+    assert torch.equal(q.cpu(), want_codes)
+    g = 16 if fmt == "nvfp4" else 32
+    dq = ops.fake_quantize(wd, fmt, hgroup, gs_d).cpu().float()
+    want_dq = fp4.dequantize(fp4.unpack_codes(want_codes), want_s, g)
+    assert torch.equal(dq, want_dq.bfloat16().float())
+    mse = ((want_dq - y) ** 2).mean().item()
+    assert 1e-6 < mse < 1e-5
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("ste", [False, True])
+def test_fake_quantize_fp32(cuda_device, fmt, ste):
+    from fpq_b200 import ops
+
+    x = inputs.outlier_activations(64, 512, seed=21, dtype=torch.float32)
+    y = fp4.fwht_butterfly(x, 64)
+    gs = _global_scale(y) if fmt == "nvfp4" else None
+    codes, _, s = _oracle_quant(y, fmt, gs)
+    dq = fp4.dequantize(fp4.unpack_codes(codes), s, 16 if fmt == "nvfp4" else 32)
+    want = y + (dq - y) if ste else dq
+    got = ops.fake_quantize(x.to(cuda_device), fmt, 64, None if gs is None else gs.to(cuda_device), ste=ste).cpu()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("group", [16, 32, 128])
+def test_apply_scales_and_pack(cuda_device, group):
+    from fpq_b200 import ops, _cabi as C
+
+    x = inputs.outlier_activations(40, 256, seed=31, dtype=torch.float32)
+    g = torch.Generator().manual_seed(32)
+    s = torch.rand(40, 256 // group, generator=g) + 0.05
+    codes = fp4.e2m1_codes(x, s, group)
+    grid = fp4.code_values(codes)
+    xd, sd = x.to(cuda_device), s.to(cuda_device)
+    assert torch.equal(ops.apply_scales(xd, sd, group, C.OUT_CODES).cpu(), fp4.pack_codes(codes))
+    got_grid = ops.apply_scales(xd, sd, group, C.OUT_GRID)
+    assert torch.equal(got_grid.cpu(), grid)
+    dq = fp4.dequantize(codes, s, group)
+    assert torch.equal(ops.apply_scales(xd, sd, group, C.OUT_DEQUANT).cpu(), dq)
+    assert torch.equal(ops.apply_scales(xd, sd, group, C.OUT_DEQUANT_STE).cpu(), x + (dq - x))
+    assert torch.equal(ops.pack_grid(got_grid).cpu(), fp4.pack_codes(codes))
+
+
+def test_bad_arguments_raise(cuda_device):
+    from fpq_b200 import ops, _cabi as C
+
+    x = torch.zeros(4, 48, device=cuda_device)
+    with pytest.raises(C.FpqError):
+        ops.quantize(x, "mxfp4", 32)
+    with pytest.raises(RuntimeError):
+        ops.quantize(torch.zeros(4, 64), "mxfp4", 32)
+    with pytest.raises(C.FpqError):
+        ops.quantize(torch.zeros(4, 64, device=cuda_device), "mxfp4", 24)
