@@ -35,6 +35,8 @@ _SIGNATURES = {
     "fpq_apply_scales": [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "fpq_pack_grid": [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p],
     "fpq_swizzle_scales": [c_void_p, c_int64, c_int64, c_void_p, c_void_p],
+    "fpq_gemm_fp4": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                     c_int64, c_int, c_void_p, c_void_p],
 }
 _RESTYPES = {"fpq_last_error": c_char_p}
 

@@ -159,3 +159,50 @@ def swizzle_scales(sb: torch.Tensor) -> torch.Tensor:
     with torch.cuda.device(sb.device):
         C.call("fpq_swizzle_scales", sb.data_ptr(), rows, sf_cols, out.data_ptr(), _stream(sb))
     return out
+
+
+_error_flags = {}
+
+
+def device_error_flag(device: torch.device) -> torch.Tensor:
+    """int32[1] on `device` that kernels with bounded waits set when a wait ran out."""
+    key = torch.device(device).index or 0
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _error_flags[key]
+
+
+def check_device_errors(device: torch.device) -> None:
+    """Synchronising check: raises if any kernel on `device` reported a timed-out wait."""
+    flag = device_error_flag(device)
+    if int(flag.item()) != 0:
+        flag.zero_()
+        raise C.FpqError(C.ERR_DEVICE_TIMEOUT, "a bounded in-kernel wait ran out; results are invalid")
+
+
+def gemm_fp4(a_codes: torch.Tensor, b_codes: torch.Tensor, a_scales_swizzled: torch.Tensor,
+             b_scales_swizzled: torch.Tensor, alpha: torch.Tensor, fmt: str,
+             bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 [M, N] = alpha * dq(A) dq(B)^T (+ bias); codes [rows, K/2] uint8, scales swizzled."""
+    a = _cuda(a_codes, "a_codes").contiguous()
+    b = _cuda(b_codes, "b_codes").contiguous()
+    M, K = a.shape[0], a.shape[1] * 2
+    N = b.shape[0]
+    if b.shape[1] * 2 != K:
+        raise ValueError(f"K mismatch: {a.shape} vs {b.shape}")
+    sa = _cuda(a_scales_swizzled, "a_scales").contiguous()
+    sb = _cuda(b_scales_swizzled, "b_scales").contiguous()
+    g = GROUP_OF[fmt]
+    for name, s, rows in (("a_scales", sa, M), ("b_scales", sb, N)):
+        pr, pc = padded_scale_shape(rows, K // g)
+        if s.numel() != pr * pc:
+            raise ValueError(f"{name} must hold the swizzled layout of [{pr}, {pc}] bytes, got {tuple(s.shape)}")
+    alpha = _cuda(alpha, "alpha").to(torch.float32).reshape(1)
+    if bias is not None:
+        bias = _cuda(bias, "bias").to(torch.bfloat16).contiguous()
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    with torch.cuda.device(a.device):
+        C.call("fpq_gemm_fp4", a.data_ptr(), b.data_ptr(), sa.data_ptr(), sb.data_ptr(), alpha.data_ptr(),
+               _ptr(bias), out.data_ptr(), M, N, K, FORMATS[fmt], device_error_flag(a.device).data_ptr(), _stream(a))
+    return out

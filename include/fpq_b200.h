@@ -137,6 +137,21 @@ int fpq_pack_grid(const void* q, int dtype, int64_t rows, int64_t cols, uint8_t*
 int fpq_swizzle_scales(const uint8_t* rowmajor, int64_t rows, int64_t sf_cols, uint8_t* swizzled,
                        fpq_stream_t stream);
 
+/*
+ * Y[M,N] (bf16) = alpha * dq(A)[M,K] * dq(B)[N,K]^T (+ bias[N]) on the tcgen05 tensor cores,
+ * A and B as packed E2M1 codes [rows, K/2] (K-major), scales in the swizzled layout.
+ * Replaces matmul_mxf4_bf16_tn_op / matmul_nvf4_bf16_tn_op and the per-call `to_blocked`
+ * (inference_lib/src/fp_quant/module/qutlass_ops.py:111-168) and `forward_gemm`
+ * (inference_lib/src/fp_quant/module/linear_fns.py:53-64).  alpha: device fp32[1];
+ * bias: device bf16[N] or NULL; K % 64 == 0, N % 8 == 0.
+ * error_flag: device int32 the caller zeroes; set to 1 if a bounded in-kernel wait ran out
+ * (the output is then invalid; the context stays usable).
+ */
+int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* a_scales_swizzled,
+                 const uint8_t* b_scales_swizzled, const float* alpha, const void* bias_bf16,
+                 void* out_bf16, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
+                 fpq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
