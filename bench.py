@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4 FP4 linear hot path (fused rotate+quantise -> block-scaled FP4 GEMM).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload linear|quantize|gemm] [--m M] [--format mxfp4|nvfp4]
+
+Workload (default): the Qwen3-8B linear shapes (K,N) in {(4096,4096),(4096,12288),(12288,4096),
+(4096,1024)} at M = 8192 tokens, MXFP4 with Hadamard group 32, activations bf16
+Student-t(4)*0.5 with 1 % outlier channels, weights N(0, 0.02^2) quantised once beforehand.
+One step = one pass over the four shapes: quantise X[M,K] (codes + swizzled scales), then
+Y[M,N] = alpha * Xq Wq^T in bf16.  `value` is total FLOP (2*M*N*K summed) / device time with
+the inputs resident in HBM; `e2e` times the same through `FPQuantLinear.forward` with host
+buffers (pinned H2D of X and D2H of Y inside the timed region).
+
+With --gpus N (launched by torchrun, one rank per GPU) every rank processes its own M tokens
+(weak scaling, no collective on the data path); the time is the max over ranks.
+
+--impl reference times the CPU restatement of the reference algorithm (the oracle) on the
+host cores for a bounded sample of the same workload.  It is the only mode that touches
+`oracle/`, besides the `cpu_baseline` leg of the default mode.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "fp-quant_b200"))
+
+import torch  # noqa: E402
+
+SHAPES = [(4096, 4096), (4096, 12288), (12288, 4096), (4096, 1024)]  # (K, N)
+HADAMARD_GROUP = {"mxfp4": 32, "nvfp4": 16}
+SCALE_GROUP = {"mxfp4": 32, "nvfp4": 16}
+NOMINAL_FP4_TFLOPS = 9000.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------------ inputs
+def make_activations(M, K, seed, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    z = torch.randn(M, K, generator=g)
+    chi = torch.zeros(M, K)
+    for _ in range(4):
+        chi += torch.randn(M, K, generator=g) ** 2
+    x = z / torch.sqrt(chi / 4) * 0.5
+    idx = torch.randperm(K, generator=torch.Generator().manual_seed(seed + 1))[: max(1, K // 100)]
+    x[:, idx] *= 20
+    return x.to(dtype)
+
+
+def make_weight(N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ------------------------------------------------------------------------------ CPU arm
+def cpu_linear_pass(xs, ws_q, fmt, hgroup):
+    """One pass of the reference algorithm on the CPU: rotate + quantise activations with the
+    restated Quantizer chain, then the dequantised fp32 matmul (what the reference's pseudo-quant
+    path computes) scaled by alpha."""
+    from oracle import fp4
+
+    flops = 0.0
+    for x, (wd, alpha) in zip(xs, ws_q):
+        xr = fp4.fwht_butterfly(x, hgroup)
+        gs = torch.tensor([3.0]) if fmt == "nvfp4" else None
+        q, sb, s = fp4.quantize(xr, fmt, gs)
+        xd = fp4.dequantize(fp4.unpack_codes(q), s, SCALE_GROUP[fmt])
+        y = ((xd @ wd.t()) * alpha).to(torch.bfloat16)
+        flops += 2.0 * x.shape[0] * wd.shape[0] * x.shape[1]
+    return flops, y
+
+
+def cpu_prepare(fmt, hgroup, m_sample):
+    from oracle import fp4
+
+    xs, ws = [], []
+    for i, (K, N) in enumerate(SHAPES):
+        xs.append(make_activations(m_sample, K, seed=100 + i))
+        w = make_weight(N, K, seed=3 + 10 * i)
+        wr = fp4.fwht_butterfly(w, hgroup)
+        gs = torch.tensor([3.0]) if fmt == "nvfp4" else None
+        q, sb, s = fp4.quantize(wr, fmt, gs)
+        ws.append((fp4.dequantize(fp4.unpack_codes(q), s, SCALE_GROUP[fmt]), 1.0))
+    return xs, ws
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    fmt, hgroup = args.format, HADAMARD_GROUP[args.format]
+    m_sample = args.cpu_rows
+    xs, ws = cpu_prepare(fmt, hgroup, m_sample)
+    for _ in range(args.warmup):
+        cpu_linear_pass(xs, ws, fmt, hgroup)
+    t0 = time.perf_counter()
+    flops = 0.0
+    for _ in range(args.steps):
+        f, _ = cpu_linear_pass(xs, ws, fmt, hgroup)
+        flops += f
+    dt = time.perf_counter() - t0
+    val = flops / dt / 1e12
+    sample = f"{m_sample} of {args.m} token rows per shape, all four (K,N) shapes, full N and K"
+    line = {
+        "impl": "reference", "metric": "w4a4_linear_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1)xfp4->f32->bf16", "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args):
+    return {"workload": f"W4A4 {args.format} linear, Qwen3-8B shapes (K,N)={SHAPES}, M={args.m} tokens per GPU, "
+                        f"Hadamard group {HADAMARD_GROUP[args.format]}, quantise activations + FP4 GEMM",
+            "format": args.format, "M_per_gpu": args.m,
+            "l2": "per-step working set ~0.8 GB (activations, weights, outputs of four shapes) > 126 MB L2"}
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def run_ours(args):
+    import torch.distributed as dist
+
+    from fpq_b200 import ops
+    from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype, FPQuantLinear
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    fmt, M = args.format, args.m
+    hgroup, g = HADAMARD_GROUP[fmt], SCALE_GROUP[fmt]
+    peaks = load_peaks()
+    shapes = SHAPES if args.workload == "linear" else SHAPES[:1]
+
+    # ---- layers (public API) and device-resident inputs
+    cfg = FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4 if fmt == "mxfp4" else FPQuantDtype.NVFP4,
+                        forward_method="abs_max", backward_dtype=FPQuantDtype.BF16, hadamard_group_size=hgroup)
+    layers, xs_dev, xs_host, ys_host = [], [], [], []
+    for i, (K, N) in enumerate(shapes):
+        layer = FPQuantLinear(K, N, cfg, bias=False, device=dev, dtype=torch.bfloat16)
+        layer.weight.data.copy_(make_weight(N, K, seed=3 + 10 * i))
+        layer.pre_forward()
+        layers.append(layer)
+        x = make_activations(M, K, seed=100 + i + 1000 * rank)
+        xs_host.append(x.pin_memory())
+        xs_dev.append(x.to(dev))
+        ys_host.append(torch.empty(M, N, dtype=torch.bfloat16).pin_memory())
+    gs = [l.act_global_scale.float() for l in layers]
+    alphas = [1.0 / (l.weight_global_scale.float() * l.act_global_scale.float()) for l in layers]
+    wscales = [l._blocked_weight_scales() for l in layers]
+    outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for (K, N) in shapes]
+    flops_step = sum(2.0 * M * N * K for (K, N) in shapes)
+
+    gemm_events = []
+
+    def step(record):
+        for i, layer in enumerate(layers):
+            if args.workload in ("linear", "quantize"):
+                q, sb, _ = ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)
+            if args.workload == "quantize":
+                continue
+            if args.workload == "gemm":
+                q, sb = step.q, step.sb
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            ops.gemm_fp4(q, layer.qweight, sb, wscales[i], alphas[i], fmt, out=outs[i])
+            if record:
+                e1.record()
+                gemm_events.append((e0, e1, i))
+
+    if args.workload == "gemm":
+        step.q, step.sb, _ = ops.quantize(xs_dev[0], fmt, hgroup, gs[0] if fmt == "nvfp4" else None, swizzled=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(False)
+    barrier()
+    with ClockSampler(local) as clocks:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            step(True)
+        stop.record()
+        barrier()
+    ops.check_device_errors(dev)
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = flops_step * world * args.steps / (ms * 1e-3) / 1e12 if args.workload != "quantize" else None
+
+    # ---- roofline of the dominant kernel
+    roofline = None
+    if gemm_events:
+        # the GEMM of the largest shape dominates; report the FLOP-weighted aggregate over all GEMM launches
+        tot_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in gemm_events)
+        tot_fl = sum(2.0 * M * shapes[i][1] * shapes[i][0] for _, _, i in gemm_events)
+        achieved = tot_fl / (tot_ms * 1e-3) / 1e12
+        peak = 4.0 * peaks["bf16_tflops"]
+        roofline = {"kernel": "gemm_fp4_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
+                    "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_source": f"4 x bf16 cuBLAS burst ({peaks['source']}); no FP4 peak was measured on this pool",
+                    "frac_of_nominal_9pf": achieved / NOMINAL_FP4_TFLOPS,
+                    "avg_launch_ms": tot_ms / len(gemm_events), "traffic": None}
+    quant_roof = None
+    if args.workload in ("linear", "quantize"):
+        # time the quantise launches alone (same inputs, back to back; 0.4 GB of input per pass > L2)
+        for _ in range(2):
+            for i in range(len(layers)):
+                ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, args.steps)
+        e0.record()
+        for _ in range(reps):
+            for i in range(len(layers)):
+                ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)
+        e1.record()
+        torch.cuda.synchronize()
+        qms = e0.elapsed_time(e1) / reps
+        qbytes = sum(M * K * (2 + 0.5 + 1.0 / g) for (K, N) in shapes)
+        quant_roof = {"kernel": "quant_kernel", "bound": "hbm", "achieved": qbytes / (qms * 1e-3) / 1e9,
+                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                      "peak_source": f"copy bandwidth ({peaks['source']})",
+                      "frac_of_nominal_8tbs": qbytes / (qms * 1e-3) / 1e9 / NOMINAL_HBM_GBS, "traffic": None}
+        if args.workload == "quantize":
+            roofline = quant_roof
+
+    # ---- end to end through FPQuantLinear.forward with host buffers
+    e2e = None
+    if args.workload == "linear":
+        def e2e_step():
+            for i, layer in enumerate(layers):
+                xd = xs_host[i].to(dev, non_blocking=True)
+                y = layer(xd)
+                ys_host[i].copy_(y, non_blocking=True)
+        for _ in range(max(1, min(args.warmup, 2))):
+            e2e_step()
+        barrier()
+        s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n2 = max(1, min(args.steps, 5))
+        s2.record()
+        for _ in range(n2):
+            e2e_step()
+        t2.record()
+        barrier()
+        ms2 = s2.elapsed_time(t2)
+        if world > 1:
+            t = torch.tensor([ms2], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms2 = float(t.item())
+        e2e = {"value": flops_step * world * n2 / (ms2 * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": sum(x.numel() * 2 for x in xs_host),
+               "d2h_bytes_per_step": sum(y.numel() * 2 for y in ys_host), "steps": n2,
+               "api": "fpq_b200.fp_quant.FPQuantLinear.forward"}
+
+    # ---- CPU baseline (rank 0, N = 1 only)
+    cpu = None
+    if rank == 0 and world == 1 and args.workload == "linear" and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        torch.set_num_threads(threads)
+        xs_c, ws_c = cpu_prepare(fmt, hgroup, args.cpu_rows)
+        cpu_linear_pass(xs_c, ws_c, fmt, hgroup)
+        t0 = time.perf_counter()
+        f, _ = cpu_linear_pass(xs_c, ws_c, fmt, hgroup)
+        dt = time.perf_counter() - t0
+        cpu = {"value": f / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+               "sample": f"{args.cpu_rows} of {M} token rows per shape, all four shapes, full N and K"}
+
+    if rank == 0:
+        n_launch = len(gemm_events) + (args.steps * len(layers) if args.workload in ("linear", "quantize") else 0)
+        line = {
+            "metric": "w4a4_linear_tflops" if args.workload != "quantize" else "quantize_gbs",
+            "value": value if value is not None else (quant_roof["achieved"] if quant_roof else None),
+            "unit": "TFLOP/s" if args.workload != "quantize" else "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp4(e2m1)xfp4->f32->bf16", "data": "synthetic", "config": workload_config(args),
+            "roofline": roofline, "quantize_roofline": quant_roof, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": n_launch, "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--format", default="mxfp4", choices=["mxfp4", "nvfp4"])
+    ap.add_argument("--cpu-rows", type=int, default=256)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -466,7 +466,9 @@ __global__ void __launch_bounds__(256) apply_scales_kernel(const void* x, int64_
     const int64_t e0 = w * 8;
     const int64_t row = e0 / cols;
     const uint32_t col = (uint32_t)(e0 - row * cols);
-    const float s = scales[row * (cols / group) + col / group];
+    const float* srow = scales + row * (cols / group);
+    const bool one_scale = (group & 7u) == 0;   // the 8 elements share a scale
+    const float s0 = srow[col / group];
     float v[8];
     if (IN_BF16) {
       uint4 raw = reinterpret_cast<const uint4*>(x)[w];
@@ -485,6 +487,7 @@ __global__ void __launch_bounds__(256) apply_scales_kernel(const void* x, int64_
     float o[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
+      const float s = one_scale ? s0 : srow[(col + j) / group];
       const uint32_t code = e2m1_code(__fdiv_rn(v[j], s));
       word |= code << (4 * j);
       float g = e2m1_value(code);
@@ -697,8 +700,8 @@ extern "C" int fpq_apply_scales(const void* x, int dtype, int64_t rows, int64_t 
                                 int group, int out_kind, void* out, fpq_stream_t stream) {
   FPQ_CHECK_ARG(x && scales && out, "NULL pointer");
   FPQ_CHECK_ARG(dtype == FPQ_DT_BF16 || dtype == FPQ_DT_F32, "bad dtype");
-  FPQ_CHECK_ARG(rows >= 0 && cols > 0 && group > 0 && cols % group == 0 && group % 8 == 0,
-                "group (%d) must be a multiple of 8 dividing cols (%lld)", group, (long long)cols);
+  FPQ_CHECK_ARG(rows >= 0 && cols > 0 && group > 0 && cols % group == 0 && cols % 8 == 0,
+                "group (%d) must divide cols (%lld) and cols must be a multiple of 8", group, (long long)cols);
   FPQ_CHECK_ARG(out_kind >= FPQ_OUT_CODES && out_kind <= FPQ_OUT_DEQUANT_STE, "bad out_kind");
   FPQ_CHECK_ARG(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0, "x and out must be 16-byte aligned");
   FPQ_CHECK_ARG(cols < ((int64_t)1 << 31), "cols too large");

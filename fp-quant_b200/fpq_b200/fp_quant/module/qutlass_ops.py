@@ -1,0 +1,155 @@
+"""The operator layer of the inference module: same op names, argument meaning and output
+shapes as inference_lib/src/fp_quant/module/qutlass_ops.py (IST-DASLab/FP-Quant), which binds
+the external QuTLASS kernels; here every op calls the fpq_b200 CUDA library.
+
+Two families:
+  * the reference names (`fused_quantize_mx_op`, `matmul_mxf4_bf16_tn_op`, ...) keep the
+    reference data flow: quantise returns ROW-MAJOR padded scales and the matmul re-lays both
+    scale tensors out on every call;
+  * the `*_blocked` ops are the fast path: quantise writes the swizzled layout directly and the
+    matmul consumes it, so nothing is re-laid out per call.
+All are registered as torch custom ops (namespace fpq_b200::) with fake implementations so that
+torch.compile(fullgraph=True) can trace through them.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from ... import ops
+from ...rotation import kind_of
+
+HAS_QUTLASS = True  # the CUDA library plays QuTLASS' part
+
+
+def _padded(rows: int, cols: int) -> Tuple[int, int]:
+    return ops.padded_scale_shape(rows, cols)
+
+
+def _rotate_then(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, rotation: int = 0):
+    """Returns (tensor to quantise, hadamard group for the fused kernel)."""
+    kind, group = kind_of(rotation, hadamard_matrix)
+    if kind == "hadamard":
+        return x_flat, group
+    if kind == "identity":
+        return x_flat, 0
+    return ops.rotate_dense(x_flat, hadamard_matrix, out_dtype=torch.float32), 0
+
+
+def _quantize(x_flat, hadamard_matrix, fmt, global_scale, swizzled, rotation=0):
+    x, group = _rotate_then(x_flat, hadamard_matrix, rotation)
+    q, sb, _ = ops.quantize(x, fmt, group, global_scale, swizzled=swizzled)
+    rows, sf_cols = x.shape[0], x.shape[1] // ops.GROUP_OF[fmt]
+    if not swizzled:
+        pr, pc = _padded(rows, sf_cols)
+        if (pr, pc) != (rows, sf_cols):
+            padded = torch.zeros(pr, pc, dtype=torch.uint8, device=sb.device)
+            padded[:rows, :sf_cols] = sb
+            sb = padded
+    return q, sb
+
+
+# --------------------------------------------------------------------------- quantise
+@torch.library.custom_op("fpq_b200::fused_quantize_mx", mutates_args=())
+def _fused_quantize_mx(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, forward_method: str,
+                       return_mask: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    if forward_method != "abs_max":
+        raise NotImplementedError("only the abs_max method is on the B200 path (QuEST scales are not built)")
+    q, sb = _quantize(x_flat, hadamard_matrix, "mxfp4", None, swizzled=False)
+    # abs_max never clips, so the mask (one bit per element, [rows, cols/8]) is all ones
+    mask = torch.full((x_flat.shape[0], x_flat.shape[1] // 8 if return_mask else 0), 0xFF, dtype=torch.uint8,
+                      device=x_flat.device)
+    return q, sb.view(torch.float8_e8m0fnu), mask
+
+
+@_fused_quantize_mx.register_fake
+def _(x_flat, hadamard_matrix, forward_method, return_mask):
+    rows, cols = x_flat.size(0), x_flat.size(1) // 32
+    pr, pc = _padded(rows, cols)
+    q = torch.empty(rows, x_flat.size(1) // 2, dtype=torch.uint8, device=x_flat.device)
+    s = torch.empty(pr, pc, dtype=torch.float8_e8m0fnu, device=x_flat.device)
+    m = torch.empty(rows, cols * 4 if return_mask else 0, dtype=torch.uint8, device=x_flat.device)
+    return q, s, m
+
+
+def fused_quantize_mx_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, forward_method: str,
+                         return_mask: bool):
+    """(codes u8 [M, K/2], e8m0 scales [ceil(M/128)*128, ceil(K/32/4)*4] row-major, mask | None)."""
+    q, s, m = _fused_quantize_mx(x_flat, hadamard_matrix, forward_method, return_mask)
+    return q, s, (m if return_mask else None)
+
+
+@torch.library.custom_op("fpq_b200::fused_quantize_nv_op", mutates_args=())
+def fused_quantize_nv_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor,
+                         global_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    q, sb = _quantize(x_flat, hadamard_matrix, "nvfp4", global_scale, swizzled=False)
+    return q, sb.view(torch.float8_e4m3fn)
+
+
+@fused_quantize_nv_op.register_fake
+def _(x_flat, hadamard_matrix, global_scale):
+    rows, cols = x_flat.size(0), x_flat.size(1) // 16
+    pr, pc = _padded(rows, cols)
+    q = torch.empty(rows, x_flat.size(1) // 2, dtype=torch.uint8, device=x_flat.device)
+    return q, torch.empty(pr, pc, dtype=torch.float8_e4m3fn, device=x_flat.device)
+
+
+@torch.library.custom_op("fpq_b200::fused_quantize_blocked_op", mutates_args=())
+def fused_quantize_blocked_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, global_scale: torch.Tensor,
+                              nvfp4: bool, rotation: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Fast path: packed codes + scale bytes already in the swizzled layout (uint8).
+    `rotation`: 0 = inspect the matrix, 1 = Hadamard butterfly, 2 = identity, 3 = dense product
+    (callers that classified the matrix once pass the verdict and skip the inspection)."""
+    q, sb = _quantize(x_flat, hadamard_matrix, "nvfp4" if nvfp4 else "mxfp4", global_scale if nvfp4 else None,
+                      swizzled=True, rotation=rotation)
+    return q, sb
+
+
+@fused_quantize_blocked_op.register_fake
+def _(x_flat, hadamard_matrix, global_scale, nvfp4, rotation=0):
+    rows, cols = x_flat.size(0), x_flat.size(1) // (16 if nvfp4 else 32)
+    pr, pc = _padded(rows, cols)
+    q = torch.empty(rows, x_flat.size(1) // 2, dtype=torch.uint8, device=x_flat.device)
+    return q, torch.empty(pr, pc, dtype=torch.uint8, device=x_flat.device)
+
+
+# --------------------------------------------------------------------------- matmul
+def to_blocked(x: torch.Tensor) -> torch.Tensor:
+    """Row-major scale matrix -> 128x4-tile swizzled layout (flat, like the reference helper)."""
+    return ops.swizzle_scales(x.view(torch.uint8) if x.dtype != torch.uint8 else x).flatten()
+
+
+def _matmul(x, w, xs_blocked, ws_blocked, alpha, fmt):
+    lead = x.shape[:-1]
+    y = ops.gemm_fp4(x.reshape(-1, x.shape[-1]), w, xs_blocked, ws_blocked, alpha, fmt)
+    return y.view(*lead, w.shape[0])
+
+
+@torch.library.custom_op("fpq_b200::matmul_mxf4_bf16_tn_op", mutates_args=())
+def matmul_mxf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
+                           alpha: torch.Tensor) -> torch.Tensor:
+    return _matmul(x, w, ops.swizzle_scales(xs.view(torch.uint8)), ops.swizzle_scales(ws.view(torch.uint8)),
+                   alpha, "mxfp4")
+
+
+@torch.library.custom_op("fpq_b200::matmul_nvf4_bf16_tn_op", mutates_args=())
+def matmul_nvf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
+                           alpha: torch.Tensor) -> torch.Tensor:
+    return _matmul(x, w, ops.swizzle_scales(xs.view(torch.uint8)), ops.swizzle_scales(ws.view(torch.uint8)),
+                   alpha, "nvfp4")
+
+
+@torch.library.custom_op("fpq_b200::matmul_fp4_bf16_tn_blocked_op", mutates_args=())
+def matmul_fp4_bf16_tn_blocked_op(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tensor,
+                                  ws_blocked: torch.Tensor, alpha: torch.Tensor, nvfp4: bool) -> torch.Tensor:
+    return _matmul(x, w, xs_blocked, ws_blocked, alpha, "nvfp4" if nvfp4 else "mxfp4")
+
+
+def _fake_mm(x, w, *rest):
+    return x.new_empty(*x.shape[:-1], w.shape[0], dtype=torch.bfloat16)
+
+
+matmul_mxf4_bf16_tn_op.register_fake(lambda x, w, xs, ws, alpha: _fake_mm(x, w))
+matmul_nvf4_bf16_tn_op.register_fake(lambda x, w, xs, ws, alpha: _fake_mm(x, w))
+matmul_fp4_bf16_tn_blocked_op.register_fake(lambda x, w, xs, ws, alpha, nvfp4: _fake_mm(x, w))

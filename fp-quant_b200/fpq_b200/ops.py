@@ -48,6 +48,11 @@ def padded_scale_shape(rows: int, sf_cols: int) -> Tuple[int, int]:
 def rotate_hadamard(x: torch.Tensor, group: int, out_dtype: Optional[torch.dtype] = None,
                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
     x, rows, cols = _2d(x)
+    if cols % group != 0:
+        raise ValueError(f"last dim ({cols}) must be a multiple of the hadamard group ({group})")
+    if cols % 32 != 0 and x.numel() % 32 == 0:
+        # groups are contiguous in memory, so any row length that keeps them whole is equivalent
+        rows, cols = x.numel() // max(32, group), max(32, group)
     if out is None:
         out = torch.empty_like(x, dtype=out_dtype or x.dtype)
     with torch.cuda.device(x.device):

@@ -118,7 +118,7 @@ int fpq_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int 
 /*
  * Quantise with scales given by the caller: Quantizer.quantize / dequantize / __call__
  * (src/quantization/quantizer.py:175-197).  scales: fp32 [rows, cols/group]; `group` any
- * divisor of cols that is a multiple of 8; out_kind one of FPQ_OUT_*.
+ * divisor of cols (1 = one scale per element); cols % 8 == 0; out_kind one of FPQ_OUT_*.
  */
 int fpq_apply_scales(const void* x, int dtype, int64_t rows, int64_t cols, const float* scales,
                      int group, int out_kind, void* out, fpq_stream_t stream);

@@ -1,0 +1,150 @@
+"""CPU tests: the oracle against the committed golden vectors (made from the unmodified
+reference by tests/golden/make_golden.py) and, when the reference tree is present, live."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import fp4, gptq as ogptq, ref_shim
+from tests import inputs
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+FORMATS = {"nvfp4": 16, "mxfp4": 32}
+
+
+def load(name):
+    d = np.load(os.path.join(GOLDEN, name))
+    return {k: torch.from_numpy(d[k]) for k in d.files}
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+def test_rtn_round_trip_matches_golden(fmt):
+    g = load(f"rtn_{fmt}.npz")
+    w = g["weight_bf16"].view(torch.bfloat16)
+    assert torch.equal(w, inputs.normal_weight(64, 512, seed=0))          # seeded input is reproducible
+    y = fp4.fwht_butterfly(w, 128)
+    assert torch.equal(y, g["rotated"])
+    gs = fp4.nvfp4_global_scale(y.abs().max()) if fmt == "nvfp4" else None
+    if fmt == "nvfp4":
+        assert torch.equal(gs, g["global_scale"])
+    codes, sb, s = fp4.quantize(y, fmt, gs)
+    assert torch.equal(codes, g["codes"]) and torch.equal(sb, g["scale_bytes"]) and torch.equal(s, g["scales"])
+    dq = fp4.dequantize(fp4.unpack_codes(codes), s, FORMATS[fmt])
+    assert abs(((dq - y) ** 2).mean().item() - g["mse"].item()) <= 1e-12
+    # the stored bytes decode to scale * global scale
+    gsv = gs if fmt == "nvfp4" else torch.tensor([3.0])
+    assert torch.allclose(fp4.decode_scale_bytes(sb, fmt), s * gsv, rtol=1e-6)
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+def test_edge_rows_match_golden(fmt):
+    g = load(f"edge_{fmt}.npz")
+    x = g["x"]
+    assert torch.equal(x, inputs.edge_case_rows(128))
+    codes, sb, s = fp4.quantize(x, fmt, torch.tensor([3.0]) if fmt == "nvfp4" else None)
+    assert torch.equal(codes, g["codes"]) and torch.equal(s, g["scales"])
+    keep = ~g["scale_underflow"]
+    assert torch.equal(sb[keep], g["scale_bytes"][keep])
+
+
+def test_log2_probes_match_golden():
+    g = load("log2_probes.npz")
+    assert torch.equal(fp4.mx_exponent(g["m"].clamp(min=2.0 ** -126)), g["exponent"])
+
+
+@pytest.mark.parametrize("fmt", list(FORMATS))
+def test_gptq_matches_golden(fmt):
+    g = load(f"gptq_{fmt}.npz")
+    Hd = ogptq.prepare_hessian(g["hessian"], g["weight"], 0.01)
+    assert torch.allclose(Hd, g["damped_hessian"])
+    U, ok = ogptq.cholesky_inverse_upper(Hd)
+    assert ok and torch.allclose(U, g["u"], rtol=1e-4, atol=1e-6)
+    wq, codes = ogptq.gptq_column_loop(g["weight"], g["scales"], g["u"], FORMATS[fmt], 128)
+    assert torch.equal(fp4.pack_codes(codes), g["codes"]) and torch.equal(wq, g["dequantized"])
+    assert abs(ogptq.relative_mse(wq, g["weight"], g["damped_hessian"]) - g["relative_mse"].item()) < 1e-6
+    # GPTQ must beat round-to-nearest on this correlated Hessian
+    rtn = fp4.dequantize(fp4.e2m1_codes(g["weight"], g["scales"], FORMATS[fmt]), g["scales"], FORMATS[fmt])
+    assert g["relative_mse"].item() < 0.5 * ogptq.relative_mse(rtn, g["weight"], g["damped_hessian"])
+
+
+def test_rotation_properties():
+    x = inputs.normal_weight(16, 256, seed=9, std=1.0, dtype=torch.float32)
+    for g in (16, 32, 64, 128):
+        y = fp4.fwht_butterfly(x, g)
+        ref = (x.double().view(-1, g) @ fp4.hadamard_matrix(g).double()).view(x.shape)
+        assert (y.double() - ref).abs().max() < 1e-5
+        assert torch.allclose(fp4.fwht_butterfly(y, g), x, atol=1e-5)      # self-inverse
+        m = fp4.hadamard_matrix(g).bfloat16()
+        assert torch.allclose(fp4.rotate_dense(x.bfloat16(), m), y, atol=0.05)
+
+
+def test_swizzle_layout_formula():
+    """Byte (r, c) lands at tile (r // 128, c // 4), offset (r % 32) * 16 + ((r // 32) % 4) * 4 + c % 4;
+    checked element by element, and against torch's own `to_blocked` helper where it imports."""
+    try:
+        from torch.testing._internal.common_quantized import to_blocked
+    except Exception:
+        to_blocked = None
+    for rows, cols in ((128, 4), (256, 8), (130, 6), (1, 128)):
+        sb = torch.arange(rows * cols, dtype=torch.int64).remainder(251).to(torch.uint8).view(rows, cols)
+        mine = fp4.swizzle_scales(sb).flatten()
+        tiles_k = (cols + 3) // 4
+        for r in range(0, rows, 7):
+            for c in range(cols):
+                off = ((r // 128) * tiles_k + c // 4) * 512 + (r % 32) * 16 + ((r // 32) % 4) * 4 + c % 4
+                assert mine[off] == sb[r, c]
+        assert int((mine != 0).sum()) == int((sb != 0).sum())          # padding is zero
+        assert torch.equal(fp4.unswizzle_scales(mine, rows, cols), sb)
+        if to_blocked is not None:
+            assert torch.equal(mine, to_blocked(sb.to(torch.float32)).to(torch.uint8).flatten())
+
+
+def test_pack_unpack_and_code_values():
+    codes = torch.arange(16, dtype=torch.uint8).repeat(4).view(2, 32)
+    assert torch.equal(fp4.unpack_codes(fp4.pack_codes(codes)), codes)
+    vals = fp4.code_values(torch.arange(16, dtype=torch.uint8))
+    assert vals.tolist() == [0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6]
+    ties = torch.tensor([[0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, 0.0, -0.0, 7.0, -7.0, 0.26, 0.74, 5.01, -5.0]])
+    c = fp4.e2m1_codes(ties, torch.ones(1, 1), 16)
+    assert c.tolist() == [[8, 2, 2, 4, 4, 6, 6, 8, 8, 8, 7, 15, 1, 1, 7, 14]]
+
+
+def test_matmul_oracle_against_dequantised_product():
+    gen = torch.Generator().manual_seed(0)
+    a = torch.randint(0, 256, (8, 64), generator=gen, dtype=torch.uint8)
+    b = torch.randint(0, 256, (12, 64), generator=gen, dtype=torch.uint8)
+    for fmt, g, lo, hi in (("mxfp4", 32, 120, 130), ("nvfp4", 16, 0x30, 0x40)):
+        sa = torch.randint(lo, hi, (8, 128 // g), generator=gen, dtype=torch.uint8)
+        sb = torch.randint(lo, hi, (12, 128 // g), generator=gen, dtype=torch.uint8)
+        y = fp4.fp4_matmul(a, b, sa, sb, 0.5, fmt).float()
+        ad = fp4.dequantize(fp4.unpack_codes(a), fp4.decode_scale_bytes(sa, fmt), g)
+        bd = fp4.dequantize(fp4.unpack_codes(b), fp4.decode_scale_bytes(sb, fmt), g)
+        assert torch.allclose(y, 0.5 * ad @ bd.t(), rtol=2 ** -7)
+
+
+def test_hessian_running_mean_equals_scaled_sum():
+    xs = [inputs.correlated_activations(64, 128, seed=20 + i).view(1, 64, 128) for i in range(5)]
+    H, n = None, 0
+    for x in xs:
+        H, n = ogptq.hessian_update(H, n, x)
+    exact = ogptq.hessian_exact(xs, 5)
+    assert n == 5 and ((H.double() - exact).norm() / exact.norm()).item() < 1e-6
+
+
+@pytest.mark.skipif(not ref_shim.available(), reason="reference tree not present")
+@pytest.mark.parametrize("fmt,name,prec", [("nvfp4", "nvfp", "e4m3"), ("mxfp4", "mxfp", "e8m0")])
+def test_oracle_equals_live_reference(fmt, name, prec):
+    ref_shim.load()
+    from src.quantization.quant_ops import cast_scales_to_eXmY, pack_fp4_to_uint8
+    from src.quantization.quantizer import Quantizer
+
+    y = fp4.fwht_butterfly(inputs.outlier_activations(96, 1024, seed=11), 64)
+    q = Quantizer(bits=4, format=name, granularity="group", group_size=FORMATS[fmt], scale_precision=prec)
+    s, z = q.get_quantization_params(y)
+    codes = pack_fp4_to_uint8(q.quantize(y, s, z))
+    sb = cast_scales_to_eXmY(s * q.global_scale, prec)
+    o_codes, o_sb, o_s = fp4.quantize(y, fmt, q.global_scale if fmt == "nvfp4" else None)
+    assert torch.equal(codes, o_codes) and torch.equal(s, o_s)
+    keep = o_sb != 0 if fmt == "nvfp4" else torch.ones_like(o_sb, dtype=torch.bool)
+    assert torch.equal(sb[keep], o_sb[keep])
