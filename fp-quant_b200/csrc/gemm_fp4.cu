@@ -16,6 +16,8 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
+#include <cstdlib>
+
 namespace fpq {
 namespace {
 
@@ -42,7 +44,23 @@ struct GemmParams {
   const __nv_bfloat16* bias;
   __nv_bfloat16* out;
   int* error_flag;
+  int raster_group;        // m-blocks per rasterisation band
+  int debug_flags;         // bit 0: skip the global stores of the epilogue (timing experiments only)
 };
+
+// Tile index -> (m block, n block): bands of `raster_group` m-blocks, n-blocks swept inside a band with
+// m fastest, so that CTAs running at the same time share both A and B tiles through L2 instead of
+// all asking for the same B tile.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
+  const int band_tiles = p.raster_group * p.num_n_blocks;
+  const int band = tile / band_tiles;
+  const int first_m = band * p.raster_group;
+  int rows = p.num_m_blocks - first_m;
+  if (rows > p.raster_group) rows = p.raster_group;
+  const int in_band = tile - band * band_tiles;
+  m_blk = first_m + in_band % rows;
+  n_blk = in_band / rows;
+}
 
 template <int BN, bool NVFP4>
 struct SmemLayout {
@@ -105,12 +123,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (lane == 0 && !(p.debug_flags & 8)) {
       uint32_t it = 0;   // global stage counter
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile % p.num_m_blocks;
-        const int n_blk = tile / p.num_m_blocks;
+        int m_blk, n_blk;
+        tile_coords(p, tile, m_blk, n_blk);
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -121,6 +139,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           for (int h = 0; h < BN / 128; ++h)
             if (n_blk * (BN / 128) + h < p.sfb_row_blocks) ++nb_rowblocks;
           const uint32_t tx = STAGE_TX_AB + (uint32_t)nblk * 512u * (1 + nb_rowblocks);
+          if (p.debug_flags & 4) { mbar_arrive(bar_full + 8 * s); continue; }   // timing experiment: no loads
           mbar_arrive_expect_tx(bar_full + 8 * s, tx);
           tma_load_2d(sbase + L::OFF_A + s * L::A_BYTES, &tmap_a, ks * BK_BYTES, m_blk * BM, bar_full + 8 * s);
           tma_load_2d(sbase + L::OFF_B + s * L::B_BYTES, &tmap_b, ks * BK_BYTES, n_blk * BN, bar_full + 8 * s);
@@ -161,14 +180,16 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag)) { ok = false; break; }
-          tc_fence_after();
+          if (!(p.debug_flags & 8)) {   // bit 3 (timing experiment): issue MMAs without waiting for data
+            if (!mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+          }
           const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + (it & 1) * SF_TMEM_BUF;
           const uint32_t sfa_t = sf_buf;            // 4 columns per 512-byte block
           const uint32_t sfb_t = sf_buf + 16;       // (BN/32) columns per block
           int nblk = p.sf_blocks_k - ks * SFBLK;
           if (nblk > SFBLK) nblk = SFBLK;
-          for (int j = 0; j < nblk; ++j) {
+          for (int j = 0; j < nblk && !((p.debug_flags & 2) && it > 0); ++j) {
             tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf_block(sbase + L::OFF_SFA + s * L::SFA_BYTES + j * 512));
             for (int h = 0; h < BN / 128; ++h)
               tc_cp_32x128b_warpx4(sfb_t + (BN / 32) * j + 4 * h,
@@ -183,10 +204,12 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             if (NVFP4) { blk = k; sf_id = 0; }           // 4 scales of 16 per MMA: one whole block
             else { blk = k >> 1; sf_id = (k & 1) * 2; }  // 2 scales of 32 per MMA: half a block
             const uint32_t idesc = make_idesc_fp4(BM, BN, !NVFP4, sf_id, sf_id);
-            tc_mma_fp4_block_scaled<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_t + 4 * blk,
+            // bit 4 (timing experiment): alternate between two accumulators to break the dependency chain
+            const uint32_t acc = tmem_base + ((p.debug_flags & 16) ? (uint32_t)((k & 1) * 256) : 0u);
+            tc_mma_fp4_block_scaled<NVFP4>(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_t + 4 * blk,
                                            sfb_t + (BN / 32) * blk, (ks > 0 || k > 0) ? 1u : 0u);
           }
-          tc_commit(bar_empty + 8 * s);   // stage reusable once these MMAs have read it
+          if (!(p.debug_flags & 8)) tc_commit(bar_empty + 8 * s);   // stage reusable once these MMAs have read it
         }
         if (ok) tc_commit(bar_acc_full);
       }
@@ -202,8 +225,8 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     uint32_t tile_count = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tile_count) {
-      const int m_blk = tile % p.num_m_blocks;
-      const int n_blk = tile / p.num_m_blocks;
+      int m_blk, n_blk;
+      tile_coords(p, tile, m_blk, n_blk);
       if (!mbar_wait_bounded(bar_acc_full, tile_count & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
@@ -214,6 +237,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, r);
         tc_wait_ld();
         const int col0 = n_blk * BN + c * 32;
+        if (p.debug_flags & 1) continue;
         if (row < p.M && col0 + 32 <= p.N) {
           uint32_t w[16];
 #pragma unroll
@@ -270,6 +294,13 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cuda
   }
   p.num_n_blocks = (p.N + BN - 1) / BN;
   p.num_tiles = p.num_m_blocks * p.num_n_blocks;
+  {
+    const char* e = getenv("FPQ_GEMM_RASTER");
+    p.raster_group = e ? atoi(e) : 8;
+    if (p.raster_group < 1) p.raster_group = 1;
+    const char* d = getenv("FPQ_GEMM_DEBUG");
+    p.debug_flags = d ? atoi(d) : 0;
+  }
   int grid = sm_count();
   if (grid > p.num_tiles) grid = p.num_tiles;
   kern<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(ta, tb, p);

@@ -1,0 +1,377 @@
+// On-device GPTQ core for sm_100a: Hessian preparation, U = chol(H^-1, upper), the column-block
+// quantise / error-propagation loop and the relative-MSE metric.  Replaces GPTQ._get_hessian_inverse,
+// GPTQ.step and get_relative_mse_error of src/quantization/gptq.py (IST-DASLab/FP-Quant), which run
+// as ~50 small torch kernels per weight column plus cuSOLVER calls.
+//
+// All arithmetic is fp32 (the reference disables TF32).  The reference chain
+// cholesky -> cholesky_inverse -> cholesky(upper) is replaced by the mathematically equal
+//   P = J H J (rows and columns reversed),  P = L L^T,  U = J L^-1 J
+// because H = (J L J)(J L J)^T with J L J upper triangular, hence H^-1 = U^T U with U = (J L J)^-1.
+// One factorisation and one triangular inverse instead of two factorisations and a full inverse.
+
+#include "common.cuh"
+#include "sgemm.cuh"
+
+namespace fpq {
+namespace {
+
+constexpr int NB = 128;   // block size of the factorisation and of the GPTQ column blocks
+
+// ------------------------------------------------------------------ Hessian preparation
+__global__ void dead_columns_kernel(const float* __restrict__ W, int64_t rows, int64_t d, uint8_t* dead) {
+  const int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= d) return;
+  bool all_zero = true;
+  for (int64_t i = 0; i < rows && all_zero; ++i) all_zero = (W[i * d + j] == 0.0f);
+  dead[j] = all_zero ? 1 : 0;
+}
+
+__global__ void mask_dead_kernel(float* H, int64_t d, const uint8_t* __restrict__ dead) {
+  const int64_t n = d * d;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = idx / d, j = idx - i * d;
+    if (dead[i] || dead[j]) H[idx] = (i == j) ? 1.0f : 0.0f;
+  }
+}
+
+__global__ void damp_kernel(float* H, int64_t d, float rel_damp) {
+  // one block: mean of the diagonal, then diag += rel_damp * mean
+  __shared__ double part[256];
+  double s = 0.0;
+  for (int64_t i = threadIdx.x; i < d; i += blockDim.x) s += (double)H[i * d + i];
+  part[threadIdx.x] = s;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) part[threadIdx.x] += part[threadIdx.x + o];
+    __syncthreads();
+  }
+  const float damp = rel_damp * (float)(part[0] / (double)d);
+  for (int64_t i = threadIdx.x; i < d; i += blockDim.x) H[i * d + i] += damp;
+}
+
+// ------------------------------------------------------------------ reversal / reflection
+__global__ void reverse_copy_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t d) {
+  const int64_t n = d * d;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x)
+    dst[idx] = src[n - 1 - idx];   // (i, j) <- (d-1-i, d-1-j)
+}
+
+__global__ void reflect_inplace_kernel(float* A, int64_t d) {
+  const int64_t n = d * d, half = n / 2;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < half; idx += (int64_t)gridDim.x * blockDim.x) {
+    const float a = A[idx], b = A[n - 1 - idx];
+    A[idx] = b;
+    A[n - 1 - idx] = a;
+  }
+}
+
+// ------------------------------------------------------------------ diagonal block: factor + invert
+// One CTA factors the nb x nb (<= 128) diagonal block A (lower Cholesky, in place) and writes
+// L^-1 (lower) to Linv.  A non-positive or non-finite pivot sets *status and is replaced by 1 so
+// that the kernel always terminates with finite data.
+__global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, float* Linv, int64_t ldi, int nb,
+                                                        int32_t* status) {
+  extern __shared__ float sm[];
+  float* L = sm;                 // NB x (NB + 1)
+  float* X = sm + NB * (NB + 1); // NB x (NB + 1)
+  const int tid = threadIdx.x;
+  for (int idx = tid; idx < nb * nb; idx += blockDim.x) {
+    const int i = idx / nb, j = idx - i * nb;
+    L[i * (NB + 1) + j] = A[(int64_t)i * lda + j];
+  }
+  __syncthreads();
+  for (int k = 0; k < nb; ++k) {
+    float piv = L[k * (NB + 1) + k];
+    __syncthreads();
+    if (!(piv > 0.0f) || !isfinite(piv)) {
+      if (tid == 0) atomicExch(status, 1);
+      piv = 1.0f;
+    }
+    const float r = sqrtf(piv);
+    // scale column k
+    for (int i = k + tid; i < nb; i += blockDim.x) L[i * (NB + 1) + k] = (i == k) ? r : L[i * (NB + 1) + k] / r;
+    __syncthreads();
+    // rank-1 update of the trailing lower triangle
+    const int m = nb - (k + 1);
+    for (int idx = tid; idx < m * m; idx += blockDim.x) {
+      const int i = k + 1 + idx / m, j = k + 1 + idx % m;
+      if (j <= i) L[i * (NB + 1) + j] = fmaf(-L[i * (NB + 1) + k], L[j * (NB + 1) + k], L[i * (NB + 1) + j]);
+    }
+    __syncthreads();
+  }
+  // X = L^-1 by forward substitution, one column per thread
+  for (int c = tid; c < nb; c += blockDim.x) {
+    for (int i = 0; i < nb; ++i) {
+      float s = (i == c) ? 1.0f : 0.0f;
+      for (int j = c; j < i; ++j) s = fmaf(-L[i * (NB + 1) + j], X[j * (NB + 1) + c], s);
+      X[i * (NB + 1) + c] = (i < c) ? 0.0f : s / L[i * (NB + 1) + i];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < nb * nb; idx += blockDim.x) {
+    const int i = idx / nb, j = idx - i * nb;
+    A[(int64_t)i * lda + j] = (j <= i) ? L[i * (NB + 1) + j] : 0.0f;
+    Linv[(int64_t)i * ldi + j] = X[i * (NB + 1) + j];
+  }
+}
+
+int grid1d(int64_t n) {
+  int64_t b = (n + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  return (int)(b > cap ? cap : (b < 1 ? 1 : b));
+}
+
+// X[lo:hi, lo:hi] = L[lo:hi, lo:hi]^-1 for block indices [lo, hi), given the inverses of the diagonal
+// blocks already in X:  L^-1 = [[X11, 0], [-X22 (L21 X11), X22]].  S = L21 X11 (n2 x n1) goes to `scratch`.
+int tri_inverse_recursive(const float* L, float* X, float* scratch, int64_t d, int lo, int hi, cudaStream_t st) {
+  if (hi - lo <= 1) return FPQ_OK;
+  const int mid = (lo + hi) / 2;
+  if (int rc = tri_inverse_recursive(L, X, scratch, d, lo, mid, st)) return rc;
+  if (int rc = tri_inverse_recursive(L, X, scratch, d, mid, hi, st)) return rc;
+  const int64_t r0 = (int64_t)lo * NB, r1 = (int64_t)mid * NB;
+  const int64_t n1 = r1 - r0;
+  int64_t n2 = (int64_t)hi * NB - r1;
+  if (r1 + n2 > d) n2 = d - r1;
+  SgemmArgs a{};
+  // S = L21 * X11
+  a.A = L + r1 * d + r0; a.lda = d;
+  a.B = X + r0 * d + r0; a.ldb = d;
+  a.C = scratch; a.ldc = n1;
+  a.M = (int)n2; a.N = (int)n1; a.K = (int)n1; a.alpha = 1.0f; a.beta = 0.0f;
+  if (int rc = sgemm(a, false, SGEMM_PLAIN, st)) return rc;
+  // X21 = -X22 * S
+  a.A = X + r1 * d + r1; a.lda = d;
+  a.B = scratch; a.ldb = n1;
+  a.C = X + r1 * d + r0; a.ldc = d;
+  a.M = (int)n2; a.N = (int)n1; a.K = (int)n2; a.alpha = -1.0f; a.beta = 0.0f;
+  return sgemm(a, false, SGEMM_PLAIN, st);
+}
+
+// ------------------------------------------------------------------ GPTQ column block
+// One thread per weight row.  The thread keeps its 128 columns of the block in registers, walks
+// them left to right: quantise column i with the row's static group scale, turn the residual into
+// err = (w - wq) / U[i,i] and subtract err * U[i, j] from the columns j > i of the block
+// (src/quantization/gptq.py:166-186).  U's diagonal block sits in shared memory and is read by
+// all threads at the same address (broadcast).  Afterwards the registers hold the errors, which go
+// to Err[rows, 128] for the trailing update, and the dequantised values are rebuilt as
+// grid(code) * scale, exactly as they were computed.
+constexpr int SUB = 32;   // columns held in registers at a time
+
+// Columns [SUB*B, SUB*B + SUB) of the 128-column block for one row: bring them up to date with the
+// errors of the earlier columns of the block (same order as the reference applies them), then walk
+// them left to right.
+template <int G, int B>
+__device__ __forceinline__ void gptq_sub_block(float (&err)[NB], uint32_t (&cw)[NB / 8], const float (&sc)[NB / G],
+                                               const float* __restrict__ Us, const float* __restrict__ wrow) {
+  float w[SUB];
+  const float4* wp = reinterpret_cast<const float4*>(wrow + SUB * B);
+#pragma unroll
+  for (int q = 0; q < SUB / 4; ++q) {
+    const float4 v = wp[q];
+    w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
+  }
+#pragma unroll
+  for (int i = 0; i < SUB * B; ++i) {
+    const float e = err[i];
+#pragma unroll
+    for (int j = 0; j < SUB; ++j) w[j] = fmaf(-e, Us[i * NB + SUB * B + j], w[j]);
+  }
+#pragma unroll
+  for (int i = 0; i < SUB; ++i) {
+    const int col = SUB * B + i;
+    const float s = sc[col / G];
+    const uint32_t code = e2m1_code(__fdiv_rn(w[i], s));
+    cw[col / 8] |= code << (4 * (col % 8));
+    const float wq = __fmul_rn(e2m1_value(code), s);
+    const float e = __fdiv_rn(__fsub_rn(w[i], wq), Us[col * NB + col]);
+#pragma unroll
+    for (int j = i + 1; j < SUB; ++j) w[j] = fmaf(-e, Us[col * NB + SUB * B + j], w[j]);
+    err[col] = e;
+  }
+}
+
+template <int G>
+__global__ void __launch_bounds__(128, 1) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C, int64_t c1,
+                                                            const float* __restrict__ scales,
+                                                            const float* __restrict__ U, float* __restrict__ Err,
+                                                            uint8_t* __restrict__ codes) {
+  extern __shared__ float Us[];   // NB x NB, row-major
+  for (int idx = threadIdx.x; idx < NB * NB / 4; idx += blockDim.x) {
+    const int i = (idx * 4) / NB, j = (idx * 4) % NB;
+    *reinterpret_cast<float4*>(&Us[i * NB + j]) = *reinterpret_cast<const float4*>(&U[(c1 + i) * C + c1 + j]);
+  }
+  __syncthreads();
+  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+
+  constexpr int NGRP = NB / G;
+  float sc[NGRP];
+#pragma unroll
+  for (int g = 0; g < NGRP; ++g) sc[g] = scales[row * (C / G) + c1 / G + g];
+  uint32_t cw[NB / 8];
+#pragma unroll
+  for (int q = 0; q < NB / 8; ++q) cw[q] = 0;
+  float err[NB];
+  const float* wrow = W + row * C + c1;
+  gptq_sub_block<G, 0>(err, cw, sc, Us, wrow);
+  gptq_sub_block<G, 1>(err, cw, sc, Us, wrow);
+  gptq_sub_block<G, 2>(err, cw, sc, Us, wrow);
+  gptq_sub_block<G, 3>(err, cw, sc, Us, wrow);
+
+  float4* ep = reinterpret_cast<float4*>(Err + row * NB);
+#pragma unroll
+  for (int q = 0; q < NB / 4; ++q) ep[q] = make_float4(err[4 * q], err[4 * q + 1], err[4 * q + 2], err[4 * q + 3]);
+  float4* op = reinterpret_cast<float4*>(W + row * C + c1);
+#pragma unroll
+  for (int q = 0; q < NB / 4; ++q) {
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = 4 * q + j;
+      o[j] = __fmul_rn(e2m1_value((cw[i / 8] >> (4 * (i % 8))) & 15u), sc[i / G]);
+    }
+    op[q] = make_float4(o[0], o[1], o[2], o[3]);
+  }
+  if (codes) {
+    uint4* cp = reinterpret_cast<uint4*>(codes + row * (C / 2) + c1 / 2);
+#pragma unroll
+    for (int q = 0; q < NB / 32; ++q) cp[q] = make_uint4(cw[4 * q], cw[4 * q + 1], cw[4 * q + 2], cw[4 * q + 3]);
+  }
+}
+
+__global__ void diff_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = a[i] - b[i];
+}
+
+__global__ void ratio_kernel(const double* acc, float* out, double count) {
+  // mean(num) / (mean(den) + 1e-6), src/quantization/gptq.py:28-30
+  out[0] = (float)((acc[0] / count) / (acc[1] / count + 1e-6));
+}
+
+}  // namespace
+}  // namespace fpq
+
+using namespace fpq;
+
+extern "C" int fpq_hessian_prepare(float* H, int64_t d, const float* W, int64_t rows, float rel_damp,
+                                   uint8_t* workspace, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(H && W && workspace, "NULL pointer");
+  FPQ_CHECK_ARG(d > 0 && rows > 0, "bad shape");
+  cudaStream_t st = (cudaStream_t)stream;
+  dead_columns_kernel<<<(unsigned)((d + 255) / 256), 256, 0, st>>>(W, rows, d, workspace);
+  FPQ_CHECK_LAUNCH();
+  mask_dead_kernel<<<grid1d(d * d), 256, 0, st>>>(H, d, workspace);
+  FPQ_CHECK_LAUNCH();
+  damp_kernel<<<1, 256, 0, st>>>(H, d, rel_damp);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+extern "C" int64_t fpq_cholesky_workspace_floats(int64_t d) {
+  const int64_t nblk = (d + NB - 1) / NB;
+  const int64_t half = ((nblk + 1) / 2) * NB;
+  return d * d + half * half;
+}
+
+extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, float* workspace, int32_t* status,
+                                          fpq_stream_t stream) {
+  FPQ_CHECK_ARG(H && U && workspace && status, "NULL pointer");
+  FPQ_CHECK_ARG(d > 0 && d < (1ll << 30), "bad size");
+  FPQ_CHECK_ARG(H != U, "U must not alias H");
+  cudaStream_t st = (cudaStream_t)stream;
+  float* L = workspace;
+  float* scratch = workspace + d * d;
+  const int nblk = (int)((d + NB - 1) / NB);
+  static bool configured[64] = {};
+  int dev = 0;
+  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
+  const int diag_smem = 2 * NB * (NB + 1) * (int)sizeof(float);
+  if (dev < 64 && !configured[dev]) {
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, diag_smem));
+    configured[dev] = true;
+  }
+  FPQ_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+  reverse_copy_kernel<<<grid1d(d * d), 256, 0, st>>>(H, L, d);
+  FPQ_CHECK_LAUNCH();
+  FPQ_CHECK_CUDA(cudaMemsetAsync(U, 0, (size_t)d * d * sizeof(float), st));
+  for (int k = 0; k < nblk; ++k) {
+    const int64_t r = (int64_t)k * NB;
+    const int nb = (int)((d - r) < NB ? (d - r) : NB);
+    chol_diag_kernel<<<1, 256, diag_smem, st>>>(L + r * d + r, d, U + r * d + r, d, nb, status);
+    FPQ_CHECK_LAUNCH();
+    const int64_t below = d - (r + nb);
+    if (below <= 0) break;
+    SgemmArgs a{};
+    // panel: L21 = A21 * L11^-T  (in place: every CTA reads only the 128 rows it then overwrites)
+    a.A = L + (r + nb) * d + r; a.lda = d;
+    a.B = U + r * d + r; a.ldb = d;
+    a.C = L + (r + nb) * d + r; a.ldc = d;
+    a.M = (int)below; a.N = nb; a.K = nb; a.alpha = 1.0f; a.beta = 0.0f;
+    if (int rc = sgemm(a, true, SGEMM_PLAIN, st)) return rc;
+    // trailing update: A22 -= L21 L21^T (lower tiles only)
+    a.A = L + (r + nb) * d + r; a.lda = d;
+    a.B = L + (r + nb) * d + r; a.ldb = d;
+    a.C = L + (r + nb) * d + (r + nb); a.ldc = d;
+    a.M = (int)below; a.N = (int)below; a.K = nb; a.alpha = -1.0f; a.beta = 1.0f;
+    if (int rc = sgemm(a, true, SGEMM_LOWER, st)) return rc;
+  }
+  if (int rc = tri_inverse_recursive(L, U, scratch, d, 0, nblk, st)) return rc;
+  reflect_inplace_kernel<<<grid1d(d * d / 2), 256, 0, st>>>(U, d);   // U <- J X J (upper triangular)
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const float* scales, int group,
+                                 const float* U, uint8_t* codes, float* err_workspace, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(W && scales && U && err_workspace, "NULL pointer");
+  FPQ_CHECK_ARG(group == 16 || group == 32, "group must be 16 (NVFP4) or 32 (MXFP4)");
+  FPQ_CHECK_ARG(rows > 0 && cols > 0 && cols % NB == 0, "cols (%lld) must be a multiple of %d", (long long)cols, NB);
+  FPQ_CHECK_ARG(((uintptr_t)W & 15) == 0 && ((uintptr_t)U & 15) == 0 && ((uintptr_t)err_workspace & 15) == 0 &&
+                    ((uintptr_t)codes & 15) == 0, "pointers must be 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  static bool configured[64] = {};
+  int dev = 0;
+  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
+  const int smem = NB * NB * (int)sizeof(float);
+  if (dev < 64 && !configured[dev]) {
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev] = true;
+  }
+  const unsigned grid = (unsigned)((rows + 127) / 128);
+  for (int64_t c1 = 0; c1 < cols; c1 += NB) {
+    if (group == 16)
+      gptq_block_kernel<16><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err_workspace, codes);
+    else
+      gptq_block_kernel<32><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err_workspace, codes);
+    FPQ_CHECK_LAUNCH();
+    const int64_t c2 = c1 + NB;
+    if (c2 >= cols) break;
+    SgemmArgs a{};   // W[:, c2:] -= Err * U[c1:c2, c2:]
+    a.A = err_workspace; a.lda = NB;
+    a.B = U + c1 * cols + c2; a.ldb = cols;
+    a.C = W + c2; a.ldc = cols;
+    a.M = (int)rows; a.N = (int)(cols - c2); a.K = NB; a.alpha = -1.0f; a.beta = 1.0f;
+    if (int rc = sgemm(a, false, SGEMM_PLAIN, st)) return rc;
+  }
+  return FPQ_OK;
+}
+
+extern "C" int fpq_relative_mse(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
+                                float* diff_workspace, double* acc_workspace, float* out, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(Wq && W && H && diff_workspace && acc_workspace && out, "NULL pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  FPQ_CHECK_CUDA(cudaMemsetAsync(acc_workspace, 0, 2 * sizeof(double), st));
+  diff_kernel<<<grid1d(rows * d), 256, 0, st>>>(Wq, W, diff_workspace, rows * d);
+  FPQ_CHECK_LAUNCH();
+  SgemmArgs a{};
+  a.lda = d; a.B = H; a.ldb = d; a.M = (int)rows; a.N = (int)d; a.K = (int)d; a.alpha = 1.0f; a.ldd = d;
+  a.A = diff_workspace; a.D = diff_workspace; a.dot_out = acc_workspace;
+  if (int rc = sgemm(a, false, SGEMM_DOT, st)) return rc;
+  a.A = W; a.D = W; a.dot_out = acc_workspace + 1;
+  if (int rc = sgemm(a, false, SGEMM_DOT, st)) return rc;
+  ratio_kernel<<<1, 1, 0, st>>>(acc_workspace, out, (double)rows * (double)d);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}

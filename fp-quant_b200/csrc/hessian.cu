@@ -1,0 +1,278 @@
+// Hessian accumulation for GPTQ on sm_100a:  H[d,d] (fp32) = beta * H + alpha * X^T X,  X [T,d] bf16.
+//
+// Replaces the Triton kernel accumulate_hessian_triton_kernel
+// (src/quantization/accumulate_hessian.py:20-109 of IST-DASLab/FP-Quant) and the rescaling around it in
+// GPTQ.update (src/quantization/gptq.py:94-102).  bf16 x bf16 products are exact in the fp32
+// accumulator, so the result is more accurate than the reference's TF32 dot of fp32-cast inputs.
+//
+// X^T X is a GEMM whose two operands are the same row-major matrix read "MN-major": a TMA box of
+// 64 columns x 64 tokens with the 128-byte swizzle lands in shared memory exactly in the canonical
+// MN-major layout of tcgen05.mma (8 token rows of 128 bytes per swizzle atom).  Persistent CTAs walk
+// the 128 x 128 tiles of the lower triangle (or all tiles for the general A^T B form); two fp32
+// accumulators in tensor memory let the read-modify-write epilogue of one tile overlap the MMAs of
+// the next.  Off-diagonal tiles are also written mirrored, so H stays fully symmetric like the
+// reference's.  Warp roles and bounded waits as in the FP4 GEMM.
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace fpq {
+namespace {
+
+using namespace ptx;
+
+constexpr int TILE = 128;            // output tile (both dims)
+constexpr int BK = 64;               // tokens per stage
+constexpr int BOX_BYTES = BK * 128;  // one 64-column x 64-token box
+constexpr int STAGES = 6;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 256;       // two 128-column accumulators
+
+struct HessParams {
+  int64_t T, d;
+  int num_blocks;      // ceil(d / 128)
+  int num_tiles;
+  int num_k_stages;    // ceil(T / 64)
+  int symmetric;
+  float alpha, beta;
+  float* H;
+  int* error_flag;
+};
+
+struct Smem {
+  static constexpr int OFF_A = 0;                               // STAGES x 2 boxes
+  static constexpr int OFF_B = OFF_A + STAGES * 2 * BOX_BYTES;
+  static constexpr int OFF_BAR = OFF_B + STAGES * 2 * BOX_BYTES;  // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr int OFF_MISC = OFF_BAR + (2 * STAGES + 4) * 8;
+  static constexpr int TOTAL = OFF_MISC + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+// MN-major operand, 128-byte swizzle: 64 contiguous MN elements per 128-byte row, 8 K rows per atom
+// (`sbo` bytes between atoms along K), further 64-wide MN blocks `lbo` bytes apart.
+__device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ void tile_coords(const HessParams& p, int tile, int& ib, int& jb) {
+  if (p.symmetric) {
+    // tile = ib * (ib + 1) / 2 + jb with jb <= ib
+    int i = (int)((sqrtf(8.0f * (float)tile + 1.0f) - 1.0f) * 0.5f);
+    while ((i + 1) * (i + 2) / 2 <= tile) ++i;
+    while (i * (i + 1) / 2 > tile) --i;
+    ib = i;
+    jb = tile - i * (i + 1) / 2;
+  } else {
+    ib = tile / p.num_blocks;
+    jb = tile - ib * p.num_blocks;
+  }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const HessParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar_full = sbase + Smem::OFF_BAR;
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_acc_full = bar_empty + STAGES * 8;   // [2]
+  const uint32_t bar_acc_empty = bar_acc_full + 16;       // [2]
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + Smem::OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::OFF_MISC + 4);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        int ib, jb;
+        tile_coords(p, tile, ib, jb);
+        for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar_full + 8 * s, 4 * BOX_BYTES);
+          const uint32_t a_dst = sbase + Smem::OFF_A + s * 2 * BOX_BYTES;
+          const uint32_t b_dst = sbase + Smem::OFF_B + s * 2 * BOX_BYTES;
+          tma_load_2d(a_dst, &tmap_a, ib * TILE, ks * BK, bar_full + 8 * s);
+          tma_load_2d(a_dst + BOX_BYTES, &tmap_a, ib * TILE + 64, ks * BK, bar_full + 8 * s);
+          tma_load_2d(b_dst, &tmap_b, jb * TILE, ks * BK, bar_full + 8 * s);
+          tma_load_2d(b_dst + BOX_BYTES, &tmap_b, jb * TILE + 64, ks * BK, bar_full + 8 * s);
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error_flag, 1);
+      }
+      const uint32_t first = it > STAGES ? it - STAGES : 0;
+      volatile int never = 0;
+      for (uint32_t j = first; j < it; ++j)
+        (void)mbar_wait_bounded(bar_full + 8 * (j % STAGES), (j / STAGES) & 1, &never, 200000000LL);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(TILE, TILE, true, true);
+      uint32_t it = 0, tile_count = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tile_count) {
+        const uint32_t buf = tile_count & 1;
+        if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tile_count >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t acc = tmem_base + buf * TILE;
+        for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_bounded(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t a_desc = make_desc_mn_sw128(sbase + Smem::OFF_A + s * 2 * BOX_BYTES, BOX_BYTES, 1024);
+          const uint64_t b_desc = make_desc_mn_sw128(sbase + Smem::OFF_B + s * 2 * BOX_BYTES, BOX_BYTES, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k)   // 16 tokens per MMA = two 8-row atoms = 2048 bytes
+            tc_mma_f16(acc, a_desc + (uint64_t)(k * (2048 >> 4)), b_desc + (uint64_t)(k * (2048 >> 4)), idesc,
+                       (ks > 0 || k > 0) ? 1u : 0u);
+          tc_commit(bar_empty + 8 * s);
+        }
+        if (ok) tc_commit(bar_acc_full + 8 * buf);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error_flag, 1);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    uint32_t tile_count = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tile_count) {
+      int ib, jb;
+      tile_coords(p, tile, ib, jb);
+      const uint32_t buf = tile_count & 1;
+      if (!mbar_wait_bounded(bar_acc_full + 8 * buf, (tile_count >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t i = (int64_t)ib * TILE + quarter * 32 + lane;
+      const bool mirror = p.symmetric && ib != jb;
+#pragma unroll 1
+      for (int c = 0; c < TILE / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE + c * 32, r);
+        tc_wait_ld();
+        const int64_t j0 = (int64_t)jb * TILE + c * 32;
+        if (i < p.d) {
+          float* hrow = p.H + i * p.d + j0;
+          if (j0 + 32 <= p.d && (p.d & 3) == 0) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 h = p.beta == 0.0f ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(hrow)[q];
+              h.x = fmaf(p.beta, h.x, p.alpha * __uint_as_float(r[4 * q]));
+              h.y = fmaf(p.beta, h.y, p.alpha * __uint_as_float(r[4 * q + 1]));
+              h.z = fmaf(p.beta, h.z, p.alpha * __uint_as_float(r[4 * q + 2]));
+              h.w = fmaf(p.beta, h.w, p.alpha * __uint_as_float(r[4 * q + 3]));
+              reinterpret_cast<float4*>(hrow)[q] = h;
+              r[4 * q] = __float_as_uint(h.x); r[4 * q + 1] = __float_as_uint(h.y);
+              r[4 * q + 2] = __float_as_uint(h.z); r[4 * q + 3] = __float_as_uint(h.w);
+            }
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj) {
+              if (j0 + jj < p.d) {
+                const float old = p.beta == 0.0f ? 0.0f : hrow[jj];
+                const float v = fmaf(p.beta, old, p.alpha * __uint_as_float(r[jj]));
+                hrow[jj] = v;
+                r[jj] = __float_as_uint(v);
+              }
+            }
+          }
+          if (mirror) {
+            // H[j, i]: consecutive lanes hold consecutive i, so each store instruction is coalesced
+#pragma unroll
+            for (int jj = 0; jj < 32; ++jj)
+              if (j0 + jj < p.d) p.H[(j0 + jj) * p.d + i] = __uint_as_float(r[jj]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicExch(p.error_flag, 1);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+}  // namespace fpq
+
+using namespace fpq;
+
+extern "C" int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, const void* xb_bf16, int64_t tokens,
+                                      float alpha, float beta, int32_t* error_flag, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(H && xa_bf16 && error_flag, "NULL pointer");
+  FPQ_CHECK_ARG(d > 0 && tokens >= 0 && d % 8 == 0, "d (%lld) must be a positive multiple of 8", (long long)d);
+  FPQ_CHECK_ARG(d < (1ll << 30) && tokens < (1ll << 31), "shape too large");
+  FPQ_CHECK_ARG(((uintptr_t)xa_bf16 & 15) == 0 && ((uintptr_t)xb_bf16 & 15) == 0 && ((uintptr_t)H & 15) == 0,
+                "pointers must be 16-byte aligned");
+  if (tokens == 0) return FPQ_OK;
+  const bool symmetric = xb_bf16 == nullptr || xb_bf16 == xa_bf16;
+  HessParams p{};
+  p.T = tokens; p.d = d;
+  p.num_blocks = (int)((d + TILE - 1) / TILE);
+  p.num_tiles = symmetric ? p.num_blocks * (p.num_blocks + 1) / 2 : p.num_blocks * p.num_blocks;
+  p.num_k_stages = (int)((tokens + BK - 1) / BK);
+  p.symmetric = symmetric ? 1 : 0;
+  p.alpha = alpha; p.beta = beta; p.H = H; p.error_flag = error_flag;
+  CUtensorMap ta, tb;
+  if (int rc = make_tensor_map_2d(&ta, xa_bf16, 2, (uint64_t)d, (uint64_t)tokens, (uint64_t)d * 2, 64, BK, 1)) return rc;
+  if (int rc = make_tensor_map_2d(&tb, symmetric ? xa_bf16 : xb_bf16, 2, (uint64_t)d, (uint64_t)tokens, (uint64_t)d * 2,
+                                  64, BK, 1)) return rc;
+  static bool configured[64] = {};
+  int dev = 0;
+  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(hessian_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::DYN_BYTES));
+    configured[dev] = true;
+  }
+  int grid = sm_count();
+  if (grid > p.num_tiles) grid = p.num_tiles;
+  hessian_kernel<<<grid, NUM_THREADS, Smem::DYN_BYTES, (cudaStream_t)stream>>>(ta, tb, p);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}

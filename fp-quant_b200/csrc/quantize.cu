@@ -105,6 +105,11 @@ __device__ __forceinline__ void load_chunk(const void* base, int64_t chunk, bool
 // Butterfly stages with pair distance 1..min(GH,32)/2 inside the thread, then the
 // cross-lane stages for distance 32 (GH >= 64) and 64 (GH == 128), then * 1/sqrt(GH).
 template <int GH>
+__device__ __forceinline__ constexpr float hadamard_scale() {
+  return GH == 16 ? 0.25f : GH == 32 ? 0.17677669529663687f : GH == 64 ? 0.125f : GH == 128 ? 0.08838834764831845f : 1.0f;
+}
+
+template <int GH, bool SCALE = true>
 __device__ __forceinline__ void rotate_chunk(u64 (&P)[16], int lane) {
   if (GH == 0) return;
   // distance 1: inside each packed pair
@@ -140,10 +145,35 @@ __device__ __forceinline__ void rotate_chunk(u64 (&P)[16], int lane) {
       }
     }
   }
-  const float c = GH == 16 ? 0.25f : GH == 32 ? 0.17677669529663687f : GH == 64 ? 0.125f : 0.08838834764831845f;
-  const u64 C = pack2(c, c);
+  if (SCALE) {
+    const float c = hadamard_scale<GH>();
+    const u64 C = pack2(c, c);
 #pragma unroll
-  for (int j = 0; j < 16; ++j) P[j] = mul2(P[j], C);
+    for (int j = 0; j < 16; ++j) P[j] = mul2(P[j], C);
+  }
+}
+
+__device__ __forceinline__ u64 mul2_rz(u64 a, u64 b) {
+  u64 r;
+  asm("mul.rz.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// MXFP4 shortcut.  With s = fl(4/3) * 2^(e-2) the E2M1 code of fl(fl(t*c) / s) -- t the unscaled
+// butterfly output, c = 1/sqrt(g) -- equals the code of ONE rounded product t * (m * 2^(2-e)):
+//   c a power of two (g = 16, 64, or no rotation): m = 0.75 * c, product rounded toward zero;
+//   g = 32, 128:                                   m = fl(c / fl(4/3)), product rounded to nearest.
+// Both were checked against the two-step form on every fp32 input within 20000 ulps of each of the
+// seven rounding boundaries (and on random inputs); away from the boundaries the two values differ
+// by a few ulps at most, which cannot change the code.
+template <int GH>
+__device__ __forceinline__ u64 mx_code_multiplier(int e) {
+  constexpr bool POW2 = GH == 0 || GH == 16 || GH == 64;
+  constexpr uint32_t mbits = GH == 0 ? 0x3f400000u : GH == 16 ? 0x3e400000u : GH == 64 ? 0x3dc00000u
+                           : GH == 32 ? 0x3e07c3b6u : 0x3d87c3b6u;
+  (void)POW2;
+  const float m = __uint_as_float(mbits + ((uint32_t)(2 - e) << 23));   // exact scaling by 2^(2-e)
+  return pack2(m, m);
 }
 
 __device__ __forceinline__ float absmax_pairs(const u64* P, int n) {
@@ -170,10 +200,10 @@ __device__ __forceinline__ int mx_exponent(float m /* >= 2^-126, finite */) {
 }
 
 // MXFP4 scale of one 32-element group: returns the divisor s and the stored byte.
-__device__ __forceinline__ float mx_scale(float a, uint32_t& byte) {
+__device__ __forceinline__ float mx_scale(float a, uint32_t& byte, int& e) {
   float s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
   float m = fmaxf(__fmul_rn(6.0f, s0), 1.17549435e-38f);
-  int e = mx_exponent(m);
+  e = mx_exponent(m);
   byte = (uint32_t)(e + 127);
   float s;
   if (e >= -124) {
@@ -267,7 +297,10 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
     const bool active = c < p.n_chunks;
     u64 P[16];
     load_chunk<IN_BF16>(p.x, c, active, P);
-    rotate_chunk<GH>(P, lane);
+    // MXFP4 codes take the unscaled butterfly output (the 1/sqrt(g) factor is folded into the
+    // code multiplier); every other mode works on the scaled rotation.
+    constexpr bool MX_FAST = MODE == MODE_CODES && FMT == FPQ_FMT_MXFP4;
+    rotate_chunk<GH, !MX_FAST>(P, lane);
 
     if (MODE == MODE_ABSMAX) {
       running_max = fmaxf(running_max, absmax_pairs(P, 16));
@@ -303,10 +336,12 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
     constexpr int PG = 16 / NG;                       // pairs per group
     float s[NG];
     uint32_t sb[NG];
+    int mx_e = 0;
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
       float a = absmax_pairs(P + g * PG, PG);
-      s[g] = FMT == FPQ_FMT_NVFP4 ? nv_scale(a, gs, rgs, sb[g]) : mx_scale(a, sb[g]);
+      if (MX_FAST && GH != 0) a = __fmul_rn(a, hadamard_scale<GH>());   // max |t*c| = fl(c * max |t|)
+      s[g] = FMT == FPQ_FMT_NVFP4 ? nv_scale(a, gs, rgs, sb[g]) : mx_scale(a, sb[g], mx_e);
     }
     if (MODE == MODE_CODES && active) {
       const uint32_t row = (uint32_t)(c / p.chunks_per_row);
@@ -337,8 +372,25 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
       for (int j = 0; j < 16; ++j) Y[j] = P[j];
     }
 
+    if (MX_FAST) {
+      if (mx_e >= -120 && mx_e <= 120) {
+        const u64 MK = mx_code_multiplier<GH>(mx_e);
+        constexpr bool RZ = GH == 0 || GH == 16 || GH == 64;
 #pragma unroll
-    for (int g = 0; g < NG; ++g) divide_pairs(P + g * PG, PG, s[g]);
+        for (int j = 0; j < 16; ++j) P[j] = RZ ? mul2_rz(P[j], MK) : mul2(P[j], MK);
+      } else {   // extreme exponents: scale, then divide exactly
+        if (GH != 0) {
+          const float cc = hadamard_scale<GH>();
+          const u64 C = pack2(cc, cc);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) P[j] = mul2(P[j], C);
+        }
+        divide_pairs(P, 16, s[0]);
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < NG; ++g) divide_pairs(P + g * PG, PG, s[g]);
+    }
 
     uint32_t cw[4];
 #pragma unroll

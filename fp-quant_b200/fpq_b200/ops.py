@@ -7,6 +7,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _cabi as C
+from ._cabi import call as _cabi_call
 
 FORMATS = {"mxfp4": C.FMT_MXFP4, "nvfp4": C.FMT_NVFP4}
 GROUP_OF = {"mxfp4": 32, "nvfp4": 16}
@@ -211,3 +212,110 @@ def gemm_fp4(a_codes: torch.Tensor, b_codes: torch.Tensor, a_scales_swizzled: to
         C.call("fpq_gemm_fp4", a.data_ptr(), b.data_ptr(), sa.data_ptr(), sb.data_ptr(), alpha.data_ptr(),
                _ptr(bias), out.data_ptr(), M, N, K, FORMATS[fmt], device_error_flag(a.device).data_ptr(), _stream(a))
     return out
+
+
+# --------------------------------------------------------------------------- GPTQ core
+def _f32(t: torch.Tensor, name: str, inplace: bool = False) -> torch.Tensor:
+    t = _cuda(t, name)
+    if t.dtype != torch.float32:
+        raise ValueError(f"{name} must be a float32 tensor")
+    if not t.is_contiguous():
+        if inplace:
+            raise ValueError(f"{name} is modified in place and must be contiguous")
+        t = t.contiguous()
+    return t
+
+
+def sgemm(A: torch.Tensor, B: torch.Tensor, b_transposed: bool = False, C: Optional[torch.Tensor] = None,
+          alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """True-fp32 matrix product C = beta*C + alpha * A @ (B^T if b_transposed else B)."""
+    A, B = _f32(A, "A"), _f32(B, "B")
+    M, K = A.shape
+    N = B.shape[0] if b_transposed else B.shape[1]
+    if C is None:
+        C = torch.zeros(M, N, dtype=torch.float32, device=A.device)
+        beta = 0.0
+    with torch.cuda.device(A.device):
+        _cabi_call("fpq_sgemm", A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), int(b_transposed), C.data_ptr(),
+                   C.stride(0), M, N, K, alpha, beta, _stream(A))
+    return C
+
+
+def hessian_prepare(H: torch.Tensor, W: torch.Tensor, rel_damp: float) -> torch.Tensor:
+    """In place: dead-column fix + damping of the Hessian (GPTQ._get_hessian_inverse, first half)."""
+    H, W = _f32(H, "H", inplace=True), _f32(W, "W")
+    d = H.shape[0]
+    ws = torch.empty(d, dtype=torch.uint8, device=H.device)
+    with torch.cuda.device(H.device):
+        C.call("fpq_hessian_prepare", H.data_ptr(), d, W.data_ptr(), W.shape[0], float(rel_damp), ws.data_ptr(),
+               _stream(H))
+    return H
+
+
+def cholesky_inverse_upper(H: torch.Tensor):
+    """(U, status): U upper with U^T U = H^-1; status is a device int32[1], 1 if H was not positive definite."""
+    H = _f32(H, "H")
+    d = H.shape[0]
+    U = torch.empty_like(H)
+    n = int(C.lib().fpq_cholesky_workspace_floats(d))
+    ws = torch.empty(n, dtype=torch.float32, device=H.device)
+    status = torch.zeros(1, dtype=torch.int32, device=H.device)
+    with torch.cuda.device(H.device):
+        C.call("fpq_cholesky_inverse_upper", H.data_ptr(), U.data_ptr(), d, ws.data_ptr(), status.data_ptr(),
+               _stream(H))
+    return U, status
+
+
+def gptq_quantize(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group: int, want_codes: bool = True):
+    """Runs the GPTQ column loop on W in place (W becomes the dequantised weight).  Returns packed codes or None."""
+    W, scales, U = _f32(W, "W", inplace=True), _f32(scales, "scales"), _f32(U, "U")
+    rows, cols = W.shape
+    codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=W.device) if want_codes else None
+    err = torch.empty(rows, 128, dtype=torch.float32, device=W.device)
+    with torch.cuda.device(W.device):
+        C.call("fpq_gptq_quantize", W.data_ptr(), rows, cols, scales.data_ptr(), group, U.data_ptr(), _ptr(codes),
+               err.data_ptr(), _stream(W))
+    return codes
+
+
+def relative_mse(Wq: torch.Tensor, W: torch.Tensor, H: torch.Tensor) -> torch.Tensor:
+    """Device fp32[1]: mean(((Wq-W) H) * (Wq-W)) / (mean((W H) * W) + 1e-6)."""
+    Wq, W, H = _f32(Wq, "Wq"), _f32(W, "W"), _f32(H, "H")
+    rows, d = W.shape
+    diff = torch.empty_like(W)
+    acc = torch.zeros(2, dtype=torch.float64, device=W.device)
+    out = torch.empty(1, dtype=torch.float32, device=W.device)
+    with torch.cuda.device(W.device):
+        C.call("fpq_relative_mse", Wq.data_ptr(), W.data_ptr(), H.data_ptr(), rows, d, diff.data_ptr(),
+               acc.data_ptr(), out.data_ptr(), _stream(W))
+    return out
+
+
+def hessian_accumulate(H: torch.Tensor, x: torch.Tensor, alpha: float = 1.0, beta: float = 1.0) -> torch.Tensor:
+    """H = beta * H + alpha * X^T X in place; X [..., d] bf16 (exact) or fp32 (split into three bf16
+    terms whose six leading cross products are accumulated, ~2^-24 relative)."""
+    H = _f32(H, "H", inplace=True)
+    x = _cuda(x, "x")
+    d = x.shape[-1]
+    x2 = x.reshape(-1, d)
+    flag = device_error_flag(H.device).data_ptr()
+
+    def call(a, b, al, be):
+        with torch.cuda.device(H.device):
+            C.call("fpq_hessian_accumulate", H.data_ptr(), d, a.data_ptr(), None if b is None else b.data_ptr(),
+                   a.shape[0], float(al), float(be), flag, _stream(H))
+
+    if x2.dtype == torch.bfloat16:
+        call(x2.contiguous(), None, alpha, beta)
+        return H
+    if x2.dtype != torch.float32:
+        x2 = x2.float()
+    t0 = x2.to(torch.bfloat16)
+    r1 = x2 - t0.float()
+    t1 = r1.to(torch.bfloat16)
+    t2 = (r1 - t1.float()).to(torch.bfloat16)
+    call(t0, None, alpha, beta)
+    call(t1, None, alpha, 1.0)
+    for a, b in ((t0, t1), (t1, t0), (t0, t2), (t2, t0)):
+        call(a, b, alpha, 1.0)
+    return H

@@ -1,3 +1,6 @@
+from .accumulate_hessian import accumulate_hessian
+from .gptq import GPTQ, get_relative_mse_error
+from .qlinear import QLinear
 from .quant_args import (QuantizationFormat, QuantizationGranularity, QuantizationObserver, QuantizationOrder,
                          ScalePrecision)
 from .quantizer import Quantizer

@@ -1,0 +1,97 @@
+"""`GPTQ` with the interface of the class in src/quantization/gptq.py:33-222 (IST-DASLab/FP-Quant);
+every numeric step runs in the CUDA library: Hessian accumulation on tensor cores, damped
+Cholesky-inverse factor, the column-block quantise / error-propagation loop, relative MSE.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .quant_args import QuantizationOrder
+from .quant_ops import FP4_CODE_VALUES
+from .quantizer import Quantizer
+
+
+def get_relative_mse_error(q: torch.Tensor, w: torch.Tensor, H: torch.Tensor) -> torch.Tensor:
+    """mean(((q - w) H) * (q - w)) / (mean((w H) * w) + 1e-6)  (gptq.py:28-30), a device scalar."""
+    return ops.relative_mse(q.float().contiguous(), w.float().contiguous(), H).reshape(())
+
+
+class GPTQ:
+    def __init__(self, layer: nn.Module, quantizer: Quantizer, quantization_order: str = "default",
+                 block_size: int = 128, rel_damp: float = 1e-2, export_quantized_model: str = ""):
+        assert isinstance(layer, nn.Linear), "the B200 path quantises linear layers"
+        if block_size != 128:
+            raise NotImplementedError("the column-block kernel is built for block_size = 128")
+        self.layer = layer
+        self.W = layer.weight
+        self.d_row, self.d_col = layer.weight.shape
+        self.quantizer = quantizer
+        self.quantization_order = QuantizationOrder(quantization_order)
+        if self.quantization_order != QuantizationOrder.DEFAULT:
+            raise NotImplementedError("activation-order GPTQ is not built yet")
+        self.block_size, self.rel_damp = block_size, rel_damp
+        self.W_device, self.W_dtype, self.W_shape = self.W.device, self.W.dtype, self.W.shape
+        self.H: Optional[torch.Tensor] = None
+        self.num_samples = 0
+        self.export_quantized_model = export_quantized_model
+        self.packed_codes: Optional[torch.Tensor] = None     # uint8 [rows, cols/2] of the last `step`
+        self.used_identity_fallback = False
+
+    @torch.no_grad()
+    def update(self, input: torch.Tensor) -> None:
+        """Fold a batch of layer inputs into the running mean H = (2/N) sum X^T X, N counted in
+        `input.shape[0]` units exactly as the reference does (gptq.py:69-102).  The mean's factors
+        go onto H (alpha, beta of the kernel) instead of rescaling the input."""
+        batch_size = input.shape[0]
+        if self.H is None:
+            self.H = torch.zeros((self.d_col, self.d_col), device=input.device, dtype=torch.float32)
+        x = input.reshape(-1, input.shape[-1])
+        beta = self.num_samples / (self.num_samples + batch_size)
+        alpha = 2.0 / (self.num_samples + batch_size)
+        ops.hessian_accumulate(self.H, x, alpha=alpha, beta=beta)
+        self.num_samples += batch_size
+
+    def reset(self) -> None:
+        self.W = self.layer.weight
+        self.H = None
+        self.num_samples = 0
+        self.packed_codes = None
+
+    @torch.no_grad()
+    def quantization_pre_step(self) -> None:
+        assert self.H is not None, "One has to process at least one sample of calibration data to run pruning"
+        self.W = self.W.clone().float()
+        self.pre_step_completed = True
+
+    @torch.no_grad()
+    def step(self) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor]:
+        """Returns (dequantised weight in the layer dtype, E2M1 grid values or None, fp32 group scales).
+        `self.H` is left damped, as in the reference, where the caller reuses it for the relative MSE."""
+        group = self.quantizer.group_size
+        scales, _ = self.quantizer.get_quantization_params(self.W)        # static scales, gptq.py:142
+        U = self._get_hessian_inverse()
+        w = self.W.clone()
+        self.packed_codes = ops.gptq_quantize(w, scales.float().contiguous(), U, group, want_codes=True)
+        qweight = None
+        if self.export_quantized_model:
+            lut = torch.tensor(FP4_CODE_VALUES, dtype=self.W_dtype, device=w.device)
+            c = self.packed_codes
+            qweight = torch.stack((lut[(c & 0xF).long()], lut[(c >> 4).long()]), dim=-1).reshape(self.W.shape)
+        return w.to(self.W_dtype), qweight, scales
+
+    @torch.no_grad()
+    def _get_hessian_inverse(self) -> torch.Tensor:
+        ops.hessian_prepare(self.H, self.W, self.rel_damp)
+        U, status = ops.cholesky_inverse_upper(self.H)
+        self.used_identity_fallback = bool(status.item())
+        if self.used_identity_fallback:      # the reference's `except:` branch (gptq.py:216-217)
+            U = torch.eye(self.d_col, device=self.H.device, dtype=torch.float32)
+        return U
+
+    def quantize(self):
+        self.quantization_pre_step()
+        return self.step()

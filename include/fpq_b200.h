@@ -152,6 +152,66 @@ int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* 
                  void* out_bf16, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
                  fpq_stream_t stream);
 
+/*
+ * C[M,N] = beta * C + alpha * A[M,K] * op(B) in true fp32 (no TF32), row-major with leading
+ * dimensions; op(B) = B[K,N] or, when b_transposed, B[N,K]^T.  Stands in for the torch fp32
+ * matmuls of the GPTQ path (src/quantization/gptq.py:29-30, :184-187; TF32 is switched off at
+ * model_quant.py:27-29).
+ */
+int fpq_sgemm(const float* A, int64_t lda, const float* B, int64_t ldb, int b_transposed, float* C,
+              int64_t ldc, int64_t M, int64_t N, int64_t K, float alpha, float beta, fpq_stream_t stream);
+
+/*
+ * H[d,d] (fp32) = beta * H + alpha * Xa^T Xb on the tcgen05 tensor cores (bf16 operands, exact products,
+ * fp32 accumulation).  With xb NULL or equal to xa only the lower-triangle tiles are computed and
+ * mirrored, as accumulate_hessian does (src/quantization/accumulate_hessian.py:20-148); alpha and beta
+ * carry the running-mean factors of GPTQ.update (src/quantization/gptq.py:94-102), so the input is
+ * not rescaled.  xa, xb: bf16 [tokens, d] row-major, d % 8 == 0.  error_flag as in fpq_gemm_fp4.
+ */
+int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, const void* xb_bf16, int64_t tokens,
+                           float alpha, float beta, int32_t* error_flag, fpq_stream_t stream);
+
+/*
+ * In-place Hessian preparation of GPTQ._get_hessian_inverse (src/quantization/gptq.py:201-211):
+ * rows/columns of H whose weight column W[:, j] is entirely zero are cleared and get a unit
+ * diagonal, then rel_damp * mean(diag H) is added to the diagonal.  H [d,d], W [rows,d] fp32;
+ * workspace: d bytes.
+ */
+int fpq_hessian_prepare(float* H, int64_t d, const float* W, int64_t rows, float rel_damp,
+                        uint8_t* workspace, fpq_stream_t stream);
+
+/* Number of floats fpq_cholesky_inverse_upper needs as workspace for a d x d matrix. */
+int64_t fpq_cholesky_workspace_floats(int64_t d);
+
+/*
+ * U = upper-triangular factor with U^T U = H^-1: what `torch.linalg.cholesky(inv_sym(H), upper=True)`
+ * returns (src/quantization/gptq.py:212-215, src/utils/linalg_utils.py:8-12), computed as one
+ * Cholesky factorisation of the index-reversed H and one triangular inverse, all in fp32.
+ * *status (device int32) becomes 1 when a pivot is not positive -- the reference then falls back to
+ * the identity (gptq.py:216-217); the caller decides.  H is not modified; U must not alias H.
+ */
+int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, float* workspace, int32_t* status,
+                               fpq_stream_t stream);
+
+/*
+ * The column loop of GPTQ.step (src/quantization/gptq.py:159-187), default column order:
+ * W [rows, cols] fp32 (rotated weights) is overwritten with the dequantised result; `scales`
+ * fp32 [rows, cols/group] are the static group scales computed beforehand from the unmodified
+ * W (gptq.py:142); U from fpq_cholesky_inverse_upper; codes (optional) receives the packed E2M1
+ * codes [rows, cols/2] (what pack_fp4_to_uint8(qweight) yields, gptq.py:429).
+ * cols % 128 == 0; group 16 or 32; err_workspace: rows * 128 floats.
+ */
+int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const float* scales, int group,
+                      const float* U, uint8_t* codes, float* err_workspace, fpq_stream_t stream);
+
+/*
+ * get_relative_mse_error (src/quantization/gptq.py:28-30):
+ * out[0] = mean(((Wq - W) H) * (Wq - W)) / (mean((W H) * W) + 1e-6).  Wq, W [rows, d], H [d, d] fp32;
+ * diff_workspace: rows * d floats; acc_workspace: 2 doubles; out: device fp32[1].
+ */
+int fpq_relative_mse(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
+                     float* diff_workspace, double* acc_workspace, float* out, fpq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
