@@ -34,7 +34,7 @@ def test_every_declaration_cites_the_reference():
         if name in ("fpq_version", "fpq_last_error", "fpq_check_device", "fpq_cholesky_workspace_floats"):
             continue
         head = text[: text.index(f" {name}(")]
-        comment = head[head.rindex("/*"):]
+        comment = re.sub(r"[\s*]+", " ", head[head.rindex("/*"):])      # undo the comment's line breaks
         assert re.search(r"\.py:\d+", comment) or "no counterpart in the reference" in comment, name
 
 
