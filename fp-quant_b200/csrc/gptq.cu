@@ -268,6 +268,42 @@ extern "C" int fpq_hessian_prepare(float* H, int64_t d, const float* W, int64_t 
   return FPQ_OK;
 }
 
+// Scratch of fpq_hessian_prepare_noalloc: one "column is dead" flag per input channel.  It lives in
+// the library image, so every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) uint8_t g_prepare_scratch[FPQ_PREPARE_NOALLOC_MAX_D];
+
+extern "C" int fpq_hessian_prepare_noalloc(float* H, int64_t d, const float* W, int64_t rows, float rel_damp,
+                                           fpq_stream_t stream) {
+  FPQ_CHECK_ARG(H && W, "NULL pointer");
+  FPQ_CHECK_ARG(d > 0 && rows > 0, "bad shape");
+  FPQ_CHECK_ARG(d <= FPQ_PREPARE_NOALLOC_MAX_D,
+                "d = %lld exceeds the built-in scratch of fpq_hessian_prepare_noalloc (%d input channels); "
+                "use fpq_hessian_prepare with a caller-provided workspace",
+                (long long)d, FPQ_PREPARE_NOALLOC_MAX_D);
+  // The array's name is only a host-side handle; kernels need its device address, which differs per
+  // GPU.  Resolve it once per device, with that device current.
+  static uint8_t* scratch_of_device[64] = {};
+  int dev = 0;
+  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
+  FPQ_CHECK_ARG(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  if (scratch_of_device[dev] == nullptr) {
+    uint8_t* ptr = nullptr;
+    FPQ_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_prepare_scratch));
+    FPQ_CHECK_ARG(ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    scratch_of_device[dev] = ptr;
+  }
+  uint8_t* scratch = scratch_of_device[dev];
+  cudaStream_t st = (cudaStream_t)stream;
+  // Every flag in [0, d) is rewritten before it is read, so nothing needs clearing between calls.
+  dead_columns_kernel<<<(unsigned)((d + 255) / 256), 256, 0, st>>>(W, rows, d, scratch);
+  FPQ_CHECK_LAUNCH();
+  mask_dead_kernel<<<grid1d(d * d), 256, 0, st>>>(H, d, scratch);
+  FPQ_CHECK_LAUNCH();
+  damp_kernel<<<1, 256, 0, st>>>(H, d, rel_damp);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
 extern "C" int64_t fpq_cholesky_workspace_floats(int64_t d) {
   const int64_t nblk = (d + NB - 1) / NB;
   const int64_t half = ((nblk + 1) / 2) * NB;

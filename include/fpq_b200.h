@@ -180,6 +180,28 @@ int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, const void*
 int fpq_hessian_prepare(float* H, int64_t d, const float* W, int64_t rows, float rel_damp,
                         uint8_t* workspace, fpq_stream_t stream);
 
+/*
+ * fpq_hessian_prepare for callers that cannot hand over a workspace.  It has no counterpart in the
+ * reference.  Some hosts may not allocate device memory at the point where they prepare a Hessian:
+ * a serving or quantisation runtime that gives all of HBM to its own pool at start-up, a plugin that
+ * runs under a framework which forbids driver allocations in its steady state, code between
+ * cudaStreamBeginCapture and EndCapture (where cudaMalloc is illegal).  This variant keeps its one
+ * scratch buffer -- a dead-column flag per input channel -- in a fixed array inside the library
+ * (FPQ_PREPARE_NOALLOC_MAX_D bytes per GPU that loads the library, held until the process exits) and
+ * calls no cudaMalloc, cudaFree or any allocating routine.
+ *   - d must not exceed FPQ_PREPARE_NOALLOC_MAX_D; larger d is rejected with FPQ_ERR_INVALID_ARGUMENT.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before any stream capture begins.
+ *   - All calls on one GPU share the array: calls whose kernels may overlap on the GPU (different
+ *     streams without ordering between them) race on it.  Serialise them, or use fpq_hessian_prepare.
+ *     The array keeps the last call's flags; every flag the next call reads is rewritten first, so no
+ *     clearing is needed.
+ * Same arithmetic and result as fpq_hessian_prepare.
+ */
+#define FPQ_PREPARE_NOALLOC_MAX_D 32768
+int fpq_hessian_prepare_noalloc(float* H, int64_t d, const float* W, int64_t rows, float rel_damp,
+                                fpq_stream_t stream);
+
 /* Number of floats fpq_cholesky_inverse_upper needs as workspace for a d x d matrix. */
 int64_t fpq_cholesky_workspace_floats(int64_t d);
 
