@@ -353,6 +353,32 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint6
   return FPQ_OK;
 }
 
+int make_tensor_map_2d_u64(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                           uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled is not available from the driver");
+    return FPQ_ERR_CUDA;
+  }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (scale tiles) failed with CUresult %d (inner=%llu outer=%llu box=%ux%u)", (int)r,
+              (unsigned long long)inner, (unsigned long long)outer, box_inner, box_outer);
+    return FPQ_ERR_CUDA;
+  }
+  return FPQ_OK;
+}
+
+int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                  const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
+                  cudaStream_t stream);
+
 }  // namespace fpq
 
 using namespace fpq;
@@ -374,6 +400,14 @@ extern "C" int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, cons
                 "pointers must be 16-byte aligned");
   FPQ_CHECK_ARG((K / 2) % 16 == 0, "K/2 must be a multiple of 16 bytes");
   if (M == 0) return FPQ_OK;
+  {
+    // Large M: CTA pairs (256 x 256 tiles).  Small M streams the weights once and stays on single CTAs.
+    const char* e = getenv("FPQ_GEMM_PAIR");
+    const bool use_pair = e ? atoi(e) != 0 : true;
+    if (use_pair && M > 128 && N >= 256)
+      return gemm_fp4_pair(a_codes, b_codes, a_scales_swizzled, b_scales_swizzled, alpha, bias_bf16, out_bf16, M, N, K,
+                           format, error_flag, (cudaStream_t)stream);
+  }
   const int g = format == FPQ_FMT_NVFP4 ? 16 : 32;
   GemmParams p{};
   p.M = (int)M; p.N = (int)N; p.K = (int)K;

@@ -1,0 +1,449 @@
+// Block-scaled FP4 GEMM on CTA pairs (tcgen05 cta_group::2) for sm_100a -- the large-M path of
+// fpq_gemm_fp4 (see gemm_fp4.cu for the interface it serves).
+//
+// A pair of CTAs (cluster of 2, two neighbouring SMs) owns a 256 x 256 output tile.  Each CTA loads
+// its own 128 rows of A and its own 128 of the 256 rows of B, so every byte of the operands is fetched
+// from L2 once per pair; one thread of the leader CTA issues MMAs that span both SMs (M = 256), each
+// SM accumulating its 128 x 256 half in its own tensor memory.  Measured on B200: a single CTA cannot
+// issue FP4 MMAs faster than one per ~180 cycles whatever their N, about half the tensor pipe; a pair
+// does twice the work per instruction.
+//
+// Warps per CTA: 0 TMA producer, 1 MMA issuer (leader CTA only) and tensor-memory owner, 2-5 epilogue,
+// 6-9 scale-factor movers.  Scale tiles go shared -> registers -> tensor memory (tcgen05.st, each of
+// the four warps filling its own 32-lane quarter) so that the MMA queue carries nothing but MMAs; a
+// tcgen05.cp per 512-byte tile in that queue cost 20-35 % of the run time.  The epilogue first drains
+// the whole accumulator into registers (packed bf16), hands it back, and only then writes to global
+// memory, so the stores overlap the next tile's MMAs.
+//
+// Barriers: the "full" barrier of a stage (operand tiles) lives in the leader; both producers announce
+// their bytes on it and both CTAs' operand loads complete on it.  Scale tiles complete on a per-CTA
+// "sf_full" barrier.  "empty" and "accumulator full" barriers exist in both CTAs and get one
+// tcgen05.commit each; "sf_ready" and "accumulator empty" live in the leader and collect the warps of
+// both CTAs.  Every wait is bounded.  Nothing is broadcast between the CTAs.
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+#include <cstdlib>
+
+namespace fpq {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM_CTA = 128;            // rows of A per CTA
+constexpr int BN = 256;                // columns of the pair tile
+constexpr int BN_CTA = 128;            // rows of B per CTA
+constexpr int BK_BYTES = 128;
+constexpr int BK_ELEMS = 256;
+constexpr int NUM_THREADS = 448;       // 14 warps: producer, MMA, 4 epilogue, 4 scale movers, 4 epilogue
+constexpr int NUM_SF_BUFS = 5;          // scale-factor buffers in tensor memory (must stay below STAGES)
+constexpr int TMEM_COLS = 512;
+constexpr int SF_TMEM_BASE = 256;
+
+
+struct PairParams {
+  int M, N, K;
+  int num_m_pairs, num_n_blocks, num_tiles;
+  int num_k_stages;
+  int sf_blocks_k;
+  const float* alpha;
+  const __nv_bfloat16* bias;
+  __nv_bfloat16* out;
+  int* error_flag;
+  int raster_group;
+  long long* profile;      // optional: per-pair cycle counters for tuning (NULL in normal use)
+};
+
+template <bool NVFP4>
+struct PairSmem {
+  static constexpr int STAGES = NVFP4 ? 5 : 6;
+  static constexpr int SFBLK = NVFP4 ? 4 : 2;                 // 512-byte scale tiles per 128 rows per stage
+  static constexpr int SFA_COLS = 4 * SFBLK;                  // tensor-memory columns of one stage's A scales
+  static constexpr int SF_TMEM_BUF = 12 * SFBLK;              // A scales + B scales (256 rows) of one stage
+  static constexpr int A_BYTES = BM_CTA * BK_BYTES;           // 16 KiB
+  static constexpr int B_BYTES = BN_CTA * BK_BYTES;           // 16 KiB
+  static constexpr int SFA_BYTES = SFBLK * 512;
+  static constexpr int SFB_BYTES = 2 * SFBLK * 512;           // scales of all 256 B rows
+  static constexpr int STAGE_TX = A_BYTES + B_BYTES;           // operand bytes per CTA (leader's barrier)
+  static constexpr int SF_TX = SFA_BYTES + SFB_BYTES;          // scale bytes per CTA (own barrier)
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
+  static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
+  // full[S], empty[S], sf_full[S], sf_ready[NUM_SF_BUFS], acc_full, acc_empty
+  static constexpr int OFF_BAR = OFF_SFB + STAGES * SFB_BYTES;
+  static constexpr int OFF_MISC = OFF_BAR + (3 * STAGES + NUM_SF_BUFS + 2) * 8;
+  static constexpr int TOTAL = OFF_MISC + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+__device__ __forceinline__ void pair_tile_coords(const PairParams& p, int tile, int& m_pair, int& n_blk) {
+  const int band_tiles = p.raster_group * p.num_n_blocks;
+  const int band = tile / band_tiles;
+  const int first_m = band * p.raster_group;
+  int rows = p.num_m_pairs - first_m;
+  if (rows > p.raster_group) rows = p.raster_group;
+  const int in_band = tile - band * band_tiles;
+  m_pair = first_m + in_band % rows;
+  n_blk = in_band / rows;
+}
+
+template <bool NVFP4>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                     const PairParams p) {
+  using L = PairSmem<NVFP4>;
+  constexpr int STAGES = L::STAGES;
+  constexpr int SFBLK = L::SFBLK;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar_full = sbase + L::OFF_BAR;
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_sf_full = bar_empty + STAGES * 8;
+  const uint32_t bar_sf_ready = bar_sf_full + STAGES * 8;
+  const uint32_t bar_acc_full = bar_sf_ready + NUM_SF_BUFS * 8;
+  const uint32_t bar_acc_empty = bar_acc_full + 8;
+  volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();        // 0 = leader
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 2);      // one announcement per producer of the pair (used in the leader)
+      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_sf_full + 8 * s, 1);
+    }
+    for (int b = 0; b < NUM_SF_BUFS; ++b) mbar_init(bar_sf_ready + 8 * b, 8);   // four mover warps per CTA (leader)
+    mbar_init(bar_acc_full, 1);
+    mbar_init(bar_acc_empty, 16);          // eight epilogue warps per CTA (used in the leader)
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    prefetch_tensormap(&tmap_sfa);
+    prefetch_tensormap(&tmap_sfb);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                       // peer barriers are initialised before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  // addresses of the leader's barriers as seen from this CTA
+  const uint32_t lead_full = map_to_cta(bar_full, 0);
+  const uint32_t lead_acc_empty = map_to_cta(bar_acc_empty, 0);
+  const uint32_t lead_sf_ready = map_to_cta(bar_sf_ready, 0);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------- TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs) {
+        int m_pair, n_blk;
+        pair_tile_coords(p, tile, m_pair, n_blk);
+        const int m_row = m_pair * 256 + (int)rank * BM_CTA;            // my rows of A
+        const int n_row = n_blk * BN + (int)rank * BN_CTA;              // my rows of B
+        for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t full = lead_full + 8 * s;
+          // scale tiles first (the movers need them earliest): 64 eight-byte words per 512-byte tile,
+          // rows of the map are 128-row blocks; they complete on this CTA's own barrier
+          mbar_arrive_expect_tx(bar_sf_full + 8 * s, L::SF_TX);
+          tma_load_2d(sbase + L::OFF_SFA + s * L::SFA_BYTES, &tmap_sfa, ks * SFBLK * 64, m_pair * 2 + (int)rank,
+                      bar_sf_full + 8 * s);
+          tma_load_2d(sbase + L::OFF_SFB + s * L::SFB_BYTES, &tmap_sfb, ks * SFBLK * 64, n_blk * 2, bar_sf_full + 8 * s);
+          mbar_arrive_expect_tx_cluster(full, L::STAGE_TX);
+          tma_load_2d_pair(sbase + L::OFF_A + s * L::A_BYTES, &tmap_a, ks * BK_BYTES, m_row, full);
+          tma_load_2d_pair(sbase + L::OFF_B + s * L::B_BYTES, &tmap_b, ks * BK_BYTES, n_row, full);
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error_flag, 1);
+      }
+      // Drain: my loads complete on the leader's barrier, which I cannot poll from the follower; the
+      // consumer frees a stage (commit on my empty barrier) only after the stage was complete, so
+      // waiting for my last min(it, STAGES) stages to be freed proves that every load has landed.
+      const uint32_t first = it > STAGES ? it - STAGES : 0;
+      volatile int never = 0;
+      for (uint32_t j = first; j < it; ++j)
+        (void)mbar_wait_bounded(bar_empty + 8 * (j % STAGES), (j / STAGES) & 1, &never, 400000000LL);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t peer_empty = map_to_cta(bar_empty, 1);
+      const uint32_t peer_acc_full = map_to_cta(bar_acc_full, 1);
+      uint32_t it = 0, tile_count = 0;
+      bool ok = true;
+      long long t_acc = 0, t_full = 0, t_sf = 0;
+      const long long t_begin = clock64();
+      for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs, ++tile_count) {
+        long long t0 = clock64();
+        if (!mbar_wait_bounded(bar_acc_empty, (tile_count & 1) ^ 1, abort_flag)) { ok = false; break; }
+        t_acc += clock64() - t0;
+        tc_fence_after();
+        for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
+          const int s = it % STAGES;
+          t0 = clock64();
+          if (!mbar_wait_bounded(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          long long t1 = clock64();
+          t_full += t1 - t0;
+          const uint32_t sfb_i = it % NUM_SF_BUFS;
+          if (!mbar_wait_bounded(bar_sf_ready + 8 * sfb_i, (it / NUM_SF_BUFS) & 1, abort_flag)) { ok = false; break; }
+          t_sf += clock64() - t1;
+          tc_fence_after();
+          const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + sfb_i * L::SF_TMEM_BUF;
+          const uint32_t sfa_t = sf_buf, sfb_t = sf_buf + L::SFA_COLS;
+          int kmma = (p.K - ks * BK_ELEMS + 63) / 64;
+          if (kmma > 4) kmma = 4;
+          const uint64_t a_desc = make_desc_k_sw128(sbase + L::OFF_A + s * L::A_BYTES);
+          const uint64_t b_desc = make_desc_k_sw128(sbase + L::OFF_B + s * L::B_BYTES);
+          for (int k = 0; k < kmma; ++k) {
+            uint32_t blk, sf_id;
+            if (NVFP4) { blk = k; sf_id = 0; }
+            else { blk = k >> 1; sf_id = (k & 1) * 2; }
+            const uint32_t idesc = make_idesc_fp4(256, BN, !NVFP4, sf_id, sf_id);
+            tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_t + 4 * blk,
+                                                sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(bar_empty + 8 * s);          // my stage ...
+          tc_commit_pair(peer_empty + 8 * s);         // ... and the follower's
+        }
+        if (ok) {
+          tc_commit_pair(bar_acc_full);
+          tc_commit_pair(peer_acc_full);
+        }
+      }
+      if (p.profile) {
+        long long* o = p.profile + (size_t)pair_id * 64;
+        o[0] = clock64() - t_begin; o[1] = t_acc; o[2] = t_full; o[3] = t_sf; o[4] = it;
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error_flag, 1);
+      }
+    }
+  } else if (warp >= 6 && warp < 10) {
+    // ------------------------------------------------------------- scale-factor movers (both CTAs)
+    // A 512-byte tile is 32 rows x 16 bytes: lane l takes row l and writes it to lane l of this warp's
+    // quarter of tensor memory, columns [c, c+4) -- the four warps together produce the replicated
+    // layout the block-scaled MMA reads.
+    const int quarter = warp & 3;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    // Stages form one flat sequence over this pair's tiles.
+    const int my_tiles = pair_id < p.num_tiles ? (p.num_tiles - pair_id + num_pairs - 1) / num_pairs : 0;
+    const uint32_t n_it = (uint32_t)my_tiles * (uint32_t)p.num_k_stages;
+    bool ok = true;
+    long long m_sf = 0, m_empty = 0, m_st = 0, m_arr = 0;
+    const long long m_begin = clock64();
+    for (uint32_t it = 0; it < n_it && ok; ++it) {
+      const int s = it % STAGES;
+      const uint32_t sfb_i = it % NUM_SF_BUFS;
+      long long t0 = clock64();
+      if (!mbar_wait_bounded(bar_sf_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+      long long t1 = clock64();
+      m_sf += t1 - t0;
+      if (it >= NUM_SF_BUFS) {
+        // The MMAs that read this tensor-memory buffer NUM_SF_BUFS stages ago must be done.  Their stage's
+        // "empty" barrier cannot have moved on by more than one phase because NUM_SF_BUFS < STAGES.
+        const uint32_t old = it - NUM_SF_BUFS;
+        if (!mbar_wait_bounded(bar_empty + 8 * (old % STAGES), (old / STAGES) & 1, abort_flag)) { ok = false; break; }
+      }
+      m_empty += clock64() - t1;
+      tc_fence_after();
+      const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + sfb_i * L::SF_TMEM_BUF + lane_base;
+      const uint8_t* sfa_s = smem + L::OFF_SFA + s * L::SFA_BYTES + lane * 16;
+      const uint8_t* sfb_s = smem + L::OFF_SFB + s * L::SFB_BYTES + lane * 16;
+#pragma unroll
+      for (int j = 0; j < SFBLK; ++j) {
+        const uint4 a = *reinterpret_cast<const uint4*>(sfa_s + j * 512);
+        tc_st_32x32b_x4(sf_buf + 4 * j, a.x, a.y, a.z, a.w);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 b = *reinterpret_cast<const uint4*>(sfb_s + (h * SFBLK + j) * 512);
+          tc_st_32x32b_x4(sf_buf + L::SFA_COLS + 8 * j + 4 * h, b.x, b.y, b.z, b.w);
+        }
+      }
+      long long t2 = clock64();
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      long long t3 = clock64();
+      m_st += t3 - t2;
+      if (lane == 0) mbar_arrive_cluster(lead_sf_ready + 8 * sfb_i);
+      m_arr += clock64() - t3;
+    }
+    if (p.profile && warp == 6 && lane == 0) {
+      long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
+      o[5] = m_sf; o[6] = m_empty; o[7] = m_st; o[8] = m_arr; o[9] = clock64() - m_begin;
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicExch(p.error_flag, 1);
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const int col_half = warp >= 10 ? 1 : 0;     // warps 2-5 drain columns 0-127, warps 10-13 columns 128-255
+    const float alpha = *p.alpha;
+    uint32_t tile_count = 0;
+    bool ok = true;
+    long long e_wait = 0, e_drain = 0, e_store = 0, e_ld0 = 0;
+    for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs, ++tile_count) {
+      int m_pair, n_blk;
+      pair_tile_coords(p, tile, m_pair, n_blk);
+      long long t0 = clock64();
+      if (!mbar_wait_bounded(bar_acc_full, tile_count & 1, abort_flag)) { ok = false; break; }
+      long long t1 = clock64();
+      e_wait += t1 - t0;
+      tc_fence_after();
+      const int row = m_pair * 256 + (int)rank * BM_CTA + quarter * 32 + lane;
+      __nv_bfloat16* orow = p.out + (size_t)row * p.N;
+      // 1) drain this warp's 128 fp32 columns into registers (four loads in flight, one wait)
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + col_half * 128;
+      tc_ld_32x32b_x32(tsrc, r0);
+      tc_ld_32x32b_x32(tsrc + 32, r1);
+      tc_ld_32x32b_x32(tsrc + 64, r2);
+      tc_ld_32x32b_x32(tsrc + 96, r3);
+      tc_wait_ld();
+      e_ld0 += clock64() - t1;
+      // 2) hand the accumulator back: the next tile's MMAs may start while we convert and store
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+      long long t2 = clock64();
+      e_drain += t2 - t1;
+      // 3) scale, round to bf16, write out (N is a multiple of 8: a 16-byte group is all in or all out)
+      if (row < p.M) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t* rc = c == 0 ? r0 : c == 1 ? r1 : c == 2 ? r2 : r3;
+          const int col0 = n_blk * BN + col_half * 128 + c * 32;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int col = col0 + q * 8;
+            if (col < p.N) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float v0 = __uint_as_float(rc[q * 8 + 2 * j]) * alpha;
+                float v1 = __uint_as_float(rc[q * 8 + 2 * j + 1]) * alpha;
+                if (p.bias) {
+                  v0 += __bfloat162float(p.bias[col + 2 * j]);
+                  v1 += __bfloat162float(p.bias[col + 2 * j + 1]);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                w[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+              *reinterpret_cast<uint4*>(orow + col) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+      e_store += clock64() - t2;
+    }
+    if (p.profile && warp == 2 && lane == 0) {
+      long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
+      o[10] = e_wait; o[11] = e_drain; o[12] = e_store; o[13] = e_ld0;
+    }
+    if (!ok && lane == 0) {
+      *abort_flag = 1;
+      atomicExch(p.error_flag, 1);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // neither CTA leaves while its peer may still signal its barriers
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool NVFP4>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
+                PairParams p, cudaStream_t stream) {
+  using L = PairSmem<NVFP4>;
+  auto kern = gemm_fp4_pair_kernel<NVFP4>;
+  static bool configured[64] = {};
+  int dev = 0;
+  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    configured[dev] = true;
+  }
+  int pairs = sm_count() / 2;
+  if (pairs > p.num_tiles) pairs = p.num_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = L::DYN_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, p));
+  return FPQ_OK;
+}
+
+}  // namespace
+
+int make_tensor_map_2d_u64(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                           uint32_t box_inner, uint32_t box_outer);
+
+// Large-M path of fpq_gemm_fp4.  Shapes and pointers were validated by the caller.
+int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                  const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
+                  cudaStream_t stream) {
+  const int g = format == FPQ_FMT_NVFP4 ? 16 : 32;
+  const int sfblk = format == FPQ_FMT_NVFP4 ? 4 : 2;
+  PairParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.num_m_pairs = (int)((M + 255) / 256);
+  p.num_n_blocks = (int)((N + BN - 1) / BN);
+  p.num_tiles = p.num_m_pairs * p.num_n_blocks;
+  p.num_k_stages = (int)((K + BK_ELEMS - 1) / BK_ELEMS);
+  p.sf_blocks_k = (int)((K / g + 3) / 4);
+  p.alpha = alpha;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.error_flag = error_flag;
+  {
+    const char* pe = getenv("FPQ_GEMM_PROFILE_PTR");   // tuning aid: address of a device buffer of 8 int64 per pair
+    p.profile = pe ? reinterpret_cast<long long*>(strtoull(pe, nullptr, 0)) : nullptr;
+  }
+  const char* e = getenv("FPQ_GEMM_RASTER");
+  p.raster_group = e ? atoi(e) : 8;
+  if (p.raster_group < 1) p.raster_group = 1;
+  CUtensorMap ta, tb, tsa, tsb;
+  if (int rc = make_tensor_map_2d(&ta, a, 1, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, BK_BYTES, BM_CTA, 1)) return rc;
+  if (int rc = make_tensor_map_2d(&tb, b, 1, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BK_BYTES, BN_CTA, 1)) return rc;
+  const uint64_t sf_row_words = (uint64_t)p.sf_blocks_k * 64;      // 8-byte words per 128-row block
+  const uint64_t a_blocks = (uint64_t)((M + 127) / 128), b_blocks = (uint64_t)((N + 127) / 128);
+  if (int rc = make_tensor_map_2d_u64(&tsa, sfa, sf_row_words, a_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 1)) return rc;
+  if (int rc = make_tensor_map_2d_u64(&tsb, sfb, sf_row_words, b_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 2)) return rc;
+  return format == FPQ_FMT_NVFP4 ? launch_pair<true>(ta, tb, tsa, tsb, p, stream)
+                                 : launch_pair<false>(ta, tb, tsa, tsb, p, stream);
+}
+
+}  // namespace fpq
