@@ -367,13 +367,136 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ MR-GPTQ of one layer
+def run_gptq(args):
+    """Second half of the metric: seconds per layer for MR-GPTQ (Hadamard 128 + NVFP4) of one linear of
+    14336 x 4096 (Llama-3.1-8B MLP up-projection shape) with 128 x 2048 calibration tokens.
+    Multi-GPU: calibration sequences are sharded over the ranks (Hessian all-reduced over NCCL) and the
+    rows of the weight are sharded for the column loop (results all-gathered)."""
+    import torch.distributed as dist
+
+    from fpq_b200 import dist as fdist, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    R, C, n_seq, T, hg = args.gptq_rows, args.gptq_cols, 128, 2048, 128
+    fmt, group = "nvfp4", 16
+    peaks = load_peaks()
+    g = torch.Generator(device=dev).manual_seed(4)
+    W = (torch.randn(R, C, device=dev, generator=g) * 0.02).bfloat16()
+    lo, hi = fdist.shard_bounds(n_seq, world, rank)
+    gx = torch.Generator(device=dev).manual_seed(100 + rank)
+    z = torch.randn((hi - lo) * T, 64, device=dev, generator=gx)
+    a = torch.randn(64, C, device=dev, generator=torch.Generator(device=dev).manual_seed(7)) / 8
+    X = (z @ a + 0.1 * torch.randn((hi - lo) * T, C, device=dev, generator=gx)).bfloat16().view(hi - lo, T, C)
+    del z
+    seq_per_call = 8
+    times = {"hessian": 0.0, "allreduce": 0.0, "cholesky": 0.0, "loop": 0.0, "other": 0.0}
+    rel_mse = None
+
+    def ev():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    def layer(record):
+        nonlocal rel_mse
+        marks = [ev()]
+        Wr = ops.rotate_hadamard(W, hg, out_dtype=torch.float32)
+        sh = fdist.ShardedLayerGPTQ(C, dev)
+        marks.append(ev())
+        for i in range(0, hi - lo, seq_per_call):
+            xr = ops.rotate_hadamard(X[i:i + seq_per_call], hg)
+            sh.update(xr, n_seq, lambda H, x2d, al, be: ops.hessian_accumulate(H, x2d, al, be))
+        marks.append(ev())
+        H = sh.finish_hessian()
+        marks.append(ev())
+        bits = ops.absmax_bits(Wr, 0)
+        gs = torch.full((1,), float("inf"), device=dev)
+        ops.global_scale_update(bits, gs)
+        _, _, scales = ops.quantize(Wr, fmt, 0, gs, codes=False, scale_bytes=False, scales_f32=True)
+        ops.hessian_prepare(H, Wr, 0.01)
+        marks.append(ev())
+        U, status = ops.cholesky_inverse_upper(H)
+        marks.append(ev())
+
+        def loop(Ws, ss, Uu, gg):
+            codes = ops.gptq_quantize(Ws, ss, Uu, gg)
+            return Ws, codes
+
+        wq, codes = sh.quantize(Wr.clone(), scales, U, group, loop)
+        marks.append(ev())
+        rel_mse = ops.relative_mse(wq, Wr, H)
+        marks.append(ev())
+        if record:
+            torch.cuda.synchronize()
+            d = [marks[i].elapsed_time(marks[i + 1]) * 1e-3 for i in range(len(marks) - 1)]
+            times["other"] += d[0] + d[3] + d[6]
+            times["hessian"] += d[1]
+            times["allreduce"] += d[2]
+            times["cholesky"] += d[4]
+            times["loop"] += d[5]
+        return status
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        layer(False)
+    barrier()
+    with ClockSampler(local) as clocks:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            status = layer(True)
+        stop.record()
+        barrier()
+    ops.check_device_errors(dev)
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        sec = ms * 1e-3 / args.steps
+        hess_flops = float((hi - lo) * T) * C * (C + 1)
+        hess_t = times["hessian"] / args.steps
+        line = {
+            "metric": "mr_gptq_s_per_layer", "value": sec, "unit": "s/layer", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 Hessian products, fp32 factorisation and column loop", "data": "synthetic",
+            "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4) of one linear {R}x{C}, {n_seq}x{T} calibration tokens, "
+                                   f"damp 0.01, block 128; sequences and weight rows sharded over {world} GPU(s)",
+                       "l2": "calibration activations 2 GB per pass > 126 MB L2"},
+            "breakdown_s": {k: v / args.steps for k, v in times.items()},
+            "relative_mse": float(rel_mse.item()), "cholesky_failed": int(status.item()),
+            "roofline": {"kernel": "hessian_kernel", "bound": "tensor", "achieved": hess_flops / hess_t / 1e12,
+                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": hess_flops / hess_t / 1e12 / peaks["bf16_tflops"],
+                         "peak_source": f"bf16 cuBLAS burst ({peaks['source']})",
+                         "note": "time includes the Hadamard rotation of the activations; flops = T*d*(d+1)", "traffic": None},
+            "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq"])
+    ap.add_argument("--gptq-rows", type=int, default=14336)
+    ap.add_argument("--gptq-cols", type=int, default=4096)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--format", default="mxfp4", choices=["mxfp4", "nvfp4"])
     ap.add_argument("--cpu-rows", type=int, default=256)
@@ -384,7 +507,10 @@ def main():
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
-        run_ours(args)
+        if args.workload == "gptq":
+            run_gptq(args)
+        else:
+            run_ours(args)
 
 
 if __name__ == "__main__":

@@ -45,7 +45,6 @@ struct GemmParams {
   __nv_bfloat16* out;
   int* error_flag;
   int raster_group;        // m-blocks per rasterisation band
-  int debug_flags;         // bit 0: skip the global stores of the epilogue (timing experiments only)
 };
 
 // Tile index -> (m block, n block): bands of `raster_group` m-blocks, n-blocks swept inside a band with
@@ -123,7 +122,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0 && !(p.debug_flags & 8)) {
+    if (lane == 0) {
       uint32_t it = 0;   // global stage counter
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
@@ -139,7 +138,6 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           for (int h = 0; h < BN / 128; ++h)
             if (n_blk * (BN / 128) + h < p.sfb_row_blocks) ++nb_rowblocks;
           const uint32_t tx = STAGE_TX_AB + (uint32_t)nblk * 512u * (1 + nb_rowblocks);
-          if (p.debug_flags & 4) { mbar_arrive(bar_full + 8 * s); continue; }   // timing experiment: no loads
           mbar_arrive_expect_tx(bar_full + 8 * s, tx);
           tma_load_2d(sbase + L::OFF_A + s * L::A_BYTES, &tmap_a, ks * BK_BYTES, m_blk * BM, bar_full + 8 * s);
           tma_load_2d(sbase + L::OFF_B + s * L::B_BYTES, &tmap_b, ks * BK_BYTES, n_blk * BN, bar_full + 8 * s);
@@ -180,16 +178,14 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!(p.debug_flags & 8)) {   // bit 3 (timing experiment): issue MMAs without waiting for data
-            if (!mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-          }
+          if (!mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
           const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + (it & 1) * SF_TMEM_BUF;
           const uint32_t sfa_t = sf_buf;            // 4 columns per 512-byte block
           const uint32_t sfb_t = sf_buf + 16;       // (BN/32) columns per block
           int nblk = p.sf_blocks_k - ks * SFBLK;
           if (nblk > SFBLK) nblk = SFBLK;
-          for (int j = 0; j < nblk && !((p.debug_flags & 2) && it > 0); ++j) {
+          for (int j = 0; j < nblk; ++j) {
             tc_cp_32x128b_warpx4(sfa_t + 4 * j, make_desc_sf_block(sbase + L::OFF_SFA + s * L::SFA_BYTES + j * 512));
             for (int h = 0; h < BN / 128; ++h)
               tc_cp_32x128b_warpx4(sfb_t + (BN / 32) * j + 4 * h,
@@ -204,12 +200,10 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             if (NVFP4) { blk = k; sf_id = 0; }           // 4 scales of 16 per MMA: one whole block
             else { blk = k >> 1; sf_id = (k & 1) * 2; }  // 2 scales of 32 per MMA: half a block
             const uint32_t idesc = make_idesc_fp4(BM, BN, !NVFP4, sf_id, sf_id);
-            // bit 4 (timing experiment): alternate between two accumulators to break the dependency chain
-            const uint32_t acc = tmem_base + ((p.debug_flags & 16) ? (uint32_t)((k & 1) * 256) : 0u);
-            tc_mma_fp4_block_scaled<NVFP4>(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_t + 4 * blk,
+            tc_mma_fp4_block_scaled<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_t + 4 * blk,
                                            sfb_t + (BN / 32) * blk, (ks > 0 || k > 0) ? 1u : 0u);
           }
-          if (!(p.debug_flags & 8)) tc_commit(bar_empty + 8 * s);   // stage reusable once these MMAs have read it
+          tc_commit(bar_empty + 8 * s);   // stage reusable once these MMAs have read it
         }
         if (ok) tc_commit(bar_acc_full);
       }
@@ -237,7 +231,6 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + c * 32, r);
         tc_wait_ld();
         const int col0 = n_blk * BN + c * 32;
-        if (p.debug_flags & 1) continue;
         if (row < p.M && col0 + 32 <= p.N) {
           uint32_t w[16];
 #pragma unroll
@@ -298,8 +291,6 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cuda
     const char* e = getenv("FPQ_GEMM_RASTER");
     p.raster_group = e ? atoi(e) : 8;
     if (p.raster_group < 1) p.raster_group = 1;
-    const char* d = getenv("FPQ_GEMM_DEBUG");
-    p.debug_flags = d ? atoi(d) : 0;
   }
   int grid = sm_count();
   if (grid > p.num_tiles) grid = p.num_tiles;
@@ -327,8 +318,40 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// Encoding a tensor map costs about a microsecond of host time; weights and their scales are the same
+// buffers call after call, so the most recent encodings are kept per thread.
+struct MapKey {
+  const void* base; uint64_t inner, outer, stride; uint32_t box_inner, box_outer; int kind;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && stride == o.stride && box_inner == o.box_inner &&
+           box_outer == o.box_outer && kind == o.kind;
+  }
+};
+struct MapCache {
+  static constexpr int N = 32;
+  MapKey keys[N];
+  CUtensorMap maps[N];
+  int used = 0, next = 0;
+  const CUtensorMap* find(const MapKey& k) const {
+    for (int i = 0; i < used; ++i)
+      if (keys[i] == k) return &maps[i];
+    return nullptr;
+  }
+  void put(const MapKey& k, const CUtensorMap& m) {
+    const int slot = used < N ? used++ : (next++ % N);
+    keys[slot] = k;
+    maps[slot] = m;
+  }
+};
+static thread_local MapCache g_map_cache;
+
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle_128b) {
+  const MapKey key{base, inner, outer, row_stride_bytes, box_inner, box_outer, elem_bytes * 2 + (swizzle_128b ? 1 : 0)};
+  if (const CUtensorMap* hit = g_map_cache.find(key)) {
+    *map = *hit;
+    return FPQ_OK;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -350,11 +373,17 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int elem_bytes, uint6
               box_outer);
     return FPQ_ERR_CUDA;
   }
+  g_map_cache.put(key, *map);
   return FPQ_OK;
 }
 
 int make_tensor_map_2d_u64(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer) {
+  const MapKey key{base, inner, outer, row_stride_bytes, box_inner, box_outer, 64};
+  if (const CUtensorMap* hit = g_map_cache.find(key)) {
+    *map = *hit;
+    return FPQ_OK;
+  }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     set_error("cuTensorMapEncodeTiled is not available from the driver");
@@ -372,12 +401,16 @@ int make_tensor_map_2d_u64(CUtensorMap* map, const void* base, uint64_t inner, u
               (unsigned long long)inner, (unsigned long long)outer, box_inner, box_outer);
     return FPQ_ERR_CUDA;
   }
+  g_map_cache.put(key, *map);
   return FPQ_OK;
 }
 
 int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
                   const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
                   cudaStream_t stream);
+int gemm_fp4_smallm(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
+                    const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
+                    cudaStream_t stream);
 
 }  // namespace fpq
 
@@ -404,6 +437,10 @@ extern "C" int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, cons
     // Large M: CTA pairs (256 x 256 tiles).  Small M streams the weights once and stays on single CTAs.
     const char* e = getenv("FPQ_GEMM_PAIR");
     const bool use_pair = e ? atoi(e) != 0 : true;
+    const char* sm = getenv("FPQ_GEMM_SMALLM");
+    if ((sm ? atoi(sm) != 0 : true) && M <= 64)
+      return gemm_fp4_smallm(a_codes, b_codes, a_scales_swizzled, b_scales_swizzled, alpha, bias_bf16, out_bf16, M, N,
+                             K, format, error_flag, (cudaStream_t)stream);
     if (use_pair && M > 128 && N >= 256)
       return gemm_fp4_pair(a_codes, b_codes, a_scales_swizzled, b_scales_swizzled, alpha, bias_bf16, out_bf16, M, N, K,
                            format, error_flag, (cudaStream_t)stream);

@@ -244,6 +244,28 @@ __global__ void diff_kernel(const float* __restrict__ a, const float* __restrict
     out[i] = a[i] - b[i];
 }
 
+// x (or x - y) in fp32 -> two bf16 terms hi + lo (relative residual ~2^-17)
+__global__ void split_bf16_kernel(const float* __restrict__ x, const float* __restrict__ y, __nv_bfloat16* __restrict__ hi,
+                                  __nv_bfloat16* __restrict__ lo, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = y ? x[i] - y[i] : x[i];
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+  }
+}
+
+// acc[0] += weight * sum(a .* b)
+__global__ void frobenius_dot_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t n, double weight,
+                                     double* acc) {
+  double s = 0.0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    s += (double)a[i] * (double)b[i];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd(acc, weight * s);
+}
+
 __global__ void ratio_kernel(const double* acc, float* out, double count) {
   // mean(num) / (mean(den) + 1e-6), src/quantization/gptq.py:28-30
   out[0] = (float)((acc[0] / count) / (acc[1] / count + 1e-6));
@@ -407,6 +429,36 @@ extern "C" int fpq_relative_mse(const float* Wq, const float* W, const float* H,
   if (int rc = sgemm(a, false, SGEMM_DOT, st)) return rc;
   a.A = W; a.D = W; a.dot_out = acc_workspace + 1;
   if (int rc = sgemm(a, false, SGEMM_DOT, st)) return rc;
+  ratio_kernel<<<1, 1, 0, st>>>(acc_workspace, out, (double)rows * (double)d);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+extern "C" int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, const void* xb_bf16, int64_t tokens,
+                                      float alpha, float beta, int32_t* error_flag, fpq_stream_t stream);
+
+// Tensor-core form of the same metric:  sum((A H) .* A) = <H, A^T A>, and A^T A is a Hessian-type product.
+// A (fp32) is split into two bf16 terms hi + lo; <H, A^T A> ~= <H, hi^T hi> + 2 <H, hi^T lo> (H is symmetric),
+// accurate to ~1e-5 relative -- ample for a logged error metric, and ~10x faster than the fp32 products.
+extern "C" int fpq_relative_mse_tc(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
+                                   void* bf16_workspace, float* gram_workspace, double* acc_workspace, float* out,
+                                   int32_t* error_flag, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(Wq && W && H && bf16_workspace && gram_workspace && acc_workspace && out && error_flag, "NULL pointer");
+  FPQ_CHECK_ARG(rows > 0 && d > 0 && d % 8 == 0, "d must be a positive multiple of 8");
+  cudaStream_t st = (cudaStream_t)stream;
+  __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(bf16_workspace);
+  __nv_bfloat16* lo = hi + rows * d;
+  FPQ_CHECK_CUDA(cudaMemsetAsync(acc_workspace, 0, 2 * sizeof(double), st));
+  for (int which = 0; which < 2; ++which) {
+    split_bf16_kernel<<<grid1d(rows * d), 256, 0, st>>>(which == 0 ? Wq : W, which == 0 ? W : nullptr, hi, lo, rows * d);
+    FPQ_CHECK_LAUNCH();
+    if (int rc = fpq_hessian_accumulate(gram_workspace, d, hi, nullptr, rows, 1.0f, 0.0f, error_flag, stream)) return rc;
+    frobenius_dot_kernel<<<grid1d(d * d), 256, 0, st>>>(H, gram_workspace, d * d, 1.0, acc_workspace + which);
+    FPQ_CHECK_LAUNCH();
+    if (int rc = fpq_hessian_accumulate(gram_workspace, d, hi, lo, rows, 1.0f, 0.0f, error_flag, stream)) return rc;
+    frobenius_dot_kernel<<<grid1d(d * d), 256, 0, st>>>(H, gram_workspace, d * d, 2.0, acc_workspace + which);
+    FPQ_CHECK_LAUNCH();
+  }
   ratio_kernel<<<1, 1, 0, st>>>(acc_workspace, out, (double)rows * (double)d);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;

@@ -31,6 +31,24 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+class _NoGuard:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _guard(device: torch.device):
+    """Make `device` current for the launch; free when it already is (the common case)."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
@@ -56,7 +74,7 @@ def rotate_hadamard(x: torch.Tensor, group: int, out_dtype: Optional[torch.dtype
         rows, cols = x.numel() // max(32, group), max(32, group)
     if out is None:
         out = torch.empty_like(x, dtype=out_dtype or x.dtype)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         C.call("fpq_rotate_hadamard", x.data_ptr(), _dt(x), out.data_ptr(), _dt(out), rows, cols, group, _stream(x))
     return out
 
@@ -65,7 +83,7 @@ def rotate_dense(x: torch.Tensor, matrix: torch.Tensor, out_dtype: Optional[torc
     x, rows, cols = _2d(x)
     m = _cuda(matrix, "matrix").to(torch.float32).contiguous()
     out = torch.empty_like(x, dtype=out_dtype or x.dtype)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         C.call("fpq_rotate_dense", x.data_ptr(), _dt(x), out.data_ptr(), _dt(out), rows, cols, m.shape[0],
                m.data_ptr(), _stream(x))
     return out
@@ -76,7 +94,7 @@ def absmax_bits(x: torch.Tensor, hadamard_group: int = 0, out: Optional[torch.Te
     x, rows, cols = _2d(x)
     if out is None:
         out = torch.zeros(1, dtype=torch.int32, device=x.device)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         C.call("fpq_absmax", x.data_ptr(), _dt(x), rows, cols, hadamard_group, out.data_ptr(), _stream(x))
     return out
 
@@ -84,7 +102,7 @@ def absmax_bits(x: torch.Tensor, hadamard_group: int = 0, out: Optional[torch.Te
 def global_scale_update(bits: torch.Tensor, global_scale: torch.Tensor,
                         status: Optional[torch.Tensor] = None) -> torch.Tensor:
     assert global_scale.dtype == torch.float32 and global_scale.is_cuda
-    with torch.cuda.device(bits.device):
+    with _guard(bits.device):
         C.call("fpq_global_scale_update", bits.data_ptr(), global_scale.data_ptr(), _ptr(status), _stream(bits))
     return global_scale
 
@@ -110,7 +128,7 @@ def quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0, global_scale: O
         if global_scale is None:
             raise ValueError("nvfp4 needs a global_scale tensor")
         global_scale = _cuda(global_scale, "global_scale").to(torch.float32)
-    with torch.cuda.device(dev):
+    with _guard(dev):
         C.call("fpq_quantize", x.data_ptr(), _dt(x), rows, cols, hadamard_group, FORMATS[fmt],
                _ptr(global_scale) if fmt == "nvfp4" else None, _ptr(q), _ptr(sb),
                C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _ptr(sf), _stream(x))
@@ -126,7 +144,7 @@ def fake_quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0,
         if global_scale is None:
             raise ValueError("nvfp4 needs a global_scale tensor")
         global_scale = _cuda(global_scale, "global_scale").to(torch.float32)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         C.call("fpq_fake_quantize", x.data_ptr(), _dt(x), rows, cols, hadamard_group, FORMATS[fmt],
                _ptr(global_scale) if fmt == "nvfp4" else None, y.data_ptr(), int(ste), _stream(x))
     return y.view(shape)
@@ -140,7 +158,7 @@ def apply_scales(x: torch.Tensor, scales: torch.Tensor, group: int, out_kind: in
         out = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
     else:
         out = torch.empty_like(x)
-    with torch.cuda.device(x.device):
+    with _guard(x.device):
         C.call("fpq_apply_scales", x.data_ptr(), _dt(x), rows, cols, s.data_ptr(), group, out_kind,
                out.data_ptr(), _stream(x))
     return out
@@ -149,7 +167,7 @@ def apply_scales(x: torch.Tensor, scales: torch.Tensor, group: int, out_kind: in
 def pack_grid(q: torch.Tensor) -> torch.Tensor:
     q, rows, cols = _2d(q)
     out = torch.empty(rows, cols // 2, dtype=torch.uint8, device=q.device)
-    with torch.cuda.device(q.device):
+    with _guard(q.device):
         C.call("fpq_pack_grid", q.data_ptr(), _dt(q), rows, cols, out.data_ptr(), _stream(q))
     return out
 
@@ -162,7 +180,7 @@ def swizzle_scales(sb: torch.Tensor) -> torch.Tensor:
     rows, sf_cols = sb.shape
     pr, pc = padded_scale_shape(rows, sf_cols)
     out = torch.empty(pr, pc, dtype=torch.uint8, device=sb.device)
-    with torch.cuda.device(sb.device):
+    with _guard(sb.device):
         C.call("fpq_swizzle_scales", sb.data_ptr(), rows, sf_cols, out.data_ptr(), _stream(sb))
     return out
 
@@ -208,7 +226,7 @@ def gemm_fp4(a_codes: torch.Tensor, b_codes: torch.Tensor, a_scales_swizzled: to
         bias = _cuda(bias, "bias").to(torch.bfloat16).contiguous()
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
-    with torch.cuda.device(a.device):
+    with _guard(a.device):
         C.call("fpq_gemm_fp4", a.data_ptr(), b.data_ptr(), sa.data_ptr(), sb.data_ptr(), alpha.data_ptr(),
                _ptr(bias), out.data_ptr(), M, N, K, FORMATS[fmt], device_error_flag(a.device).data_ptr(), _stream(a))
     return out
@@ -235,7 +253,7 @@ def sgemm(A: torch.Tensor, B: torch.Tensor, b_transposed: bool = False, C: Optio
     if C is None:
         C = torch.zeros(M, N, dtype=torch.float32, device=A.device)
         beta = 0.0
-    with torch.cuda.device(A.device):
+    with _guard(A.device):
         _cabi_call("fpq_sgemm", A.data_ptr(), A.stride(0), B.data_ptr(), B.stride(0), int(b_transposed), C.data_ptr(),
                    C.stride(0), M, N, K, alpha, beta, _stream(A))
     return C
@@ -246,7 +264,7 @@ def hessian_prepare(H: torch.Tensor, W: torch.Tensor, rel_damp: float) -> torch.
     H, W = _f32(H, "H", inplace=True), _f32(W, "W")
     d = H.shape[0]
     ws = torch.empty(d, dtype=torch.uint8, device=H.device)
-    with torch.cuda.device(H.device):
+    with _guard(H.device):
         C.call("fpq_hessian_prepare", H.data_ptr(), d, W.data_ptr(), W.shape[0], float(rel_damp), ws.data_ptr(),
                _stream(H))
     return H
@@ -260,7 +278,7 @@ def cholesky_inverse_upper(H: torch.Tensor):
     n = int(C.lib().fpq_cholesky_workspace_floats(d))
     ws = torch.empty(n, dtype=torch.float32, device=H.device)
     status = torch.zeros(1, dtype=torch.int32, device=H.device)
-    with torch.cuda.device(H.device):
+    with _guard(H.device):
         C.call("fpq_cholesky_inverse_upper", H.data_ptr(), U.data_ptr(), d, ws.data_ptr(), status.data_ptr(),
                _stream(H))
     return U, status
@@ -272,20 +290,30 @@ def gptq_quantize(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group:
     rows, cols = W.shape
     codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=W.device) if want_codes else None
     err = torch.empty(rows, 128, dtype=torch.float32, device=W.device)
-    with torch.cuda.device(W.device):
+    with _guard(W.device):
         C.call("fpq_gptq_quantize", W.data_ptr(), rows, cols, scales.data_ptr(), group, U.data_ptr(), _ptr(codes),
                err.data_ptr(), _stream(W))
     return codes
 
 
-def relative_mse(Wq: torch.Tensor, W: torch.Tensor, H: torch.Tensor) -> torch.Tensor:
-    """Device fp32[1]: mean(((Wq-W) H) * (Wq-W)) / (mean((W H) * W) + 1e-6)."""
+def relative_mse(Wq: torch.Tensor, W: torch.Tensor, H: torch.Tensor, exact_fp32: bool = False) -> torch.Tensor:
+    """Device fp32[1]: mean(((Wq-W) H) * (Wq-W)) / (mean((W H) * W) + 1e-6).
+    Default: tensor-core form <H, A^T A> (~1e-5 relative); exact_fp32=True runs the two fp32 products."""
     Wq, W, H = _f32(Wq, "Wq"), _f32(W, "W"), _f32(H, "H")
     rows, d = W.shape
+    if not exact_fp32 and d % 8 == 0:
+        bf = torch.empty(2 * rows * d, dtype=torch.bfloat16, device=W.device)
+        gram = torch.empty(d, d, dtype=torch.float32, device=W.device)
+        acc = torch.zeros(2, dtype=torch.float64, device=W.device)
+        out = torch.empty(1, dtype=torch.float32, device=W.device)
+        with _guard(W.device):
+            C.call("fpq_relative_mse_tc", Wq.data_ptr(), W.data_ptr(), H.data_ptr(), rows, d, bf.data_ptr(),
+                   gram.data_ptr(), acc.data_ptr(), out.data_ptr(), device_error_flag(W.device).data_ptr(), _stream(W))
+        return out
     diff = torch.empty_like(W)
     acc = torch.zeros(2, dtype=torch.float64, device=W.device)
     out = torch.empty(1, dtype=torch.float32, device=W.device)
-    with torch.cuda.device(W.device):
+    with _guard(W.device):
         C.call("fpq_relative_mse", Wq.data_ptr(), W.data_ptr(), H.data_ptr(), rows, d, diff.data_ptr(),
                acc.data_ptr(), out.data_ptr(), _stream(W))
     return out
@@ -301,7 +329,7 @@ def hessian_accumulate(H: torch.Tensor, x: torch.Tensor, alpha: float = 1.0, bet
     flag = device_error_flag(H.device).data_ptr()
 
     def call(a, b, al, be):
-        with torch.cuda.device(H.device):
+        with _guard(H.device):
             C.call("fpq_hessian_accumulate", H.data_ptr(), d, a.data_ptr(), None if b is None else b.data_ptr(),
                    a.shape[0], float(al), float(be), flag, _stream(H))
 

@@ -1,0 +1,265 @@
+"""Model-level MR-GPTQ / RTN drivers with the call signature and return value of
+`gptq_quantization` (src/quantization/gptq.py:225-470) and `rtn_quantization`
+(src/quantization/rtn.py:17-237) of IST-DASLab/FP-Quant.
+
+Differences in structure (same mathematics):
+  * instead of swapping the attention / MLP modules for model-specific classes, every nn.Linear of a
+    transformer block is wrapped by `RotatedLinear`, which rotates its input, optionally fake-quantises
+    it and multiplies by the (rotated) weight -- (x H)(W H)^T = x W^T, so the block computes the same
+    function for any architecture whose blocks are built from nn.Linear;
+  * linears that read the same tensor (q/k/v, gate/up) share one Hessian accumulation instead of
+    accumulating identical matrices once per layer;
+  * all numeric steps are the CUDA kernels of this package.
+"""
+from __future__ import annotations
+
+import re
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..transforms.transforms import build_transform, get_transform_matrix
+from .gptq import GPTQ, get_relative_mse_error
+from .quant_args import ScalePrecision
+from .quant_ops import cast_scales_to_eXmY
+from .quantizer import Quantizer
+
+
+class ForwardInterrupt(Exception):
+    pass
+
+
+class InputCollector(nn.Module):
+    """Records the positional and keyword inputs of the wrapped block and stops the forward pass
+    (src/utils/model_utils.py:19-38)."""
+
+    def __init__(self, module: nn.Module, cpu_offload: bool = False):
+        super().__init__()
+        self.module, self.cpu_offload = module, cpu_offload
+        self.input_args, self.input_kwargs = [], []
+
+    def forward(self, *args, **kwargs):
+        if self.cpu_offload:
+            args, kwargs = _to(args, "cpu"), _to(kwargs, "cpu")
+        self.input_args.append(args)
+        self.input_kwargs.append(kwargs)
+        raise ForwardInterrupt
+
+
+def _to(obj, device):
+    if isinstance(obj, torch.Tensor):
+        return obj.to(device)
+    if isinstance(obj, (list, tuple)):
+        return type(obj)(_to(o, device) for o in obj)
+    if isinstance(obj, dict):
+        return {k: _to(v, device) for k, v in obj.items()}
+    return obj
+
+
+def _first(x):
+    return x[0] if isinstance(x, (list, tuple)) else x
+
+
+class RotatedLinear(nn.Module):
+    """y = fake_quant(rotate(x)) @ rotate(W)^T + b.  While `_train_mode` the weight is rotated on the
+    fly (it is still the original); afterwards it holds the rotated, quantised weight."""
+
+    def __init__(self, linear: nn.Linear, transform, act_quantizer: Optional[Quantizer]):
+        super().__init__()
+        self.weight, self.bias = linear.weight, linear.bias
+        self.in_features, self.out_features = linear.in_features, linear.out_features
+        self.transform, self.act_quantizer = transform, act_quantizer
+        self._train_mode = True
+        self.input_sink = None          # called with the rotated, unquantised input (Hessian accumulation)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        xr = self.transform(x)
+        if self.input_sink is not None:
+            self.input_sink(xr)
+        w = self.transform(self.weight, inv_t=True) if self._train_mode else self.weight
+        if self.act_quantizer is not None:
+            xr = self.act_quantizer.fused_fake_quantize(xr, hadamard_group=0, ste=False)
+        return F.linear(xr, w, self.bias)
+
+
+# linears that are fed the same tensor share a Hessian
+_INPUT_GROUPS = (("qkv", r"(q|k|v)_proj$"), ("o", r"o_proj$"), ("gate_up", r"(gate|up)_proj$"), ("down", r"down_proj$"))
+
+
+def _input_group(name: str) -> str:
+    for key, pat in _INPUT_GROUPS:
+        if re.search(pat, name):
+            return key
+    return name
+
+
+def _quantizer_kwargs(args, prefix: str) -> Optional[dict]:
+    bits = getattr(args, f"{prefix}_bits")
+    if bits >= 16:
+        return None
+    return dict(bits=bits, symmetric=True, format=args.format, granularity=getattr(args, f"{prefix}_granularity"),
+                observer=getattr(args, f"{prefix}_observer"), group_size=getattr(args, f"{prefix}_group_size"),
+                scale_precision=args.scale_precision)
+
+
+def _wrap_block(block: nn.Module, args, device) -> Dict[str, RotatedLinear]:
+    akw = _quantizer_kwargs(args, "a")
+    wrapped = {}
+    for name, module in list(block.named_modules()):
+        if isinstance(module, nn.Linear):
+            parent = block
+            *path, leaf = name.split(".")
+            for p in path:
+                parent = getattr(parent, p)
+            t = build_transform(args.transform_class, size=module.in_features, device=device,
+                                group_size=args.hadamard_group_size)
+            r = RotatedLinear(module, t, Quantizer(**akw) if akw else None)
+            setattr(parent, leaf, r)
+            wrapped[name] = r
+    return wrapped
+
+
+def _export_entry(args, orig_dtype, device, weight_gs, act_gs, **tensors) -> dict:
+    m = get_transform_matrix(args.transform_class, args.hadamard_group_size, device, orig_dtype).cpu()
+    entry = {k: v.cpu() for k, v in tensors.items()}
+    entry.update({"forward_hadamard_matrix": m, "backward_hadamard_matrix": m.clone(),
+                  "weight_global_scale": weight_gs.clone(), "act_global_scale": act_gs.clone()})
+    return entry
+
+
+def _collect_block_inputs(model, calibration_data, args, device):
+    blocks = model.model.layers
+    blocks[0] = InputCollector(blocks[0], cpu_offload=args.cpu_offload_activations)
+    for sample in calibration_data:
+        try:
+            with torch.no_grad():
+                model(sample.to(device=device))
+        except ForwardInterrupt:
+            pass
+    collector = blocks[0]
+    blocks[0] = collector.module
+    return collector.input_args, collector.input_kwargs
+
+
+def _run_block(block, input_args, input_kwargs, device, args, keep_outputs: bool, offload_device):
+    for a, kw in zip(input_args, input_kwargs):
+        with torch.no_grad(), torch.amp.autocast(device_type="cuda", enabled=getattr(args, "amp", False)):
+            out = block(*_to(a, device), **_to(kw, device))
+        if keep_outputs:
+            out = _first(out).to(offload_device)
+            if len(a) > 0:
+                a[0].data = out
+            elif "hidden_states" in kw:
+                kw["hidden_states"] = out
+            else:
+                raise ValueError("Unsupported block input format.")
+
+
+@torch.no_grad()
+def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device) -> Tuple[dict, dict]:
+    """MR-GPTQ over the transformer blocks of `model` (gptq.py:225-470).  Returns
+    (quantized_state_dict, non_quantized_state_dict) with the reference's per-layer keys."""
+    print("GPTQ quantization...")
+    orig_dtype = model.config.torch_dtype if args.dtype == "auto" else args.dtype
+    offload = "cpu" if args.cpu_offload_activations else device
+    quantized, non_quantized = {}, {}
+    wkw = _quantizer_kwargs(args, "w")
+    input_args, input_kwargs = _collect_block_inputs(model, calibration_data, args, device)
+
+    for block_idx, block in enumerate(model.model.layers):
+        print(f"Processing block {block_idx}...")
+        block.to(device=device, dtype=orig_dtype).requires_grad_(False)
+        layers = _wrap_block(block, args, device)
+
+        # one GPTQ handle per linear; one Hessian per distinct input
+        handles: Dict[str, GPTQ] = {}
+        leaders: Dict[str, str] = {}
+        for name, layer in layers.items():
+            handles[name] = GPTQ(layer, Quantizer(**wkw) if wkw else None, quantization_order=args.quantization_order,
+                                 rel_damp=args.rel_damp, export_quantized_model=args.export_quantized_model)
+            if args.scale_precision == ScalePrecision.E4M3:        # fix the weight global scale now (gptq.py:343-358)
+                handles[name].quantizer.get_quantization_params(layer.transform(layer.weight, inv_t=True).float())
+                handles[name].quantizer._track_global_scale = False
+            grp = _input_group(name.split(".")[-1])
+            if grp not in leaders:
+                leaders[grp] = name
+                layer.input_sink = (lambda h: (lambda x: h.update(x)))(handles[name])
+        if getattr(args, "fuse_global_scale", False) and args.scale_precision == ScalePrecision.E4M3:
+            for pat in (r"(q|k|v)_proj$", r"(gate|up)_proj$"):       # gptq.py:367-383
+                names = [n for n in handles if re.search(pat, n)]
+                if names:
+                    fused = torch.stack([handles[n].quantizer.global_scale.to(device) for n in names]).min(dim=0).values
+                    for n in names:
+                        handles[n].quantizer.global_scale = fused.clone()
+
+        _run_block(block, input_args, input_kwargs, device, args, keep_outputs=False, offload_device=offload)   # Hessians
+
+        for name, layer in layers.items():
+            layer.input_sink = None
+            layer.weight.data = layer.transform(layer.weight, inv_t=True)      # rotate once (gptq.py:395-401)
+            layer._train_mode = False
+            if layer.act_quantizer is not None:
+                layer.act_quantizer._track_global_scale = False
+
+        for name, handle in handles.items():
+            leader = handles[leaders[_input_group(name.split(".")[-1])]]
+            if handle is not leader:
+                handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
+            else:
+                handle.H_undamped = handle.H.clone()
+            wq, qweight, scales = handle.quantize()
+            orig = handle.layer.weight
+            rel = get_relative_mse_error(wq.float(), orig.float(), handle.H)
+            print(f"[{name:16}]: Relative MSE error: {rel.item():.2e}")
+            handle.layer.weight.data = wq
+            if args.export_quantized_model:
+                wgs = handle.quantizer.global_scale.to(scales.device)
+                ags = handle.layer.act_quantizer.global_scale if handle.layer.act_quantizer is not None else torch.ones(1)
+                key = f"model.layers.{block_idx}.{name}"
+                if args.export_quantized_model == "realquant":
+                    quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, qweight=handle.packed_codes,
+                                                   scales=cast_scales_to_eXmY(scales * wgs, args.scale_precision))
+                else:
+                    quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, dqweight=wq)
+
+        _run_block(block, input_args, input_kwargs, device, args, keep_outputs=True, offload_device=offload)
+        if getattr(args, "cpu_offload_modules", False):
+            block.cpu()
+        del handles
+    return quantized, non_quantized
+
+
+@torch.no_grad()
+def rtn_quantization(model, calibration_data: List[torch.Tensor], args, device) -> Tuple[dict, dict]:
+    """Round-to-nearest over all blocks (rtn.py:17-237): rotate each weight, quantise it with the
+    fused kernel, keep the dequantised weight in the model and the packed form in the export dict."""
+    print("RTN quantization...")
+    orig_dtype = model.config.torch_dtype if args.dtype == "auto" else args.dtype
+    quantized, non_quantized = {}, {}
+    wkw = _quantizer_kwargs(args, "w")
+    fmt = {"nvfp": "nvfp4", "mxfp": "mxfp4"}[str(args.format)]
+    for block_idx, block in enumerate(model.model.layers):
+        block.to(device=device, dtype=orig_dtype).requires_grad_(False)
+        layers = _wrap_block(block, args, device)
+        for name, layer in layers.items():
+            q = Quantizer(**wkw)
+            w = layer.transform(layer.weight, inv_t=True)
+            gs = None
+            if fmt == "nvfp4":
+                q.get_quantization_params(w.float())               # sets the tensor scale
+                gs = q.global_scale
+            codes, sbytes, _ = ops.quantize(w, fmt, 0, gs)
+            wq = ops.fake_quantize(w, fmt, 0, gs)
+            layer.weight.data = wq
+            layer._train_mode = False
+            if args.export_quantized_model:
+                ags = layer.act_quantizer.global_scale if layer.act_quantizer is not None else torch.ones(1)
+                key = f"model.layers.{block_idx}.{name}"
+                if args.export_quantized_model == "realquant":
+                    quantized[key] = _export_entry(args, orig_dtype, device, q.global_scale, ags, qweight=codes, scales=sbytes)
+                else:
+                    quantized[key] = _export_entry(args, orig_dtype, device, q.global_scale, ags, dqweight=wq)
+    return quantized, non_quantized

@@ -234,6 +234,15 @@ int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const float* scales,
 int fpq_relative_mse(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
                      float* diff_workspace, double* acc_workspace, float* out, fpq_stream_t stream);
 
+/*
+ * The same metric (src/quantization/gptq.py:28-30) on the tensor cores: sum((A H) .* A) = <H, A^T A>, with
+ * A^T A computed like a Hessian from a two-term bf16 split of A (~1e-5 relative accuracy).
+ * bf16_workspace: 2 * rows * d bf16; gram_workspace: d * d floats; acc_workspace: 2 doubles; d % 8 == 0.
+ */
+int fpq_relative_mse_tc(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
+                        void* bf16_workspace, float* gram_workspace, double* acc_workspace, float* out,
+                        int32_t* error_flag, fpq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,83 @@
+"""World-size-2 gloo test of the multi-GPU partitioning logic (token-sharded Hessian + all-reduce,
+row-sharded column loop + all-gather).  Runs on CPU tensors; the numeric callbacks are the oracle's,
+so this checks the host logic only: the sharded run must reproduce the unsharded one."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world_size, port, tmpdir):
+    for p in (ROOT, os.path.join(ROOT, "fp-quant_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world_size)
+    try:
+        from fpq_b200 import dist as fdist
+        from oracle import fp4, gptq as ogptq
+        from tests import inputs
+
+        torch.set_num_threads(2)
+        R, C, n_seq, T = 320, 256, 6, 128            # 320 rows -> slabs of 256 and 64 (multiples of 128)
+        w = fp4.fwht_butterfly(inputs.normal_weight(R, C, seed=0, dtype=torch.float32), 128)
+        xs = [fp4.fwht_butterfly(inputs.correlated_activations(T, C, seed=60 + i), 128) for i in range(n_seq)]
+
+        def accumulate(H, x2d, alpha, beta):
+            H.mul_(beta).add_(alpha * (x2d.float().t() @ x2d.float()))
+
+        def column_loop(W, s, U, g):
+            wq, codes = ogptq.gptq_column_loop(W, s, U, g, 128)
+            return wq, fp4.pack_codes(codes)
+
+        sh = fdist.ShardedLayerGPTQ(C, torch.device("cpu"))
+        lo, hi = fdist.shard_bounds(n_seq, world_size, rank)
+        for i in range(lo, hi):
+            sh.update(xs[i].view(1, T, C), n_seq, accumulate)
+        H = sh.finish_hessian()
+        exact = ogptq.hessian_exact([x.view(1, T, C) for x in xs], n_seq)
+        assert ((H.double() - exact).norm() / exact.norm()).item() < 1e-6
+
+        gs = fp4.nvfp4_global_scale(w.abs().max())
+        _, _, s = fp4.quantize(w, "nvfp4", gs)
+        Hd = ogptq.prepare_hessian(H, w, 0.01)
+        U, ok = ogptq.cholesky_inverse_upper(Hd)
+        wq, codes = sh.quantize(w, s, U, 16, column_loop)
+        wq_full, codes_full = ogptq.gptq_column_loop(w, s, U, 16, 128)
+        assert torch.equal(wq, wq_full) and torch.equal(codes, fp4.pack_codes(codes_full))
+
+        # helpers
+        assert fdist.all_bounds(10, 3) == [(0, 4), (4, 7), (7, 10)]
+        assert fdist.all_bounds(320, 2, 128) == [(0, 256), (256, 320)]
+        assert fdist.all_bounds(128, 4, 128) == [(0, 128), (128, 128), (128, 128), (128, 128)]
+        t = torch.tensor([float(rank + 1)])
+        assert fdist.allreduce_min_(t.clone()).item() == 1.0
+        assert fdist.allreduce_sum_(t.clone()).item() == sum(range(1, world_size + 1))
+        open(os.path.join(tmpdir, f"ok{rank}"), "w").write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_gptq_matches_unsharded_on_two_gloo_ranks(tmp_path):
+    port = 29500 + (os.getpid() % 2000)
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def test_shard_bounds_cover_everything():
+    sys.path.insert(0, os.path.join(ROOT, "fp-quant_b200"))
+    from fpq_b200 import dist as fdist
+
+    for n in (0, 1, 7, 128, 1000, 14336):
+        for ws in (1, 2, 3, 8):
+            for mult in (1, 128):
+                b = fdist.all_bounds(n, ws, mult)
+                assert b[0][0] == 0 and b[-1][1] == n
+                assert all(b[i][1] == b[i + 1][0] for i in range(ws - 1))
+                assert all((lo % mult == 0) for lo, hi in b if lo < n)

@@ -125,8 +125,9 @@ def test_gptq_column_loop_matches_golden(cuda_device, fmt):
     assert torch.equal(W.cpu(), fp4.dequantize(got, g["scales"], GROUP[fmt]))
     rel = ogptq.relative_mse(W.cpu(), g["weight"], g["damped_hessian"])
     assert abs(rel - g["relative_mse"].item()) <= 0.01 * g["relative_mse"].item()
-    got_rel = ops.relative_mse(W, g["weight"].to(cuda_device), g["damped_hessian"].to(cuda_device)).item()
-    assert got_rel == pytest.approx(rel, rel=1e-3)
+    for exact in (False, True):        # tensor-core form and fp32 form of the metric
+        got_rel = ops.relative_mse(W, g["weight"].to(cuda_device), g["damped_hessian"].to(cuda_device), exact_fp32=exact).item()
+        assert got_rel == pytest.approx(rel, rel=1e-3)
 
 
 @pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
