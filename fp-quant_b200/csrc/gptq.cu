@@ -69,49 +69,91 @@ __global__ void reflect_inplace_kernel(float* A, int64_t d) {
 // One CTA factors the nb x nb (<= 128) diagonal block A (lower Cholesky, in place) and writes
 // L^-1 (lower) to Linv.  A non-positive or non-finite pivot sets *status and is replaced by 1 so
 // that the kernel always terminates with finite data.
+//
+// Both matrices live in registers: the 256 threads form a 16 x 16 grid, thread (ty, tx) owns the
+// entries (ty + 16 r, tx + 16 c), r, c = 0..7, of A and of X (X starts as the identity).  Step k
+// is one right-looking elimination step applied to both: column k of A and row k of X go through
+// shared memory (double buffered, so one barrier per step), then
+//     L[:, k] = A[:, k] / sqrt(A[k, k]),    X[k, :] /= L[k, k],
+//     A[i, j] -= L[i, k] L[j, k]  (i, j > k),    X[i, :] -= L[i, k] X[k, :]  (i > k).
+// The loop over the register index k / 16 is unrolled so that every register index is static;
+// register blocks that are already final (or still zero) are skipped at compile time.
 __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, float* Linv, int64_t ldi, int nb,
                                                         int32_t* status) {
-  extern __shared__ float sm[];
-  float* L = sm;                 // NB x (NB + 1)
-  float* X = sm + NB * (NB + 1); // NB x (NB + 1)
+  __shared__ float colbuf[2][NB];
+  __shared__ float rowbuf[2][NB];
   const int tid = threadIdx.x;
-  for (int idx = tid; idx < nb * nb; idx += blockDim.x) {
-    const int i = idx / nb, j = idx - i * nb;
-    L[i * (NB + 1) + j] = A[(int64_t)i * lda + j];
-  }
-  __syncthreads();
-  for (int k = 0; k < nb; ++k) {
-    float piv = L[k * (NB + 1) + k];
-    __syncthreads();
-    if (!(piv > 0.0f) || !isfinite(piv)) {
-      if (tid == 0) atomicExch(status, 1);
-      piv = 1.0f;
-    }
-    const float r = sqrtf(piv);
-    // scale column k
-    for (int i = k + tid; i < nb; i += blockDim.x) L[i * (NB + 1) + k] = (i == k) ? r : L[i * (NB + 1) + k] / r;
-    __syncthreads();
-    // rank-1 update of the trailing lower triangle
-    const int m = nb - (k + 1);
-    for (int idx = tid; idx < m * m; idx += blockDim.x) {
-      const int i = k + 1 + idx / m, j = k + 1 + idx % m;
-      if (j <= i) L[i * (NB + 1) + j] = fmaf(-L[i * (NB + 1) + k], L[j * (NB + 1) + k], L[i * (NB + 1) + j]);
-    }
-    __syncthreads();
-  }
-  // X = L^-1 by forward substitution, one column per thread
-  for (int c = tid; c < nb; c += blockDim.x) {
-    for (int i = 0; i < nb; ++i) {
-      float s = (i == c) ? 1.0f : 0.0f;
-      for (int j = c; j < i; ++j) s = fmaf(-L[i * (NB + 1) + j], X[j * (NB + 1) + c], s);
-      X[i * (NB + 1) + c] = (i < c) ? 0.0f : s / L[i * (NB + 1) + i];
+  const int ty = tid >> 4, tx = tid & 15;
+  float a[8][8], x[8][8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int i = ty + 16 * r, j = tx + 16 * c;
+      a[r][c] = (i < nb && j < nb) ? A[(int64_t)i * lda + j] : (i == j ? 1.0f : 0.0f);
+      x[r][c] = i == j ? 1.0f : 0.0f;
     }
   }
-  __syncthreads();
-  for (int idx = tid; idx < nb * nb; idx += blockDim.x) {
-    const int i = idx / nb, j = idx - i * nb;
-    A[(int64_t)i * lda + j] = (j <= i) ? L[i * (NB + 1) + j] : 0.0f;
-    Linv[(int64_t)i * ldi + j] = X[i * (NB + 1) + j];
+#pragma unroll
+  for (int cc = 0; cc < 8; ++cc) {
+    for (int t = 0; t < 16; ++t) {
+      const int k = 16 * cc + t;
+      float* cb = colbuf[k & 1];
+      float* rb = rowbuf[k & 1];
+      if (tx == t) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) cb[ty + 16 * r] = a[r][cc];
+      }
+      if (ty == t) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) rb[tx + 16 * c] = x[cc][c];
+      }
+      __syncthreads();
+      float piv = cb[k];
+      if (!(piv > 0.0f) || !isfinite(piv)) {
+        if (tid == 0) atomicExch(status, 1);
+        piv = 1.0f;
+      }
+      const float rinv = 1.0f / sqrtf(piv);
+      float li[8], lj[8], xr[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) li[r] = r >= cc ? cb[ty + 16 * r] * rinv : 0.0f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        lj[c] = c >= cc ? cb[tx + 16 * c] * rinv : 0.0f;
+        xr[c] = c <= cc ? rb[tx + 16 * c] * rinv : 0.0f;
+      }
+      const bool below = ty > t;   // row ty + 16 cc lies below row k
+#pragma unroll
+      for (int r = cc; r < 8; ++r) {
+        if (r > cc || below) {
+#pragma unroll
+          for (int c = cc; c < 8; ++c)
+            if (c > cc || tx > t) a[r][c] = fmaf(-li[r], lj[c], a[r][c]);
+#pragma unroll
+          for (int c = 0; c <= cc; ++c) x[r][c] = fmaf(-li[r], xr[c], x[r][c]);
+        }
+      }
+      if (tx == t) {
+#pragma unroll
+        for (int r = cc; r < 8; ++r) a[r][cc] = li[r];
+      }
+      if (ty == t) {
+#pragma unroll
+        for (int c = 0; c <= cc; ++c) x[cc][c] = xr[c];
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int i = ty + 16 * r, j = tx + 16 * c;
+      if (i < nb && j < nb) {
+        A[(int64_t)i * lda + j] = j <= i ? a[r][c] : 0.0f;
+        Linv[(int64_t)i * ldi + j] = j <= i ? x[r][c] : 0.0f;
+      }
+    }
   }
 }
 
@@ -341,14 +383,6 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
   float* L = workspace;
   float* scratch = workspace + d * d;
   const int nblk = (int)((d + NB - 1) / NB);
-  static bool configured[64] = {};
-  int dev = 0;
-  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
-  const int diag_smem = 2 * NB * (NB + 1) * (int)sizeof(float);
-  if (dev < 64 && !configured[dev]) {
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(chol_diag_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, diag_smem));
-    configured[dev] = true;
-  }
   FPQ_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
   reverse_copy_kernel<<<grid1d(d * d), 256, 0, st>>>(H, L, d);
   FPQ_CHECK_LAUNCH();
@@ -356,7 +390,7 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
   for (int k = 0; k < nblk; ++k) {
     const int64_t r = (int64_t)k * NB;
     const int nb = (int)((d - r) < NB ? (d - r) : NB);
-    chol_diag_kernel<<<1, 256, diag_smem, st>>>(L + r * d + r, d, U + r * d + r, d, nb, status);
+    chol_diag_kernel<<<1, 256, 0, st>>>(L + r * d + r, d, U + r * d + r, d, nb, status);
     FPQ_CHECK_LAUNCH();
     const int64_t below = d - (r + nb);
     if (below <= 0) break;

@@ -22,6 +22,7 @@ struct QuantParams {
   const void* x;
   int64_t n_chunks;     // rows * cols / 32
   uint32_t chunks_per_row;
+  uint64_t row_magic;   // ceil(2^64 / chunks_per_row) (0 when chunks_per_row == 1): chunk -> row by one multiply
   uint8_t* codes;       // [rows, cols/2]
   uint8_t* sbytes;      // scale bytes
   float* sf32;          // fp32 scales, row-major
@@ -65,39 +66,85 @@ __device__ __forceinline__ u64 fma2(u64 a, u64 b, u64 c) {
   return r;
 }
 
-// 32 contiguous elements -> 16 packed pairs (element 2j in the low half of P[j]).
-template <bool IN_BF16>
-__device__ __forceinline__ void load_chunk(const void* base, int64_t chunk, bool active, u64 (&P)[16]) {
-  if (IN_BF16) {
-    uint32_t w[16];
-    if (active) {
-      const uint32_t* p = reinterpret_cast<const uint32_t*>(base) + chunk * 16;
-      asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                   : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]),
-                     "=r"(w[6]), "=r"(w[7])
-                   : "l"(p));
-      asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                   : "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]),
-                     "=r"(w[14]), "=r"(w[15])
-                   : "l"(p + 8));
-    } else {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) w[j] = 0;
-    }
-#pragma unroll
-    for (int j = 0; j < 16; ++j)
-      P[j] = pack2(__uint_as_float(w[j] << 16), __uint_as_float(w[j] & 0xffff0000u));
+// 32 contiguous elements of a row as they lie in memory: sixteen 32-bit words of bf16 pairs, or
+// sixteen 64-bit words of fp32 pairs (element 2j in the low half of word j).
+template <bool IN_BF16> struct RawChunk;
+template <> struct RawChunk<true> { uint32_t w[16]; };
+template <> struct RawChunk<false> { u64 w[16]; };
+
+__device__ __forceinline__ void load_raw(const void* base, int64_t chunk, bool active, RawChunk<true>& r) {
+  if (active) {
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(base) + chunk * 16;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.w[0]), "=r"(r.w[1]), "=r"(r.w[2]), "=r"(r.w[3]), "=r"(r.w[4]), "=r"(r.w[5]),
+                   "=r"(r.w[6]), "=r"(r.w[7])
+                 : "l"(p));
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.w[8]), "=r"(r.w[9]), "=r"(r.w[10]), "=r"(r.w[11]), "=r"(r.w[12]), "=r"(r.w[13]),
+                   "=r"(r.w[14]), "=r"(r.w[15])
+                 : "l"(p + 8));
   } else {
-    if (active) {
-      const u64* p = reinterpret_cast<const u64*>(base) + chunk * 16;
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        asm volatile("ld.global.nc.L1::no_allocate.v4.b64 {%0,%1,%2,%3}, [%4];"
-                     : "=l"(P[4 * q]), "=l"(P[4 * q + 1]), "=l"(P[4 * q + 2]), "=l"(P[4 * q + 3])
-                     : "l"(p + 4 * q));
+    for (int j = 0; j < 16; ++j) r.w[j] = 0;
+  }
+}
+__device__ __forceinline__ void load_raw(const void* base, int64_t chunk, bool active, RawChunk<false>& r) {
+  if (active) {
+    const u64* p = reinterpret_cast<const u64*>(base) + chunk * 16;
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      asm volatile("ld.global.nc.L1::no_allocate.v4.b64 {%0,%1,%2,%3}, [%4];"
+                   : "=l"(r.w[4 * q]), "=l"(r.w[4 * q + 1]), "=l"(r.w[4 * q + 2]), "=l"(r.w[4 * q + 3])
+                   : "l"(p + 4 * q));
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r.w[j] = 0ull;
+  }
+}
+
+#ifndef FPQ_Q_MIXED
+#define FPQ_Q_MIXED 1
+#endif
+#ifndef FPQ_Q_MAX3
+#define FPQ_Q_MAX3 1
+#endif
+
+// Raw words -> fp32 pairs.  With STAGE1 the first butterfly stage (distance 1: the two elements
+// of a pair become their sum and difference) is applied on the way.  For bf16 input that stage
+// is done by the mixed-precision bf16/fp32 add and fma of sm_100, which widen the bf16 operand
+// exactly and round once, like the fp32 add/sub they replace.
+template <bool STAGE1>
+__device__ __forceinline__ void unpack_chunk(const RawChunk<true>& r, u64 (&P)[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (STAGE1 && FPQ_Q_MIXED) {
+      float lo, s, d;
+      asm("{ .reg .b16 l, h, one, mone;\n"
+          "  mov.b32 {l, h}, %3;\n"
+          "  mov.b16 one, 0x3f80;\n"
+          "  mov.b16 mone, 0xbf80;\n"
+          "  fma.rn.f32.bf16 %0, l, one, 0f00000000;\n"
+          "  add.rn.f32.bf16 %1, h, %0;\n"
+          "  fma.rn.f32.bf16 %2, h, mone, %0; }"
+          : "=&f"(lo), "=f"(s), "=f"(d)
+          : "r"(r.w[j]));
+      P[j] = pack2(s, d);
     } else {
+      const float a = __uint_as_float(r.w[j] << 16), b = __uint_as_float(r.w[j] & 0xffff0000u);
+      P[j] = STAGE1 ? pack2(__fadd_rn(a, b), __fsub_rn(a, b)) : pack2(a, b);
+    }
+  }
+}
+template <bool STAGE1>
+__device__ __forceinline__ void unpack_chunk(const RawChunk<false>& r, u64 (&P)[16]) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) P[j] = 0ull;
+  for (int j = 0; j < 16; ++j) {
+    if (STAGE1) {
+      float a, b;
+      unpack2(r.w[j], a, b);
+      P[j] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));
+    } else {
+      P[j] = r.w[j];
     }
   }
 }
@@ -111,18 +158,11 @@ __device__ __forceinline__ constexpr float hadamard_scale() {
 
 template <int GH, bool SCALE = true>
 __device__ __forceinline__ void rotate_chunk(u64 (&P)[16], int lane) {
-  if (GH == 0) return;
-  // distance 1: inside each packed pair
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    float a, b;
-    unpack2(P[j], a, b);
-    P[j] = pack2(__fadd_rn(a, b), __fsub_rn(a, b));
-  }
+  // distance 1 (inside each packed pair) was applied by unpack_chunk<true>
   // distances 2, 4, 8, 16 <-> pair index distance 1, 2, 4, 8
 #pragma unroll
   for (int d = 1; d < 16; d <<= 1) {
-    if (2 * d < (GH < 32 ? GH : 32)) {
+    if (GH != 0 && 2 * d < (GH < 32 ? GH : 32)) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         if ((j & d) == 0) {
@@ -145,7 +185,7 @@ __device__ __forceinline__ void rotate_chunk(u64 (&P)[16], int lane) {
       }
     }
   }
-  if (SCALE) {
+  if (SCALE && GH != 0) {
     const float c = hadamard_scale<GH>();
     const u64 C = pack2(c, c);
 #pragma unroll
@@ -182,7 +222,11 @@ __device__ __forceinline__ float absmax_pairs(const u64* P, int n) {
   for (int j = 0; j < n; ++j) {
     float a, b;
     unpack2(P[j], a, b);
+#if FPQ_Q_MAX3
+    asm("max.f32 %0, %0, %1, %2;" : "+f"(m) : "f"(fabsf(a)), "f"(fabsf(b)));
+#else
     m = fmaxf(m, fmaxf(fabsf(a), fabsf(b)));
+#endif
   }
   return m;
 }
@@ -280,23 +324,28 @@ __device__ __forceinline__ size_t swizzled_offset(uint32_t row, uint32_t sfc, ui
          ((row >> 5) & 3u) * 4u + (sfc & 3u);
 }
 
-template <int GH, int FMT, bool IN_BF16, int MODE>
-__global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  float gs = 0.0f, rgs = 0.0f;
-  if (FMT == FPQ_FMT_NVFP4 && (MODE == MODE_CODES || MODE == MODE_DEQUANT)) {
-    gs = *p.gs;
-    rgs = gs == 0.0f ? 0.0f : __frcp_rn(gs);
+// chunk index -> (row, chunk in row).  One 64 x 64 -> high 64 multiply: with M = ceil(2^64 / d)
+// the quotient floor(c * M / 2^64) is exact whenever c * (M d - 2^64) < 2^64, which holds for
+// c, d < 2^32.  Larger chunk counts take the division.
+__device__ __forceinline__ void chunk_row(const QuantParams& p, int64_t c, uint32_t& row, uint32_t& cir) {
+  if (p.chunks_per_row == 1) {
+    row = (uint32_t)c;
+    cir = 0;
+  } else if (p.row_magic) {
+    row = (uint32_t)__umul64hi((u64)c, p.row_magic);
+    cir = (uint32_t)c - row * p.chunks_per_row;
+  } else {
+    row = (uint32_t)(c / p.chunks_per_row);
+    cir = (uint32_t)(c - (int64_t)row * p.chunks_per_row);
   }
-  float running_max = 0.0f;
+}
 
-  for (int64_t cb = warp * 32; cb < p.n_chunks; cb += nwarps * 32) {
-    const int64_t c = cb + lane;
-    const bool active = c < p.n_chunks;
+// Everything that happens to one chunk of 32 elements after its load.
+template <int GH, int FMT, bool IN_BF16, int MODE>
+__device__ __forceinline__ void process_chunk(const QuantParams& p, const RawChunk<IN_BF16>& raw, int64_t c,
+                                              bool active, int lane, float gs, float rgs, float& running_max) {
     u64 P[16];
-    load_chunk<IN_BF16>(p.x, c, active, P);
+    unpack_chunk<GH != 0>(raw, P);
     // MXFP4 codes take the unscaled butterfly output (the 1/sqrt(g) factor is folded into the
     // code multiplier); every other mode works on the scaled rotation.
     constexpr bool MX_FAST = MODE == MODE_CODES && FMT == FPQ_FMT_MXFP4;
@@ -304,7 +353,7 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
 
     if (MODE == MODE_ABSMAX) {
       running_max = fmaxf(running_max, absmax_pairs(P, 16));
-      continue;
+      return;
     }
     if (MODE == MODE_ROTATE) {
       if (active) {
@@ -328,7 +377,7 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
           for (int q = 0; q < 8; ++q) o[q] = make_ulonglong2(P[2 * q], P[2 * q + 1]);
         }
       }
-      continue;
+      return;
     }
 
     // ---- scales
@@ -344,13 +393,13 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
       s[g] = FMT == FPQ_FMT_NVFP4 ? nv_scale(a, gs, rgs, sb[g]) : mx_scale(a, sb[g], mx_e);
     }
     if (MODE == MODE_CODES && active) {
-      const uint32_t row = (uint32_t)(c / p.chunks_per_row);
-      const uint32_t cir = (uint32_t)(c - (int64_t)row * p.chunks_per_row);
       if (p.sbytes) {
-        const uint32_t sfc = cir * NG;
-        size_t off = p.layout == FPQ_SCALES_SWIZZLED
-                         ? swizzled_offset(row, sfc, p.sf_tiles_per_row_block)
-                         : (size_t)c * NG;
+        size_t off = (size_t)c * NG;
+        if (p.layout == FPQ_SCALES_SWIZZLED) {
+          uint32_t row, cir;
+          chunk_row(p, c, row, cir);
+          off = swizzled_offset(row, cir * NG, p.sf_tiles_per_row_block);
+        }
         if (NG == 2)
           *reinterpret_cast<uint16_t*>(p.sbytes + off) = (uint16_t)(sb[0] | (sb[NG - 1] << 8));
         else
@@ -363,7 +412,7 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
           p.sf32[c] = s[0];
       }
     }
-    if (MODE == MODE_CODES && p.codes == nullptr) continue;
+    if (MODE == MODE_CODES && p.codes == nullptr) return;
 
     // ---- keep the rotated values when the straight-through form needs them
     u64 Y[MODE == MODE_DEQUANT ? 16 : 1];
@@ -433,6 +482,55 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
         }
       }
     }
+}
+
+#ifndef FPQ_Q_PREFETCH
+#define FPQ_Q_PREFETCH 1
+#endif
+#ifndef FPQ_Q_MINBLOCKS
+#define FPQ_Q_MINBLOCKS 3
+#endif
+
+// A warp walks the chunks 32 at a time with a grid-wide stride.  For bf16 input the next chunk's
+// sixteen words are loaded into a second register set before the current chunk is processed, so
+// every thread keeps two 64-byte requests in flight.
+template <bool IN_BF16, int MODE>
+struct Prefetches { static constexpr bool value = FPQ_Q_PREFETCH && IN_BF16 && MODE != MODE_DEQUANT; };
+
+template <int GH, int FMT, bool IN_BF16, int MODE>
+__global__ void __launch_bounds__(256, Prefetches<IN_BF16, MODE>::value ? FPQ_Q_MINBLOCKS : 1) quant_kernel(const QuantParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * 32;
+  float gs = 0.0f, rgs = 0.0f;
+  if (FMT == FPQ_FMT_NVFP4 && (MODE == MODE_CODES || MODE == MODE_DEQUANT)) {
+    gs = *p.gs;
+    rgs = gs == 0.0f ? 0.0f : __frcp_rn(gs);
+  }
+  float running_max = 0.0f;
+
+  int64_t cb = warp * 32;
+  if (Prefetches<IN_BF16, MODE>::value) {
+    RawChunk<IN_BF16> r0, r1;
+    if (cb < p.n_chunks) load_raw(p.x, cb + lane, cb + lane < p.n_chunks, r0);
+    while (cb < p.n_chunks) {
+      int64_t nx = cb + stride + lane;
+      load_raw(p.x, nx, nx < p.n_chunks, r1);
+      process_chunk<GH, FMT, IN_BF16, MODE>(p, r0, cb + lane, cb + lane < p.n_chunks, lane, gs, rgs, running_max);
+      cb += stride;
+      if (cb >= p.n_chunks) break;
+      nx = cb + stride + lane;
+      load_raw(p.x, nx, nx < p.n_chunks, r0);
+      process_chunk<GH, FMT, IN_BF16, MODE>(p, r1, cb + lane, cb + lane < p.n_chunks, lane, gs, rgs, running_max);
+      cb += stride;
+    }
+  } else {
+    for (; cb < p.n_chunks; cb += stride) {
+      const int64_t c = cb + lane;
+      RawChunk<IN_BF16> r;
+      load_raw(p.x, c, c < p.n_chunks, r);
+      process_chunk<GH, FMT, IN_BF16, MODE>(p, r, c, c < p.n_chunks, lane, gs, rgs, running_max);
+    }
   }
 
   if (MODE == MODE_ABSMAX) {
@@ -444,10 +542,22 @@ __global__ void __launch_bounds__(256) quant_kernel(const QuantParams p) {
 }
 
 template <int GH, int FMT, bool IN_BF16, int MODE>
-int launch_one(const QuantParams& p, cudaStream_t stream) {
+int launch_one(const QuantParams& params, cudaStream_t stream) {
+  QuantParams p = params;
+  p.row_magic = (p.chunks_per_row >= 2 && p.n_chunks < (1ll << 32)) ? ~0ull / p.chunks_per_row + 1 : 0;
+  // persistent grid: exactly the number of blocks that are resident at once
+  static int resident[64] = {};
+  int dev = 0;
+  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
+  int per_sm = dev < 64 ? resident[dev] : 0;
+  if (per_sm == 0) {
+    FPQ_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_kernel<GH, FMT, IN_BF16, MODE>, 256, 0));
+    if (per_sm < 1) per_sm = 1;
+    if (dev < 64) resident[dev] = per_sm;
+  }
   const int64_t warps_needed = ceil_div64(p.n_chunks, 32);
   const int64_t blocks_needed = ceil_div64(warps_needed, 8);
-  int64_t blocks = (int64_t)sm_count() * 8;
+  int64_t blocks = (int64_t)sm_count() * per_sm;
   if (blocks > blocks_needed) blocks = blocks_needed;
   if (blocks < 1) blocks = 1;
   quant_kernel<GH, FMT, IN_BF16, MODE><<<(unsigned)blocks, 256, 0, stream>>>(p);
