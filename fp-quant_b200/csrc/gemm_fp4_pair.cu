@@ -15,11 +15,16 @@
 // the whole accumulator into registers (packed bf16), hands it back, and only then writes to global
 // memory, so the stores overlap the next tile's MMAs.
 //
-// Barriers: the "full" barrier of a stage (operand tiles) lives in the leader; both producers announce
-// their bytes on it and both CTAs' operand loads complete on it.  Scale tiles complete on a per-CTA
-// "sf_full" barrier.  "empty" and "accumulator full" barriers exist in both CTAs and get one
-// tcgen05.commit each; "sf_ready" and "accumulator empty" live in the leader and collect the warps of
-// both CTAs.  Every wait is bounded.  Nothing is broadcast between the CTAs.
+// Barriers: the "full" barrier of a stage lives in the leader and collects everything the MMAs of that
+// stage need: the operand bytes of both CTAs (both producers announce theirs on it) and one arrival
+// per scale-mover warp of both CTAs once the stage's scales sit in tensor memory.  Scale tiles land on
+// a per-CTA "sf_full" barrier that only the movers watch.  The issuing thread pays 75-150 cycles for
+// every tcgen05 instruction and ~100 for every barrier wait, more than the tensor pipe needs for the
+// four MMAs of a stage, so its loop is kept to one wait, four MMAs and one commit per stage: the
+// commit frees the stage in the leader, whose producer passes the news on to the follower's "empty"
+// barrier.  "accumulator full" exists in both CTAs (one commit each per tile), "accumulator empty"
+// lives in the leader and collects the epilogue warps of both CTAs.  Every wait is bounded.  Nothing
+// is broadcast between the CTAs.
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -37,7 +42,6 @@ constexpr int BN_CTA = 128;            // rows of B per CTA
 constexpr int BK_BYTES = 128;
 constexpr int BK_ELEMS = 256;
 constexpr int NUM_THREADS = 448;       // 14 warps: producer, MMA, 4 epilogue, 4 scale movers, 4 epilogue
-constexpr int NUM_SF_BUFS = 5;          // scale-factor buffers in tensor memory (must stay below STAGES)
 constexpr int TMEM_COLS = 512;
 constexpr int SF_TMEM_BASE = 256;
 
@@ -71,9 +75,9 @@ struct PairSmem {
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
-  // full[S], empty[S], sf_full[S], sf_ready[NUM_SF_BUFS], acc_full, acc_empty
+  // full[S], empty[S], sf_full[S], acc_full, acc_empty
   static constexpr int OFF_BAR = OFF_SFB + STAGES * SFB_BYTES;
-  static constexpr int OFF_MISC = OFF_BAR + (3 * STAGES + NUM_SF_BUFS + 2) * 8;
+  static constexpr int OFF_MISC = OFF_BAR + (3 * STAGES + 2) * 8;
   static constexpr int TOTAL = OFF_MISC + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -89,7 +93,11 @@ __device__ __forceinline__ void pair_tile_coords(const PairParams& p, int tile, 
   n_blk = in_band / rows;
 }
 
-template <bool NVFP4>
+// Cycle counter for the tuning counters; compiled out (constant 0) in the normal instantiation.
+template <bool PROF>
+__device__ __forceinline__ long long tick() { return PROF ? clock64() : 0ll; }
+
+template <bool NVFP4, bool PROF>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -103,8 +111,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t bar_full = sbase + L::OFF_BAR;
   const uint32_t bar_empty = bar_full + STAGES * 8;
   const uint32_t bar_sf_full = bar_empty + STAGES * 8;
-  const uint32_t bar_sf_ready = bar_sf_full + STAGES * 8;
-  const uint32_t bar_acc_full = bar_sf_ready + NUM_SF_BUFS * 8;
+  const uint32_t bar_acc_full = bar_sf_full + STAGES * 8;
   const uint32_t bar_acc_empty = bar_acc_full + 8;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
@@ -115,11 +122,10 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 2);      // one announcement per producer of the pair (used in the leader)
+      mbar_init(bar_full + 8 * s, 2 + 8);  // both producers' announcements + four mover warps per CTA (leader)
       mbar_init(bar_empty + 8 * s, 1);
       mbar_init(bar_sf_full + 8 * s, 1);
     }
-    for (int b = 0; b < NUM_SF_BUFS; ++b) mbar_init(bar_sf_ready + 8 * b, 8);   // four mover warps per CTA (leader)
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, 16);          // eight epilogue warps per CTA (used in the leader)
     *abort_flag = 0;
@@ -142,11 +148,11 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   // addresses of the leader's barriers as seen from this CTA
   const uint32_t lead_full = map_to_cta(bar_full, 0);
   const uint32_t lead_acc_empty = map_to_cta(bar_acc_empty, 0);
-  const uint32_t lead_sf_ready = map_to_cta(bar_sf_ready, 0);
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (both CTAs)
     if (lane == 0) {
+      const uint32_t peer_empty = map_to_cta(bar_empty, 1);
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs) {
@@ -156,7 +162,11 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int n_row = n_blk * BN + (int)rank * BN_CTA;              // my rows of B
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
+          const long long pt0 = tick<PROF>();
           if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          // the MMA thread frees a stage in the leader only; the leader tells the follower
+          if (rank == 0 && it >= (uint32_t)STAGES) mbar_arrive_cluster(peer_empty + 8 * s);
+          const long long pt1 = tick<PROF>();
           const uint32_t full = lead_full + 8 * s;
           // scale tiles first (the movers need them earliest): 64 eight-byte words per 512-byte tile,
           // rows of the map are 128-row blocks; they complete on this CTA's own barrier
@@ -167,69 +177,86 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           mbar_arrive_expect_tx_cluster(full, L::STAGE_TX);
           tma_load_2d_pair(sbase + L::OFF_A + s * L::A_BYTES, &tmap_a, ks * BK_BYTES, m_row, full);
           tma_load_2d_pair(sbase + L::OFF_B + s * L::B_BYTES, &tmap_b, ks * BK_BYTES, n_row, full);
+          if (PROF && p.profile && pair_id == 0 && it < 512) {
+            long long* o = p.profile + 74 * 64 + 2048 + (size_t)rank * 2048 + (size_t)it * 4;
+            o[0] = pt0; o[1] = pt1; o[2] = tick<PROF>();
+          }
         }
       }
       if (!ok) {
         *abort_flag = 1;
         atomicExch(p.error_flag, 1);
       }
-      // Drain: my loads complete on the leader's barrier, which I cannot poll from the follower; the
-      // consumer frees a stage (commit on my empty barrier) only after the stage was complete, so
-      // waiting for my last min(it, STAGES) stages to be freed proves that every load has landed.
+      // Drain: my loads complete on the leader's barrier, which I cannot poll from the follower; a stage
+      // is freed only after it was complete, so waiting for my last min(it, STAGES) stages to be freed
+      // proves that every load has landed.  The leader keeps passing the news on.
       const uint32_t first = it > STAGES ? it - STAGES : 0;
       volatile int never = 0;
-      for (uint32_t j = first; j < it; ++j)
-        (void)mbar_wait_bounded(bar_empty + 8 * (j % STAGES), (j / STAGES) & 1, &never, 400000000LL);
+      for (uint32_t j = first; j < it; ++j) {
+        const bool freed = mbar_wait_bounded(bar_empty + 8 * (j % STAGES), (j / STAGES) & 1, &never, 400000000LL);
+        if (rank == 0 && freed) mbar_arrive_cluster(peer_empty + 8 * (j % STAGES));
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (leader only)
     if (lane == 0 && rank == 0) {
-      const uint32_t peer_empty = map_to_cta(bar_empty, 1);
       const uint32_t peer_acc_full = map_to_cta(bar_acc_full, 1);
+      uint32_t idesc_k[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t sf_id = NVFP4 ? 0u : (uint32_t)((k & 1) * 2);
+        idesc_k[k] = make_idesc_fp4(256, BN, !NVFP4, sf_id, sf_id);
+      }
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
-      long long t_acc = 0, t_full = 0, t_sf = 0;
-      const long long t_begin = clock64();
+      long long t_acc = 0, t_full = 0;
+      const long long t_begin = tick<PROF>();
       for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs, ++tile_count) {
-        long long t0 = clock64();
-        if (!mbar_wait_bounded(bar_acc_empty, (tile_count & 1) ^ 1, abort_flag)) { ok = false; break; }
-        t_acc += clock64() - t0;
+        long long t0 = tick<PROF>();
+        if (!mbar_wait_bounded_spin(bar_acc_empty, (tile_count & 1) ^ 1, abort_flag)) { ok = false; break; }
+        t_acc += tick<PROF>() - t0;
         tc_fence_after();
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
-          t0 = clock64();
-          if (!mbar_wait_bounded(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
-          long long t1 = clock64();
+          t0 = tick<PROF>();
+          if (!mbar_wait_bounded_spin(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          const long long t1 = tick<PROF>();
           t_full += t1 - t0;
-          const uint32_t sfb_i = it % NUM_SF_BUFS;
-          if (!mbar_wait_bounded(bar_sf_ready + 8 * sfb_i, (it / NUM_SF_BUFS) & 1, abort_flag)) { ok = false; break; }
-          t_sf += clock64() - t1;
           tc_fence_after();
-          const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + sfb_i * L::SF_TMEM_BUF;
+          const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + s * L::SF_TMEM_BUF;
           const uint32_t sfa_t = sf_buf, sfb_t = sf_buf + L::SFA_COLS;
-          int kmma = (p.K - ks * BK_ELEMS + 63) / 64;
-          if (kmma > 4) kmma = 4;
           const uint64_t a_desc = make_desc_k_sw128(sbase + L::OFF_A + s * L::A_BYTES);
           const uint64_t b_desc = make_desc_k_sw128(sbase + L::OFF_B + s * L::B_BYTES);
-          for (int k = 0; k < kmma; ++k) {
-            uint32_t blk, sf_id;
-            if (NVFP4) { blk = k; sf_id = 0; }
-            else { blk = k >> 1; sf_id = (k & 1) * 2; }
-            const uint32_t idesc = make_idesc_fp4(256, BN, !NVFP4, sf_id, sf_id);
-            tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, sfa_t + 4 * blk,
-                                                sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+          const int k_left = p.K - ks * BK_ELEMS;
+          if (k_left >= BK_ELEMS) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t blk = NVFP4 ? (uint32_t)k : (uint32_t)(k >> 1);
+              tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k], sfa_t + 4 * blk,
+                                                  sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+            }
+          } else {
+            const int kmma = (k_left + 63) / 64;
+            for (int k = 0; k < kmma; ++k) {
+              const uint32_t blk = NVFP4 ? (uint32_t)k : (uint32_t)(k >> 1);
+              tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k & 3],
+                                                  sfa_t + 4 * blk, sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+            }
           }
-          tc_commit_pair(bar_empty + 8 * s);          // my stage ...
-          tc_commit_pair(peer_empty + 8 * s);         // ... and the follower's
+          tc_commit_pair(bar_empty + 8 * s);          // frees the stage (the leader's producer tells the follower)
+          if (PROF && p.profile && pair_id == 0 && it < 512) {
+            long long* o = p.profile + 74 * 64 + (size_t)it * 4;
+            o[0] = t0 - t_begin; o[1] = t1 - t_begin; o[2] = tick<PROF>() - t_begin; o[3] = 0;
+          }
         }
         if (ok) {
           tc_commit_pair(bar_acc_full);
           tc_commit_pair(peer_acc_full);
         }
       }
-      if (p.profile) {
+      if (PROF && p.profile) {
         long long* o = p.profile + (size_t)pair_id * 64;
-        o[0] = clock64() - t_begin; o[1] = t_acc; o[2] = t_full; o[3] = t_sf; o[4] = it;
+        o[0] = tick<PROF>() - t_begin; o[1] = t_acc; o[2] = t_full; o[3] = 0; o[4] = it; o[14] = t_begin;
       }
       if (!ok) {
         *abort_flag = 1;
@@ -240,31 +267,25 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------------------------------------- scale-factor movers (both CTAs)
     // A 512-byte tile is 32 rows x 16 bytes: lane l takes row l and writes it to lane l of this warp's
     // quarter of tensor memory, columns [c, c+4) -- the four warps together produce the replicated
-    // layout the block-scaled MMA reads.
+    // layout the block-scaled MMA reads.  One tensor-memory buffer per stage: the scales of a stage can
+    // only have landed (sf_full) after the producer saw the stage freed, i.e. after the MMAs that read
+    // the buffer's previous contents completed.
     const int quarter = warp & 3;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     // Stages form one flat sequence over this pair's tiles.
     const int my_tiles = pair_id < p.num_tiles ? (p.num_tiles - pair_id + num_pairs - 1) / num_pairs : 0;
     const uint32_t n_it = (uint32_t)my_tiles * (uint32_t)p.num_k_stages;
     bool ok = true;
-    long long m_sf = 0, m_empty = 0, m_st = 0, m_arr = 0;
-    const long long m_begin = clock64();
+    long long m_sf = 0, m_st = 0, m_arr = 0;
+    const long long m_begin = tick<PROF>();
     for (uint32_t it = 0; it < n_it && ok; ++it) {
       const int s = it % STAGES;
-      const uint32_t sfb_i = it % NUM_SF_BUFS;
-      long long t0 = clock64();
+      long long t0 = tick<PROF>();
       if (!mbar_wait_bounded(bar_sf_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
-      long long t1 = clock64();
+      long long t1 = tick<PROF>();
       m_sf += t1 - t0;
-      if (it >= NUM_SF_BUFS) {
-        // The MMAs that read this tensor-memory buffer NUM_SF_BUFS stages ago must be done.  Their stage's
-        // "empty" barrier cannot have moved on by more than one phase because NUM_SF_BUFS < STAGES.
-        const uint32_t old = it - NUM_SF_BUFS;
-        if (!mbar_wait_bounded(bar_empty + 8 * (old % STAGES), (old / STAGES) & 1, abort_flag)) { ok = false; break; }
-      }
-      m_empty += clock64() - t1;
       tc_fence_after();
-      const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + sfb_i * L::SF_TMEM_BUF + lane_base;
+      const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + s * L::SF_TMEM_BUF + lane_base;
       const uint8_t* sfa_s = smem + L::OFF_SFA + s * L::SFA_BYTES + lane * 16;
       const uint8_t* sfb_s = smem + L::OFF_SFB + s * L::SFB_BYTES + lane * 16;
 #pragma unroll
@@ -277,18 +298,18 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           tc_st_32x32b_x4(sf_buf + L::SFA_COLS + 8 * j + 4 * h, b.x, b.y, b.z, b.w);
         }
       }
-      long long t2 = clock64();
+      long long t2 = tick<PROF>();
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      long long t3 = clock64();
+      long long t3 = tick<PROF>();
       m_st += t3 - t2;
-      if (lane == 0) mbar_arrive_cluster(lead_sf_ready + 8 * sfb_i);
-      m_arr += clock64() - t3;
+      if (lane == 0) mbar_arrive_cluster(lead_full + 8 * s);
+      m_arr += tick<PROF>() - t3;
     }
-    if (p.profile && warp == 6 && lane == 0) {
+    if (PROF && p.profile && warp == 6 && lane == 0) {
       long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
-      o[5] = m_sf; o[6] = m_empty; o[7] = m_st; o[8] = m_arr; o[9] = clock64() - m_begin;
+      o[5] = m_sf; o[6] = 0; o[7] = m_st; o[8] = m_arr; o[9] = tick<PROF>() - m_begin;
     }
     if (!ok && lane == 0) {
       *abort_flag = 1;
@@ -305,9 +326,9 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs, ++tile_count) {
       int m_pair, n_blk;
       pair_tile_coords(p, tile, m_pair, n_blk);
-      long long t0 = clock64();
+      long long t0 = tick<PROF>();
       if (!mbar_wait_bounded(bar_acc_full, tile_count & 1, abort_flag)) { ok = false; break; }
-      long long t1 = clock64();
+      long long t1 = tick<PROF>();
       e_wait += t1 - t0;
       tc_fence_after();
       const int row = m_pair * 256 + (int)rank * BM_CTA + quarter * 32 + lane;
@@ -320,12 +341,12 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       tc_ld_32x32b_x32(tsrc + 64, r2);
       tc_ld_32x32b_x32(tsrc + 96, r3);
       tc_wait_ld();
-      e_ld0 += clock64() - t1;
+      e_ld0 += tick<PROF>() - t1;
       // 2) hand the accumulator back: the next tile's MMAs may start while we convert and store
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
-      long long t2 = clock64();
+      long long t2 = tick<PROF>();
       e_drain += t2 - t1;
       // 3) scale, round to bf16, write out (N is a multiple of 8: a 16-byte group is all in or all out)
       if (row < p.M) {
@@ -354,9 +375,9 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
         }
       }
-      e_store += clock64() - t2;
+      e_store += tick<PROF>() - t2;
     }
-    if (p.profile && warp == 2 && lane == 0) {
+    if (PROF && p.profile && warp == 2 && lane == 0) {
       long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
       o[10] = e_wait; o[11] = e_drain; o[12] = e_store; o[13] = e_ld0;
     }
@@ -380,12 +401,13 @@ template <bool NVFP4>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                 PairParams p, cudaStream_t stream) {
   using L = PairSmem<NVFP4>;
-  auto kern = gemm_fp4_pair_kernel<NVFP4>;
+  auto kern = p.profile ? gemm_fp4_pair_kernel<NVFP4, true> : gemm_fp4_pair_kernel<NVFP4, false>;
   static bool configured[64] = {};
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
     configured[dev] = true;
   }
   int pairs = sm_count() / 2;

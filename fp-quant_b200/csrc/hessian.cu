@@ -8,10 +8,12 @@
 // X^T X is a GEMM whose two operands are the same row-major matrix read "MN-major": a TMA box of
 // 64 columns x 64 tokens with the 128-byte swizzle lands in shared memory exactly in the canonical
 // MN-major layout of tcgen05.mma (8 token rows of 128 bytes per swizzle atom).  Persistent CTAs walk
-// the 128 x 128 tiles of the lower triangle (or all tiles for the general A^T B form); two fp32
-// accumulators in tensor memory let the read-modify-write epilogue of one tile overlap the MMAs of
-// the next.  Off-diagonal tiles are also written mirrored, so H stays fully symmetric like the
-// reference's.  Warp roles and bounded waits as in the FP4 GEMM.
+// 128 x 256 tiles (an MMA instruction costs the same ~180 cycles for N = 128 and N = 256, so only the
+// wide tile keeps the tensor pipe busy) that touch the lower triangle (or all tiles for the general
+// A^T B form); two fp32 accumulators fill tensor memory so that the read-modify-write epilogue of one
+// tile overlaps the MMAs of the next.  Of a tile on the diagonal only the 128-column blocks at or
+// below it are written; blocks below the diagonal are also written mirrored, so H stays fully
+// symmetric like the reference's.  Warp roles and bounded waits as in the FP4 GEMM.
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -21,16 +23,19 @@ namespace {
 
 using namespace ptx;
 
-constexpr int TILE = 128;            // output tile (both dims)
+constexpr int TILE = 128;            // output tile rows (A^T side) and the unit of the triangle
+constexpr int TILE_N = 256;          // output tile columns
 constexpr int BK = 64;               // tokens per stage
 constexpr int BOX_BYTES = BK * 128;  // one 64-column x 64-token box
-constexpr int STAGES = 6;
+constexpr int A_BOXES = TILE / 64, B_BOXES = TILE_N / 64;
+constexpr int STAGES = 4;
 constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 256;       // two 128-column accumulators
+constexpr int TMEM_COLS = 512;       // two 256-column accumulators
 
 struct HessParams {
   int64_t T, d;
   int num_blocks;      // ceil(d / 128)
+  int num_blocks_n;    // ceil(d / 256)
   int num_tiles;
   int num_k_stages;    // ceil(T / 64)
   int symmetric;
@@ -41,8 +46,8 @@ struct HessParams {
 
 struct Smem {
   static constexpr int OFF_A = 0;                               // STAGES x 2 boxes
-  static constexpr int OFF_B = OFF_A + STAGES * 2 * BOX_BYTES;
-  static constexpr int OFF_BAR = OFF_B + STAGES * 2 * BOX_BYTES;  // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr int OFF_B = OFF_A + STAGES * A_BOXES * BOX_BYTES;   // STAGES x 4 boxes
+  static constexpr int OFF_BAR = OFF_B + STAGES * B_BOXES * BOX_BYTES;  // full[S], empty[S], acc_full[2], acc_empty[2]
   static constexpr int OFF_MISC = OFF_BAR + (2 * STAGES + 4) * 8;
   static constexpr int TOTAL = OFF_MISC + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
@@ -60,17 +65,24 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint3
   return d;
 }
 
-__device__ __forceinline__ void tile_coords(const HessParams& p, int tile, int& ib, int& jb) {
+// Symmetric form: row block ib (128 rows) needs the column tiles jb2 = 0 .. ib / 2 (256 columns each).
+// Tiles are numbered row by row; rows 0 .. ib-1 hold q (q + 1) tiles for ib = 2 q and (q + 1)^2 for ib = 2 q + 1.
+__host__ __device__ inline int tiles_before_row(int ib) {
+  const int q = ib >> 1;
+  return (ib & 1) ? (q + 1) * (q + 1) : q * (q + 1);
+}
+
+__device__ __forceinline__ void tile_coords(const HessParams& p, int tile, int& ib, int& jb2) {
   if (p.symmetric) {
-    // tile = ib * (ib + 1) / 2 + jb with jb <= ib
-    int i = (int)((sqrtf(8.0f * (float)tile + 1.0f) - 1.0f) * 0.5f);
-    while ((i + 1) * (i + 2) / 2 <= tile) ++i;
-    while (i * (i + 1) / 2 > tile) --i;
+    int i = (int)(2.0f * sqrtf((float)tile)) - 1;
+    if (i < 0) i = 0;
+    while (tiles_before_row(i + 1) <= tile) ++i;
+    while (tiles_before_row(i) > tile) --i;
     ib = i;
-    jb = tile - i * (i + 1) / 2;
+    jb2 = tile - tiles_before_row(i);
   } else {
-    ib = tile / p.num_blocks;
-    jb = tile - ib * p.num_blocks;
+    ib = tile / p.num_blocks_n;
+    jb2 = tile - ib * p.num_blocks_n;
   }
 }
 
@@ -121,13 +133,15 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          mbar_arrive_expect_tx(bar_full + 8 * s, 4 * BOX_BYTES);
-          const uint32_t a_dst = sbase + Smem::OFF_A + s * 2 * BOX_BYTES;
-          const uint32_t b_dst = sbase + Smem::OFF_B + s * 2 * BOX_BYTES;
-          tma_load_2d(a_dst, &tmap_a, ib * TILE, ks * BK, bar_full + 8 * s);
-          tma_load_2d(a_dst + BOX_BYTES, &tmap_a, ib * TILE + 64, ks * BK, bar_full + 8 * s);
-          tma_load_2d(b_dst, &tmap_b, jb * TILE, ks * BK, bar_full + 8 * s);
-          tma_load_2d(b_dst + BOX_BYTES, &tmap_b, jb * TILE + 64, ks * BK, bar_full + 8 * s);
+          mbar_arrive_expect_tx(bar_full + 8 * s, (A_BOXES + B_BOXES) * BOX_BYTES);
+          const uint32_t a_dst = sbase + Smem::OFF_A + s * A_BOXES * BOX_BYTES;
+          const uint32_t b_dst = sbase + Smem::OFF_B + s * B_BOXES * BOX_BYTES;
+#pragma unroll
+          for (int b = 0; b < A_BOXES; ++b)
+            tma_load_2d(a_dst + b * BOX_BYTES, &tmap_a, ib * TILE + 64 * b, ks * BK, bar_full + 8 * s);
+#pragma unroll
+          for (int b = 0; b < B_BOXES; ++b)
+            tma_load_2d(b_dst + b * BOX_BYTES, &tmap_b, jb * TILE_N + 64 * b, ks * BK, bar_full + 8 * s);
         }
       }
       if (!ok) {
@@ -141,20 +155,20 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(TILE, TILE, true, true);
+      const uint32_t idesc = make_idesc_bf16(TILE, TILE_N, true, true);
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tile_count) {
         const uint32_t buf = tile_count & 1;
         if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tile_count >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t acc = tmem_base + buf * TILE;
+        const uint32_t acc = tmem_base + buf * TILE_N;
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait_bounded(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint64_t a_desc = make_desc_mn_sw128(sbase + Smem::OFF_A + s * 2 * BOX_BYTES, BOX_BYTES, 1024);
-          const uint64_t b_desc = make_desc_mn_sw128(sbase + Smem::OFF_B + s * 2 * BOX_BYTES, BOX_BYTES, 1024);
+          const uint64_t a_desc = make_desc_mn_sw128(sbase + Smem::OFF_A + s * A_BOXES * BOX_BYTES, BOX_BYTES, 1024);
+          const uint64_t b_desc = make_desc_mn_sw128(sbase + Smem::OFF_B + s * B_BOXES * BOX_BYTES, BOX_BYTES, 1024);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)   // 16 tokens per MMA = two 8-row atoms = 2048 bytes
             tc_mma_f16(acc, a_desc + (uint64_t)(k * (2048 >> 4)), b_desc + (uint64_t)(k * (2048 >> 4)), idesc,
@@ -179,13 +193,15 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!mbar_wait_bounded(bar_acc_full + 8 * buf, (tile_count >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int64_t i = (int64_t)ib * TILE + quarter * 32 + lane;
-      const bool mirror = p.symmetric && ib != jb;
 #pragma unroll 1
-      for (int c = 0; c < TILE / 32; ++c) {
+      for (int c = 0; c < TILE_N / 32; ++c) {
+        const int64_t j0 = (int64_t)jb * TILE_N + c * 32;
+        const int jblock = (int)(j0 / TILE);                 // 128-column block of this chunk
+        if (j0 >= p.d || (p.symmetric && jblock > ib)) break;   // beyond the matrix / above the diagonal
+        const bool mirror = p.symmetric && jblock < ib;
         uint32_t r[32];
-        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE + c * 32, r);
+        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE_N + c * 32, r);
         tc_wait_ld();
-        const int64_t j0 = (int64_t)jb * TILE + c * 32;
         if (i < p.d) {
           float* hrow = p.H + i * p.d + j0;
           if (j0 + 32 <= p.d && (p.d & 3) == 0) {
@@ -255,7 +271,8 @@ extern "C" int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, 
   HessParams p{};
   p.T = tokens; p.d = d;
   p.num_blocks = (int)((d + TILE - 1) / TILE);
-  p.num_tiles = symmetric ? p.num_blocks * (p.num_blocks + 1) / 2 : p.num_blocks * p.num_blocks;
+  p.num_blocks_n = (int)((d + TILE_N - 1) / TILE_N);
+  p.num_tiles = symmetric ? tiles_before_row(p.num_blocks) : p.num_blocks * p.num_blocks_n;
   p.num_k_stages = (int)((tokens + BK - 1) / BK);
   p.symmetric = symmetric ? 1 : 0;
   p.alpha = alpha; p.beta = beta; p.H = H; p.error_flag = error_flag;

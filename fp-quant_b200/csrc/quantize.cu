@@ -102,37 +102,18 @@ __device__ __forceinline__ void load_raw(const void* base, int64_t chunk, bool a
   }
 }
 
-#ifndef FPQ_Q_MIXED
-#define FPQ_Q_MIXED 1
-#endif
 #ifndef FPQ_Q_MAX3
 #define FPQ_Q_MAX3 1
 #endif
 
 // Raw words -> fp32 pairs.  With STAGE1 the first butterfly stage (distance 1: the two elements
-// of a pair become their sum and difference) is applied on the way.  For bf16 input that stage
-// is done by the mixed-precision bf16/fp32 add and fma of sm_100, which widen the bf16 operand
-// exactly and round once, like the fp32 add/sub they replace.
+// of a pair become their sum and difference) is applied on the way.
 template <bool STAGE1>
 __device__ __forceinline__ void unpack_chunk(const RawChunk<true>& r, u64 (&P)[16]) {
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    if (STAGE1 && FPQ_Q_MIXED) {
-      float lo, s, d;
-      asm("{ .reg .b16 l, h, one, mone;\n"
-          "  mov.b32 {l, h}, %3;\n"
-          "  mov.b16 one, 0x3f80;\n"
-          "  mov.b16 mone, 0xbf80;\n"
-          "  fma.rn.f32.bf16 %0, l, one, 0f00000000;\n"
-          "  add.rn.f32.bf16 %1, h, %0;\n"
-          "  fma.rn.f32.bf16 %2, h, mone, %0; }"
-          : "=&f"(lo), "=f"(s), "=f"(d)
-          : "r"(r.w[j]));
-      P[j] = pack2(s, d);
-    } else {
-      const float a = __uint_as_float(r.w[j] << 16), b = __uint_as_float(r.w[j] & 0xffff0000u);
-      P[j] = STAGE1 ? pack2(__fadd_rn(a, b), __fsub_rn(a, b)) : pack2(a, b);
-    }
+    const float a = __uint_as_float(r.w[j] << 16), b = __uint_as_float(r.w[j] & 0xffff0000u);
+    P[j] = STAGE1 ? pack2(__fadd_rn(a, b), __fsub_rn(a, b)) : pack2(a, b);
   }
 }
 template <bool STAGE1>
@@ -244,7 +225,18 @@ __device__ __forceinline__ int mx_exponent(float m /* >= 2^-126, finite */) {
 }
 
 // MXFP4 scale of one 32-element group: returns the divisor s and the stored byte.
+// The reference computes e = floor(log2(m)) with m = fl(6 * fl(fl(2a) / 12)), which lies within
+// two ulps of a.  When a's mantissa is at least four ulps away from both ends of its binade (and
+// from the 0x7fff00 threshold of the logarithm's rounding artefact) m has a's exponent, so the
+// division chain is only evaluated for the rare group maxima near a power of two.
 __device__ __forceinline__ float mx_scale(float a, uint32_t& byte, int& e) {
+  const uint32_t bits = __float_as_uint(a);
+  const uint32_t mant = bits & 0x7fffffu, ex = bits >> 23;   // a >= 0
+  if (mant - 4u <= 0x7ffef7u && ex - 8u <= 239u) {           // mant in [4, 0x7ffefb], ex in [8, 247]
+    e = (int)ex - 127;
+    byte = ex;
+    return __uint_as_float(((ex - 2u) << 23) | 0x2aaaabu);
+  }
   float s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
   float m = fmaxf(__fmul_rn(6.0f, s0), 1.17549435e-38f);
   e = mx_exponent(m);
@@ -304,8 +296,26 @@ __device__ __forceinline__ void divide_pairs(u64* P, int n, float s) {
 }
 
 // Eight quotients (4 pairs) -> one word of eight 4-bit codes, element 0 in the lowest nibble.
+#ifndef FPQ_Q_PACKMOV
+#define FPQ_Q_PACKMOV 1
+#endif
 __device__ __forceinline__ uint32_t codes_word(const u64* P) {
   uint32_t w = 0;
+#if FPQ_Q_PACKMOV
+  float a0, b0, a1, b1, a2, b2, a3, b3;
+  unpack2(P[0], a0, b0);
+  unpack2(P[1], a1, b1);
+  unpack2(P[2], a2, b2);
+  unpack2(P[3], a3, b3);
+  asm("{ .reg .b8 t0, t1, t2, t3;\n"
+      "  cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n"
+      "  cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n"
+      "  cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n"
+      "  cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n"
+      "  mov.b32 %0, {t0, t1, t2, t3}; }"
+      : "=r"(w)
+      : "f"(a0), "f"(b0), "f"(a1), "f"(b1), "f"(a2), "f"(b2), "f"(a3), "f"(b3));
+#else
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     float a, b;
@@ -316,6 +326,7 @@ __device__ __forceinline__ uint32_t codes_word(const u64* P) {
         : "f"(b), "f"(a));
     w |= byte << (8 * j);
   }
+#endif
   return patch_zero_codes(w);
 }
 

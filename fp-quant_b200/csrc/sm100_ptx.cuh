@@ -55,6 +55,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait without a suspend-time hint: the thread keeps polling (lowest wake-up latency).
+__device__ __forceinline__ bool mbar_try_wait_spin(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Same contract as mbar_wait_bounded, for the latency-critical waits of an MMA-issuing thread.
+__device__ __forceinline__ bool mbar_wait_bounded_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                       long long limit_cycles = 2000000000LL) {
+  if (mbar_try_wait_spin(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (!mbar_try_wait_spin(bar, parity)) {
+    if ((++polls & 63u) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - t0 > limit_cycles) return false;
+    }
+  }
+  return true;
+}
+
 // Waits for the phase with the given parity to complete.  Gives up (returns false) after
 // about `limit_cycles` SM cycles or as soon as *abort_flag becomes non-zero.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
