@@ -61,7 +61,7 @@ struct PairParams {
 
 template <bool NVFP4>
 struct PairSmem {
-  static constexpr int STAGES = NVFP4 ? 5 : 6;
+  static constexpr int STAGES = 5;
   static constexpr int SFBLK = NVFP4 ? 4 : 2;                 // 512-byte scale tiles per 128 rows per stage
   static constexpr int SFA_COLS = 4 * SFBLK;                  // tensor-memory columns of one stage's A scales
   static constexpr int SF_TMEM_BUF = 12 * SFBLK;              // A scales + B scales (256 rows) of one stage
@@ -75,8 +75,10 @@ struct PairSmem {
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
+  static constexpr int OFF_OUT = OFF_SFB + STAGES * SFB_BYTES;  // eight 32-row x 128-byte staging boxes (epilogue)
+  static constexpr int OUT_BOX_BYTES = 32 * 128;
   // full[S], empty[S], sf_full[S], acc_full, acc_empty
-  static constexpr int OFF_BAR = OFF_SFB + STAGES * SFB_BYTES;
+  static constexpr int OFF_BAR = OFF_OUT + 8 * OUT_BOX_BYTES;
   static constexpr int OFF_MISC = OFF_BAR + (3 * STAGES + 2) * 8;
   static constexpr int TOTAL = OFF_MISC + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
@@ -101,7 +103,7 @@ template <bool NVFP4, bool PROF>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                     const PairParams p) {
+                     const __grid_constant__ CUtensorMap tmap_out, const PairParams p) {
   using L = PairSmem<NVFP4>;
   constexpr int STAGES = L::STAGES;
   constexpr int SFBLK = L::SFBLK;
@@ -134,6 +136,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     prefetch_tensormap(&tmap_b);
     prefetch_tensormap(&tmap_sfa);
     prefetch_tensormap(&tmap_sfb);
+    prefetch_tensormap(&tmap_out);
   }
   if (warp == 1) {
     tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_base_slot)), TMEM_COLS);
@@ -331,52 +334,74 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       long long t1 = tick<PROF>();
       e_wait += t1 - t0;
       tc_fence_after();
-      const int row = m_pair * 256 + (int)rank * BM_CTA + quarter * 32 + lane;
-      __nv_bfloat16* orow = p.out + (size_t)row * p.N;
-      // 1) drain this warp's 128 fp32 columns into registers (four loads in flight, one wait)
-      uint32_t r0[32], r1[32], r2[32], r3[32];
+      // 1) drain this warp's 128 fp32 columns in two halves of 64 (two 32-column loads in flight each);
+      //    the first half is packed to bf16 pairs (x alpha, + bias) while still holding the accumulator,
+      //    which frees the registers for the second half
+      const int row0 = m_pair * 256 + (int)rank * BM_CTA + quarter * 32;
+      const int col_w = n_blk * BN + col_half * 128;           // first of my 128 columns
+      uint32_t pk[64];
       const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + col_half * 128;
-      tc_ld_32x32b_x32(tsrc, r0);
-      tc_ld_32x32b_x32(tsrc + 32, r1);
-      tc_ld_32x32b_x32(tsrc + 64, r2);
-      tc_ld_32x32b_x32(tsrc + 96, r3);
+      auto pack_half = [&](int half, const uint32_t (&ra)[32], const uint32_t (&rb)[32]) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const uint32_t* rr = j < 16 ? ra : rb;
+          float v0 = __uint_as_float(rr[(2 * j) & 31]) * alpha;
+          float v1 = __uint_as_float(rr[(2 * j + 1) & 31]) * alpha;
+          if (p.bias) {
+            const int col = col_w + half * 64 + 2 * j;
+            if (col < p.N) {
+              v0 += __bfloat162float(p.bias[col]);
+              v1 += __bfloat162float(p.bias[col + 1]);
+            }
+          }
+          __nv_bfloat162 hh = __floats2bfloat162_rn(v0, v1);
+          pk[half * 32 + j] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+      };
+      {
+        uint32_t ra[32], rb[32];
+        tc_ld_32x32b_x32(tsrc, ra);
+        tc_ld_32x32b_x32(tsrc + 32, rb);
+        tc_wait_ld();
+        pack_half(0, ra, rb);
+      }
+      uint32_t rc[32], rd[32];
+      tc_ld_32x32b_x32(tsrc + 64, rc);
+      tc_ld_32x32b_x32(tsrc + 96, rd);
       tc_wait_ld();
       e_ld0 += tick<PROF>() - t1;
-      // 2) hand the accumulator back: the next tile's MMAs may start while we convert and store
+      // 2) hand the accumulator back: the next tile's MMAs may start while we convert and write out
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
       long long t2 = tick<PROF>();
       e_drain += t2 - t1;
-      // 3) scale, round to bf16, write out (N is a multiple of 8: a 16-byte group is all in or all out)
-      if (row < p.M) {
+      pack_half(1, rc, rd);
+      // 3) write out through shared memory: each warp owns a 32-row x 128-byte staging box (128-byte
+      //    swizzle, so the 16-byte row pieces of the 32 lanes spread over all banks) and sends it with
+      //    one TMA store per 64 columns; the store clips rows >= M and columns >= N.  Direct 16-byte
+      //    stores from 32 different rows per instruction kept the load/store path busy for ~7000
+      //    cycles per tile and slowed the MMA issue in that time.
+      const uint32_t stage_out = sbase + L::OFF_OUT + (uint32_t)(col_half * 4 + quarter) * L::OUT_BOX_BYTES;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t* rc = c == 0 ? r0 : c == 1 ? r1 : c == 2 ? r2 : r3;
-          const int col0 = n_blk * BN + col_half * 128 + c * 32;
+      for (int h = 0; h < 2; ++h) {
+        if (lane == 0) bulk_wait_group_read0();      // the previous store has read the box
+        __syncwarp();
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int col = col0 + q * 8;
-            if (col < p.N) {
-              uint32_t w[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float v0 = __uint_as_float(rc[q * 8 + 2 * j]) * alpha;
-                float v1 = __uint_as_float(rc[q * 8 + 2 * j + 1]) * alpha;
-                if (p.bias) {
-                  v0 += __bfloat162float(p.bias[col + 2 * j]);
-                  v1 += __bfloat162float(p.bias[col + 2 * j + 1]);
-                }
-                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-                w[j] = *reinterpret_cast<uint32_t*>(&h);
-              }
-              *reinterpret_cast<uint4*>(orow + col) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          }
+        for (int q = 0; q < 8; ++q)
+          st_shared_v4(stage_out + (uint32_t)lane * 128u + (uint32_t)((q ^ (lane & 7)) * 16), pk[h * 32 + 4 * q],
+                       pk[h * 32 + 4 * q + 1], pk[h * 32 + 4 * q + 2], pk[h * 32 + 4 * q + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        const int colh = col_w + h * 64;
+        if (lane == 0 && row0 < p.M && colh < p.N) {
+          tma_store_2d(&tmap_out, stage_out, colh, row0);
+          bulk_commit_group();
         }
       }
       e_store += tick<PROF>() - t2;
     }
+    if (lane == 0) bulk_wait_group0();   // my stores are complete before the CTA may exit
     if (PROF && p.profile && warp == 2 && lane == 0) {
       long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
       o[10] = e_wait; o[11] = e_drain; o[12] = e_store; o[13] = e_ld0;
@@ -399,7 +424,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
 template <bool NVFP4>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
-                PairParams p, cudaStream_t stream) {
+                const CUtensorMap& tout, PairParams p, cudaStream_t stream) {
   using L = PairSmem<NVFP4>;
   auto kern = p.profile ? gemm_fp4_pair_kernel<NVFP4, true> : gemm_fp4_pair_kernel<NVFP4, false>;
   static bool configured[64] = {};
@@ -424,7 +449,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, p));
+  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, tout, p));
   return FPQ_OK;
 }
 
@@ -457,15 +482,17 @@ int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const 
   const char* e = getenv("FPQ_GEMM_RASTER");
   p.raster_group = e ? atoi(e) : 8;
   if (p.raster_group < 1) p.raster_group = 1;
-  CUtensorMap ta, tb, tsa, tsb;
+  CUtensorMap ta, tb, tsa, tsb, tout;
+  // output as 64-column x 32-row boxes of bf16 (128 bytes per box row, 128-byte swizzle)
+  if (int rc = make_tensor_map_2d(&tout, out, 2, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 32, 1)) return rc;
   if (int rc = make_tensor_map_2d(&ta, a, 1, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, BK_BYTES, BM_CTA, 1)) return rc;
   if (int rc = make_tensor_map_2d(&tb, b, 1, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BK_BYTES, BN_CTA, 1)) return rc;
   const uint64_t sf_row_words = (uint64_t)p.sf_blocks_k * 64;      // 8-byte words per 128-row block
   const uint64_t a_blocks = (uint64_t)((M + 127) / 128), b_blocks = (uint64_t)((N + 127) / 128);
   if (int rc = make_tensor_map_2d_u64(&tsa, sfa, sf_row_words, a_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 1)) return rc;
   if (int rc = make_tensor_map_2d_u64(&tsb, sfb, sf_row_words, b_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 2)) return rc;
-  return format == FPQ_FMT_NVFP4 ? launch_pair<true>(ta, tb, tsa, tsb, p, stream)
-                                 : launch_pair<false>(ta, tb, tsa, tsb, p, stream);
+  return format == FPQ_FMT_NVFP4 ? launch_pair<true>(ta, tb, tsa, tsb, tout, p, stream)
+                                 : launch_pair<false>(ta, tb, tsa, tsb, tout, p, stream);
 }
 
 }  // namespace fpq
