@@ -190,95 +190,105 @@ int tri_inverse_recursive(const float* L, float* X, float* scratch, int64_t d, i
 }
 
 // ------------------------------------------------------------------ GPTQ column block
-// One thread per weight row.  The thread keeps its 128 columns of the block in registers, walks
-// them left to right: quantise column i with the row's static group scale, turn the residual into
-// err = (w - wq) / U[i,i] and subtract err * U[i, j] from the columns j > i of the block
-// (src/quantization/gptq.py:166-186).  U's diagonal block sits in shared memory and is read by
-// all threads at the same address (broadcast).  Afterwards the registers hold the errors, which go
-// to Err[rows, 128] for the trailing update, and the dequantised values are rebuilt as
-// grid(code) * scale, exactly as they were computed.
-constexpr int SUB = 32;   // columns held in registers at a time
-
-// Columns [SUB*B, SUB*B + SUB) of the 128-column block for one row: bring them up to date with the
-// errors of the earlier columns of the block (same order as the reference applies them), then walk
-// them left to right.
-template <int G, int B>
-__device__ __forceinline__ void gptq_sub_block(float (&err)[NB], uint32_t (&cw)[NB / 8], const float (&sc)[NB / G],
-                                               const float* __restrict__ Us, const float* __restrict__ wrow) {
-  float w[SUB];
-  const float4* wp = reinterpret_cast<const float4*>(wrow + SUB * B);
-#pragma unroll
-  for (int q = 0; q < SUB / 4; ++q) {
-    const float4 v = wp[q];
-    w[4 * q] = v.x; w[4 * q + 1] = v.y; w[4 * q + 2] = v.z; w[4 * q + 3] = v.w;
-  }
-#pragma unroll
-  for (int i = 0; i < SUB * B; ++i) {
-    const float e = err[i];
-#pragma unroll
-    for (int j = 0; j < SUB; ++j) w[j] = fmaf(-e, Us[i * NB + SUB * B + j], w[j]);
-  }
-#pragma unroll
-  for (int i = 0; i < SUB; ++i) {
-    const int col = SUB * B + i;
-    const float s = sc[col / G];
-    const uint32_t code = e2m1_code(__fdiv_rn(w[i], s));
-    cw[col / 8] |= code << (4 * (col % 8));
-    const float wq = __fmul_rn(e2m1_value(code), s);
-    const float e = __fdiv_rn(__fsub_rn(w[i], wq), Us[col * NB + col]);
-#pragma unroll
-    for (int j = i + 1; j < SUB; ++j) w[j] = fmaf(-e, Us[col * NB + SUB * B + j], w[j]);
-    err[col] = e;
-  }
-}
+// Four threads per weight row, each holding 32 of the block's 128 columns in registers.  Columns are
+// walked left to right: the owner of column i quantises it with the row's static group scale and
+// turns the residual into err = (w - wq) / U[i,i]; the error is broadcast inside the quad and every
+// thread subtracts err * U[i, j] from its columns j > i (src/quantization/gptq.py:166-186), in the
+// same order as the reference applies them.  U's diagonal block sits in shared memory; a quad reads
+// four 16-byte pieces of one row per load.  The outer loop over the four 32-column owners is a real
+// loop (the unrolled body of 32 steps stays inside the instruction cache: a fully unrolled
+// thread-per-row version was instruction-fetch bound at three warps per SM).  Afterwards each thread
+// writes its 32 errors to Err[rows, 128] for the trailing update, the dequantised values, rebuilt
+// as grid(code) * scale exactly as they were computed, and its 16 code bytes.
+constexpr int SUB = 32;   // columns per thread
+// Shared-memory image of U's diagonal block: every 32-column piece of a row is shifted by another
+// 16 bytes, so that the four pieces a quad reads with one 128-bit load start in different banks.
+constexpr int US_LD = NB + 4 * (NB / SUB);
+__device__ __forceinline__ int us_col(int col) { return col + 4 * (col / SUB); }
 
 template <int G>
-__global__ void __launch_bounds__(128, 1) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C, int64_t c1,
-                                                            const float* __restrict__ scales,
-                                                            const float* __restrict__ U, float* __restrict__ Err,
-                                                            uint8_t* __restrict__ codes) {
-  extern __shared__ float Us[];   // NB x NB, row-major
+__global__ void __launch_bounds__(128) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C, int64_t c1,
+                                                         const float* __restrict__ scales,
+                                                         const float* __restrict__ U, float* __restrict__ Err,
+                                                         uint8_t* __restrict__ codes) {
+  extern __shared__ float Us[];   // NB rows of US_LD floats
   for (int idx = threadIdx.x; idx < NB * NB / 4; idx += blockDim.x) {
     const int i = (idx * 4) / NB, j = (idx * 4) % NB;
-    *reinterpret_cast<float4*>(&Us[i * NB + j]) = *reinterpret_cast<const float4*>(&U[(c1 + i) * C + c1 + j]);
+    *reinterpret_cast<float4*>(&Us[i * US_LD + us_col(j)]) = *reinterpret_cast<const float4*>(&U[(c1 + i) * C + c1 + j]);
   }
   __syncthreads();
-  const int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int q = lane & 3;                      // which 32 columns of the block are mine
+  int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 2;
+  const bool live = row < rows;
+  if (!live) row = rows - 1;                   // keep the quad's shuffles uniform; nothing is stored
 
-  constexpr int NGRP = NB / G;
+  constexpr int NGRP = SUB / G;
   float sc[NGRP];
 #pragma unroll
-  for (int g = 0; g < NGRP; ++g) sc[g] = scales[row * (C / G) + c1 / G + g];
-  uint32_t cw[NB / 8];
+  for (int g = 0; g < NGRP; ++g) sc[g] = scales[row * (C / G) + (c1 + SUB * q) / G + g];
+  float w[SUB], err[SUB];
+  {
+    const float4* wp = reinterpret_cast<const float4*>(W + row * C + c1 + SUB * q);
 #pragma unroll
-  for (int q = 0; q < NB / 8; ++q) cw[q] = 0;
-  float err[NB];
-  const float* wrow = W + row * C + c1;
-  gptq_sub_block<G, 0>(err, cw, sc, Us, wrow);
-  gptq_sub_block<G, 1>(err, cw, sc, Us, wrow);
-  gptq_sub_block<G, 2>(err, cw, sc, Us, wrow);
-  gptq_sub_block<G, 3>(err, cw, sc, Us, wrow);
+    for (int v = 0; v < SUB / 4; ++v) {
+      const float4 t = wp[v];
+      w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+    }
+  }
+  uint32_t cw[SUB / 8];
+#pragma unroll
+  for (int v = 0; v < SUB / 8; ++v) cw[v] = 0;
+#pragma unroll
+  for (int j = 0; j < SUB; ++j) err[j] = 0.0f;
 
-  float4* ep = reinterpret_cast<float4*>(Err + row * NB);
+#pragma unroll 1
+  for (int b = 0; b < NB / SUB; ++b) {
+    const bool owner = q == b;
+    const float* Ub = Us + (SUB * b) * US_LD;  // rows of U for the owner's columns
 #pragma unroll
-  for (int q = 0; q < NB / 4; ++q) ep[q] = make_float4(err[4 * q], err[4 * q + 1], err[4 * q + 2], err[4 * q + 3]);
-  float4* op = reinterpret_cast<float4*>(W + row * C + c1);
+    for (int ii = 0; ii < SUB; ++ii) {
+      float e = 0.0f;
+      if (owner) {
+        const float s = sc[ii / G];
+        const uint32_t code = e2m1_code(__fdiv_rn(w[ii], s));
+        cw[ii / 8] |= code << (4 * (ii % 8));
+        const float wq = __fmul_rn(e2m1_value(code), s);
+        e = __fdiv_rn(__fsub_rn(w[ii], wq), Ub[ii * US_LD + (SUB + 4) * b + ii]);
+        err[ii] = e;
+      }
+      e = __shfl_sync(0xffffffffu, e, (lane & ~3) | b);
+      const float e_ge = q >= b ? -e : 0.0f;   // applies to my columns right of ii when I am the owner or later
+      const float e_gt = q > b ? -e : 0.0f;    // applies to all my columns only when I come after the owner
+      const float4* up = reinterpret_cast<const float4*>(Ub + ii * US_LD + (SUB + 4) * q);
 #pragma unroll
-  for (int q = 0; q < NB / 4; ++q) {
+      for (int v = 0; v < SUB / 4; ++v) {
+        const float4 u = up[v];
+        w[4 * v] = fmaf(4 * v > ii ? e_ge : e_gt, u.x, w[4 * v]);
+        w[4 * v + 1] = fmaf(4 * v + 1 > ii ? e_ge : e_gt, u.y, w[4 * v + 1]);
+        w[4 * v + 2] = fmaf(4 * v + 2 > ii ? e_ge : e_gt, u.z, w[4 * v + 2]);
+        w[4 * v + 3] = fmaf(4 * v + 3 > ii ? e_ge : e_gt, u.w, w[4 * v + 3]);
+      }
+    }
+  }
+  if (!live) return;
+
+  float4* ep = reinterpret_cast<float4*>(Err + row * NB + SUB * q);
+#pragma unroll
+  for (int v = 0; v < SUB / 4; ++v) ep[v] = make_float4(err[4 * v], err[4 * v + 1], err[4 * v + 2], err[4 * v + 3]);
+  float4* op = reinterpret_cast<float4*>(W + row * C + c1 + SUB * q);
+#pragma unroll
+  for (int v = 0; v < SUB / 4; ++v) {
     float o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int i = 4 * q + j;
+      const int i = 4 * v + j;
       o[j] = __fmul_rn(e2m1_value((cw[i / 8] >> (4 * (i % 8))) & 15u), sc[i / G]);
     }
-    op[q] = make_float4(o[0], o[1], o[2], o[3]);
+    op[v] = make_float4(o[0], o[1], o[2], o[3]);
   }
-  if (codes) {
-    uint4* cp = reinterpret_cast<uint4*>(codes + row * (C / 2) + c1 / 2);
-#pragma unroll
-    for (int q = 0; q < NB / 32; ++q) cp[q] = make_uint4(cw[4 * q], cw[4 * q + 1], cw[4 * q + 2], cw[4 * q + 3]);
-  }
+  if (codes)
+    *reinterpret_cast<uint4*>(codes + row * (C / 2) + (c1 + SUB * q) / 2) = make_uint4(cw[0], cw[1], cw[2], cw[3]);
 }
 
 __global__ void diff_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int64_t n) {
@@ -313,8 +323,53 @@ __global__ void ratio_kernel(const double* acc, float* out, double count) {
   out[0] = (float)((acc[0] / count) / (acc[1] / count + 1e-6));
 }
 
+// x in fp32 -> three bf16 terms hi + mid + lo that together carry all 24 mantissa bits.
+__device__ __forceinline__ void split3(float v, __nv_bfloat16& h, __nv_bfloat16& m, __nv_bfloat16& l) {
+  h = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(h);
+  m = __float2bfloat16_rn(r1);
+  l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+}
+
+// out is three planes of n elements: hi, mid, lo
+__global__ void split3_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    __nv_bfloat16 h, m, l;
+    split3(x[i], h, m, l);
+    out[i] = h; out[n + i] = m; out[2 * n + i] = l;
+  }
+}
+
+// Err [rows, 128] fp32 -> ErrT3 [3 * 128, lda] bf16: plane s, row k, column r holds term s of Err[r, k].
+__global__ void __launch_bounds__(256) err_transpose_split_kernel(const float* __restrict__ Err, int64_t rows, int64_t lda,
+                                                                  __nv_bfloat16* __restrict__ out) {
+  __shared__ float tile[32][NB + 1];
+  const int64_t r0 = (int64_t)blockIdx.x * 32;
+  for (int idx = threadIdx.x; idx < 32 * NB; idx += 256) {
+    const int r = idx / NB, k = idx % NB;
+    tile[r][k] = r0 + r < rows ? Err[(r0 + r) * NB + k] : 0.0f;
+  }
+  __syncthreads();
+  const int r = threadIdx.x & 31;
+  for (int k = threadIdx.x >> 5; k < NB; k += 8) {
+    __nv_bfloat16 h, m, l;
+    split3(tile[r][k], h, m, l);
+    if (r0 + r < lda) {
+      out[(int64_t)k * lda + r0 + r] = h;
+      out[(int64_t)(NB + k) * lda + r0 + r] = m;
+      out[(int64_t)(2 * NB + k) * lda + r0 + r] = l;
+    }
+  }
+}
+
 }  // namespace
 }  // namespace fpq
+
+namespace fpq {
+int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A, int64_t lda, int64_t a_rows,
+                  const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, int64_t T, bool symmetric, const int* a_y,
+                  const int* b_y, int n_table, float alpha, float beta, int32_t* error_flag, cudaStream_t stream);
+}
 
 using namespace fpq;
 
@@ -414,38 +469,70 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
   return FPQ_OK;
 }
 
+namespace {
+int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
+int64_t gptq_lda(int64_t rows) { return (rows + 63) & ~(int64_t)63; }
+}  // namespace
+
+extern "C" int64_t fpq_gptq_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return align256(rows * NB * (int64_t)sizeof(float)) + align256(3 * NB * gptq_lda(rows) * 2) + align256(3 * cols * cols * 2);
+}
+
 extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const float* scales, int group,
-                                 const float* U, uint8_t* codes, float* err_workspace, fpq_stream_t stream) {
-  FPQ_CHECK_ARG(W && scales && U && err_workspace, "NULL pointer");
+                                 const float* U, uint8_t* codes, void* workspace, int32_t* error_flag,
+                                 fpq_stream_t stream) {
+  FPQ_CHECK_ARG(W && scales && U && workspace && error_flag, "NULL pointer");
   FPQ_CHECK_ARG(group == 16 || group == 32, "group must be 16 (NVFP4) or 32 (MXFP4)");
   FPQ_CHECK_ARG(rows > 0 && cols > 0 && cols % NB == 0, "cols (%lld) must be a multiple of %d", (long long)cols, NB);
-  FPQ_CHECK_ARG(((uintptr_t)W & 15) == 0 && ((uintptr_t)U & 15) == 0 && ((uintptr_t)err_workspace & 15) == 0 &&
-                    ((uintptr_t)codes & 15) == 0, "pointers must be 16-byte aligned");
+  FPQ_CHECK_ARG(rows < (1ll << 30) && 3 * cols < (1ll << 31), "shape too large");
+  FPQ_CHECK_ARG(((uintptr_t)W & 15) == 0 && ((uintptr_t)U & 15) == 0 && ((uintptr_t)workspace & 255) == 0 &&
+                    ((uintptr_t)codes & 15) == 0, "W, U, codes must be 16-byte aligned, the workspace 256-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
   static bool configured[64] = {};
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
-  const int smem = NB * NB * (int)sizeof(float);
+  const int smem = NB * US_LD * (int)sizeof(float);
   if (dev < 64 && !configured[dev]) {
     FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev] = true;
   }
-  const unsigned grid = (unsigned)((rows + 127) / 128);
+  // workspace: block errors (fp32) | their transposed three-term bf16 split | three-term bf16 split of U
+  const int64_t lda = gptq_lda(rows);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  float* err = reinterpret_cast<float*>(ws);
+  __nv_bfloat16* errT3 = reinterpret_cast<__nv_bfloat16*>(ws + align256(rows * NB * (int64_t)sizeof(float)));
+  __nv_bfloat16* U3 = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(errT3) + align256(3 * NB * lda * 2));
+  if (cols > NB) {
+    split3_bf16_kernel<<<grid1d(cols * cols), 256, 0, st>>>(U, U3, cols * cols);
+    FPQ_CHECK_LAUNCH();
+  }
+  // The trailing update W[:, c2:] -= Err U[c1:c2, c2:] runs on the tensor cores: both factors are split
+  // into three bf16 terms and the six leading cross products (hi*hi, hi*mid, mid*hi, hi*lo, lo*hi,
+  // mid*mid; the dropped ones are below 2^-24 relative) are accumulated in fp32 as one GEMM whose K
+  // dimension is the concatenation of the six 128-row slabs.
+  static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
+  const unsigned grid = (unsigned)((rows * 4 + 127) / 128);   // four threads per row
   for (int64_t c1 = 0; c1 < cols; c1 += NB) {
     if (group == 16)
-      gptq_block_kernel<16><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err_workspace, codes);
+      gptq_block_kernel<16><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
     else
-      gptq_block_kernel<32><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err_workspace, codes);
+      gptq_block_kernel<32><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
     FPQ_CHECK_LAUNCH();
     const int64_t c2 = c1 + NB;
     if (c2 >= cols) break;
-    SgemmArgs a{};   // W[:, c2:] -= Err * U[c1:c2, c2:]
-    a.A = err_workspace; a.lda = NB;
-    a.B = U + c1 * cols + c2; a.ldb = cols;
-    a.C = W + c2; a.ldc = cols;
-    a.M = (int)rows; a.N = (int)(cols - c2); a.K = NB; a.alpha = -1.0f; a.beta = 1.0f;
-    if (int rc = sgemm(a, false, SGEMM_PLAIN, st)) return rc;
+    err_transpose_split_kernel<<<(unsigned)((lda + 31) / 32), 256, 0, st>>>(err, rows, lda, errT3);
+    FPQ_CHECK_LAUNCH();
+    int a_y[12], b_y[12];
+    for (int t = 0; t < 6; ++t)
+      for (int kk = 0; kk < 2; ++kk) {
+        a_y[2 * t + kk] = pa[t] * NB + kk * 64;
+        b_y[2 * t + kk] = (int)(pb[t] * cols + c1 + kk * 64);
+      }
+    if (int rc = gemm_atb_bf16(W + c2, cols, rows, cols - c2, errT3, lda, 3 * NB, U3, cols, 3 * cols, c2, 0, false, a_y, b_y,
+                               12, -1.0f, 1.0f, error_flag, st))
+      return rc;
   }
   return FPQ_OK;
 }

@@ -32,13 +32,18 @@ constexpr int STAGES = 4;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;       // two 256-column accumulators
 
+constexpr int MAX_K_TABLE = 16;
+
 struct HessParams {
-  int64_t T, d;
-  int num_blocks;      // ceil(d / 128)
-  int num_blocks_n;    // ceil(d / 256)
+  int64_t d1, d2, ldc;  // output rows (A's width), columns (B's width), row stride of the output
+  int num_blocks;      // ceil(d1 / 128)
+  int num_blocks_n;    // ceil(d2 / 256)
   int num_tiles;
-  int num_k_stages;    // ceil(T / 64)
+  int num_k_stages;    // ceil(T / 64), or the number of table entries
   int symmetric;
+  int use_table;       // token rows of stage ks come from a_y[ks] / b_y[ks] instead of ks * 64
+  int b_x0;            // first column of B (added to the TMA x coordinate)
+  int a_y[MAX_K_TABLE], b_y[MAX_K_TABLE];
   float alpha, beta;
   float* H;
   int* error_flag;
@@ -136,12 +141,14 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           mbar_arrive_expect_tx(bar_full + 8 * s, (A_BOXES + B_BOXES) * BOX_BYTES);
           const uint32_t a_dst = sbase + Smem::OFF_A + s * A_BOXES * BOX_BYTES;
           const uint32_t b_dst = sbase + Smem::OFF_B + s * B_BOXES * BOX_BYTES;
+          const int ya = p.use_table ? p.a_y[ks] : ks * BK;
+          const int yb = p.use_table ? p.b_y[ks] : ks * BK;
 #pragma unroll
           for (int b = 0; b < A_BOXES; ++b)
-            tma_load_2d(a_dst + b * BOX_BYTES, &tmap_a, ib * TILE + 64 * b, ks * BK, bar_full + 8 * s);
+            tma_load_2d(a_dst + b * BOX_BYTES, &tmap_a, ib * TILE + 64 * b, ya, bar_full + 8 * s);
 #pragma unroll
           for (int b = 0; b < B_BOXES; ++b)
-            tma_load_2d(b_dst + b * BOX_BYTES, &tmap_b, jb * TILE_N + 64 * b, ks * BK, bar_full + 8 * s);
+            tma_load_2d(b_dst + b * BOX_BYTES, &tmap_b, p.b_x0 + jb * TILE_N + 64 * b, yb, bar_full + 8 * s);
         }
       }
       if (!ok) {
@@ -197,14 +204,14 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int c = 0; c < TILE_N / 32; ++c) {
         const int64_t j0 = (int64_t)jb * TILE_N + c * 32;
         const int jblock = (int)(j0 / TILE);                 // 128-column block of this chunk
-        if (j0 >= p.d || (p.symmetric && jblock > ib)) break;   // beyond the matrix / above the diagonal
+        if (j0 >= p.d2 || (p.symmetric && jblock > ib)) break;   // beyond the matrix / above the diagonal
         const bool mirror = p.symmetric && jblock < ib;
         uint32_t r[32];
         tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE_N + c * 32, r);
         tc_wait_ld();
-        if (i < p.d) {
-          float* hrow = p.H + i * p.d + j0;
-          if (j0 + 32 <= p.d && (p.d & 3) == 0) {
+        if (i < p.d1) {
+          float* hrow = p.H + i * p.ldc + j0;
+          if (j0 + 32 <= p.d2 && (p.ldc & 3) == 0) {
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               float4 h = p.beta == 0.0f ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<float4*>(hrow)[q];
@@ -219,7 +226,7 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           } else {
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj) {
-              if (j0 + jj < p.d) {
+              if (j0 + jj < p.d2) {
                 const float old = p.beta == 0.0f ? 0.0f : hrow[jj];
                 const float v = fmaf(p.beta, old, p.alpha * __uint_as_float(r[jj]));
                 hrow[jj] = v;
@@ -231,7 +238,7 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             // H[j, i]: consecutive lanes hold consecutive i, so each store instruction is coalesced
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj)
-              if (j0 + jj < p.d) p.H[(j0 + jj) * p.d + i] = __uint_as_float(r[jj]);
+              if (j0 + jj < p.d2) p.H[(j0 + jj) * p.ldc + i] = __uint_as_float(r[jj]);
           }
         }
       }
@@ -257,6 +264,53 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 }  // namespace
 }  // namespace fpq
 
+namespace fpq {
+
+// out[d1, d2] (row stride ldc) = beta * out + alpha * A^T B with A [T, d1] and B [T, d2] bf16 row-major
+// (row strides lda, ldb in elements; B starts at column b_x0 of its matrix).  With `table` the K
+// dimension is the concatenation of n_table 64-row slabs whose first rows are a_y[i] / b_y[i].
+int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A, int64_t lda, int64_t a_rows,
+                  const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, int64_t T, bool symmetric, const int* a_y,
+                  const int* b_y, int n_table, float alpha, float beta, int32_t* error_flag, cudaStream_t stream) {
+  HessParams p{};
+  p.d1 = d1; p.d2 = d2; p.ldc = ldc;
+  p.num_blocks = (int)((d1 + TILE - 1) / TILE);
+  p.num_blocks_n = (int)((d2 + TILE_N - 1) / TILE_N);
+  p.num_tiles = symmetric ? tiles_before_row(p.num_blocks) : p.num_blocks * p.num_blocks_n;
+  p.symmetric = symmetric ? 1 : 0;
+  p.b_x0 = (int)b_x0;
+  if (n_table > 0) {
+    if (n_table > MAX_K_TABLE) {
+      set_error("K table too long (%d)", n_table);
+      return FPQ_ERR_INVALID_ARGUMENT;
+    }
+    p.use_table = 1;
+    p.num_k_stages = n_table;
+    for (int i = 0; i < n_table; ++i) { p.a_y[i] = a_y[i]; p.b_y[i] = b_y[i]; }
+  } else {
+    p.num_k_stages = (int)((T + BK - 1) / BK);
+  }
+  p.alpha = alpha; p.beta = beta; p.H = out; p.error_flag = error_flag;
+  CUtensorMap ta, tb;
+  if (int rc = make_tensor_map_2d(&ta, A, 2, (uint64_t)lda, (uint64_t)a_rows, (uint64_t)lda * 2, 64, BK, 1)) return rc;
+  if (int rc = make_tensor_map_2d(&tb, B, 2, (uint64_t)ldb, (uint64_t)b_rows, (uint64_t)ldb * 2, 64, BK, 1)) return rc;
+  static bool configured[64] = {};
+  int dev = 0;
+  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(hessian_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::DYN_BYTES));
+    configured[dev] = true;
+  }
+  int grid = sm_count();
+  if (grid > p.num_tiles) grid = p.num_tiles;
+  if (grid < 1) return FPQ_OK;
+  hessian_kernel<<<grid, NUM_THREADS, Smem::DYN_BYTES, stream>>>(ta, tb, p);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
+}  // namespace fpq
+
 using namespace fpq;
 
 extern "C" int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, const void* xb_bf16, int64_t tokens,
@@ -268,28 +322,6 @@ extern "C" int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, 
                 "pointers must be 16-byte aligned");
   if (tokens == 0) return FPQ_OK;
   const bool symmetric = xb_bf16 == nullptr || xb_bf16 == xa_bf16;
-  HessParams p{};
-  p.T = tokens; p.d = d;
-  p.num_blocks = (int)((d + TILE - 1) / TILE);
-  p.num_blocks_n = (int)((d + TILE_N - 1) / TILE_N);
-  p.num_tiles = symmetric ? tiles_before_row(p.num_blocks) : p.num_blocks * p.num_blocks_n;
-  p.num_k_stages = (int)((tokens + BK - 1) / BK);
-  p.symmetric = symmetric ? 1 : 0;
-  p.alpha = alpha; p.beta = beta; p.H = H; p.error_flag = error_flag;
-  CUtensorMap ta, tb;
-  if (int rc = make_tensor_map_2d(&ta, xa_bf16, 2, (uint64_t)d, (uint64_t)tokens, (uint64_t)d * 2, 64, BK, 1)) return rc;
-  if (int rc = make_tensor_map_2d(&tb, symmetric ? xa_bf16 : xb_bf16, 2, (uint64_t)d, (uint64_t)tokens, (uint64_t)d * 2,
-                                  64, BK, 1)) return rc;
-  static bool configured[64] = {};
-  int dev = 0;
-  FPQ_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(hessian_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::DYN_BYTES));
-    configured[dev] = true;
-  }
-  int grid = sm_count();
-  if (grid > p.num_tiles) grid = p.num_tiles;
-  hessian_kernel<<<grid, NUM_THREADS, Smem::DYN_BYTES, (cudaStream_t)stream>>>(ta, tb, p);
-  FPQ_CHECK_LAUNCH();
-  return FPQ_OK;
+  return gemm_atb_bf16(H, d, d, d, xa_bf16, d, tokens, symmetric ? xa_bf16 : xb_bf16, d, tokens, 0, tokens, symmetric,
+                       nullptr, nullptr, 0, alpha, beta, error_flag, (cudaStream_t)stream);
 }

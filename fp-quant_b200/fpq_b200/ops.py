@@ -289,10 +289,10 @@ def gptq_quantize(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group:
     W, scales, U = _f32(W, "W", inplace=True), _f32(scales, "scales"), _f32(U, "U")
     rows, cols = W.shape
     codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=W.device) if want_codes else None
-    err = torch.empty(rows, 128, dtype=torch.float32, device=W.device)
+    ws = torch.empty(int(C.lib().fpq_gptq_workspace_bytes(rows, cols)), dtype=torch.uint8, device=W.device)
     with _guard(W.device):
         C.call("fpq_gptq_quantize", W.data_ptr(), rows, cols, scales.data_ptr(), group, U.data_ptr(), _ptr(codes),
-               err.data_ptr(), _stream(W))
+               ws.data_ptr(), device_error_flag(W.device).data_ptr(), _stream(W))
     return codes
 
 

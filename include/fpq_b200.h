@@ -221,10 +221,17 @@ int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, float* works
  * fp32 [rows, cols/group] are the static group scales computed beforehand from the unmodified
  * W (gptq.py:142); U from fpq_cholesky_inverse_upper; codes (optional) receives the packed E2M1
  * codes [rows, cols/2] (what pack_fp4_to_uint8(qweight) yields, gptq.py:429).
- * cols % 128 == 0; group 16 or 32; err_workspace: rows * 128 floats.
+ * cols % 128 == 0; group 16 or 32.  The update of the columns right of each 128-column block
+ * (gptq.py:186-187, an fp32 addmm in the reference) runs on the tensor cores as a three-term bf16
+ * split of both factors (fp32-level accuracy); workspace: fpq_gptq_workspace_bytes(rows, cols) bytes,
+ * 256-byte aligned; error_flag as for fpq_gemm_fp4.
  */
 int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const float* scales, int group,
-                      const float* U, uint8_t* codes, float* err_workspace, fpq_stream_t stream);
+                      const float* U, uint8_t* codes, void* workspace, int32_t* error_flag, fpq_stream_t stream);
+
+/* Bytes of workspace fpq_gptq_quantize needs for a [rows, cols] weight (sizing helper for the call above;
+ * the reference allocates its temporaries implicitly, gptq.py:159-187). */
+int64_t fpq_gptq_workspace_bytes(int64_t rows, int64_t cols);
 
 /*
  * get_relative_mse_error (src/quantization/gptq.py:28-30):
