@@ -153,12 +153,53 @@ def cpu_prepare(fmt, hgroup, m_sample):
     return xs, ws
 
 
+def cpu_gptq_sample(C, R, n_tokens, rows_sample=2048, tokens_sample=8192, hg=128):
+    """The reference algorithm for one MR-GPTQ layer on the host cores (the CPU restatement under oracle/), on a
+    bounded sample: `tokens_sample` calibration tokens for the Hessian and `rows_sample` weight rows for the column
+    loop; the Cholesky-inverse runs at full size.  Returns the per-layer estimate (each part scaled linearly to the
+    full token / row count) and the parts."""
+    from oracle import fp4, gptq as ogptq
+
+    g = torch.Generator().manual_seed(4)
+    W = fp4.fwht_butterfly(torch.randn(rows_sample, C, generator=g) * 0.02, hg)
+    z = torch.randn(tokens_sample, 64, generator=g)
+    a = torch.randn(64, C, generator=g) / 8
+    X = fp4.fwht_butterfly((z @ a + 0.1 * torch.randn(tokens_sample, C, generator=g)).bfloat16().float(), hg)
+    t0 = time.perf_counter()
+    H, _ = ogptq.hessian_update(None, 0, X.view(1, tokens_sample, C))
+    t1 = time.perf_counter()
+    Hd = ogptq.prepare_hessian(H, W, 0.01)
+    U, _ = ogptq.cholesky_inverse_upper(Hd)
+    t2 = time.perf_counter()
+    gs = fp4.nvfp4_global_scale(W.abs().max())
+    _, scales = fp4.nvfp4_scales(W, gs)
+    ogptq.gptq_column_loop(W, scales, U, 16)
+    t3 = time.perf_counter()
+    parts = {"hessian": (t1 - t0) * n_tokens / tokens_sample, "cholesky": t2 - t1, "loop": (t3 - t2) * R / rows_sample}
+    return sum(parts.values()), parts
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
+    if args.workload == "gptq":
+        R, C, n_tok = args.gptq_rows, args.gptq_cols, 128 * 2048
+        sec, parts = cpu_gptq_sample(C, R, n_tok)
+        sample = "8192 of 262144 calibration tokens, 2048 of %d weight rows, full-size Cholesky; parts scaled linearly" % R
+        line = {
+            "impl": "reference", "metric": "mr_gptq_s_per_layer", "value": sec, "unit": "s/layer", "n_gpus": args.gpus,
+            "steps": 1, "warmup": 0, "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4) of one linear {R}x{C}, 128x2048 calibration tokens"},
+            "breakdown_s": parts,
+            "cpu_baseline": {"value": sec, "unit": "s/layer", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": sec, "unit": "s/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }
+        print(json.dumps(line), flush=True)
+        return
     fmt, hgroup = args.format, HADAMARD_GROUP[args.format]
     m_sample = args.cpu_rows
     xs, ws = cpu_prepare(fmt, hgroup, m_sample)
@@ -280,11 +321,17 @@ def run_ours(args):
         tot_fl = sum(2.0 * M * shapes[i][1] * shapes[i][0] for _, _, i in gemm_events)
         achieved = tot_fl / (tot_ms * 1e-3) / 1e12
         peak = 4.0 * peaks["bf16_tflops"]
-        roofline = {"kernel": "gemm_fp4_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
+        # DRAM traffic per launch: ncu saw 44.15 MB on the 8192 x 4096 x 4096 launch (93.85 MB algorithmic:
+        # operands that the quantise kernel just wrote are still in L2, part of the output still is when
+        # the kernel ends); scaled to the average launch of this run by its algorithmic bytes
+        alg = sum(M * shapes[i][0] / 2 + shapes[i][1] * shapes[i][0] / 2 + (M + shapes[i][1]) * shapes[i][0] / g
+                  + 2.0 * M * shapes[i][1] for _, _, i in gemm_events) / len(gemm_events)
+        roofline = {"kernel": "gemm_fp4_pair_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
                     "unit": "TFLOP/s", "frac": achieved / peak,
                     "peak_source": f"4 x bf16 cuBLAS burst ({peaks['source']}); no FP4 peak was measured on this pool",
                     "frac_of_nominal_9pf": achieved / NOMINAL_FP4_TFLOPS,
-                    "avg_launch_ms": tot_ms / len(gemm_events), "traffic": None}
+                    "avg_launch_ms": tot_ms / len(gemm_events), "traffic": alg * (44.148e6 / 93.847e6),
+                    "traffic_note": "bytes per launch, ncu dram read+write of the 8192x4096x4096 launch scaled by algorithmic bytes"}
     quant_roof = None
     if args.workload in ("linear", "quantize"):
         # time the quantise launches alone (same inputs, back to back; 0.4 GB of input per pass > L2)
@@ -305,26 +352,49 @@ def run_ours(args):
         quant_roof = {"kernel": "quant_kernel", "bound": "hbm", "achieved": qbytes / (qms * 1e-3) / 1e9,
                       "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                       "peak_source": f"copy bandwidth ({peaks['source']})",
-                      "frac_of_nominal_8tbs": qbytes / (qms * 1e-3) / 1e9 / NOMINAL_HBM_GBS, "traffic": None}
+                      "frac_of_nominal_8tbs": qbytes / (qms * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
+                      # ncu: 324.4 MB read+write on a [32768, 4096] launch whose algorithmic bytes are 339.7 MB
+                      "traffic": qbytes / len(shapes) * (324.366e6 / 339.739e6),
+                      "traffic_note": "bytes per launch, ncu dram read+write of a [32768,4096] launch scaled by elements"}
         if args.workload == "quantize":
             roofline = quant_roof
 
     # ---- end to end through FPQuantLinear.forward with host buffers
     e2e = None
     if args.workload == "linear":
+        # uploads, the layer calls and downloads run on three streams, so the two copy directions overlap
+        # each other and the kernels; every step still moves all inputs in and all outputs out
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
         def e2e_step():
+            cur = torch.cuda.current_stream(dev)
+            xds, ev_in = [], []
+            with torch.cuda.stream(s_in):
+                for i in range(len(layers)):
+                    xds.append(xs_host[i].to(dev, non_blocking=True))
+                    ev = torch.cuda.Event()
+                    ev.record(s_in)
+                    ev_in.append(ev)
             for i, layer in enumerate(layers):
-                xd = xs_host[i].to(dev, non_blocking=True)
-                y = layer(xd)
-                ys_host[i].copy_(y, non_blocking=True)
+                cur.wait_event(ev_in[i])
+                xds[i].record_stream(cur)
+                y = layer(xds[i])
+                ev = torch.cuda.Event()
+                ev.record(cur)
+                s_out.wait_event(ev)
+                y.record_stream(s_out)
+                with torch.cuda.stream(s_out):
+                    ys_host[i].copy_(y, non_blocking=True)
         for _ in range(max(1, min(args.warmup, 2))):
             e2e_step()
+        torch.cuda.current_stream(dev).wait_stream(s_out)
         barrier()
         s2, t2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         n2 = max(1, min(args.steps, 5))
         s2.record()
         for _ in range(n2):
             e2e_step()
+        torch.cuda.current_stream(dev).wait_stream(s_out)   # the last downloads end inside the timed region
         t2.record()
         barrier()
         ms2 = s2.elapsed_time(t2)
@@ -464,6 +534,13 @@ def run_gptq(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        torch.set_num_threads(threads)
+        csec, cparts = cpu_gptq_sample(C, R, n_seq * T)
+        cpu = {"value": csec, "unit": "s/layer", "cores": threads, "kind": "port", "breakdown_s": cparts,
+               "sample": f"8192 of {n_seq * T} calibration tokens, 2048 of {R} weight rows, full-size Cholesky; parts scaled linearly"}
     if rank == 0:
         sec = ms * 1e-3 / args.steps
         hess_flops = float((hi - lo) * T) * C * (C + 1)
@@ -481,7 +558,7 @@ def run_gptq(args):
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": hess_flops / hess_t / 1e12 / peaks["bf16_tflops"],
                          "peak_source": f"bf16 cuBLAS burst ({peaks['source']})",
                          "note": "time includes the Hadamard rotation of the activations; flops = T*d*(d+1)", "traffic": None},
-            "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
+            "cpu_baseline": cpu, "e2e": None, "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
     if world > 1:
