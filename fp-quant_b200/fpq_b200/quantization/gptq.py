@@ -23,7 +23,8 @@ def get_relative_mse_error(q: torch.Tensor, w: torch.Tensor, H: torch.Tensor) ->
 class GPTQ:
     def __init__(self, layer: nn.Module, quantizer: Quantizer, quantization_order: str = "default",
                  block_size: int = 128, rel_damp: float = 1e-2, export_quantized_model: str = ""):
-        assert isinstance(layer, nn.Linear), "the B200 path quantises linear layers"
+        w = getattr(layer, "weight", None)
+        assert isinstance(w, torch.Tensor) and w.dim() == 2, "the B200 path quantises layers with a 2-D weight"
         if block_size != 128:
             raise NotImplementedError("the column-block kernel is built for block_size = 128")
         self.layer = layer

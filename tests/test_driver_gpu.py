@@ -1,0 +1,92 @@
+"""Model-level drivers (gptq_quantization / rtn_quantization) on a tiny randomly initialised Llama:
+the same call a user of the reference's model_quant.py makes (src/quantization/gptq.py:225-470,
+src/quantization/rtn.py:17-237), checked for the export format, for consistency between the exported
+codes / scales and the weights left in the model, and for GPTQ beating RTN on the calibration data."""
+import types
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import fp4  # noqa: E402  (checker only)
+
+
+def _tiny_llama(device):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=160, max_position_embeddings=128)
+    model = LlamaForCausalLM(cfg).to(device=device, dtype=torch.bfloat16).eval()
+    model.config.use_cache = False
+    return model
+
+
+def _args(fmt):
+    from fpq_b200.quantization.quant_args import (QuantizationFormat, QuantizationGranularity, QuantizationObserver,
+                                                  QuantizationOrder, ScalePrecision)
+    nv = fmt == "nvfp"
+    return types.SimpleNamespace(
+        format=QuantizationFormat.NVFP if nv else QuantizationFormat.MXFP,
+        w_bits=4, a_bits=4, w_granularity=QuantizationGranularity.GROUP, a_granularity=QuantizationGranularity.GROUP,
+        w_observer=QuantizationObserver.MINMAX, a_observer=QuantizationObserver.MINMAX,
+        w_group_size=16 if nv else 32, a_group_size=16 if nv else 32,
+        scale_precision=ScalePrecision.E4M3 if nv else ScalePrecision.E8M0,
+        transform_class="hadamard", hadamard_group_size=128, cpu_offload_activations=False, cpu_offload_modules=False,
+        quantization_order=QuantizationOrder.DEFAULT, rel_damp=0.01, export_quantized_model="realquant",
+        dtype=torch.bfloat16, fuse_global_scale=False, amp=False)
+
+
+def _calibration(device, n=6, t=96):
+    g = torch.Generator().manual_seed(1)
+    return [torch.randint(0, 160, (1, t), generator=g) for _ in range(n)]
+
+
+LINEARS = ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj", "mlp.gate_proj",
+           "mlp.up_proj", "mlp.down_proj"]
+
+
+@pytest.mark.parametrize("fmt", ["nvfp", "mxfp"])
+def test_gptq_quantization_tiny_llama(fmt):
+    from fpq_b200.quantization.driver import gptq_quantization, rtn_quantization
+
+    dev = torch.device("cuda:0")
+    data = _calibration(dev)
+    ref_model = _tiny_llama(dev)
+    with torch.no_grad():
+        ref_logits = torch.cat([ref_model(x.to(dev)).logits.float() for x in data])
+
+    def run(driver):
+        model = _tiny_llama(dev)
+        quantized, non_quantized = driver(model, data, _args(fmt), dev)
+        with torch.no_grad():
+            logits = torch.cat([model(x.to(dev)).logits.float() for x in data])
+        return model, quantized, logits
+
+    model, quantized, logits = run(gptq_quantization)
+    assert torch.isfinite(logits).all()
+    group = 16 if fmt == "nvfp" else 32
+    for b in range(2):
+        for name in LINEARS:
+            key = f"model.layers.{b}.{name}"
+            assert key in quantized, key
+            e = quantized[key]
+            mod = model.model.layers[b].get_submodule(name)
+            n, k = mod.out_features, mod.in_features
+            assert e["qweight"].dtype == torch.uint8 and tuple(e["qweight"].shape) == (n, k // 2)
+            assert tuple(e["scales"].shape) == (n, k // group)
+            assert tuple(e["forward_hadamard_matrix"].shape) == (128, 128)
+            # exported codes x exported scales reproduce the weight the model now computes with
+            sc = fp4.decode_scale_bytes(e["scales"].view(torch.uint8), "nvfp4" if fmt == "nvfp" else "mxfp4")
+            sc = sc / e["weight_global_scale"].float().cpu()     # exported scales carry the tensor scale
+            deq = fp4.dequantize(fp4.unpack_codes(e["qweight"]), sc, group)
+            w = mod.weight.detach().float().cpu()
+            assert torch.allclose(deq, w, rtol=2 ** -7, atol=1e-6), (key, (deq - w).abs().max())
+
+    _, _, logits_rtn = run(rtn_quantization)
+    err_gptq = ((logits - ref_logits) ** 2).mean() / (ref_logits ** 2).mean()
+    err_rtn = ((logits_rtn - ref_logits) ** 2).mean() / (ref_logits ** 2).mean()
+    assert err_gptq < 0.5 and err_rtn < 0.5, (err_gptq, err_rtn)
+    # error compensation must not be worse than plain rounding on the data it was calibrated on
+    assert err_gptq < 1.1 * err_rtn, (err_gptq, err_rtn)
