@@ -214,6 +214,8 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       bool ok = true;
       long long t_acc = 0, t_full = 0;
       const long long t_begin = tick<PROF>();
+      unsigned long long ns_begin = 0;
+      if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
       for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs, ++tile_count) {
         long long t0 = tick<PROF>();
         if (!mbar_wait_bounded_spin(bar_acc_empty, (tile_count & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -259,7 +261,10 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
       if (PROF && p.profile) {
         long long* o = p.profile + (size_t)pair_id * 64;
+        unsigned long long ns_end = 0;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
         o[0] = tick<PROF>() - t_begin; o[1] = t_acc; o[2] = t_full; o[3] = 0; o[4] = it; o[14] = t_begin;
+        o[15] = (long long)(ns_end - ns_begin);
       }
       if (!ok) {
         *abort_flag = 1;

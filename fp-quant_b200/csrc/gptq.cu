@@ -13,6 +13,14 @@
 #include "sgemm.cuh"
 
 namespace fpq {
+// defined in hessian.cu: out = beta * out + alpha * A^T B on the tensor cores (bf16 operands, fp32 accumulation)
+int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A, int64_t lda, int64_t a_rows,
+                  int64_t a_x0, const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, bool symmetric, bool mirror,
+                  int n_seg, int64_t seg_rows, const int* a_seg_y, const int* b_seg_y, float alpha, float beta,
+                  int32_t* error_flag, cudaStream_t stream);
+}  // namespace fpq
+
+namespace fpq {
 namespace {
 
 constexpr int NB = 128;   // block size of the factorisation and of the GPTQ column blocks
@@ -163,17 +171,111 @@ int grid1d(int64_t n) {
   return (int)(b > cap ? cap : (b < 1 ? 1 : b));
 }
 
+// ------------------------------------------------------------------ fp32-accurate products on the tensor cores
+// x in fp32 -> three bf16 terms hi + mid + lo that together carry all 24 mantissa bits.
+__device__ __forceinline__ void split3(float v, __nv_bfloat16& h, __nv_bfloat16& m, __nv_bfloat16& l) {
+  h = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(h);
+  m = __float2bfloat16_rn(r1);
+  l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+}
+
+// in [K, N] fp32 (row stride ld_in) -> out: three planes [K, ld_out] bf16 (hi, mid, lo), plane p at row p * K
+__global__ void split3_rows_kernel(const float* __restrict__ in, int64_t ld_in, int64_t K, int64_t N,
+                                   __nv_bfloat16* __restrict__ out, int64_t ld_out) {
+  const int64_t total = K * N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t k = i / N, n = i - k * N;
+    __nv_bfloat16 h, m, l;
+    split3(in[k * ld_in + n], h, m, l);
+    out[k * ld_out + n] = h;
+    out[(K + k) * ld_out + n] = m;
+    out[(2 * K + k) * ld_out + n] = l;
+  }
+}
+
+// in [R, K] fp32 (row stride ld_in) -> out: three planes [K, ld_out] bf16 holding the transposed terms:
+// plane p, row k, column r = term p of in[r, k].  Tiles of 32 x 32 through shared memory.
+__global__ void __launch_bounds__(256) transpose_split3_kernel(const float* __restrict__ in, int64_t ld_in, int64_t R,
+                                                               int64_t K, __nv_bfloat16* __restrict__ out, int64_t ld_out) {
+  __shared__ float tile[32][33];
+  const int64_t r0 = (int64_t)blockIdx.x * 32, k0 = (int64_t)blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int rr = ty; rr < 32; rr += 8)
+    tile[rr][tx] = (r0 + rr < R && k0 + tx < K) ? in[(r0 + rr) * ld_in + k0 + tx] : 0.0f;
+  __syncthreads();
+  for (int kk = ty; kk < 32; kk += 8) {
+    if (k0 + kk < K && r0 + tx < ld_out) {
+      __nv_bfloat16 h, m, l;
+      split3(tile[tx][kk], h, m, l);
+      out[(k0 + kk) * ld_out + r0 + tx] = h;
+      out[(K + k0 + kk) * ld_out + r0 + tx] = m;
+      out[(2 * K + k0 + kk) * ld_out + r0 + tx] = l;
+    }
+  }
+}
+
+int64_t round64(int64_t x) { return (x + 63) & ~(int64_t)63; }
+
+// bf16 elements of workspace tc_gemm3 needs
+int64_t tc_gemm3_workspace(int64_t M, int64_t N, int64_t K, bool b_is_a_transposed) {
+  return 3 * K * round64(M) + (b_is_a_transposed ? 0 : 3 * K * round64(N));
+}
+
+// C[M, N] (row stride ldc) = beta * C + alpha * A B with fp32-level accuracy on the tensor cores:
+// A [M, K] row-major (lda); B [K, N] row-major (ldb), or B == nullptr for B = A^T (N == M, the symmetric
+// rank-K update; only the tiles touching the lower triangle are then computed).  Both factors are split
+// into three bf16 terms and the six leading cross products (hi*hi, hi*mid, mid*hi, hi*lo, lo*hi, mid*mid;
+// the dropped ones are below 2^-24 relative) are accumulated in fp32 in one launch whose K dimension is
+// the concatenation of the six slabs.  K must be a multiple of 64.
+int tc_gemm3(float* C, int64_t ldc, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+             int64_t ldb, float alpha, float beta, __nv_bfloat16* ws, int32_t* error_flag, cudaStream_t st) {
+  static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
+  const int64_t ldat = round64(M);
+  __nv_bfloat16* at3 = ws;
+  dim3 tgrid((unsigned)((ldat + 31) / 32), (unsigned)((K + 31) / 32));
+  transpose_split3_kernel<<<tgrid, 256, 0, st>>>(A, lda, M, K, at3, ldat);
+  FPQ_CHECK_LAUNCH();
+  const __nv_bfloat16* b3 = at3;
+  int64_t ldbt = ldat;
+  if (B) {
+    ldbt = round64(N);
+    __nv_bfloat16* bw = ws + 3 * K * ldat;
+    split3_rows_kernel<<<grid1d(K * N), 256, 0, st>>>(B, ldb, K, N, bw, ldbt);
+    FPQ_CHECK_LAUNCH();
+    b3 = bw;
+  }
+  int a_y[6], b_y[6];
+  for (int t = 0; t < 6; ++t) {
+    a_y[t] = (int)(pa[t] * K);
+    b_y[t] = (int)(pb[t] * K);
+  }
+  return gemm_atb_bf16(C, ldc, M, N, at3, ldat, 3 * K, 0, b3, ldbt, 3 * K, 0, B == nullptr, false, 6, K, a_y, b_y, alpha,
+                       beta, error_flag, st);
+}
+
+// Products at least this large go to the tensor cores; smaller ones stay on the fp32 SIMT kernel, whose
+// launch is cheaper than the two conversion passes.
+bool tc_worthwhile(int64_t M, int64_t N, int64_t K) { return K % 64 == 0 && M * N * K >= (int64_t)512 * 512 * 128; }
+
 // X[lo:hi, lo:hi] = L[lo:hi, lo:hi]^-1 for block indices [lo, hi), given the inverses of the diagonal
 // blocks already in X:  L^-1 = [[X11, 0], [-X22 (L21 X11), X22]].  S = L21 X11 (n2 x n1) goes to `scratch`.
-int tri_inverse_recursive(const float* L, float* X, float* scratch, int64_t d, int lo, int hi, cudaStream_t st) {
+int tri_inverse_recursive(const float* L, float* X, float* scratch, __nv_bfloat16* ws, int32_t* error_flag, int64_t d,
+                          int lo, int hi, cudaStream_t st) {
   if (hi - lo <= 1) return FPQ_OK;
   const int mid = (lo + hi) / 2;
-  if (int rc = tri_inverse_recursive(L, X, scratch, d, lo, mid, st)) return rc;
-  if (int rc = tri_inverse_recursive(L, X, scratch, d, mid, hi, st)) return rc;
+  if (int rc = tri_inverse_recursive(L, X, scratch, ws, error_flag, d, lo, mid, st)) return rc;
+  if (int rc = tri_inverse_recursive(L, X, scratch, ws, error_flag, d, mid, hi, st)) return rc;
   const int64_t r0 = (int64_t)lo * NB, r1 = (int64_t)mid * NB;
   const int64_t n1 = r1 - r0;
   int64_t n2 = (int64_t)hi * NB - r1;
   if (r1 + n2 > d) n2 = d - r1;
+  if (tc_worthwhile(n2, n1, n1) && n2 % 64 == 0) {
+    // S = L21 * X11, then X21 = -X22 * S
+    if (int rc = tc_gemm3(scratch, n1, n2, n1, n1, L + r1 * d + r0, d, X + r0 * d + r0, d, 1.0f, 0.0f, ws, error_flag, st))
+      return rc;
+    return tc_gemm3(X + r1 * d + r0, d, n2, n1, n2, X + r1 * d + r1, d, scratch, n1, -1.0f, 0.0f, ws, error_flag, st);
+  }
   SgemmArgs a{};
   // S = L21 * X11
   a.A = L + r1 * d + r0; a.lda = d;
@@ -323,53 +425,8 @@ __global__ void ratio_kernel(const double* acc, float* out, double count) {
   out[0] = (float)((acc[0] / count) / (acc[1] / count + 1e-6));
 }
 
-// x in fp32 -> three bf16 terms hi + mid + lo that together carry all 24 mantissa bits.
-__device__ __forceinline__ void split3(float v, __nv_bfloat16& h, __nv_bfloat16& m, __nv_bfloat16& l) {
-  h = __float2bfloat16_rn(v);
-  const float r1 = v - __bfloat162float(h);
-  m = __float2bfloat16_rn(r1);
-  l = __float2bfloat16_rn(r1 - __bfloat162float(m));
-}
-
-// out is three planes of n elements: hi, mid, lo
-__global__ void split3_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ out, int64_t n) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    __nv_bfloat16 h, m, l;
-    split3(x[i], h, m, l);
-    out[i] = h; out[n + i] = m; out[2 * n + i] = l;
-  }
-}
-
-// Err [rows, 128] fp32 -> ErrT3 [3 * 128, lda] bf16: plane s, row k, column r holds term s of Err[r, k].
-__global__ void __launch_bounds__(256) err_transpose_split_kernel(const float* __restrict__ Err, int64_t rows, int64_t lda,
-                                                                  __nv_bfloat16* __restrict__ out) {
-  __shared__ float tile[32][NB + 1];
-  const int64_t r0 = (int64_t)blockIdx.x * 32;
-  for (int idx = threadIdx.x; idx < 32 * NB; idx += 256) {
-    const int r = idx / NB, k = idx % NB;
-    tile[r][k] = r0 + r < rows ? Err[(r0 + r) * NB + k] : 0.0f;
-  }
-  __syncthreads();
-  const int r = threadIdx.x & 31;
-  for (int k = threadIdx.x >> 5; k < NB; k += 8) {
-    __nv_bfloat16 h, m, l;
-    split3(tile[r][k], h, m, l);
-    if (r0 + r < lda) {
-      out[(int64_t)k * lda + r0 + r] = h;
-      out[(int64_t)(NB + k) * lda + r0 + r] = m;
-      out[(int64_t)(2 * NB + k) * lda + r0 + r] = l;
-    }
-  }
-}
-
 }  // namespace
 }  // namespace fpq
-
-namespace fpq {
-int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A, int64_t lda, int64_t a_rows,
-                  const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, int64_t T, bool symmetric, const int* a_y,
-                  const int* b_y, int n_table, float alpha, float beta, int32_t* error_flag, cudaStream_t stream);
-}
 
 using namespace fpq;
 
@@ -424,20 +481,24 @@ extern "C" int fpq_hessian_prepare_noalloc(float* H, int64_t d, const float* W, 
 }
 
 extern "C" int64_t fpq_cholesky_workspace_floats(int64_t d) {
+  // L (d x d) | scratch of the triangular inverse (half x half) | bf16 operand splits (6 half^2 bf16 = 3 half^2 floats)
   const int64_t nblk = (d + NB - 1) / NB;
   const int64_t half = ((nblk + 1) / 2) * NB;
-  return d * d + half * half;
+  return d * d + 4 * half * half + 64;
 }
 
 extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, float* workspace, int32_t* status,
-                                          fpq_stream_t stream) {
-  FPQ_CHECK_ARG(H && U && workspace && status, "NULL pointer");
+                                          int32_t* error_flag, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(H && U && workspace && status && error_flag, "NULL pointer");
   FPQ_CHECK_ARG(d > 0 && d < (1ll << 30), "bad size");
   FPQ_CHECK_ARG(H != U, "U must not alias H");
+  FPQ_CHECK_ARG(((uintptr_t)workspace & 15) == 0, "workspace must be 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
-  float* L = workspace;
-  float* scratch = workspace + d * d;
   const int nblk = (int)((d + NB - 1) / NB);
+  const int64_t half = (int64_t)((nblk + 1) / 2) * NB;
+  float* L = workspace;
+  float* scratch = workspace + ((d * d + 3) & ~(int64_t)3);
+  __nv_bfloat16* ws = reinterpret_cast<__nv_bfloat16*>(scratch + half * half);
   FPQ_CHECK_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
   reverse_copy_kernel<<<grid1d(d * d), 256, 0, st>>>(H, L, d);
   FPQ_CHECK_LAUNCH();
@@ -457,13 +518,19 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
     a.M = (int)below; a.N = nb; a.K = nb; a.alpha = 1.0f; a.beta = 0.0f;
     if (int rc = sgemm(a, true, SGEMM_PLAIN, st)) return rc;
     // trailing update: A22 -= L21 L21^T (lower tiles only)
+    if (nb == NB && tc_worthwhile(below, below, nb) && 3 * (int64_t)nb * round64(below) <= 6 * half * half) {
+      if (int rc = tc_gemm3(L + (r + nb) * d + (r + nb), d, below, below, nb, L + (r + nb) * d + r, d, nullptr, 0, -1.0f,
+                            1.0f, ws, error_flag, st))
+        return rc;
+      continue;
+    }
     a.A = L + (r + nb) * d + r; a.lda = d;
     a.B = L + (r + nb) * d + r; a.ldb = d;
     a.C = L + (r + nb) * d + (r + nb); a.ldc = d;
     a.M = (int)below; a.N = (int)below; a.K = nb; a.alpha = -1.0f; a.beta = 1.0f;
     if (int rc = sgemm(a, true, SGEMM_LOWER, st)) return rc;
   }
-  if (int rc = tri_inverse_recursive(L, U, scratch, d, 0, nblk, st)) return rc;
+  if (int rc = tri_inverse_recursive(L, U, scratch, ws, error_flag, d, 0, nblk, st)) return rc;
   reflect_inplace_kernel<<<grid1d(d * d / 2), 256, 0, st>>>(U, d);   // U <- J X J (upper triangular)
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
@@ -505,7 +572,7 @@ extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const flo
   __nv_bfloat16* errT3 = reinterpret_cast<__nv_bfloat16*>(ws + align256(rows * NB * (int64_t)sizeof(float)));
   __nv_bfloat16* U3 = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(errT3) + align256(3 * NB * lda * 2));
   if (cols > NB) {
-    split3_bf16_kernel<<<grid1d(cols * cols), 256, 0, st>>>(U, U3, cols * cols);
+    split3_rows_kernel<<<grid1d(cols * cols), 256, 0, st>>>(U, cols, cols, cols, U3, cols);
     FPQ_CHECK_LAUNCH();
   }
   // The trailing update W[:, c2:] -= Err U[c1:c2, c2:] runs on the tensor cores: both factors are split
@@ -522,16 +589,16 @@ extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const flo
     FPQ_CHECK_LAUNCH();
     const int64_t c2 = c1 + NB;
     if (c2 >= cols) break;
-    err_transpose_split_kernel<<<(unsigned)((lda + 31) / 32), 256, 0, st>>>(err, rows, lda, errT3);
+    dim3 tgrid((unsigned)((lda + 31) / 32), NB / 32);
+    transpose_split3_kernel<<<tgrid, 256, 0, st>>>(err, NB, rows, NB, errT3, lda);
     FPQ_CHECK_LAUNCH();
-    int a_y[12], b_y[12];
-    for (int t = 0; t < 6; ++t)
-      for (int kk = 0; kk < 2; ++kk) {
-        a_y[2 * t + kk] = pa[t] * NB + kk * 64;
-        b_y[2 * t + kk] = (int)(pb[t] * cols + c1 + kk * 64);
-      }
-    if (int rc = gemm_atb_bf16(W + c2, cols, rows, cols - c2, errT3, lda, 3 * NB, U3, cols, 3 * cols, c2, 0, false, a_y, b_y,
-                               12, -1.0f, 1.0f, error_flag, st))
+    int a_y[6], b_y[6];
+    for (int t = 0; t < 6; ++t) {
+      a_y[t] = pa[t] * NB;
+      b_y[t] = (int)(pb[t] * cols + c1);
+    }
+    if (int rc = gemm_atb_bf16(W + c2, cols, rows, cols - c2, errT3, lda, 3 * NB, 0, U3, cols, 3 * cols, c2, false, false, 6,
+                               NB, a_y, b_y, -1.0f, 1.0f, error_flag, st))
       return rc;
   }
   return FPQ_OK;

@@ -32,18 +32,19 @@ constexpr int STAGES = 4;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;       // two 256-column accumulators
 
-constexpr int MAX_K_TABLE = 16;
+constexpr int MAX_SEGMENTS = 6;
 
 struct HessParams {
   int64_t d1, d2, ldc;  // output rows (A's width), columns (B's width), row stride of the output
   int num_blocks;      // ceil(d1 / 128)
   int num_blocks_n;    // ceil(d2 / 256)
   int num_tiles;
-  int num_k_stages;    // ceil(T / 64), or the number of table entries
-  int symmetric;
-  int use_table;       // token rows of stage ks come from a_y[ks] / b_y[ks] instead of ks * 64
-  int b_x0;            // first column of B (added to the TMA x coordinate)
-  int a_y[MAX_K_TABLE], b_y[MAX_K_TABLE];
+  int num_k_stages;    // stages of 64 token rows over all segments
+  int seg_stages;      // stages per segment: stage ks reads rows a_seg_y[ks / seg_stages] + (ks % seg_stages) * 64
+  int symmetric;       // only tiles that touch the lower triangle
+  int mirror;          // symmetric form: also write the transposed blocks above the diagonal
+  int a_x0, b_x0;      // first column of A / B inside their matrices (added to the TMA x coordinate)
+  int a_seg_y[MAX_SEGMENTS], b_seg_y[MAX_SEGMENTS];
   float alpha, beta;
   float* H;
   int* error_flag;
@@ -141,11 +142,12 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           mbar_arrive_expect_tx(bar_full + 8 * s, (A_BOXES + B_BOXES) * BOX_BYTES);
           const uint32_t a_dst = sbase + Smem::OFF_A + s * A_BOXES * BOX_BYTES;
           const uint32_t b_dst = sbase + Smem::OFF_B + s * B_BOXES * BOX_BYTES;
-          const int ya = p.use_table ? p.a_y[ks] : ks * BK;
-          const int yb = p.use_table ? p.b_y[ks] : ks * BK;
+          const int seg = ks / p.seg_stages, kk = ks - seg * p.seg_stages;
+          const int ya = p.a_seg_y[seg] + kk * BK;
+          const int yb = p.b_seg_y[seg] + kk * BK;
 #pragma unroll
           for (int b = 0; b < A_BOXES; ++b)
-            tma_load_2d(a_dst + b * BOX_BYTES, &tmap_a, ib * TILE + 64 * b, ya, bar_full + 8 * s);
+            tma_load_2d(a_dst + b * BOX_BYTES, &tmap_a, p.a_x0 + ib * TILE + 64 * b, ya, bar_full + 8 * s);
 #pragma unroll
           for (int b = 0; b < B_BOXES; ++b)
             tma_load_2d(b_dst + b * BOX_BYTES, &tmap_b, p.b_x0 + jb * TILE_N + 64 * b, yb, bar_full + 8 * s);
@@ -205,7 +207,7 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int64_t j0 = (int64_t)jb * TILE_N + c * 32;
         const int jblock = (int)(j0 / TILE);                 // 128-column block of this chunk
         if (j0 >= p.d2 || (p.symmetric && jblock > ib)) break;   // beyond the matrix / above the diagonal
-        const bool mirror = p.symmetric && jblock < ib;
+        const bool mirror = p.mirror && jblock < ib;
         uint32_t r[32];
         tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE_N + c * 32, r);
         tc_wait_ld();
@@ -266,29 +268,35 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 namespace fpq {
 
-// out[d1, d2] (row stride ldc) = beta * out + alpha * A^T B with A [T, d1] and B [T, d2] bf16 row-major
-// (row strides lda, ldb in elements; B starts at column b_x0 of its matrix).  With `table` the K
-// dimension is the concatenation of n_table 64-row slabs whose first rows are a_y[i] / b_y[i].
+// out[d1, d2] (row stride ldc) = beta * out + alpha * A^T B with A [*, d1] and B [*, d2] bf16 row-major
+// matrices of a_rows / b_rows rows (row strides lda, ldb in elements; the operands start at columns
+// a_x0 / b_x0).  The K dimension is the concatenation of n_seg segments of seg_rows rows each, segment
+// i starting at row a_seg_y[i] of A and b_seg_y[i] of B (one segment from row 0: the plain product).
+// With more than one segment seg_rows must be a multiple of 64.  symmetric: only tiles that touch the
+// lower triangle are computed (d1 == d2); mirror: the blocks below the diagonal are also written
+// transposed.
 int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A, int64_t lda, int64_t a_rows,
-                  const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, int64_t T, bool symmetric, const int* a_y,
-                  const int* b_y, int n_table, float alpha, float beta, int32_t* error_flag, cudaStream_t stream) {
+                  int64_t a_x0, const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, bool symmetric, bool mirror,
+                  int n_seg, int64_t seg_rows, const int* a_seg_y, const int* b_seg_y, float alpha, float beta,
+                  int32_t* error_flag, cudaStream_t stream) {
+  if (n_seg < 1 || n_seg > MAX_SEGMENTS || (n_seg > 1 && seg_rows % BK != 0)) {
+    set_error("bad K segmentation (%d segments of %lld rows)", n_seg, (long long)seg_rows);
+    return FPQ_ERR_INVALID_ARGUMENT;
+  }
+  if (d1 <= 0 || d2 <= 0 || seg_rows <= 0) return FPQ_OK;
   HessParams p{};
   p.d1 = d1; p.d2 = d2; p.ldc = ldc;
   p.num_blocks = (int)((d1 + TILE - 1) / TILE);
   p.num_blocks_n = (int)((d2 + TILE_N - 1) / TILE_N);
   p.num_tiles = symmetric ? tiles_before_row(p.num_blocks) : p.num_blocks * p.num_blocks_n;
   p.symmetric = symmetric ? 1 : 0;
-  p.b_x0 = (int)b_x0;
-  if (n_table > 0) {
-    if (n_table > MAX_K_TABLE) {
-      set_error("K table too long (%d)", n_table);
-      return FPQ_ERR_INVALID_ARGUMENT;
-    }
-    p.use_table = 1;
-    p.num_k_stages = n_table;
-    for (int i = 0; i < n_table; ++i) { p.a_y[i] = a_y[i]; p.b_y[i] = b_y[i]; }
-  } else {
-    p.num_k_stages = (int)((T + BK - 1) / BK);
+  p.mirror = (symmetric && mirror) ? 1 : 0;
+  p.a_x0 = (int)a_x0; p.b_x0 = (int)b_x0;
+  p.seg_stages = (int)((seg_rows + BK - 1) / BK);
+  p.num_k_stages = p.seg_stages * n_seg;
+  for (int i = 0; i < n_seg; ++i) {
+    p.a_seg_y[i] = a_seg_y ? a_seg_y[i] : 0;
+    p.b_seg_y[i] = b_seg_y ? b_seg_y[i] : 0;
   }
   p.alpha = alpha; p.beta = beta; p.H = out; p.error_flag = error_flag;
   CUtensorMap ta, tb;
@@ -322,6 +330,6 @@ extern "C" int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, 
                 "pointers must be 16-byte aligned");
   if (tokens == 0) return FPQ_OK;
   const bool symmetric = xb_bf16 == nullptr || xb_bf16 == xa_bf16;
-  return gemm_atb_bf16(H, d, d, d, xa_bf16, d, tokens, symmetric ? xa_bf16 : xb_bf16, d, tokens, 0, tokens, symmetric,
-                       nullptr, nullptr, 0, alpha, beta, error_flag, (cudaStream_t)stream);
+  return gemm_atb_bf16(H, d, d, d, xa_bf16, d, tokens, 0, symmetric ? xa_bf16 : xb_bf16, d, tokens, 0, symmetric, true,
+                       1, tokens, nullptr, nullptr, alpha, beta, error_flag, (cudaStream_t)stream);
 }

@@ -41,7 +41,7 @@ _SIGNATURES = {
     "fpq_hessian_prepare": [c_void_p, c_int64, c_void_p, c_int64, c_float, c_void_p, c_void_p],
     "fpq_hessian_prepare_noalloc": [c_void_p, c_int64, c_void_p, c_int64, c_float, c_void_p],
     "fpq_cholesky_workspace_floats": [c_int64],
-    "fpq_cholesky_inverse_upper": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p],
+    "fpq_cholesky_inverse_upper": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     "fpq_gptq_quantize": [c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p],
     "fpq_gptq_workspace_bytes": [c_int64, c_int64],

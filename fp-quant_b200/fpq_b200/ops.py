@@ -280,7 +280,7 @@ def cholesky_inverse_upper(H: torch.Tensor):
     status = torch.zeros(1, dtype=torch.int32, device=H.device)
     with _guard(H.device):
         C.call("fpq_cholesky_inverse_upper", H.data_ptr(), U.data_ptr(), d, ws.data_ptr(), status.data_ptr(),
-               _stream(H))
+               device_error_flag(H.device).data_ptr(), _stream(H))
     return U, status
 
 

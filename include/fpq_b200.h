@@ -202,7 +202,8 @@ int fpq_hessian_prepare(float* H, int64_t d, const float* W, int64_t rows, float
 int fpq_hessian_prepare_noalloc(float* H, int64_t d, const float* W, int64_t rows, float rel_damp,
                                 fpq_stream_t stream);
 
-/* Number of floats fpq_cholesky_inverse_upper needs as workspace for a d x d matrix. */
+/* Number of floats fpq_cholesky_inverse_upper needs as workspace for a d x d matrix (sizing helper; the
+ * reference's torch.linalg calls allocate their own, src/utils/linalg_utils.py:8-12). */
 int64_t fpq_cholesky_workspace_floats(int64_t d);
 
 /*
@@ -211,9 +212,11 @@ int64_t fpq_cholesky_workspace_floats(int64_t d);
  * Cholesky factorisation of the index-reversed H and one triangular inverse, all in fp32.
  * *status (device int32) becomes 1 when a pivot is not positive -- the reference then falls back to
  * the identity (gptq.py:216-217); the caller decides.  H is not modified; U must not alias H.
+ * The large trailing updates and triangular-inverse products run on the tensor cores as three-term
+ * bf16 splits (fp32-level accuracy); error_flag as for fpq_gemm_fp4.
  */
 int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, float* workspace, int32_t* status,
-                               fpq_stream_t stream);
+                               int32_t* error_flag, fpq_stream_t stream);
 
 /*
  * The column loop of GPTQ.step (src/quantization/gptq.py:159-187), default column order:

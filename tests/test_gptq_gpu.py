@@ -69,7 +69,7 @@ def test_hessian_prepare_matches_oracle(cuda_device):
     assert H[5, 5].item() == pytest.approx(1.0 + 0.01 * torch.diag(want - torch.diag(torch.diag(want)) + torch.diag(torch.diag(want))).mean().item(), rel=1e-2) or True
 
 
-@pytest.mark.parametrize("d", [128, 256, 384, 1000])
+@pytest.mark.parametrize("d", [128, 256, 384, 1000, 1664, 2048])
 def test_cholesky_inverse_upper(cuda_device, d):
     from fpq_b200 import ops
 
