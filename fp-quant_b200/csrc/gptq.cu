@@ -88,8 +88,10 @@ __global__ void reflect_inplace_kernel(float* A, int64_t d) {
 // register blocks that are already final (or still zero) are skipped at compile time.
 __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, float* Linv, int64_t ldi, int nb,
                                                         int32_t* status) {
-  __shared__ float colbuf[2][NB];
-  __shared__ float rowbuf[2][NB];
+  // Column k of A and row k of X as the threads need them: entry i sits at perm(i), so that the eight
+  // values of a thread (i = t + 16 c) are two contiguous groups of four: perm(i) = (c / 4) * 64 + t * 4 + c % 4.
+  __shared__ __align__(16) float colbuf[2][NB];
+  __shared__ __align__(16) float rowbuf[2][NB];
   const int tid = threadIdx.x;
   const int ty = tid >> 4, tx = tid & 15;
   float a[8][8], x[8][8];
@@ -110,26 +112,36 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, f
       float* rb = rowbuf[k & 1];
       if (tx == t) {
 #pragma unroll
-        for (int r = 0; r < 8; ++r) cb[ty + 16 * r] = a[r][cc];
+        for (int r = 0; r < 8; ++r) cb[(r >> 2) * 64 + ty * 4 + (r & 3)] = a[r][cc];
       }
       if (ty == t) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) rb[tx + 16 * c] = x[cc][c];
+        for (int c = 0; c < 8; ++c) rb[(c >> 2) * 64 + tx * 4 + (c & 3)] = x[cc][c];
       }
       __syncthreads();
-      float piv = cb[k];
+      float piv = cb[(cc >> 2) * 64 + t * 4 + (cc & 3)];
       if (!(piv > 0.0f) || !isfinite(piv)) {
         if (tid == 0) atomicExch(status, 1);
         piv = 1.0f;
       }
-      const float rinv = 1.0f / sqrtf(piv);
+      // The updates need only 1 / pivot: with c = A[:, k] and y = X[k, :] (both unscaled),
+      //   A[i, j] -= c_i c_j / piv,   X[i, :] -= c_i y / piv;
+      // the square root is taken off the critical path, by the owners of column k / row k alone.
+      const float pinv = __frcp_rn(piv);
       float li[8], lj[8], xr[8];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) li[r] = r >= cc ? cb[ty + 16 * r] * rinv : 0.0f;
+      {
+        const float4 v0 = *reinterpret_cast<const float4*>(&cb[ty * 4]), v1 = *reinterpret_cast<const float4*>(&cb[64 + ty * 4]);
+        li[0] = v0.x; li[1] = v0.y; li[2] = v0.z; li[3] = v0.w; li[4] = v1.x; li[5] = v1.y; li[6] = v1.z; li[7] = v1.w;
+        const float4 w0 = *reinterpret_cast<const float4*>(&cb[tx * 4]), w1 = *reinterpret_cast<const float4*>(&cb[64 + tx * 4]);
+        lj[0] = w0.x; lj[1] = w0.y; lj[2] = w0.z; lj[3] = w0.w; lj[4] = w1.x; lj[5] = w1.y; lj[6] = w1.z; lj[7] = w1.w;
+        const float4 y0 = *reinterpret_cast<const float4*>(&rb[tx * 4]), y1 = *reinterpret_cast<const float4*>(&rb[64 + tx * 4]);
+        xr[0] = y0.x; xr[1] = y0.y; xr[2] = y0.z; xr[3] = y0.w; xr[4] = y1.x; xr[5] = y1.y; xr[6] = y1.z; xr[7] = y1.w;
+      }
+      float ljs[8], xrs[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        lj[c] = c >= cc ? cb[tx + 16 * c] * rinv : 0.0f;
-        xr[c] = c <= cc ? rb[tx + 16 * c] * rinv : 0.0f;
+        ljs[c] = lj[c] * pinv;
+        xrs[c] = xr[c] * pinv;
       }
       const bool below = ty > t;   // row ty + 16 cc lies below row k
 #pragma unroll
@@ -137,18 +149,22 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(float* A, int64_t lda, f
         if (r > cc || below) {
 #pragma unroll
           for (int c = cc; c < 8; ++c)
-            if (c > cc || tx > t) a[r][c] = fmaf(-li[r], lj[c], a[r][c]);
+            if (c > cc || tx > t) a[r][c] = fmaf(-li[r], ljs[c], a[r][c]);
 #pragma unroll
-          for (int c = 0; c <= cc; ++c) x[r][c] = fmaf(-li[r], xr[c], x[r][c]);
+          for (int c = 0; c <= cc; ++c) x[r][c] = fmaf(-li[r], xrs[c], x[r][c]);
         }
       }
-      if (tx == t) {
+      if (tx == t || ty == t) {
+        float rinv = rsqrtf(piv);
+        rinv = rinv * fmaf(-0.5f * piv * rinv, rinv, 1.5f);   // one Newton step: full fp32 accuracy
+        if (tx == t) {
 #pragma unroll
-        for (int r = cc; r < 8; ++r) a[r][cc] = li[r];
-      }
-      if (ty == t) {
+          for (int r = cc; r < 8; ++r) a[r][cc] = li[r] * rinv;
+        }
+        if (ty == t) {
 #pragma unroll
-        for (int c = 0; c <= cc; ++c) x[cc][c] = xr[c];
+          for (int c = 0; c <= cc; ++c) x[cc][c] = xr[c] * rinv;
+        }
       }
     }
   }
@@ -309,7 +325,7 @@ constexpr int US_LD = NB + 4 * (NB / SUB);
 __device__ __forceinline__ int us_col(int col) { return col + 4 * (col / SUB); }
 
 template <int G>
-__global__ void __launch_bounds__(128) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C, int64_t c1,
+__global__ void __launch_bounds__(512) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C, int64_t c1,
                                                          const float* __restrict__ scales,
                                                          const float* __restrict__ U, float* __restrict__ Err,
                                                          uint8_t* __restrict__ codes) {
@@ -580,12 +596,20 @@ extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const flo
   // mid*mid; the dropped ones are below 2^-24 relative) are accumulated in fp32 as one GEMM whose K
   // dimension is the concatenation of the six 128-row slabs.
   static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
-  const unsigned grid = (unsigned)((rows * 4 + 127) / 128);   // four threads per row
+  // Four threads per row, eight rows per warp.  The kernel is bound by the latency of its 128 dependent
+  // steps, so all rows should be resident at once: warps per block are chosen so that one block per SM
+  // covers everything when that is possible (14336 rows: 13 warps on 138 SMs) instead of leaving a
+  // handful of blocks for a second pass.
+  const int64_t units = (rows + 7) / 8;
+  int wpb = (int)((units + sm_count() - 1) / sm_count());
+  wpb = wpb < 4 ? 4 : (wpb > 16 ? 16 : wpb);
+  const unsigned threads = (unsigned)wpb * 32;
+  const unsigned grid = (unsigned)((units + wpb - 1) / wpb);
   for (int64_t c1 = 0; c1 < cols; c1 += NB) {
     if (group == 16)
-      gptq_block_kernel<16><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
+      gptq_block_kernel<16><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
     else
-      gptq_block_kernel<32><<<grid, 128, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
+      gptq_block_kernel<32><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
     FPQ_CHECK_LAUNCH();
     const int64_t c2 = c1 + NB;
     if (c2 >= cols) break;
