@@ -565,13 +565,109 @@ def run_gptq(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ MR-GPTQ of a model
+def run_gptq_model(args):
+    """Model-level MR-GPTQ through the public driver (`gptq_quantization`) on a randomly initialised Llama-3.1-8B
+    shaped model (hidden 4096, MLP 14336, 32/8 heads, vocab 128256) truncated to `--model-layers` blocks, with
+    `--calib-seqs` x 2048 uniformly random token ids, NVFP4 W4A4, Hadamard 128.  Multi-GPU: sequences, Cholesky
+    chains and weight rows are partitioned over the ranks inside the driver.  Reports seconds per transformer
+    block (7 linears: 4 distinct Hessians, 4 Cholesky chains, 7 column loops, two passes over the calibration set)."""
+    import types
+
+    import torch.distributed as dist
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    from fpq_b200 import ops
+    from fpq_b200.quantization.driver import gptq_quantization
+    from fpq_b200.quantization.quant_args import (QuantizationFormat, QuantizationGranularity, QuantizationObserver,
+                                                  QuantizationOrder, ScalePrecision)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    n_layers, n_seq, T = args.model_layers, args.calib_seqs, 2048
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=n_layers, num_attention_heads=32,
+                      num_key_value_heads=8, vocab_size=128256, max_position_embeddings=T)
+    qargs = types.SimpleNamespace(
+        format=QuantizationFormat.NVFP, w_bits=4, a_bits=4, w_granularity=QuantizationGranularity.GROUP,
+        a_granularity=QuantizationGranularity.GROUP, w_observer=QuantizationObserver.MINMAX,
+        a_observer=QuantizationObserver.MINMAX, w_group_size=16, a_group_size=16, scale_precision=ScalePrecision.E4M3,
+        transform_class="hadamard", hadamard_group_size=128, cpu_offload_activations=False, cpu_offload_modules=False,
+        quantization_order=QuantizationOrder.DEFAULT, rel_damp=0.01, export_quantized_model="realquant",
+        dtype=torch.bfloat16, fuse_global_scale=False, amp=False)
+    g = torch.Generator().manual_seed(5)
+    data = [torch.randint(0, cfg.vocab_size, (1, T), generator=g) for _ in range(n_seq)]
+
+    def build():
+        torch.manual_seed(0)                     # every rank holds the same model
+        with torch.device(dev):
+            m = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+        m.config.use_cache = False
+        return m
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    import contextlib
+    import io
+
+    times = []
+    with ClockSampler(local) as clocks:
+        for it in range(args.warmup + args.steps):
+            model = build()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            with contextlib.redirect_stdout(io.StringIO()):
+                quantized, _ = gptq_quantization(model, data, qargs, dev)
+            e1.record()
+            barrier()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            if it >= args.warmup:
+                times.append(ms)
+            n_keys = len(quantized)
+            from fpq_b200.quantization import driver as _drv
+            phases = _drv.last_phases.summary()
+            del model, quantized
+            torch.cuda.empty_cache()
+    ops.check_device_errors(dev)
+    if rank == 0:
+        ms = sum(times) / len(times)
+        line = {
+            "metric": "mr_gptq_model_s_per_block", "value": ms * 1e-3 / n_layers, "unit": "s/block", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16 forward and Hessian products, fp32-accurate factorisation and column loop",
+            "data": "synthetic",
+            "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4 W4A4) of a random-init Llama-3.1-8B-shaped model truncated to "
+                                   f"{n_layers} blocks, {n_seq}x{T} random token ids, through gptq_quantization(); sequences, "
+                                   f"Cholesky chains and weight rows partitioned over {world} GPU(s)",
+                       "l2": "calibration activations of a block (2 GB) > 126 MB L2"},
+            "exported_layers": n_keys, "phases_s": phases, "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model"])
+    ap.add_argument("--model-layers", type=int, default=2)
+    ap.add_argument("--calib-seqs", type=int, default=128)
     ap.add_argument("--gptq-rows", type=int, default=14336)
     ap.add_argument("--gptq-cols", type=int, default=4096)
     ap.add_argument("--m", type=int, default=8192)
@@ -586,6 +682,8 @@ def main():
             raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
         if args.workload == "gptq":
             run_gptq(args)
+        elif args.workload == "gptq-model":
+            run_gptq_model(args)
         else:
             run_ours(args)
 

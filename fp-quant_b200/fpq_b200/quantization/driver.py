@@ -9,7 +9,12 @@ Differences in structure (same mathematics):
     function for any architecture whose blocks are built from nn.Linear;
   * linears that read the same tensor (q/k/v, gate/up) share one Hessian accumulation instead of
     accumulating identical matrices once per layer;
-  * all numeric steps are the CUDA kernels of this package.
+  * all numeric steps are the CUDA kernels of this package;
+  * when torch.distributed is initialised with several ranks (one per GPU, every rank holding the same
+    model), the calibration sequences are split over the ranks, the Hessians are all-reduced, the
+    Cholesky-inverse chains of a block's distinct Hessians run on different ranks and their factors are
+    broadcast, and the rows of every weight are split for the column loop and gathered.  Every rank
+    returns the full result.
 """
 from __future__ import annotations
 
@@ -20,6 +25,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .. import dist as fdist
 from .. import ops
 from ..transforms.transforms import build_transform, get_transform_matrix
 from .gptq import GPTQ, get_relative_mse_error
@@ -30,6 +36,28 @@ from .quantizer import Quantizer
 
 class ForwardInterrupt(Exception):
     pass
+
+
+class _Phases:
+    """Device time per phase of the driver (CUDA events; read with `.summary()` after a synchronise)."""
+
+    def __init__(self):
+        self.marks = []
+
+    def mark(self, name: str) -> None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.marks.append((name, e))
+
+    def summary(self) -> Dict[str, float]:
+        torch.cuda.synchronize()
+        out: Dict[str, float] = {}
+        for (n0, e0), (n1, e1) in zip(self.marks[:-1], self.marks[1:]):
+            out[n1] = out.get(n1, 0.0) + e0.elapsed_time(e1) * 1e-3
+        return out
+
+
+last_phases: Optional[_Phases] = None     # phases of the most recent gptq_quantization call
 
 
 class InputCollector(nn.Module):
@@ -162,15 +190,25 @@ def _run_block(block, input_args, input_kwargs, device, args, keep_outputs: bool
 def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device) -> Tuple[dict, dict]:
     """MR-GPTQ over the transformer blocks of `model` (gptq.py:225-470).  Returns
     (quantized_state_dict, non_quantized_state_dict) with the reference's per-layer keys."""
-    print("GPTQ quantization...")
+    if fdist.world()[0] == 0:
+        print("GPTQ quantization...")
     orig_dtype = model.config.torch_dtype if args.dtype == "auto" else args.dtype
     offload = "cpu" if args.cpu_offload_activations else device
     quantized, non_quantized = {}, {}
     wkw = _quantizer_kwargs(args, "w")
-    input_args, input_kwargs = _collect_block_inputs(model, calibration_data, args, device)
+    global last_phases
+    ph = last_phases = _Phases()
+    ph.mark("start")
+    rank, world_size = fdist.world()
+    n_total = len(calibration_data)
+    lo, hi = fdist.shard_bounds(n_total, world_size, rank)
+    n_local = hi - lo
+    input_args, input_kwargs = _collect_block_inputs(model, calibration_data[lo:hi], args, device)
+    ph.mark("collect_inputs")
 
     for block_idx, block in enumerate(model.model.layers):
-        print(f"Processing block {block_idx}...")
+        if rank == 0:
+            print(f"Processing block {block_idx}...")
         block.to(device=device, dtype=orig_dtype).requires_grad_(False)
         layers = _wrap_block(block, args, device)
 
@@ -195,7 +233,9 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                     for n in names:
                         handles[n].quantizer.global_scale = fused.clone()
 
+        ph.mark("setup")
         _run_block(block, input_args, input_kwargs, device, args, keep_outputs=False, offload_device=offload)   # Hessians
+        ph.mark("hessian_pass")
 
         for name, layer in layers.items():
             layer.input_sink = None
@@ -204,16 +244,70 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             if layer.act_quantizer is not None:
                 layer.act_quantizer._track_global_scale = False
 
+        # ---- multi-GPU: one Hessian per distinct input, summed over the ranks' sequences
+        if world_size > 1:
+            for grp, lname in leaders.items():
+                h = handles[lname]
+                if h.H is None:
+                    h.H = torch.zeros((h.d_col, h.d_col), device=device, dtype=torch.float32)
+                h.H.mul_(float(n_local) / float(n_total))     # local running mean -> this rank's share of the global mean
+                fdist.allreduce_sum_(h.H)
+                h.num_samples = n_total
+            for layer in layers.values():
+                if layer.act_quantizer is not None and layer.act_quantizer.global_scale.numel() == 1:
+                    gs = layer.act_quantizer.global_scale.to(device)
+                    layer.act_quantizer.global_scale = fdist.allreduce_min_(gs)
+
+        ph.mark("allreduce")
+        # ---- Cholesky-inverse factors: one per distinct Hessian when no linear of the group has an
+        # all-zero weight column (the dead-column fix of gptq.py:203-208 is then the identity and the damped
+        # H, hence U, is the same for all of them); the chains of a block run on different ranks
+        shared_U: Dict[str, torch.Tensor] = {}
+        group_members: Dict[str, List[str]] = {}
+        for name in handles:
+            group_members.setdefault(_input_group(name.split(".")[-1]), []).append(name)
+        share_ok = {grp: not any(bool((handles[n].layer.weight == 0).all(dim=0).any().item()) for n in names)
+                    for grp, names in group_members.items()}
+        if True:
+            order = sorted((g for g in group_members if share_ok[g]), key=lambda g: -handles[leaders[g]].d_col)
+            for i, grp in enumerate(order):
+                owner = i % world_size
+                lead = handles[leaders[grp]]
+                lead.H_undamped = lead.H.clone()
+                lead.quantization_pre_step()
+                lead.prepare_hessian()
+                if rank == owner:
+                    U = lead._get_hessian_inverse(prepared=True)
+                else:
+                    U = torch.empty((lead.d_col, lead.d_col), device=device, dtype=torch.float32)
+                shared_U[grp] = (U, owner)
+            for grp, (U, owner) in shared_U.items():      # after all chains were queued: they overlap across ranks
+                if world_size > 1:
+                    torch.distributed.broadcast(U, src=owner)
+                shared_U[grp] = U
+
+        ph.mark("factor")
         for name, handle in handles.items():
-            leader = handles[leaders[_input_group(name.split(".")[-1])]]
+            grp = _input_group(name.split(".")[-1])
+            leader = handles[leaders[grp]]
             if handle is not leader:
                 handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
-            else:
+            elif not hasattr(handle, "H_undamped"):
                 handle.H_undamped = handle.H.clone()
-            wq, qweight, scales = handle.quantize()
+            U_in = None
+            if grp in shared_U:
+                U_in = shared_U[grp]
+                if handle is not leader:
+                    handle.quantization_pre_step()
+                    handle.prepare_hessian()       # same damping as the leader's: leaves the damped H for the MSE
+            if U_in is not None:
+                wq, qweight, scales = handle.step(U_in)
+            else:
+                wq, qweight, scales = handle.quantize()
             orig = handle.layer.weight
             rel = get_relative_mse_error(wq.float(), orig.float(), handle.H)
-            print(f"[{name:16}]: Relative MSE error: {rel.item():.2e}")
+            if rank == 0:
+                print(f"[{name:16}]: Relative MSE error: {rel.item():.2e}")
             handle.layer.weight.data = wq
             if args.export_quantized_model:
                 wgs = handle.quantizer.global_scale.to(scales.device)
@@ -225,7 +319,9 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                 else:
                     quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, dqweight=wq)
 
+        ph.mark("column_loops")
         _run_block(block, input_args, input_kwargs, device, args, keep_outputs=True, offload_device=offload)
+        ph.mark("update_pass")
         if getattr(args, "cpu_offload_modules", False):
             block.cpu()
         del handles

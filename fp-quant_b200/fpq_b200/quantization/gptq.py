@@ -69,14 +69,30 @@ class GPTQ:
         self.pre_step_completed = True
 
     @torch.no_grad()
-    def step(self) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor]:
+    def step(self, U: Optional[torch.Tensor] = None, process_group=None) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor]:
         """Returns (dequantised weight in the layer dtype, E2M1 grid values or None, fp32 group scales).
-        `self.H` is left damped, as in the reference, where the caller reuses it for the relative MSE."""
+        `self.H` is left damped, as in the reference, where the caller reuses it for the relative MSE.
+
+        Two additions for multi-GPU drivers (the reference is single-GPU): `U` hands in a factor that was
+        computed elsewhere (then `self.H` must already be damped), and when torch.distributed is
+        initialised with more than one rank the rows of the weight -- independent given U -- are split
+        over the ranks of `process_group` and the results gathered, so every rank returns the full tensors."""
+        from .. import dist as fdist
+
         group = self.quantizer.group_size
         scales, _ = self.quantizer.get_quantization_params(self.W)        # static scales, gptq.py:142
-        U = self._get_hessian_inverse()
-        w = self.W.clone()
-        self.packed_codes = ops.gptq_quantize(w, scales.float().contiguous(), U, group, want_codes=True)
+        if U is None:
+            U = self._get_hessian_inverse()
+        rank, ws = fdist.world(process_group)
+        if ws > 1 and self.d_row >= 128 * ws:
+            lo, hi = fdist.shard_bounds(self.d_row, ws, rank, multiple=128)
+            w_loc = self.W[lo:hi].clone()
+            codes_loc = ops.gptq_quantize(w_loc, scales[lo:hi].float().contiguous(), U, group, want_codes=True)
+            w = fdist.allgather_rows(w_loc, self.d_row, 128, process_group)
+            self.packed_codes = fdist.allgather_rows(codes_loc, self.d_row, 128, process_group)
+        else:
+            w = self.W.clone()
+            self.packed_codes = ops.gptq_quantize(w, scales.float().contiguous(), U, group, want_codes=True)
         qweight = None
         if self.export_quantized_model:
             lut = torch.tensor(FP4_CODE_VALUES, dtype=self.W_dtype, device=w.device)
@@ -85,14 +101,20 @@ class GPTQ:
         return w.to(self.W_dtype), qweight, scales
 
     @torch.no_grad()
-    def _get_hessian_inverse(self) -> torch.Tensor:
+    def prepare_hessian(self) -> None:
+        """Dead-column fix and damping of `self.H` in place (first half of gptq.py:200-211)."""
         ops.hessian_prepare(self.H, self.W, self.rel_damp)
+
+    @torch.no_grad()
+    def _get_hessian_inverse(self, prepared: bool = False) -> torch.Tensor:
+        if not prepared:
+            self.prepare_hessian()
         U, status = ops.cholesky_inverse_upper(self.H)
         self.used_identity_fallback = bool(status.item())
         if self.used_identity_fallback:      # the reference's `except:` branch (gptq.py:216-217)
             U = torch.eye(self.d_col, device=self.H.device, dtype=torch.float32)
         return U
 
-    def quantize(self):
+    def quantize(self, U: Optional[torch.Tensor] = None, process_group=None):
         self.quantization_pre_step()
-        return self.step()
+        return self.step(U, process_group)
