@@ -598,7 +598,7 @@ def run_gptq_model(args):
         a_observer=QuantizationObserver.MINMAX, w_group_size=16, a_group_size=16, scale_precision=ScalePrecision.E4M3,
         transform_class="hadamard", hadamard_group_size=128, cpu_offload_activations=False, cpu_offload_modules=False,
         quantization_order=QuantizationOrder.DEFAULT, rel_damp=0.01, export_quantized_model="realquant",
-        dtype=torch.bfloat16, fuse_global_scale=False, amp=False)
+        dtype=torch.bfloat16, fuse_global_scale=False, amp=False, calibration_batch=args.calib_batch)
     g = torch.Generator().manual_seed(5)
     data = [torch.randint(0, cfg.vocab_size, (1, T), generator=g) for _ in range(n_seq)]
 
@@ -649,7 +649,7 @@ def run_gptq_model(args):
             "vs_baseline": None, "dtype": "bf16 forward and Hessian products, fp32-accurate factorisation and column loop",
             "data": "synthetic",
             "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4 W4A4) of a random-init Llama-3.1-8B-shaped model truncated to "
-                                   f"{n_layers} blocks, {n_seq}x{T} random token ids, through gptq_quantization(); sequences, "
+                                   f"{n_layers} blocks, {n_seq}x{T} random token ids ({args.calib_batch} per block call), through gptq_quantization(); sequences, "
                                    f"Cholesky chains and weight rows partitioned over {world} GPU(s)",
                        "l2": "calibration activations of a block (2 GB) > 126 MB L2"},
             "exported_layers": n_keys, "phases_s": phases, "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
@@ -668,6 +668,7 @@ def main():
     ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model"])
     ap.add_argument("--model-layers", type=int, default=2)
     ap.add_argument("--calib-seqs", type=int, default=128)
+    ap.add_argument("--calib-batch", type=int, default=1, help="sequences per block call in the model-level GPTQ driver")
     ap.add_argument("--gptq-rows", type=int, default=14336)
     ap.add_argument("--gptq-cols", type=int, default=4096)
     ap.add_argument("--m", type=int, default=8192)

@@ -324,15 +324,45 @@ constexpr int SUB = 32;   // columns per thread
 constexpr int US_LD = NB + 4 * (NB / SUB);
 __device__ __forceinline__ int us_col(int col) { return col + 4 * (col / SUB); }
 
+// Correctly rounded y / s from r = rcp(s): multiply and two fused residual corrections (valid while s, r and
+// the quotient stay in the normal range; the caller checks s).
+__device__ __forceinline__ float div_by(float y, float s, float r) {
+  float q = y * r;
+  float e = fmaf(-s, q, y);
+  q = fmaf(e, r, q);
+  e = fmaf(-s, q, y);
+  return fmaf(e, r, q);
+}
+__device__ __forceinline__ bool rcp_safe(float s) {
+  const float a = fabsf(s);
+  return a > 7.8886e-31f /* 2^-100 */ && a < 1.2676e30f /* 2^100 */;
+}
+// E2M1 code of v (round to nearest, ties to even, saturating; every zero as 0x8) and its grid value.
+__device__ __forceinline__ uint32_t e2m1_code_hw(float v, float& value) {
+  uint32_t byte;
+  asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t; }" : "=r"(byte) : "f"(0.0f), "f"(v));
+  uint32_t code = byte & 0xFu;
+  if ((code & 7u) == 0u) code = 8u;
+  uint32_t h2;
+  asm("{ .reg .b8 t; cvt.u8.u32 t, %1; cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "r"(code));
+  value = __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
+  return code;
+}
+
 template <int G>
 __global__ void __launch_bounds__(512) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C, int64_t c1,
                                                          const float* __restrict__ scales,
                                                          const float* __restrict__ U, float* __restrict__ Err,
                                                          uint8_t* __restrict__ codes) {
-  extern __shared__ float Us[];   // NB rows of US_LD floats
+  extern __shared__ float Us[];   // NB rows of US_LD floats, then the reciprocals of the diagonal
+  float* rdiag = Us + NB * US_LD;
   for (int idx = threadIdx.x; idx < NB * NB / 4; idx += blockDim.x) {
     const int i = (idx * 4) / NB, j = (idx * 4) % NB;
     *reinterpret_cast<float4*>(&Us[i * US_LD + us_col(j)]) = *reinterpret_cast<const float4*>(&U[(c1 + i) * C + c1 + j]);
+  }
+  for (int i = threadIdx.x; i < NB; i += blockDim.x) {
+    const float dgl = U[(c1 + i) * C + c1 + i];
+    rdiag[i] = rcp_safe(dgl) ? __frcp_rn(dgl) : 0.0f;      // 0 marks "divide the slow way"
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
@@ -342,9 +372,12 @@ __global__ void __launch_bounds__(512) gptq_block_kernel(float* __restrict__ W, 
   if (!live) row = rows - 1;                   // keep the quad's shuffles uniform; nothing is stored
 
   constexpr int NGRP = SUB / G;
-  float sc[NGRP];
+  float sc[NGRP], rsc[NGRP];
 #pragma unroll
-  for (int g = 0; g < NGRP; ++g) sc[g] = scales[row * (C / G) + (c1 + SUB * q) / G + g];
+  for (int g = 0; g < NGRP; ++g) {
+    sc[g] = scales[row * (C / G) + (c1 + SUB * q) / G + g];
+    rsc[g] = rcp_safe(sc[g]) ? __frcp_rn(sc[g]) : 0.0f;
+  }
   float w[SUB], err[SUB];
   {
     const float4* wp = reinterpret_cast<const float4*>(W + row * C + c1 + SUB * q);
@@ -368,11 +401,16 @@ __global__ void __launch_bounds__(512) gptq_block_kernel(float* __restrict__ W, 
     for (int ii = 0; ii < SUB; ++ii) {
       float e = 0.0f;
       if (owner) {
-        const float s = sc[ii / G];
-        const uint32_t code = e2m1_code(__fdiv_rn(w[ii], s));
+        // w / s and (w - wq) / U[i,i] as IEEE divisions (the reference's), computed from reciprocals
+        const float s = sc[ii / G], rs = rsc[ii / G];
+        const float qv = rs != 0.0f ? div_by(w[ii], s, rs) : __fdiv_rn(w[ii], s);
+        float gv;
+        const uint32_t code = e2m1_code_hw(qv, gv);
         cw[ii / 8] |= code << (4 * (ii % 8));
-        const float wq = __fmul_rn(e2m1_value(code), s);
-        e = __fdiv_rn(__fsub_rn(w[ii], wq), Ub[ii * US_LD + (SUB + 4) * b + ii]);
+        const float wq = __fmul_rn(gv, s);
+        const float dgl = Ub[ii * US_LD + (SUB + 4) * b + ii], rd = rdiag[SUB * b + ii];
+        const float diff = __fsub_rn(w[ii], wq);
+        e = rd != 0.0f ? div_by(diff, dgl, rd) : __fdiv_rn(diff, dgl);
         err[ii] = e;
       }
       e = __shfl_sync(0xffffffffu, e, (lane & ~3) | b);
@@ -575,7 +613,7 @@ extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const flo
   static bool configured[64] = {};
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
-  const int smem = NB * US_LD * (int)sizeof(float);
+  const int smem = (NB * US_LD + NB) * (int)sizeof(float);
   if (dev < 64 && !configured[dev]) {
     FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

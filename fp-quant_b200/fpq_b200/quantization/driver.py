@@ -93,24 +93,48 @@ def _first(x):
 
 class RotatedLinear(nn.Module):
     """y = fake_quant(rotate(x)) @ rotate(W)^T + b.  While `_train_mode` the weight is rotated on the
-    fly (it is still the original); afterwards it holds the rotated, quantised weight."""
+    fly (it is still the original); afterwards it holds the rotated, quantised weight.
 
-    def __init__(self, linear: nn.Linear, transform, act_quantizer: Optional[Quantizer]):
+    Linears that are fed the same tensor (q/k/v, gate/up) share `group_state`: the first of them to see a
+    tensor rotates and fake-quantises it, the others reuse the result (same activation quantiser, so the
+    numbers are the ones each would have computed)."""
+
+    def __init__(self, linear: nn.Linear, transform, act_quantizer: Optional[Quantizer], group_state: Optional[dict] = None):
         super().__init__()
         self.weight, self.bias = linear.weight, linear.bias
         self.in_features, self.out_features = linear.in_features, linear.out_features
         self.transform, self.act_quantizer = transform, act_quantizer
         self._train_mode = True
         self.input_sink = None          # called with the rotated, unquantised input (Hessian accumulation)
+        self.group_state = group_state if group_state is not None else {}
+        self._rotated = None            # (weight version, rotated weight) while the weight is still the original
+
+    def _prepared_input(self, x: torch.Tensor) -> torch.Tensor:
+        st = self.group_state
+        if st.get("x") is x and st.get("version") == x._version:
+            return st["xq"]
+        xr = self.transform(x)
+        if st.get("sink") is not None:
+            st["sink"](xr)
+        xq = xr
+        if self.act_quantizer is not None:
+            xq = self.act_quantizer.fused_fake_quantize(xr, hadamard_group=0, ste=False)
+        st["x"], st["version"], st["xq"] = x, x._version, xq
+        return xq
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        xr = self.transform(x)
-        if self.input_sink is not None:
-            self.input_sink(xr)
-        w = self.transform(self.weight, inv_t=True) if self._train_mode else self.weight
-        if self.act_quantizer is not None:
-            xr = self.act_quantizer.fused_fake_quantize(xr, hadamard_group=0, ste=False)
-        return F.linear(xr, w, self.bias)
+        if self.input_sink is not None:          # legacy hook of a stand-alone module
+            self.group_state["sink"] = self.input_sink
+        xq = self._prepared_input(x)
+        if self._train_mode:
+            # the same weight is rotated for every calibration sequence: keep the result until the weight changes
+            if self._rotated is None or self._rotated[0] != self.weight._version:
+                self._rotated = (self.weight._version, self.transform(self.weight, inv_t=True))
+            w = self._rotated[1]
+        else:
+            self._rotated = None
+            w = self.weight
+        return F.linear(xq, w, self.bias)
 
 
 # linears that are fed the same tensor share a Hessian
@@ -136,6 +160,8 @@ def _quantizer_kwargs(args, prefix: str) -> Optional[dict]:
 def _wrap_block(block: nn.Module, args, device) -> Dict[str, RotatedLinear]:
     akw = _quantizer_kwargs(args, "a")
     wrapped = {}
+    states: Dict[str, dict] = {}
+    quantizers: Dict[str, Optional[Quantizer]] = {}
     for name, module in list(block.named_modules()):
         if isinstance(module, nn.Linear):
             parent = block
@@ -144,15 +170,41 @@ def _wrap_block(block: nn.Module, args, device) -> Dict[str, RotatedLinear]:
                 parent = getattr(parent, p)
             t = build_transform(args.transform_class, size=module.in_features, device=device,
                                 group_size=args.hadamard_group_size)
-            r = RotatedLinear(module, t, Quantizer(**akw) if akw else None)
+            grp = ".".join(path + [_input_group(leaf)])          # same parent module, same input
+            if grp not in states:
+                states[grp] = {}
+                quantizers[grp] = Quantizer(**akw) if akw else None
+            r = RotatedLinear(module, t, quantizers[grp], states[grp])
             setattr(parent, leaf, r)
             wrapped[name] = r
     return wrapped
 
 
+def _release_group_states(layers: Dict[str, "RotatedLinear"]) -> None:
+    for layer in layers.values():
+        layer.group_state.pop("x", None)
+        layer.group_state.pop("xq", None)
+
+
+def _to_host_async(t: torch.Tensor) -> torch.Tensor:
+    """Device tensor -> page-locked host tensor without stalling the stream (the drivers synchronise once
+    before they return the export dicts)."""
+    if not t.is_cuda:
+        return t
+    out = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+    out.copy_(t, non_blocking=True)
+    return out
+
+
+_matrix_cache: Dict[tuple, torch.Tensor] = {}
+
+
 def _export_entry(args, orig_dtype, device, weight_gs, act_gs, **tensors) -> dict:
-    m = get_transform_matrix(args.transform_class, args.hadamard_group_size, device, orig_dtype).cpu()
-    entry = {k: v.cpu() for k, v in tensors.items()}
+    key = (str(args.transform_class), args.hadamard_group_size, str(orig_dtype))
+    if key not in _matrix_cache:
+        _matrix_cache[key] = get_transform_matrix(args.transform_class, args.hadamard_group_size, device, orig_dtype).cpu()
+    m = _matrix_cache[key].clone()
+    entry = {k: _to_host_async(v.contiguous()) for k, v in tensors.items()}
     entry.update({"forward_hadamard_matrix": m, "backward_hadamard_matrix": m.clone(),
                   "weight_global_scale": weight_gs.clone(), "act_global_scale": act_gs.clone()})
     return entry
@@ -173,17 +225,39 @@ def _collect_block_inputs(model, calibration_data, args, device):
 
 
 def _run_block(block, input_args, input_kwargs, device, args, keep_outputs: bool, offload_device):
-    for a, kw in zip(input_args, input_kwargs):
+    """Runs the block over the recorded calibration inputs (gptq.py:389-393, 446-457).  With
+    `args.calibration_batch` > 1 several sequences go through the block in one call (their hidden states
+    concatenated along the batch dimension, the other arguments taken from the first of them, which must
+    therefore be the same for all sequences: no padding masks): fewer, larger launches.  The Hessian is
+    unchanged by this (a sum over sequences); the activation quantiser's running-minimum tensor scale
+    then advances per batch instead of per sequence."""
+    batch = max(1, int(getattr(args, "calibration_batch", 1)))
+    n = len(input_args)
+    for i0 in range(0, n, batch):
+        idx = list(range(i0, min(i0 + batch, n)))
+        a0, kw0 = input_args[i0], input_kwargs[i0]
+        if len(idx) == 1:
+            call_args, call_kw = _to(a0, device), _to(kw0, device)
+        elif len(a0) > 0:
+            hs = torch.cat([_to(input_args[i][0], device) for i in idx], dim=0)
+            call_args, call_kw = (hs,) + tuple(_to(a0[1:], device)), _to(kw0, device)
+        elif "hidden_states" in kw0:
+            call_kw = dict(_to(kw0, device))
+            call_kw["hidden_states"] = torch.cat([_to(input_kwargs[i]["hidden_states"], device) for i in idx], dim=0)
+            call_args = ()
+        else:
+            raise ValueError("Unsupported block input format.")
         with torch.no_grad(), torch.amp.autocast(device_type="cuda", enabled=getattr(args, "amp", False)):
-            out = block(*_to(a, device), **_to(kw, device))
+            out = block(*call_args, **call_kw)
         if keep_outputs:
             out = _first(out).to(offload_device)
-            if len(a) > 0:
-                a[0].data = out
-            elif "hidden_states" in kw:
-                kw["hidden_states"] = out
-            else:
-                raise ValueError("Unsupported block input format.")
+            rows = [x.shape[0] for x in ([input_args[i][0] for i in idx] if len(a0) > 0
+                                        else [input_kwargs[i]["hidden_states"] for i in idx])]
+            for i, piece in zip(idx, torch.split(out, rows, dim=0)):
+                if len(a0) > 0:
+                    input_args[i][0].data = piece
+                else:
+                    input_kwargs[i]["hidden_states"] = piece
 
 
 @torch.no_grad()
@@ -224,7 +298,7 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             grp = _input_group(name.split(".")[-1])
             if grp not in leaders:
                 leaders[grp] = name
-                layer.input_sink = (lambda h: (lambda x: h.update(x)))(handles[name])
+                layer.group_state["sink"] = (lambda h: (lambda x: h.update(x)))(handles[name])
         if getattr(args, "fuse_global_scale", False) and args.scale_precision == ScalePrecision.E4M3:
             for pat in (r"(q|k|v)_proj$", r"(gate|up)_proj$"):       # gptq.py:367-383
                 names = [n for n in handles if re.search(pat, n)]
@@ -239,7 +313,11 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
 
         for name, layer in layers.items():
             layer.input_sink = None
-            layer.weight.data = layer.transform(layer.weight, inv_t=True)      # rotate once (gptq.py:395-401)
+            layer.group_state["sink"] = None
+            cached = layer._rotated
+            layer.weight.data = (cached[1] if cached is not None and cached[0] == layer.weight._version
+                                 else layer.transform(layer.weight, inv_t=True))      # rotate once (gptq.py:395-401)
+            layer._rotated = None
             layer._train_mode = False
             if layer.act_quantizer is not None:
                 layer.act_quantizer._track_global_scale = False
@@ -320,11 +398,14 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                     quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, dqweight=wq)
 
         ph.mark("column_loops")
+        _release_group_states(layers)
         _run_block(block, input_args, input_kwargs, device, args, keep_outputs=True, offload_device=offload)
+        _release_group_states(layers)
         ph.mark("update_pass")
         if getattr(args, "cpu_offload_modules", False):
             block.cpu()
         del handles
+    torch.cuda.synchronize(device)        # the asynchronous copies of the export tensors have landed
     return quantized, non_quantized
 
 
@@ -358,4 +439,5 @@ def rtn_quantization(model, calibration_data: List[torch.Tensor], args, device) 
                     quantized[key] = _export_entry(args, orig_dtype, device, q.global_scale, ags, qweight=codes, scales=sbytes)
                 else:
                     quantized[key] = _export_entry(args, orig_dtype, device, q.global_scale, ags, dqweight=wq)
+    torch.cuda.synchronize(device)
     return quantized, non_quantized

@@ -95,9 +95,11 @@ class GPTQ:
             self.packed_codes = ops.gptq_quantize(w, scales.float().contiguous(), U, group, want_codes=True)
         qweight = None
         if self.export_quantized_model:
+            # grid values of both nibbles of a byte from one 256-entry table
             lut = torch.tensor(FP4_CODE_VALUES, dtype=self.W_dtype, device=w.device)
-            c = self.packed_codes
-            qweight = torch.stack((lut[(c & 0xF).long()], lut[(c >> 4).long()]), dim=-1).reshape(self.W.shape)
+            byte = torch.arange(256, device=w.device)
+            lut2 = torch.stack((lut[byte & 0xF], lut[byte >> 4]), dim=-1)
+            qweight = lut2[self.packed_codes.int()].reshape(self.W.shape)
         return w.to(self.W_dtype), qweight, scales
 
     @torch.no_grad()
