@@ -337,65 +337,89 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                     layer.act_quantizer.global_scale = fdist.allreduce_min_(gs)
 
         ph.mark("allreduce")
-        # ---- Cholesky-inverse factors: one per distinct Hessian when no linear of the group has an
-        # all-zero weight column (the dead-column fix of gptq.py:203-208 is then the identity and the damped
-        # H, hence U, is the same for all of them); the chains of a block run on different ranks
-        shared_U: Dict[str, torch.Tensor] = {}
+        # ---- who does what.  One Cholesky-inverse chain per distinct Hessian when no linear of the group has an
+        # all-zero weight column (the dead-column fix of gptq.py:203-208 is then the identity and the damped H,
+        # hence U, is the same for all of them).  The chains go to different ranks, largest first; every linear
+        # is quantised, whole, by one rank (the column loop is bound by the latency of its dependent steps, not
+        # by the number of rows): the leader of a group stays with the rank that factors its Hessian, the other
+        # members move to idle ranks when there are any.  Results are broadcast.
         group_members: Dict[str, List[str]] = {}
         for name in handles:
             group_members.setdefault(_input_group(name.split(".")[-1]), []).append(name)
         share_ok = {grp: not any(bool((handles[n].layer.weight == 0).all(dim=0).any().item()) for n in names)
                     for grp, names in group_members.items()}
-        if True:
-            order = sorted((g for g in group_members if share_ok[g]), key=lambda g: -handles[leaders[g]].d_col)
-            for i, grp in enumerate(order):
-                owner = i % world_size
-                lead = handles[leaders[grp]]
-                lead.H_undamped = lead.H.clone()
+        group_order = sorted(group_members, key=lambda g: -handles[leaders[g]].d_col)
+        group_owner = {g: i % world_size for i, g in enumerate(group_order)}
+        idle = [r for r in range(world_size) if r not in set(group_owner.values())]
+        layer_owner: Dict[str, int] = {}
+        for g in group_order:
+            for k, n in enumerate(group_members[g]):
+                layer_owner[n] = group_owner[g] if (k == 0 or not idle) else idle.pop(0)
+
+        shared_U: Dict[str, torch.Tensor] = {}
+        for g in group_order:
+            lead = handles[leaders[g]]
+            lead.H_undamped = lead.H.clone()
+            if not share_ok[g]:
+                continue
+            owner = group_owner[g]
+            elsewhere = any(layer_owner[n] != owner for n in group_members[g])
+            if rank == owner:
                 lead.quantization_pre_step()
                 lead.prepare_hessian()
-                if rank == owner:
-                    U = lead._get_hessian_inverse(prepared=True)
-                else:
-                    U = torch.empty((lead.d_col, lead.d_col), device=device, dtype=torch.float32)
-                shared_U[grp] = (U, owner)
-            for grp, (U, owner) in shared_U.items():      # after all chains were queued: they overlap across ranks
-                if world_size > 1:
-                    torch.distributed.broadcast(U, src=owner)
-                shared_U[grp] = U
+                shared_U[g] = lead._get_hessian_inverse(prepared=True)
+            elif elsewhere:
+                shared_U[g] = torch.empty((lead.d_col, lead.d_col), device=device, dtype=torch.float32)
+        for g in group_order:                       # after all chains were queued: they overlap across ranks
+            if share_ok[g] and world_size > 1 and any(layer_owner[n] != group_owner[g] for n in group_members[g]):
+                torch.distributed.broadcast(shared_U[g], src=group_owner[g])
 
         ph.mark("factor")
+        results = {}
         for name, handle in handles.items():
+            if layer_owner[name] != rank:
+                continue
             grp = _input_group(name.split(".")[-1])
             leader = handles[leaders[grp]]
-            if handle is not leader:
-                handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
-            elif not hasattr(handle, "H_undamped"):
-                handle.H_undamped = handle.H.clone()
-            U_in = None
-            if grp in shared_U:
-                U_in = shared_U[grp]
-                if handle is not leader:
+            if grp in shared_U and share_ok[grp]:
+                if not (handle is leader and rank == group_owner[grp]):     # the factoring rank's leader is prepared
+                    handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
                     handle.quantization_pre_step()
                     handle.prepare_hessian()       # same damping as the leader's: leaves the damped H for the MSE
-            if U_in is not None:
-                wq, qweight, scales = handle.step(U_in)
+                wq, qweight, scales = handle.step(shared_U[grp])
             else:
+                if handle is not leader:
+                    handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
                 wq, qweight, scales = handle.quantize()
-            orig = handle.layer.weight
-            rel = get_relative_mse_error(wq.float(), orig.float(), handle.H)
+            rel = get_relative_mse_error(wq.float(), handle.layer.weight.float(), handle.H)
+            results[name] = (wq, handle.packed_codes, scales.float().contiguous(), rel.reshape(1))
+        shared_U.clear()
+
+        for name, handle in handles.items():        # same order on every rank: one broadcast group per linear
+            rows, cols = handle.d_row, handle.d_col
+            if name in results:
+                wq, codes, scales, rel = results[name]
+            else:
+                wq = torch.empty((rows, cols), device=device, dtype=handle.W_dtype)
+                codes = torch.empty((rows, cols // 2), device=device, dtype=torch.uint8)
+                scales = torch.empty((rows, cols // handle.quantizer.group_size), device=device, dtype=torch.float32)
+                rel = torch.empty(1, device=device, dtype=torch.float32)
+            if world_size > 1:
+                for t in (wq, codes, scales, rel):
+                    torch.distributed.broadcast(t, src=layer_owner[name])
             if rank == 0:
                 print(f"[{name:16}]: Relative MSE error: {rel.item():.2e}")
             handle.layer.weight.data = wq
             if args.export_quantized_model:
-                wgs = handle.quantizer.global_scale.to(scales.device)
+                wgs = handle.quantizer.global_scale.to(device)
                 ags = handle.layer.act_quantizer.global_scale if handle.layer.act_quantizer is not None else torch.ones(1)
                 key = f"model.layers.{block_idx}.{name}"
                 if args.export_quantized_model == "realquant":
-                    quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, qweight=handle.packed_codes,
+                    quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, qweight=codes,
                                                    scales=cast_scales_to_eXmY(scales * wgs, args.scale_precision))
                 else:
                     quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, dqweight=wq)
+        results.clear()
 
         ph.mark("column_loops")
         _release_group_states(layers)

@@ -69,14 +69,15 @@ class GPTQ:
         self.pre_step_completed = True
 
     @torch.no_grad()
-    def step(self, U: Optional[torch.Tensor] = None, process_group=None) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor]:
+    def step(self, U: Optional[torch.Tensor] = None, shard_rows: bool = False,
+             process_group=None) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor]:
         """Returns (dequantised weight in the layer dtype, E2M1 grid values or None, fp32 group scales).
         `self.H` is left damped, as in the reference, where the caller reuses it for the relative MSE.
 
         Two additions for multi-GPU drivers (the reference is single-GPU): `U` hands in a factor that was
-        computed elsewhere (then `self.H` must already be damped), and when torch.distributed is
-        initialised with more than one rank the rows of the weight -- independent given U -- are split
-        over the ranks of `process_group` and the results gathered, so every rank returns the full tensors."""
+        computed elsewhere (then `self.H` must already be damped); with `shard_rows` (a collective call:
+        every rank of `process_group` must make it) the rows of the weight -- independent given U -- are
+        split over the ranks and the results gathered, so every rank returns the full tensors."""
         from .. import dist as fdist
 
         group = self.quantizer.group_size
@@ -84,7 +85,7 @@ class GPTQ:
         if U is None:
             U = self._get_hessian_inverse()
         rank, ws = fdist.world(process_group)
-        if ws > 1 and self.d_row >= 128 * ws:
+        if shard_rows and ws > 1 and self.d_row >= 128 * ws:
             lo, hi = fdist.shard_bounds(self.d_row, ws, rank, multiple=128)
             w_loc = self.W[lo:hi].clone()
             codes_loc = ops.gptq_quantize(w_loc, scales[lo:hi].float().contiguous(), U, group, want_codes=True)
@@ -117,6 +118,6 @@ class GPTQ:
             U = torch.eye(self.d_col, device=self.H.device, dtype=torch.float32)
         return U
 
-    def quantize(self, U: Optional[torch.Tensor] = None, process_group=None):
+    def quantize(self, U: Optional[torch.Tensor] = None, shard_rows: bool = False, process_group=None):
         self.quantization_pre_step()
-        return self.step(U, process_group)
+        return self.step(U, shard_rows, process_group)
