@@ -684,15 +684,84 @@ def run_gptq_model(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ column-parallel W4A4 linear
+def run_tp_linear(args):
+    """The largest linear of a Qwen3-14B block (gate/up projection, K = 5120, N = 17408) as a column-split
+    tensor-parallel FPQuantLinear: every rank quantises the replicated activations (prefill M = 8 x 2048 = 16384
+    tokens, or --m), multiplies by its N/p rows and the slices are all-gathered along N.  Strong scaling: the
+    layer is fixed, `value` is the whole layer's TFLOP/s."""
+    import torch.distributed as dist
+
+    from fpq_b200 import ops
+    from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    from fpq_b200.fp_quant.module.tp_linear import column_parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    K, N, M = 5120, 17408, args.m if args.m != 8192 else 16384
+    cfg = FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, forward_method="abs_max", backward_dtype=FPQuantDtype.BF16,
+                        hadamard_group_size=32)
+    full = FPQuantLinear(K, N, cfg, bias=False, device=dev, dtype=torch.bfloat16)
+    full.weight.data.copy_(make_weight(N, K, seed=3))
+    full.pre_forward()
+    layer = column_parallel(full, None, gather_output=True, fused=args.tp_fused)
+    del full
+    xs = [make_activations(M, K, seed=100 + i).to(dev) for i in range(3)]      # rotate inputs: 3 x 168 MB > L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        layer(xs[i % 3])
+    barrier()
+    with ClockSampler(local) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            y = layer(xs[i % 3])
+        e1.record()
+        barrier()
+    ops.check_device_errors(dev)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        line = {
+            "metric": "w4a4_tp_linear_tflops", "value": 2.0 * M * N * K * args.steps / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)xfp4->f32->bf16",
+            "data": "synthetic",
+            "config": {"workload": f"column-parallel W4A4 mxfp4 linear K={K} N={N} (Qwen3-14B gate/up), M={M}, activations replicated, "
+                                   f"N split over {world} GPU(s), " + ("output tiles pushed to all ranks from the GEMM epilogue over NVLink"
+                                                                       if args.tp_fused else "NCCL all-gather of the output"),
+                       "l2": "three rotating activation buffers of 168 MB > 126 MB L2"},
+            "gather_bytes_per_rank": 2 * M * N * (world - 1) // max(world, 1), "roofline": None, "cpu_baseline": None,
+            "e2e": None, "gpu_launches": 2 * args.steps, "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model", "tp-linear"])
     ap.add_argument("--model-layers", type=int, default=2)
     ap.add_argument("--calib-seqs", type=int, default=128)
+    ap.add_argument("--tp-fused", action="store_true", help="tp-linear: push output tiles to the peers from the GEMM epilogue")
     ap.add_argument("--calib-batch", type=int, default=1, help="sequences per block call in the model-level GPTQ driver")
     ap.add_argument("--gptq-rows", type=int, default=14336)
     ap.add_argument("--gptq-cols", type=int, default=4096)
@@ -710,6 +779,8 @@ def main():
             run_gptq(args)
         elif args.workload == "gptq-model":
             run_gptq_model(args)
+        elif args.workload == "tp-linear":
+            run_tp_linear(args)
         else:
             run_ours(args)
 

@@ -407,7 +407,7 @@ int make_tensor_map_2d_u64(CUtensorMap* map, const void* base, uint64_t inner, u
 
 int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
                   const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
-                  cudaStream_t stream);
+                  cudaStream_t stream, int64_t ldc = 0, void* const* peers = nullptr, int n_peers = 0);
 int gemm_fp4_smallm(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
                     const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
                     cudaStream_t stream);
@@ -471,4 +471,27 @@ extern "C" int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, cons
   if (format == FPQ_FMT_NVFP4)
     return bn256 ? launch_gemm<256, true>(ta, tb, p, st) : launch_gemm<128, true>(ta, tb, p, st);
   return bn256 ? launch_gemm<256, false>(ta, tb, p, st) : launch_gemm<128, false>(ta, tb, p, st);
+}
+
+extern "C" int fpq_gemm_fp4_push(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* a_scales_swizzled,
+                                 const uint8_t* b_scales_swizzled, const float* alpha, const void* bias_bf16,
+                                 void* out_bf16, void* const* peer_outs, int n_peers, int64_t ldc, int64_t col_offset,
+                                 int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(a_codes && b_codes && a_scales_swizzled && b_scales_swizzled && alpha && out_bf16 && error_flag,
+                "NULL pointer");
+  FPQ_CHECK_ARG(format == FPQ_FMT_MXFP4 || format == FPQ_FMT_NVFP4, "bad format");
+  FPQ_CHECK_ARG(n_peers >= 0 && n_peers <= 7 && (n_peers == 0 || peer_outs), "0..7 peer buffers");
+  FPQ_CHECK_ARG(M > 128 && N >= 256 && K > 0, "the pushing GEMM is the large-M kernel: M > 128, N >= 256");
+  FPQ_CHECK_ARG(K % 64 == 0 && (K / 2) % 16 == 0 && N % 8 == 0, "K must be a multiple of 64, N of 8");
+  FPQ_CHECK_ARG(ldc >= col_offset + N && ldc % 8 == 0 && col_offset % 8 == 0, "bad output stride / column offset");
+  FPQ_CHECK_ARG(M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30), "shape too large");
+  FPQ_CHECK_ARG(((uintptr_t)out_bf16 & 15) == 0, "pointers must be 16-byte aligned");
+  void* peers[7] = {};
+  for (int i = 0; i < n_peers; ++i) {
+    FPQ_CHECK_ARG(peer_outs[i] && ((uintptr_t)peer_outs[i] & 15) == 0, "peer pointers must be 16-byte aligned");
+    peers[i] = reinterpret_cast<__nv_bfloat16*>(peer_outs[i]) + col_offset;
+  }
+  return gemm_fp4_pair(a_codes, b_codes, a_scales_swizzled, b_scales_swizzled, alpha, bias_bf16,
+                       reinterpret_cast<__nv_bfloat16*>(out_bf16) + col_offset, M, N, K, format, error_flag,
+                       (cudaStream_t)stream, ldc, peers, n_peers);
 }

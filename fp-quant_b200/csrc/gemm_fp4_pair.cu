@@ -59,6 +59,14 @@ struct PairParams {
   long long* profile;      // optional: per-pair cycle counters for tuning (NULL in normal use)
 };
 
+// Tensor-parallel push: the tile also goes to the same place of up to seven other GPUs' output buffers
+// (P2P-mapped pointers, already offset to this rank's first column), row stride ld elements.
+struct PushParams {
+  __nv_bfloat16* out[7];
+  int n;
+  long long ld;
+};
+
 template <bool NVFP4>
 struct PairSmem {
   static constexpr int STAGES = 5;
@@ -99,11 +107,11 @@ __device__ __forceinline__ void pair_tile_coords(const PairParams& p, int tile, 
 template <bool PROF>
 __device__ __forceinline__ long long tick() { return PROF ? clock64() : 0ll; }
 
-template <bool NVFP4, bool PROF>
+template <bool NVFP4, bool PROF, bool PUSH>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                     const __grid_constant__ CUtensorMap tmap_out, const PairParams p) {
+                     const __grid_constant__ CUtensorMap tmap_out, const PairParams p, const PushParams push) {
   using L = PairSmem<NVFP4>;
   constexpr int STAGES = L::STAGES;
   constexpr int SFBLK = L::SFBLK;
@@ -403,6 +411,24 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           tma_store_2d(&tmap_out, stage_out, colh, row0);
           bulk_commit_group();
         }
+        if (PUSH && push.n > 0) {
+          // Same box to the peers with ordinary 16-byte stores over NVLink: eight lanes cover the 128 bytes
+          // of one row, so every instruction writes four full lines (the box is read back un-swizzled).
+          const int rsub = lane >> 3, chunk = lane & 7;
+          const int col = colh + chunk * 8;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = rsub + 4 * i;
+            const uint4 v = *reinterpret_cast<const uint4*>(smem + L::OFF_OUT +
+                                                             (col_half * 4 + quarter) * L::OUT_BOX_BYTES + r * 128 +
+                                                             ((chunk ^ (r & 7)) * 16));
+            if (row0 + r < p.M && col < p.N) {
+#pragma unroll
+              for (int pr = 0; pr < 7; ++pr)
+                if (pr < push.n) *reinterpret_cast<uint4*>(push.out[pr] + (long long)(row0 + r) * push.ld + col) = v;
+            }
+          }
+        }
       }
       e_store += tick<PROF>() - t2;
     }
@@ -429,15 +455,18 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
 template <bool NVFP4>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
-                const CUtensorMap& tout, PairParams p, cudaStream_t stream) {
+                const CUtensorMap& tout, PairParams p, const PushParams& push, cudaStream_t stream) {
   using L = PairSmem<NVFP4>;
-  auto kern = p.profile ? gemm_fp4_pair_kernel<NVFP4, true> : gemm_fp4_pair_kernel<NVFP4, false>;
+  auto kern = push.n > 0 ? gemm_fp4_pair_kernel<NVFP4, false, true>
+              : p.profile   ? gemm_fp4_pair_kernel<NVFP4, true, false>
+                            : gemm_fp4_pair_kernel<NVFP4, false, false>;
   static bool configured[64] = {};
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
     configured[dev] = true;
   }
   int pairs = sm_count() / 2;
@@ -454,7 +483,7 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, tout, p));
+  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, tout, p, push));
   return FPQ_OK;
 }
 
@@ -466,7 +495,8 @@ int make_tensor_map_2d_u64(CUtensorMap* map, const void* base, uint64_t inner, u
 // Large-M path of fpq_gemm_fp4.  Shapes and pointers were validated by the caller.
 int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
                   const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, int64_t ldc, void* const* peers, int n_peers) {
+  if (ldc <= 0) ldc = N;
   const int g = format == FPQ_FMT_NVFP4 ? 16 : 32;
   const int sfblk = format == FPQ_FMT_NVFP4 ? 4 : 2;
   PairParams p{};
@@ -480,6 +510,10 @@ int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const 
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out = reinterpret_cast<__nv_bfloat16*>(out);
   p.error_flag = error_flag;
+  PushParams push{};
+  push.n = n_peers;
+  push.ld = ldc;
+  for (int i = 0; i < n_peers && i < 7; ++i) push.out[i] = reinterpret_cast<__nv_bfloat16*>(peers[i]);
   {
     const char* pe = getenv("FPQ_GEMM_PROFILE_PTR");   // tuning aid: address of a device buffer of 8 int64 per pair
     p.profile = pe ? reinterpret_cast<long long*>(strtoull(pe, nullptr, 0)) : nullptr;
@@ -489,15 +523,15 @@ int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const 
   if (p.raster_group < 1) p.raster_group = 1;
   CUtensorMap ta, tb, tsa, tsb, tout;
   // output as 64-column x 32-row boxes of bf16 (128 bytes per box row, 128-byte swizzle)
-  if (int rc = make_tensor_map_2d(&tout, out, 2, (uint64_t)N, (uint64_t)M, (uint64_t)N * 2, 64, 32, 1)) return rc;
+  if (int rc = make_tensor_map_2d(&tout, out, 2, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 32, 1)) return rc;
   if (int rc = make_tensor_map_2d(&ta, a, 1, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, BK_BYTES, BM_CTA, 1)) return rc;
   if (int rc = make_tensor_map_2d(&tb, b, 1, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BK_BYTES, BN_CTA, 1)) return rc;
   const uint64_t sf_row_words = (uint64_t)p.sf_blocks_k * 64;      // 8-byte words per 128-row block
   const uint64_t a_blocks = (uint64_t)((M + 127) / 128), b_blocks = (uint64_t)((N + 127) / 128);
   if (int rc = make_tensor_map_2d_u64(&tsa, sfa, sf_row_words, a_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 1)) return rc;
   if (int rc = make_tensor_map_2d_u64(&tsb, sfb, sf_row_words, b_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 2)) return rc;
-  return format == FPQ_FMT_NVFP4 ? launch_pair<true>(ta, tb, tsa, tsb, tout, p, stream)
-                                 : launch_pair<false>(ta, tb, tsa, tsb, tout, p, stream);
+  return format == FPQ_FMT_NVFP4 ? launch_pair<true>(ta, tb, tsa, tsb, tout, p, push, stream)
+                                 : launch_pair<false>(ta, tb, tsa, tsb, tout, p, push, stream);
 }
 
 }  // namespace fpq

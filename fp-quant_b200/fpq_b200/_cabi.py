@@ -48,6 +48,8 @@ _SIGNATURES = {
     "fpq_relative_mse": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     "fpq_relative_mse_tc": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_void_p],
+    "fpq_gemm_fp4_push": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+                          c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p],
     "fpq_gemm_fp4": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                      c_int64, c_int, c_void_p, c_void_p],
 }

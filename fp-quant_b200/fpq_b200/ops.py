@@ -233,6 +233,31 @@ def gemm_fp4(a_codes: torch.Tensor, b_codes: torch.Tensor, a_scales_swizzled: to
 
 
 # --------------------------------------------------------------------------- GPTQ core
+def gemm_fp4_push(a_codes: torch.Tensor, b_codes: torch.Tensor, a_scales_swizzled: torch.Tensor,
+                  b_scales_swizzled: torch.Tensor, alpha: torch.Tensor, fmt: str, out: torch.Tensor, peer_ptrs,
+                  col_offset: int, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Column-parallel GEMM: writes this rank's [M, n_loc] product into columns [col_offset, col_offset + n_loc)
+    of `out` [M, ldc] and of the other ranks' buffers (`peer_ptrs`: their device addresses as mapped on this
+    GPU), from the same epilogue.  The caller synchronises the ranks afterwards."""
+    import ctypes
+
+    _cuda(a_codes, "a_codes"), _cuda(b_codes, "b_codes"), _cuda(out, "out")
+    m, k = a_codes.shape[0], a_codes.shape[1] * 2
+    n = b_codes.shape[0]
+    if out.dtype != torch.bfloat16 or out.dim() != 2 or out.shape[0] != m or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 [M, ldc] tensor")
+    ptrs = (ctypes.c_void_p * max(1, len(peer_ptrs)))(*[int(p) for p in peer_ptrs])
+    alpha = _cuda(alpha, "alpha").to(torch.float32).reshape(1)
+    if bias is not None:
+        bias = _cuda(bias, "bias").to(torch.bfloat16).contiguous()
+    with _guard(out.device):
+        C.call("fpq_gemm_fp4_push", a_codes.data_ptr(), b_codes.data_ptr(), a_scales_swizzled.data_ptr(),
+               b_scales_swizzled.data_ptr(), alpha.data_ptr(), _ptr(bias), out.data_ptr(), ptrs, len(peer_ptrs),
+               out.shape[1], col_offset, m, n, k, FORMATS[fmt],
+               device_error_flag(out.device).data_ptr(), _stream(out))
+    return out
+
+
 def _f32(t: torch.Tensor, name: str, inplace: bool = False) -> torch.Tensor:
     t = _cuda(t, name)
     if t.dtype != torch.float32:

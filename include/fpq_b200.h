@@ -153,6 +153,21 @@ int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* 
                  fpq_stream_t stream);
 
 /*
+ * Column-parallel form of fpq_gemm_fp4 for tensor parallelism over NVLink (no counterpart in the reference,
+ * which is single-GPU, README.md:92): this rank holds N of the layer's ldc output features, starting at
+ * col_offset.  Its [M, N] product is written into columns [col_offset, col_offset + N) of its own
+ * [M, ldc] buffer `out_bf16` and, from the same epilogue, of the n_peers (<= 7) other ranks' buffers
+ * `peer_outs[i]` (device pointers that are valid on this GPU: P2P / symmetric-memory mappings), with
+ * ordinary stores, so the all-gather of the slices overlaps the GEMM.  When the kernel has finished its
+ * stores are complete; the ranks then synchronise among themselves before reading their buffers.
+ * M > 128, N >= 256 (the large-M kernel); other constraints as for fpq_gemm_fp4.
+ */
+int fpq_gemm_fp4_push(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* a_scales_swizzled,
+                      const uint8_t* b_scales_swizzled, const float* alpha, const void* bias_bf16,
+                      void* out_bf16, void* const* peer_outs, int n_peers, int64_t ldc, int64_t col_offset,
+                      int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag, fpq_stream_t stream);
+
+/*
  * C[M,N] = beta * C + alpha * A[M,K] * op(B) in true fp32 (no TF32), row-major with leading
  * dimensions; op(B) = B[K,N] or, when b_transposed, B[N,K]^T.  Stands in for the torch fp32
  * matmuls of the GPTQ path (src/quantization/gptq.py:29-30, :184-187; TF32 is switched off at
