@@ -17,7 +17,7 @@ namespace fpq {
 int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A, int64_t lda, int64_t a_rows,
                   int64_t a_x0, const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, bool symmetric, bool mirror,
                   int n_seg, int64_t seg_rows, const int* a_seg_y, const int* b_seg_y, float alpha, float beta,
-                  int32_t* error_flag, cudaStream_t stream);
+                  int32_t* error_flag, cudaStream_t stream, int tri = 0);
 }  // namespace fpq
 
 namespace fpq {
@@ -245,7 +245,7 @@ int64_t tc_gemm3_workspace(int64_t M, int64_t N, int64_t K, bool b_is_a_transpos
 // the dropped ones are below 2^-24 relative) are accumulated in fp32 in one launch whose K dimension is
 // the concatenation of the six slabs.  K must be a multiple of 64.
 int tc_gemm3(float* C, int64_t ldc, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
-             int64_t ldb, float alpha, float beta, __nv_bfloat16* ws, int32_t* error_flag, cudaStream_t st) {
+             int64_t ldb, float alpha, float beta, __nv_bfloat16* ws, int32_t* error_flag, cudaStream_t st, int tri = 0) {
   static const int pa[6] = {0, 0, 1, 0, 2, 1}, pb[6] = {0, 1, 0, 2, 0, 1};
   const int64_t ldat = round64(M);
   __nv_bfloat16* at3 = ws;
@@ -267,7 +267,7 @@ int tc_gemm3(float* C, int64_t ldc, int64_t M, int64_t N, int64_t K, const float
     b_y[t] = (int)(pb[t] * K);
   }
   return gemm_atb_bf16(C, ldc, M, N, at3, ldat, 3 * K, 0, b3, ldbt, 3 * K, 0, B == nullptr, false, 6, K, a_y, b_y, alpha,
-                       beta, error_flag, st);
+                       beta, error_flag, st, tri);
 }
 
 // Products at least this large go to the tensor cores; smaller ones stay on the fp32 SIMT kernel, whose
@@ -287,10 +287,11 @@ int tri_inverse_recursive(const float* L, float* X, float* scratch, __nv_bfloat1
   int64_t n2 = (int64_t)hi * NB - r1;
   if (r1 + n2 > d) n2 = d - r1;
   if (tc_worthwhile(n2, n1, n1) && n2 % 64 == 0) {
-    // S = L21 * X11, then X21 = -X22 * S
-    if (int rc = tc_gemm3(scratch, n1, n2, n1, n1, L + r1 * d + r0, d, X + r0 * d + r0, d, 1.0f, 0.0f, ws, error_flag, st))
+    // S = L21 * X11 (X11 lower triangular), then X21 = -X22 * S (X22 lower triangular): the stages that
+    // would only multiply the zero halves are skipped
+    if (int rc = tc_gemm3(scratch, n1, n2, n1, n1, L + r1 * d + r0, d, X + r0 * d + r0, d, 1.0f, 0.0f, ws, error_flag, st, 1))
       return rc;
-    return tc_gemm3(X + r1 * d + r0, d, n2, n1, n2, X + r1 * d + r1, d, scratch, n1, -1.0f, 0.0f, ws, error_flag, st);
+    return tc_gemm3(X + r1 * d + r0, d, n2, n1, n2, X + r1 * d + r1, d, scratch, n1, -1.0f, 0.0f, ws, error_flag, st, 2);
   }
   SgemmArgs a{};
   // S = L21 * X11

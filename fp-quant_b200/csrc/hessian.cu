@@ -39,11 +39,14 @@ struct HessParams {
   int num_blocks;      // ceil(d1 / 128)
   int num_blocks_n;    // ceil(d2 / 256)
   int num_tiles;
-  int num_k_stages;    // stages of 64 token rows over all segments
+  int n_seg;           // K segments
   int seg_stages;      // stages per segment: stage ks reads rows a_seg_y[ks / seg_stages] + (ks % seg_stages) * 64
   int symmetric;       // only tiles that touch the lower triangle
   int mirror;          // symmetric form: also write the transposed blocks above the diagonal
   int a_x0, b_x0;      // first column of A / B inside their matrices (added to the TMA x coordinate)
+  int tri;             // 0: dense; 1: B is lower triangular (B[k, j] = 0 for k < j): stages below the tile's first
+                       // column are skipped; 2: A^T is lower triangular (A[k, i] = 0 for k > i): stages beyond the
+                       // tile's last row are skipped
   int a_seg_y[MAX_SEGMENTS], b_seg_y[MAX_SEGMENTS];
   float alpha, beta;
   float* H;
@@ -92,6 +95,14 @@ __device__ __forceinline__ void tile_coords(const HessParams& p, int tile, int& 
   }
 }
 
+// Stages [lo, hi) of every K segment that can contribute to tile (ib, jb2).
+__device__ __forceinline__ void stage_range(const HessParams& p, int ib, int jb2, int& lo, int& hi) {
+  lo = 0;
+  hi = p.seg_stages;
+  if (p.tri == 1) lo = min(jb2 * (TILE_N / BK), p.seg_stages - 1);
+  if (p.tri == 2) hi = max(1, min(p.seg_stages, (ib + 1) * (TILE / BK)));
+}
+
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const HessParams p) {
@@ -136,13 +147,16 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         int ib, jb;
         tile_coords(p, tile, ib, jb);
-        for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
+        int lo, hi;
+        stage_range(p, ib, jb, lo, hi);
+        const int per_seg = hi - lo, n_st = per_seg * p.n_seg;
+        for (int ks = 0; ks < n_st; ++ks, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
           mbar_arrive_expect_tx(bar_full + 8 * s, (A_BOXES + B_BOXES) * BOX_BYTES);
           const uint32_t a_dst = sbase + Smem::OFF_A + s * A_BOXES * BOX_BYTES;
           const uint32_t b_dst = sbase + Smem::OFF_B + s * B_BOXES * BOX_BYTES;
-          const int seg = ks / p.seg_stages, kk = ks - seg * p.seg_stages;
+          const int seg = ks / per_seg, kk = lo + (ks - seg * per_seg);
           const int ya = p.a_seg_y[seg] + kk * BK;
           const int yb = p.b_seg_y[seg] + kk * BK;
 #pragma unroll
@@ -172,10 +186,15 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tile_count >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t acc = tmem_base + buf * TILE_N;
-        for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
+        int ib, jb, lo, hi;
+        tile_coords(p, tile, ib, jb);
+        stage_range(p, ib, jb, lo, hi);
+        const int n_st = (hi - lo) * p.n_seg;
+        // one barrier wait, four MMAs and one commit per stage: every other instruction here is time the
+        // tensor pipe idles (the operands come through TMA, which needs no tcgen05 fence)
+        for (int ks = 0; ks < n_st; ++ks, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait_bounded(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
+          if (!mbar_wait_bounded_spin(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
           const uint64_t a_desc = make_desc_mn_sw128(sbase + Smem::OFF_A + s * A_BOXES * BOX_BYTES, BOX_BYTES, 1024);
           const uint64_t b_desc = make_desc_mn_sw128(sbase + Smem::OFF_B + s * B_BOXES * BOX_BYTES, BOX_BYTES, 1024);
 #pragma unroll
@@ -274,11 +293,12 @@ namespace fpq {
 // i starting at row a_seg_y[i] of A and b_seg_y[i] of B (one segment from row 0: the plain product).
 // With more than one segment seg_rows must be a multiple of 64.  symmetric: only tiles that touch the
 // lower triangle are computed (d1 == d2); mirror: the blocks below the diagonal are also written
-// transposed.
+// transposed.  tri = 1: B (as the [K, d2] matrix of one segment) is lower triangular, tri = 2: A^T (the
+// [d1, K] matrix) is lower triangular -- the stages that only multiply zeros are skipped.
 int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A, int64_t lda, int64_t a_rows,
                   int64_t a_x0, const void* B, int64_t ldb, int64_t b_rows, int64_t b_x0, bool symmetric, bool mirror,
                   int n_seg, int64_t seg_rows, const int* a_seg_y, const int* b_seg_y, float alpha, float beta,
-                  int32_t* error_flag, cudaStream_t stream) {
+                  int32_t* error_flag, cudaStream_t stream, int tri) {
   if (n_seg < 1 || n_seg > MAX_SEGMENTS || (n_seg > 1 && seg_rows % BK != 0)) {
     set_error("bad K segmentation (%d segments of %lld rows)", n_seg, (long long)seg_rows);
     return FPQ_ERR_INVALID_ARGUMENT;
@@ -293,7 +313,8 @@ int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A
   p.mirror = (symmetric && mirror) ? 1 : 0;
   p.a_x0 = (int)a_x0; p.b_x0 = (int)b_x0;
   p.seg_stages = (int)((seg_rows + BK - 1) / BK);
-  p.num_k_stages = p.seg_stages * n_seg;
+  p.n_seg = n_seg;
+  p.tri = tri;
   for (int i = 0; i < n_seg; ++i) {
     p.a_seg_y[i] = a_seg_y ? a_seg_y[i] : 0;
     p.b_seg_y[i] = b_seg_y ? b_seg_y[i] : 0;
@@ -331,5 +352,5 @@ extern "C" int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, 
   if (tokens == 0) return FPQ_OK;
   const bool symmetric = xb_bf16 == nullptr || xb_bf16 == xa_bf16;
   return gemm_atb_bf16(H, d, d, d, xa_bf16, d, tokens, 0, symmetric ? xa_bf16 : xb_bf16, d, tokens, 0, symmetric, true,
-                       1, tokens, nullptr, nullptr, alpha, beta, error_flag, (cudaStream_t)stream);
+                       1, tokens, nullptr, nullptr, alpha, beta, error_flag, (cudaStream_t)stream, 0);
 }

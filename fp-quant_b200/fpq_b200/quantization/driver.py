@@ -60,6 +60,32 @@ class _Phases:
 last_phases: Optional[_Phases] = None     # phases of the most recent gptq_quantization call
 
 
+class _HessianSink:
+    """Collects the rotated inputs of consecutive calibration sequences and hands them to `GPTQ.update` a
+    few at a time: every update reads and rewrites the whole d x d Hessian (0.8 GB for d = 14336), so one
+    update per 2048-token sequence spends more time on that than on the product.  The running mean is the
+    same (update counts sequences by the leading dimension)."""
+
+    def __init__(self, handle: "GPTQ", tokens_per_update: int = 16384):
+        self.handle, self.limit = handle, tokens_per_update
+        self.pending: List[torch.Tensor] = []
+        self.tokens = 0
+
+    def __call__(self, x: torch.Tensor) -> None:
+        x = x if x.dim() >= 3 else x.unsqueeze(0)
+        if self.pending and self.pending[0].shape[1:] != x.shape[1:]:
+            self.flush()
+        self.pending.append(x)
+        self.tokens += x.numel() // x.shape[-1]
+        if self.tokens >= self.limit:
+            self.flush()
+
+    def flush(self) -> None:
+        if self.pending:
+            self.handle.update(self.pending[0] if len(self.pending) == 1 else torch.cat(self.pending, dim=0))
+        self.pending, self.tokens = [], 0
+
+
 class InputCollector(nn.Module):
     """Records the positional and keyword inputs of the wrapped block and stops the forward pass
     (src/utils/model_utils.py:19-38)."""
@@ -260,6 +286,24 @@ def _run_block(block, input_args, input_kwargs, device, args, keep_outputs: bool
                     input_kwargs[i]["hidden_states"] = piece
 
 
+def plan_ranks(group_members: Dict[str, List[str]], group_cols: Dict[str, int], world_size: int):
+    """Which rank factors which Hessian and quantises which linear of a block.
+
+    group_members: input group -> its linears (the first is the group's leader); group_cols: input width of
+    the group (the Cholesky chain costs ~ width^3).  Returns (groups ordered by cost, group -> rank that runs
+    its chain, linear -> rank that runs its column loop).  Chains go round-robin, largest first; a group's
+    leader stays on the chain's rank (no transfer of U needed), the other members move to ranks that have
+    no chain, while there are any."""
+    group_order = sorted(group_members, key=lambda g: -group_cols[g])
+    group_owner = {g: i % world_size for i, g in enumerate(group_order)}
+    idle = [r for r in range(world_size) if r not in set(group_owner.values())]
+    layer_owner: Dict[str, int] = {}
+    for g in group_order:
+        for k, n in enumerate(group_members[g]):
+            layer_owner[n] = group_owner[g] if (k == 0 or not idle) else idle.pop(0)
+    return group_order, group_owner, layer_owner
+
+
 @torch.no_grad()
 def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device) -> Tuple[dict, dict]:
     """MR-GPTQ over the transformer blocks of `model` (gptq.py:225-470).  Returns
@@ -298,7 +342,7 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             grp = _input_group(name.split(".")[-1])
             if grp not in leaders:
                 leaders[grp] = name
-                layer.group_state["sink"] = (lambda h: (lambda x: h.update(x)))(handles[name])
+                layer.group_state["sink"] = _HessianSink(handles[name])
         if getattr(args, "fuse_global_scale", False) and args.scale_precision == ScalePrecision.E4M3:
             for pat in (r"(q|k|v)_proj$", r"(gate|up)_proj$"):       # gptq.py:367-383
                 names = [n for n in handles if re.search(pat, n)]
@@ -309,6 +353,10 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
 
         ph.mark("setup")
         _run_block(block, input_args, input_kwargs, device, args, keep_outputs=False, offload_device=offload)   # Hessians
+        for layer in layers.values():
+            sink = layer.group_state.get("sink")
+            if isinstance(sink, _HessianSink):
+                sink.flush()
         ph.mark("hessian_pass")
 
         for name, layer in layers.items():
@@ -348,13 +396,8 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             group_members.setdefault(_input_group(name.split(".")[-1]), []).append(name)
         share_ok = {grp: not any(bool((handles[n].layer.weight == 0).all(dim=0).any().item()) for n in names)
                     for grp, names in group_members.items()}
-        group_order = sorted(group_members, key=lambda g: -handles[leaders[g]].d_col)
-        group_owner = {g: i % world_size for i, g in enumerate(group_order)}
-        idle = [r for r in range(world_size) if r not in set(group_owner.values())]
-        layer_owner: Dict[str, int] = {}
-        for g in group_order:
-            for k, n in enumerate(group_members[g]):
-                layer_owner[n] = group_owner[g] if (k == 0 or not idle) else idle.pop(0)
+        group_order, group_owner, layer_owner = plan_ranks(
+            group_members, {g: handles[leaders[g]].d_col for g in group_members}, world_size)
 
         shared_U: Dict[str, torch.Tensor] = {}
         for g in group_order:
@@ -367,7 +410,9 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             if rank == owner:
                 lead.quantization_pre_step()
                 lead.prepare_hessian()
+                ph.mark("factor_prepare")
                 shared_U[g] = lead._get_hessian_inverse(prepared=True)
+                ph.mark("factor_chain")
             elif elsewhere:
                 shared_U[g] = torch.empty((lead.d_col, lead.d_col), device=device, dtype=torch.float32)
         for g in group_order:                       # after all chains were queued: they overlap across ranks

@@ -90,3 +90,29 @@ def test_gptq_quantization_tiny_llama(fmt):
     assert err_gptq < 0.5 and err_rtn < 0.5, (err_gptq, err_rtn)
     # error compensation must not be worse than plain rounding on the data it was calibrated on
     assert err_gptq < 1.1 * err_rtn, (err_gptq, err_rtn)
+
+
+def test_calibration_batching_gives_an_equivalent_model():
+    """Several calibration sequences per block call: same Hessians (a sum over sequences) up to summation
+    order; the activation tensor scale advances per batch instead of per sequence."""
+    from fpq_b200.quantization.driver import gptq_quantization
+
+    dev = torch.device("cuda:0")
+    data = _calibration(dev)
+
+    def run(batch):
+        model = _tiny_llama(dev)
+        args = _args("nvfp")
+        args.calibration_batch = batch
+        quantized, _ = gptq_quantization(model, data, args, dev)
+        with torch.no_grad():
+            return quantized, torch.cat([model(x.to(dev)).logits.float() for x in data])
+
+    q1, l1 = run(1)
+    q3, l3 = run(3)
+    assert sorted(q1) == sorted(q3)
+    first = "model.layers.0.self_attn.q_proj"       # identical inputs: only the order of the Hessian sum differs
+    a, b = q1[first]["qweight"], q3[first]["qweight"]
+    agree = float((((a & 0xF) == (b & 0xF)).sum() + ((a >> 4) == (b >> 4)).sum()) / (2 * a.numel()))
+    assert agree > 0.99, agree
+    assert float(((l1 - l3) ** 2).mean() / (l1 ** 2).mean()) < 0.05
