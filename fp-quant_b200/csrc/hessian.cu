@@ -8,12 +8,15 @@
 // X^T X is a GEMM whose two operands are the same row-major matrix read "MN-major": a TMA box of
 // 64 columns x 64 tokens with the 128-byte swizzle lands in shared memory exactly in the canonical
 // MN-major layout of tcgen05.mma (8 token rows of 128 bytes per swizzle atom).  Persistent CTAs walk
-// 128 x 256 tiles (an MMA instruction costs the same ~180 cycles for N = 128 and N = 256, so only the
-// wide tile keeps the tensor pipe busy) that touch the lower triangle (or all tiles for the general
-// A^T B form); two fp32 accumulators fill tensor memory so that the read-modify-write epilogue of one
-// tile overlaps the MMAs of the next.  Of a tile on the diagonal only the 128-column blocks at or
-// below it are written; blocks below the diagonal are also written mirrored, so H stays fully
-// symmetric like the reference's.  Warp roles and bounded waits as in the FP4 GEMM.
+// tiles that are 256 columns wide (an MMA instruction costs the same ~180 cycles for N = 128 and N = 256,
+// so only the wide tile keeps the tensor pipe busy) and 128 or 256 rows high (see Shape below), those that
+// touch the lower triangle or all of them for the general A^T B form.  Of a tile on the diagonal only the
+// 128-column blocks at or below it are written; blocks below the diagonal are also written mirrored, so
+// H stays fully symmetric like the reference's.  Warp roles and bounded waits as in the FP4 GEMM.
+//
+// The same kernel is the package's general bf16 A^T B product: K may be a concatenation of segments (the
+// cross products of multi-term bf16 splits in one launch), operands may start at a column offset, and the
+// stages that would only multiply the zero half of a triangular factor can be skipped.
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -27,10 +30,28 @@ constexpr int TILE = 128;            // output tile rows (A^T side) and the unit
 constexpr int TILE_N = 256;          // output tile columns
 constexpr int BK = 64;               // tokens per stage
 constexpr int BOX_BYTES = BK * 128;  // one 64-column x 64-token box
-constexpr int A_BOXES = TILE / 64, B_BOXES = TILE_N / 64;
-constexpr int STAGES = 4;
+constexpr int B_BOXES = TILE_N / 64;
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;       // two 256-column accumulators
+
+// Two tile shapes.  128 x 256 with two accumulators in flight (the epilogue of a tile overlaps the next
+// tile's MMAs) for short K; 256 x 256 (two 128-row halves that share every B stage, all of tensor memory,
+// no overlap of the epilogue) for long K, where what limits the kernel is the operand traffic from L2:
+// 64 KB per eight MMAs instead of 48 KB per four.
+template <bool BIG>
+struct Shape {
+  static constexpr int TM = BIG ? 256 : 128;
+  static constexpr int HALVES = TM / 128;
+  static constexpr int A_BOXES = TM / 64;
+  static constexpr int STAGES = BIG ? 3 : 4;
+  static constexpr int NBUF = BIG ? 1 : 2;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BOXES * BOX_BYTES;
+  static constexpr int OFF_BAR = OFF_B + STAGES * B_BOXES * BOX_BYTES;   // full[S], empty[S], acc_full[2], acc_empty[2]
+  static constexpr int OFF_MISC = OFF_BAR + (2 * STAGES + 4) * 8;
+  static constexpr int TOTAL = OFF_MISC + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
 
 constexpr int MAX_SEGMENTS = 6;
 
@@ -53,14 +74,6 @@ struct HessParams {
   int* error_flag;
 };
 
-struct Smem {
-  static constexpr int OFF_A = 0;                               // STAGES x 2 boxes
-  static constexpr int OFF_B = OFF_A + STAGES * A_BOXES * BOX_BYTES;   // STAGES x 4 boxes
-  static constexpr int OFF_BAR = OFF_B + STAGES * B_BOXES * BOX_BYTES;  // full[S], empty[S], acc_full[2], acc_empty[2]
-  static constexpr int OFF_MISC = OFF_BAR + (2 * STAGES + 4) * 8;
-  static constexpr int TOTAL = OFF_MISC + 16;
-  static constexpr int DYN_BYTES = TOTAL + 1024;
-};
 
 // MN-major operand, 128-byte swizzle: 64 contiguous MN elements per 128-byte row, 8 K rows per atom
 // (`sbo` bytes between atoms along K), further 64-wide MN blocks `lbo` bytes apart.
@@ -74,21 +87,24 @@ __device__ __forceinline__ uint64_t make_desc_mn_sw128(uint32_t smem_addr, uint3
   return d;
 }
 
-// Symmetric form: row block ib (128 rows) needs the column tiles jb2 = 0 .. ib / 2 (256 columns each).
-// Tiles are numbered row by row; rows 0 .. ib-1 hold q (q + 1) tiles for ib = 2 q and (q + 1)^2 for ib = 2 q + 1.
-__host__ __device__ inline int tiles_before_row(int ib) {
+// Symmetric form, 128 x 256 tiles: row block ib (128 rows) needs the column tiles jb2 = 0 .. ib / 2 (256 columns
+// each).  Tiles are numbered row by row; rows 0 .. ib-1 hold q (q + 1) tiles for ib = 2 q and (q + 1)^2 for
+// ib = 2 q + 1.  256 x 256 tiles: the plain lower triangle of 256-blocks, ib (ib + 1) / 2 tiles before row ib.
+__host__ __device__ inline int tiles_before_row(int ib, bool big) {
+  if (big) return ib * (ib + 1) / 2;
   const int q = ib >> 1;
   return (ib & 1) ? (q + 1) * (q + 1) : q * (q + 1);
 }
 
+template <bool BIG>
 __device__ __forceinline__ void tile_coords(const HessParams& p, int tile, int& ib, int& jb2) {
   if (p.symmetric) {
-    int i = (int)(2.0f * sqrtf((float)tile)) - 1;
+    int i = (int)((BIG ? 1.41421356f : 2.0f) * sqrtf((float)tile)) - 1;
     if (i < 0) i = 0;
-    while (tiles_before_row(i + 1) <= tile) ++i;
-    while (tiles_before_row(i) > tile) --i;
+    while (tiles_before_row(i + 1, BIG) <= tile) ++i;
+    while (tiles_before_row(i, BIG) > tile) --i;
     ib = i;
-    jb2 = tile - tiles_before_row(i);
+    jb2 = tile - tiles_before_row(i, BIG);
   } else {
     ib = tile / p.num_blocks_n;
     jb2 = tile - ib * p.num_blocks_n;
@@ -103,9 +119,12 @@ __device__ __forceinline__ void stage_range(const HessParams& p, int ib, int jb2
   if (p.tri == 2) hi = max(1, min(p.seg_stages, (ib + 1) * (TILE / BK)));
 }
 
+template <bool BIG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const HessParams p) {
+  using Smem = Shape<BIG>;
+  constexpr int STAGES = Smem::STAGES, A_BOXES = Smem::A_BOXES, TM = Smem::TM, HALVES = Smem::HALVES, NBUF = Smem::NBUF;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -146,7 +165,7 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
         int ib, jb;
-        tile_coords(p, tile, ib, jb);
+        tile_coords<BIG>(p, tile, ib, jb);
         int lo, hi;
         stage_range(p, ib, jb, lo, hi);
         const int per_seg = hi - lo, n_st = per_seg * p.n_seg;
@@ -161,7 +180,7 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int yb = p.b_seg_y[seg] + kk * BK;
 #pragma unroll
           for (int b = 0; b < A_BOXES; ++b)
-            tma_load_2d(a_dst + b * BOX_BYTES, &tmap_a, p.a_x0 + ib * TILE + 64 * b, ya, bar_full + 8 * s);
+            tma_load_2d(a_dst + b * BOX_BYTES, &tmap_a, p.a_x0 + ib * TM + 64 * b, ya, bar_full + 8 * s);
 #pragma unroll
           for (int b = 0; b < B_BOXES; ++b)
             tma_load_2d(b_dst + b * BOX_BYTES, &tmap_b, p.b_x0 + jb * TILE_N + 64 * b, yb, bar_full + 8 * s);
@@ -178,16 +197,17 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16(TILE, TILE_N, true, true);
+      const uint32_t idesc = make_idesc_bf16(TILE, TILE_N, true, true);   // per 128-row half
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tile_count) {
-        const uint32_t buf = tile_count & 1;
-        if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, ((tile_count >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const uint32_t buf = NBUF == 2 ? (tile_count & 1) : 0;
+        const uint32_t acc_parity = NBUF == 2 ? ((tile_count >> 1) & 1) : (tile_count & 1);
+        if (!mbar_wait_bounded(bar_acc_empty + 8 * buf, acc_parity ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t acc = tmem_base + buf * TILE_N;
         int ib, jb, lo, hi;
-        tile_coords(p, tile, ib, jb);
+        tile_coords<BIG>(p, tile, ib, jb);
         stage_range(p, ib, jb, lo, hi);
         const int n_st = (hi - lo) * p.n_seg;
         // one barrier wait, four MMAs and one commit per stage: every other instruction here is time the
@@ -198,9 +218,12 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const uint64_t a_desc = make_desc_mn_sw128(sbase + Smem::OFF_A + s * A_BOXES * BOX_BYTES, BOX_BYTES, 1024);
           const uint64_t b_desc = make_desc_mn_sw128(sbase + Smem::OFF_B + s * B_BOXES * BOX_BYTES, BOX_BYTES, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)   // 16 tokens per MMA = two 8-row atoms = 2048 bytes
-            tc_mma_f16(acc, a_desc + (uint64_t)(k * (2048 >> 4)), b_desc + (uint64_t)(k * (2048 >> 4)), idesc,
-                       (ks > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k) {  // 16 tokens per MMA = two 8-row atoms = 2048 bytes
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)   // 128-row halves of the tile: boxes 2h, 2h+1 of A, accumulator h
+              tc_mma_f16(acc + h * TILE_N, a_desc + (uint64_t)((h * 2 * BOX_BYTES + k * 2048) >> 4),
+                         b_desc + (uint64_t)(k * (2048 >> 4)), idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          }
           tc_commit(bar_empty + 8 * s);
         }
         if (ok) tc_commit(bar_acc_full + 8 * buf);
@@ -216,19 +239,22 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++tile_count) {
       int ib, jb;
-      tile_coords(p, tile, ib, jb);
-      const uint32_t buf = tile_count & 1;
-      if (!mbar_wait_bounded(bar_acc_full + 8 * buf, (tile_count >> 1) & 1, abort_flag)) { ok = false; break; }
+      tile_coords<BIG>(p, tile, ib, jb);
+      const uint32_t buf = NBUF == 2 ? (tile_count & 1) : 0;
+      const uint32_t acc_parity = NBUF == 2 ? ((tile_count >> 1) & 1) : (tile_count & 1);
+      if (!mbar_wait_bounded(bar_acc_full + 8 * buf, acc_parity, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int64_t i = (int64_t)ib * TILE + quarter * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < TILE_N / 32; ++c) {
+      for (int hc = 0; hc < HALVES * (TILE_N / 32); ++hc) {
+        const int h = hc / (TILE_N / 32), c = hc % (TILE_N / 32);
+        const int rb = ib * HALVES + h;                      // 128-row block of this half
+        const int64_t i = (int64_t)rb * TILE + quarter * 32 + lane;
         const int64_t j0 = (int64_t)jb * TILE_N + c * 32;
         const int jblock = (int)(j0 / TILE);                 // 128-column block of this chunk
-        if (j0 >= p.d2 || (p.symmetric && jblock > ib)) break;   // beyond the matrix / above the diagonal
-        const bool mirror = p.mirror && jblock < ib;
+        if (j0 >= p.d2 || (p.symmetric && jblock > rb)) continue;   // beyond the matrix / above the diagonal
+        const bool mirror = p.mirror && jblock < rb;
         uint32_t r[32];
-        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE_N + c * 32, r);
+        tc_ld_32x32b_x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TILE_N + h * TILE_N + c * 32, r);
         tc_wait_ld();
         if (i < p.d1) {
           float* hrow = p.H + i * p.ldc + j0;
@@ -306,9 +332,15 @@ int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A
   if (d1 <= 0 || d2 <= 0 || seg_rows <= 0) return FPQ_OK;
   HessParams p{};
   p.d1 = d1; p.d2 = d2; p.ldc = ldc;
-  p.num_blocks = (int)((d1 + TILE - 1) / TILE);
+  // long K, no triangular skipping, enough 256-row tiles to fill the GPU: the 256 x 256 shape
+  const int64_t total_stages = (int64_t)n_seg * ((seg_rows + BK - 1) / BK);
+  const int64_t rows256 = (d1 + 255) / 256, cols256 = (d2 + TILE_N - 1) / TILE_N;
+  const int64_t big_tiles = symmetric ? rows256 * (rows256 + 1) / 2 : rows256 * cols256;
+  const bool big = tri == 0 && total_stages >= 64 && big_tiles >= sm_count() / 2;
+  const int tm = big ? 256 : TILE;
+  p.num_blocks = (int)((d1 + tm - 1) / tm);
   p.num_blocks_n = (int)((d2 + TILE_N - 1) / TILE_N);
-  p.num_tiles = symmetric ? tiles_before_row(p.num_blocks) : p.num_blocks * p.num_blocks_n;
+  p.num_tiles = symmetric ? tiles_before_row(p.num_blocks, big) : p.num_blocks * p.num_blocks_n;
   p.symmetric = symmetric ? 1 : 0;
   p.mirror = (symmetric && mirror) ? 1 : 0;
   p.a_x0 = (int)a_x0; p.b_x0 = (int)b_x0;
@@ -327,13 +359,19 @@ int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(hessian_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(hessian_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Shape<false>::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(hessian_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Shape<true>::DYN_BYTES));
     configured[dev] = true;
   }
   int grid = sm_count();
   if (grid > p.num_tiles) grid = p.num_tiles;
   if (grid < 1) return FPQ_OK;
-  hessian_kernel<<<grid, NUM_THREADS, Smem::DYN_BYTES, stream>>>(ta, tb, p);
+  if (big)
+    hessian_kernel<true><<<grid, NUM_THREADS, Shape<true>::DYN_BYTES, stream>>>(ta, tb, p);
+  else
+    hessian_kernel<false><<<grid, NUM_THREADS, Shape<false>::DYN_BYTES, stream>>>(ta, tb, p);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
 }

@@ -212,25 +212,42 @@ def _release_group_states(layers: Dict[str, "RotatedLinear"]) -> None:
         layer.group_state.pop("xq", None)
 
 
-def _to_host_async(t: torch.Tensor) -> torch.Tensor:
-    """Device tensor -> page-locked host tensor without stalling the stream (the drivers synchronise once
-    before they return the export dicts)."""
-    if not t.is_cuda:
-        return t
-    out = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
-    out.copy_(t, non_blocking=True)
-    return out
+class _HostCopies:
+    """Device -> host copies of the export tensors without stalling the stream: every tensor goes to a
+    page-locked destination with an asynchronous copy, and `finish()` synchronises once.  Measured on the
+    model-level benchmark (per transformer block): plain `.cpu()` per layer 48 ms; this 3 ms of copies plus
+    the page-locking; a worker thread doing the same blocked the kernel launches of the next block's
+    Cholesky chain (+100 ms); keeping everything on the device and copying to pageable memory at the end
+    moved 220 MB at 2 GB/s (+55 ms)."""
+
+    def __init__(self, device):
+        self.device = device
+
+    def put(self, entry: dict, key: str, tensor: torch.Tensor) -> None:
+        """entry[key] becomes the host copy of `tensor` (which must not be modified afterwards)."""
+        if not tensor.is_cuda:
+            entry[key] = tensor
+            return
+        out = torch.empty(tensor.shape, dtype=tensor.dtype, pin_memory=True)
+        out.copy_(tensor, non_blocking=True)
+        entry[key] = out
+
+    def finish(self) -> None:
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
 
 
 _matrix_cache: Dict[tuple, torch.Tensor] = {}
 
 
-def _export_entry(args, orig_dtype, device, weight_gs, act_gs, **tensors) -> dict:
+def _export_entry(copies: _HostCopies, args, orig_dtype, device, weight_gs, act_gs, **tensors) -> dict:
     key = (str(args.transform_class), args.hadamard_group_size, str(orig_dtype))
     if key not in _matrix_cache:
         _matrix_cache[key] = get_transform_matrix(args.transform_class, args.hadamard_group_size, device, orig_dtype).cpu()
     m = _matrix_cache[key].clone()
-    entry = {k: _to_host_async(v.contiguous()) for k, v in tensors.items()}
+    entry: dict = {}
+    for k, v in tensors.items():
+        copies.put(entry, k, v.contiguous())
     entry.update({"forward_hadamard_matrix": m, "backward_hadamard_matrix": m.clone(),
                   "weight_global_scale": weight_gs.clone(), "act_global_scale": act_gs.clone()})
     return entry
@@ -316,6 +333,7 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
     wkw = _quantizer_kwargs(args, "w")
     global last_phases
     ph = last_phases = _Phases()
+    copies = _HostCopies(device)
     ph.mark("start")
     rank, world_size = fdist.world()
     n_total = len(calibration_data)
@@ -431,11 +449,11 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                     handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
                     handle.quantization_pre_step()
                     handle.prepare_hessian()       # same damping as the leader's: leaves the damped H for the MSE
-                wq, qweight, scales = handle.step(shared_U[grp])
+                wq, qweight, scales = handle.step(shared_U[grp], want_grid_values=False)   # the packed codes are exported
             else:
                 if handle is not leader:
                     handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
-                wq, qweight, scales = handle.quantize()
+                wq, qweight, scales = handle.quantize(want_grid_values=False)
             rel = get_relative_mse_error(wq.float(), handle.layer.weight.float(), handle.H)
             results[name] = (wq, handle.packed_codes, scales.float().contiguous(), rel.reshape(1))
         shared_U.clear()
@@ -460,10 +478,10 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                 ags = handle.layer.act_quantizer.global_scale if handle.layer.act_quantizer is not None else torch.ones(1)
                 key = f"model.layers.{block_idx}.{name}"
                 if args.export_quantized_model == "realquant":
-                    quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, qweight=codes,
+                    quantized[key] = _export_entry(copies, args, orig_dtype, device, wgs, ags, qweight=codes,
                                                    scales=cast_scales_to_eXmY(scales * wgs, args.scale_precision))
                 else:
-                    quantized[key] = _export_entry(args, orig_dtype, device, wgs, ags, dqweight=wq)
+                    quantized[key] = _export_entry(copies, args, orig_dtype, device, wgs, ags, dqweight=wq)
         results.clear()
 
         ph.mark("column_loops")
@@ -474,7 +492,7 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
         if getattr(args, "cpu_offload_modules", False):
             block.cpu()
         del handles
-    torch.cuda.synchronize(device)        # the asynchronous copies of the export tensors have landed
+    copies.finish()                       # the background copies of the export tensors have landed
     return quantized, non_quantized
 
 
@@ -485,6 +503,7 @@ def rtn_quantization(model, calibration_data: List[torch.Tensor], args, device) 
     print("RTN quantization...")
     orig_dtype = model.config.torch_dtype if args.dtype == "auto" else args.dtype
     quantized, non_quantized = {}, {}
+    copies = _HostCopies(device)
     wkw = _quantizer_kwargs(args, "w")
     fmt = {"nvfp": "nvfp4", "mxfp": "mxfp4"}[str(args.format)]
     for block_idx, block in enumerate(model.model.layers):
@@ -505,8 +524,8 @@ def rtn_quantization(model, calibration_data: List[torch.Tensor], args, device) 
                 ags = layer.act_quantizer.global_scale if layer.act_quantizer is not None else torch.ones(1)
                 key = f"model.layers.{block_idx}.{name}"
                 if args.export_quantized_model == "realquant":
-                    quantized[key] = _export_entry(args, orig_dtype, device, q.global_scale, ags, qweight=codes, scales=sbytes)
+                    quantized[key] = _export_entry(copies, args, orig_dtype, device, q.global_scale, ags, qweight=codes, scales=sbytes)
                 else:
-                    quantized[key] = _export_entry(args, orig_dtype, device, q.global_scale, ags, dqweight=wq)
-    torch.cuda.synchronize(device)
+                    quantized[key] = _export_entry(copies, args, orig_dtype, device, q.global_scale, ags, dqweight=wq)
+    copies.finish()
     return quantized, non_quantized

@@ -69,8 +69,8 @@ class GPTQ:
         self.pre_step_completed = True
 
     @torch.no_grad()
-    def step(self, U: Optional[torch.Tensor] = None, shard_rows: bool = False,
-             process_group=None) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor]:
+    def step(self, U: Optional[torch.Tensor] = None, shard_rows: bool = False, process_group=None,
+             want_grid_values: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor], torch.Tensor]:
         """Returns (dequantised weight in the layer dtype, E2M1 grid values or None, fp32 group scales).
         `self.H` is left damped, as in the reference, where the caller reuses it for the relative MSE.
 
@@ -95,7 +95,7 @@ class GPTQ:
             w = self.W.clone()
             self.packed_codes = ops.gptq_quantize(w, scales.float().contiguous(), U, group, want_codes=True)
         qweight = None
-        if self.export_quantized_model:
+        if self.export_quantized_model and want_grid_values:
             # grid values of both nibbles of a byte from one 256-entry table
             lut = torch.tensor(FP4_CODE_VALUES, dtype=self.W_dtype, device=w.device)
             byte = torch.arange(256, device=w.device)
@@ -118,6 +118,7 @@ class GPTQ:
             U = torch.eye(self.d_col, device=self.H.device, dtype=torch.float32)
         return U
 
-    def quantize(self, U: Optional[torch.Tensor] = None, shard_rows: bool = False, process_group=None):
+    def quantize(self, U: Optional[torch.Tensor] = None, shard_rows: bool = False, process_group=None,
+                 want_grid_values: bool = True):
         self.quantization_pre_step()
-        return self.step(U, shard_rows, process_group)
+        return self.step(U, shard_rows, process_group, want_grid_values)
