@@ -752,13 +752,98 @@ def run_tp_linear(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------ W4A4 forward of a model
+def run_model_forward(args):
+    """Forward of a randomly initialised Qwen3-14B-shaped decoder stack (hidden 5120, 40/8 heads of 128, MLP
+    17408) truncated to `--model-layers` blocks, with every linear replaced by a real-quantised MXFP4
+    `FPQuantLinear` through `replace_quantize_with_fp_quant_linear` (the call a user of the reference's
+    inference library makes).  Prefill: 8 x 2048 tokens; decode: batch 64, one token per step on a 128-token
+    cache.  The same stack in bf16 (`nn.Linear`, cuBLAS) is timed beside it in the same run."""
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+
+    from fpq_b200 import ops
+    from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype
+    from fpq_b200.fp_quant.utils.replace import replace_quantize_with_fp_quant_linear
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    n_layers = args.model_layers
+    cfg = Qwen3Config(hidden_size=5120, intermediate_size=17408, num_hidden_layers=n_layers, num_attention_heads=40,
+                      num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=4096)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = Qwen3ForCausalLM(cfg).to(torch.bfloat16).eval()
+    body = model.model
+    g = torch.Generator().manual_seed(5)
+    prefill_ids = torch.randint(0, cfg.vocab_size, (8, 2048), generator=g).to(dev)
+    decode_prompt = torch.randint(0, cfg.vocab_size, (64, 128), generator=g).to(dev)
+    decode_ids = torch.randint(0, cfg.vocab_size, (64, 1), generator=g).to(dev)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / steps
+
+    @torch.no_grad()
+    def prefill():
+        return body(input_ids=prefill_ids, use_cache=False).last_hidden_state
+
+    @torch.no_grad()
+    def decode_rate(steps, warmup):
+        out = body(input_ids=decode_prompt, use_cache=True)
+        cache = out.past_key_values
+        for _ in range(warmup):
+            cache = body(input_ids=decode_ids, past_key_values=cache, use_cache=True).past_key_values
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            cache = body(input_ids=decode_ids, past_key_values=cache, use_cache=True).past_key_values
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e-3 / steps
+
+    with ClockSampler(0) as clocks:
+        bf16_prefill = timed(prefill, args.steps, args.warmup)
+        bf16_decode = decode_rate(16, 4)
+        qcfg = FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, forward_method="abs_max", backward_dtype=FPQuantDtype.BF16,
+                             hadamard_group_size=32, modules_to_not_convert=["lm_head"])
+        replace_quantize_with_fp_quant_linear(model, qcfg)
+        torch.cuda.empty_cache()
+        fp4_prefill = timed(prefill, args.steps, args.warmup)
+        fp4_decode = decode_rate(16, 4)
+    ops.check_device_errors(dev)
+    tokens = prefill_ids.numel()
+    line = {
+        "metric": "w4a4_model_prefill_tokens_per_s", "value": tokens / fp4_prefill, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": fp4_prefill * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1)xfp4->f32->bf16 linears, bf16 attention", "data": "synthetic",
+        "config": {"workload": f"forward of {n_layers} Qwen3-14B-shaped decoder blocks, all linears W4A4 MXFP4 FPQuantLinear "
+                               f"(Hadamard 32), prefill 8x2048 tokens, decode batch 64 on a 128-token cache, HF eager modules",
+                   "l2": "weights of a block (0.6 GB bf16, 0.17 GB FP4) and activations exceed the 126 MB L2"},
+        "prefill": {"w4a4_tokens_per_s": tokens / fp4_prefill, "bf16_tokens_per_s": tokens / bf16_prefill,
+                    "speedup_vs_bf16": bf16_prefill / fp4_prefill},
+        "decode": {"w4a4_tokens_per_s": 64 / fp4_decode, "bf16_tokens_per_s": 64 / bf16_decode,
+                   "speedup_vs_bf16": bf16_decode / fp4_decode, "ms_per_step_w4a4": fp4_decode * 1e3},
+        "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model", "tp-linear"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model", "tp-linear", "model-forward"])
     ap.add_argument("--model-layers", type=int, default=2)
     ap.add_argument("--calib-seqs", type=int, default=128)
     ap.add_argument("--tp-fused", action="store_true", help="tp-linear: push output tiles to the peers from the GEMM epilogue")
@@ -781,6 +866,8 @@ def main():
             run_gptq_model(args)
         elif args.workload == "tp-linear":
             run_tp_linear(args)
+        elif args.workload == "model-forward":
+            run_model_forward(args)
         else:
             run_ours(args)
 
