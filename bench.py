@@ -384,6 +384,47 @@ def run_ours(args):
         if args.workload == "quantize":
             roofline = quant_roof
 
+    # ---- the vendor library on the same operands, for orientation only (never on the product path):
+    # cuBLASLt block-scaled FP4 through torch._scaled_mm, same codes, same swizzled scale bytes
+    library = None
+    if args.workload in ("linear", "gemm") and rank == 0 and not args.no_library_gemm:
+        try:
+            sdt = torch.float8_e8m0fnu if fmt == "mxfp4" else torch.float8_e4m3fn
+            ops_l = []
+            for i, layer in enumerate(layers):
+                q, sb, _ = ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)
+                ops_l.append((q.view(torch.float4_e2m1fn_x2), layer.qweight.view(torch.float4_e2m1fn_x2).t(),
+                              sb.flatten().view(sdt), wscales[i].flatten().view(sdt), q, sb, i))
+            same = True
+            for a4, b4t, sa, sbw, q, sb, i in ops_l:
+                y = torch._scaled_mm(a4, b4t, sa, sbw, out_dtype=torch.bfloat16).float()
+                ours = ops.gemm_fp4(q, layers[i].qweight, sb, wscales[i], torch.ones(1, device=dev), fmt).float()
+                same = same and bool(torch.allclose(y, ours, rtol=2e-2, atol=1e-2 * float(ours.abs().max())))
+            for _ in range(3):
+                for a4, b4t, sa, sbw, *_ in ops_l:
+                    torch._scaled_mm(a4, b4t, sa, sbw, out_dtype=torch.bfloat16)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                for a4, b4t, sa, sbw, *_ in ops_l:
+                    torch._scaled_mm(a4, b4t, sa, sbw, out_dtype=torch.bfloat16)
+            e1.record()
+            torch.cuda.synchronize()
+            lms = e0.elapsed_time(e1) / args.steps
+            e0.record()
+            for _ in range(args.steps):
+                for a4, b4t, sa, sbw, q, sb, i in ops_l:
+                    ops.gemm_fp4(q, layers[i].qweight, sb, wscales[i], alphas[i], fmt, out=outs[i])
+            e1.record()
+            torch.cuda.synchronize()
+            oms = e0.elapsed_time(e1) / args.steps
+            library = {"name": "cuBLASLt block-scaled FP4 via torch._scaled_mm (comparison only)",
+                       "tflops": flops_step / (lms * 1e-3) / 1e12, "ours_same_loop_tflops": flops_step / (oms * 1e-3) / 1e12,
+                       "results_agree": same}
+        except Exception as exc:  # the comparison is optional
+            library = {"unavailable": repr(exc)[:200]}
+
     # ---- end to end through FPQuantLinear.forward with host buffers
     e2e = None
     if args.workload == "linear":
@@ -454,7 +495,7 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp4(e2m1)xfp4->f32->bf16", "data": "synthetic", "config": workload_config(args),
-            "roofline": roofline, "quantize_roofline": quant_roof, "cpu_baseline": cpu, "e2e": e2e,
+            "roofline": roofline, "quantize_roofline": quant_roof, "library_gemm": library, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": n_launch, "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
@@ -854,6 +895,7 @@ def main():
     ap.add_argument("--format", default="mxfp4", choices=["mxfp4", "nvfp4"])
     ap.add_argument("--cpu-rows", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-library-gemm", action="store_true", help="skip the cuBLASLt comparison line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdarg>
+#include <cstdlib>
 
 #include "../../include/fpq_b200.h"
 
@@ -78,6 +79,22 @@ __device__ __forceinline__ uint32_t patch_zero_codes(uint32_t w) {
   uint32_t t = w | (w >> 1) | (w >> 2);
   uint32_t z = ~t & 0x11111111u;
   return w | (z << 3);
+}
+
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization attribute may
+// start while the previous kernel of the stream is still finishing; it calls grid_dependency_wait() before it
+// touches anything that kernel (or an earlier one) wrote.  launch_dependents() lets the NEXT kernel's blocks be
+// scheduled as soon as resources free up.  Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Whether launches carry the attribute (environment FPQ_PDL=0 switches it off).
+inline bool use_dependent_launch() {
+  static const bool on = [] {
+    const char* e = getenv("FPQ_PDL");
+    return e ? atoi(e) != 0 : true;
+  }();
+  return on;
 }
 
 }  // namespace fpq

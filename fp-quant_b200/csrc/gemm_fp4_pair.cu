@@ -56,6 +56,7 @@ struct PairParams {
   __nv_bfloat16* out;
   int* error_flag;
   int raster_group;
+  int tune_n;              // tuning aid: issue the MMAs with this N instead of 256 (timing only, results are wrong)
   long long* profile;      // optional: per-pair cycle counters for tuning (NULL in normal use)
 };
 
@@ -155,6 +156,10 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   cluster_sync_all();                       // peer barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Everything above (barriers, tensor memory, descriptor prefetch) touched nothing another kernel wrote and
+  // may overlap the tail of the previous kernel; from here on operands and outputs are accessed.
+  launch_dependents();
+  grid_dependency_wait();
 
   // addresses of the leader's barriers as seen from this CTA
   const uint32_t lead_full = map_to_cta(bar_full, 0);
@@ -216,7 +221,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const uint32_t sf_id = NVFP4 ? 0u : (uint32_t)((k & 1) * 2);
-        idesc_k[k] = make_idesc_fp4(256, BN, !NVFP4, sf_id, sf_id);
+        idesc_k[k] = make_idesc_fp4(256, p.tune_n ? p.tune_n : BN, !NVFP4, sf_id, sf_id);
       }
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
@@ -476,13 +481,15 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = L::DYN_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = use_dependent_launch() ? 2 : 1;
   FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, tout, p, push));
   return FPQ_OK;
 }
@@ -517,6 +524,10 @@ int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const 
   {
     const char* pe = getenv("FPQ_GEMM_PROFILE_PTR");   // tuning aid: address of a device buffer of 8 int64 per pair
     p.profile = pe ? reinterpret_cast<long long*>(strtoull(pe, nullptr, 0)) : nullptr;
+  }
+  {
+    const char* tn = getenv("FPQ_GEMM_TUNE_N");
+    p.tune_n = tn ? atoi(tn) : 0;
   }
   const char* e = getenv("FPQ_GEMM_RASTER");
   p.raster_group = e ? atoi(e) : 8;

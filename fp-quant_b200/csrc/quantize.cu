@@ -513,6 +513,8 @@ __global__ void __launch_bounds__(256, Prefetches<IN_BF16, MODE>::value ? FPQ_Q_
   const int lane = threadIdx.x & 31;
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * 32;
+  launch_dependents();         // the next kernel may set itself up while this one runs
+  grid_dependency_wait();      // the input (and the global scale) may come from the previous kernel
   float gs = 0.0f, rgs = 0.0f;
   if (FMT == FPQ_FMT_NVFP4 && (MODE == MODE_CODES || MODE == MODE_DEQUANT)) {
     gs = *p.gs;
@@ -571,8 +573,17 @@ int launch_one(const QuantParams& params, cudaStream_t stream) {
   int64_t blocks = (int64_t)sm_count() * per_sm;
   if (blocks > blocks_needed) blocks = blocks_needed;
   if (blocks < 1) blocks = 1;
-  quant_kernel<GH, FMT, IN_BF16, MODE><<<(unsigned)blocks, 256, 0, stream>>>(p);
-  FPQ_CHECK_LAUNCH();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_dependent_launch() ? 1 : 0;
+  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, quant_kernel<GH, FMT, IN_BF16, MODE>, p));
   return FPQ_OK;
 }
 
