@@ -116,6 +116,8 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   using L = PairSmem<NVFP4>;
   constexpr int STAGES = L::STAGES;
   constexpr int SFBLK = L::SFBLK;
+  unsigned long long ns_entry = 0;
+  if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_entry));
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const uint32_t sbase = smem_u32(smem);
@@ -160,6 +162,8 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   // may overlap the tail of the previous kernel; from here on operands and outputs are accessed.
   launch_dependents();
   grid_dependency_wait();
+  unsigned long long ns_setup = 0;
+  if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_setup));
 
   // addresses of the leader's barriers as seen from this CTA
   const uint32_t lead_full = map_to_cta(bar_full, 0);
@@ -278,6 +282,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
         o[0] = tick<PROF>() - t_begin; o[1] = t_acc; o[2] = t_full; o[3] = 0; o[4] = it; o[14] = t_begin;
         o[15] = (long long)(ns_end - ns_begin);
+        o[16] = (long long)ns_entry; o[17] = (long long)ns_setup; o[18] = (long long)ns_begin; o[19] = (long long)ns_end;
       }
       if (!ok) {
         *abort_flag = 1;
@@ -450,6 +455,11 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   tc_fence_before();
   __syncthreads();
+  if (PROF && p.profile && threadIdx.x == 0 && rank == 0) {
+    unsigned long long ns_done = 0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_done));
+    p.profile[(size_t)pair_id * 64 + 20] = (long long)ns_done;
+  }
   cluster_sync_all();          // neither CTA leaves while its peer may still signal its barriers
   if (warp == 1) {
     __syncwarp();
