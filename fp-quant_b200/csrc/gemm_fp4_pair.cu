@@ -29,6 +29,7 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
+#include <cstdio>
 #include <cstdlib>
 
 namespace fpq {
@@ -41,7 +42,7 @@ constexpr int BN = 256;                // columns of the pair tile
 constexpr int BN_CTA = 128;            // rows of B per CTA
 constexpr int BK_BYTES = 128;
 constexpr int BK_ELEMS = 256;
-constexpr int NUM_THREADS = 448;       // 14 warps: producer, MMA, 4 epilogue, 4 scale movers, 4 epilogue
+constexpr int NUM_THREADS = 704;       // 22 warps: producer, MMA, 4 scale movers, 16 epilogue (one per 32 rows x 64 columns)
 constexpr int TMEM_COLS = 512;
 constexpr int SF_TMEM_BASE = 256;
 
@@ -56,6 +57,8 @@ struct PairParams {
   __nv_bfloat16* out;
   int* error_flag;
   int raster_group;
+  int stagger_base, stagger_step;   // cycles after the accumulator release before epilogue warp i converts and stores: base + i * step
+  int tune_skip;           // tuning aid (tuning instantiation only): 1 = no conversion math, 2 = no staging and store
   int tune_n;              // tuning aid: issue the MMAs with this N instead of 256 (timing only, results are wrong)
   long long* profile;      // optional: per-pair cycle counters for tuning (NULL in normal use)
 };
@@ -70,7 +73,7 @@ struct PushParams {
 
 template <bool NVFP4>
 struct PairSmem {
-  static constexpr int STAGES = 5;
+  static constexpr int STAGES = 4;
   static constexpr int SFBLK = NVFP4 ? 4 : 2;                 // 512-byte scale tiles per 128 rows per stage
   static constexpr int SFA_COLS = 4 * SFBLK;                  // tensor-memory columns of one stage's A scales
   static constexpr int SF_TMEM_BUF = 12 * SFBLK;              // A scales + B scales (256 rows) of one stage
@@ -84,10 +87,10 @@ struct PairSmem {
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
-  static constexpr int OFF_OUT = OFF_SFB + STAGES * SFB_BYTES;  // eight 32-row x 128-byte staging boxes (epilogue)
+  static constexpr int OFF_OUT = OFF_SFB + STAGES * SFB_BYTES;  // sixteen 32-row x 128-byte staging boxes (epilogue)
   static constexpr int OUT_BOX_BYTES = 32 * 128;
   // full[S], empty[S], sf_full[S], acc_full, acc_empty
-  static constexpr int OFF_BAR = OFF_OUT + 8 * OUT_BOX_BYTES;
+  static constexpr int OFF_BAR = OFF_OUT + 16 * OUT_BOX_BYTES;
   static constexpr int OFF_MISC = OFF_BAR + (3 * STAGES + 2) * 8;
   static constexpr int TOTAL = OFF_MISC + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
@@ -140,7 +143,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       mbar_init(bar_sf_full + 8 * s, 1);
     }
     mbar_init(bar_acc_full, 1);
-    mbar_init(bar_acc_empty, 16);          // eight epilogue warps per CTA (used in the leader)
+    mbar_init(bar_acc_empty, 32);          // sixteen epilogue warps per CTA (used in the leader)
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
@@ -289,7 +292,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         atomicExch(p.error_flag, 1);
       }
     }
-  } else if (warp >= 6 && warp < 10) {
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------- scale-factor movers (both CTAs)
     // A 512-byte tile is 32 rows x 16 bytes: lane l takes row l and writes it to lane l of this warp's
     // quarter of tensor memory, columns [c, c+4) -- the four warps together produce the replicated
@@ -333,7 +336,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       if (lane == 0) mbar_arrive_cluster(lead_full + 8 * s);
       m_arr += tick<PROF>() - t3;
     }
-    if (PROF && p.profile && warp == 6 && lane == 0) {
+    if (PROF && p.profile && warp == 2 && lane == 0) {
       long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
       o[5] = m_sf; o[6] = 0; o[7] = m_st; o[8] = m_arr; o[9] = tick<PROF>() - m_begin;
     }
@@ -343,8 +346,8 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   } else {
     // ------------------------------------------------------------- epilogue (both CTAs)
-    const int quarter = warp & 3;
-    const int col_half = warp >= 10 ? 1 : 0;     // warps 2-5 drain columns 0-127, warps 10-13 columns 128-255
+    const int quarter = warp & 3;                // the 32 lanes of tensor memory this warp may read
+    const int col_q = (warp - 6) >> 2;           // which 64 of the tile's 256 columns
     const float alpha = *p.alpha;
     uint32_t tile_count = 0;
     bool ok = true;
@@ -357,40 +360,14 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       long long t1 = tick<PROF>();
       e_wait += t1 - t0;
       tc_fence_after();
-      // 1) drain this warp's 128 fp32 columns in two halves of 64 (two 32-column loads in flight each);
-      //    the first half is packed to bf16 pairs (x alpha, + bias) while still holding the accumulator,
-      //    which frees the registers for the second half
+      // 1) drain this warp's 64 fp32 columns in one round (two 32-column loads in flight): with sixteen
+      //    warps the whole accumulator is in registers after a single load latency
       const int row0 = m_pair * 256 + (int)rank * BM_CTA + quarter * 32;
-      const int col_w = n_blk * BN + col_half * 128;           // first of my 128 columns
-      uint32_t pk[64];
-      const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + col_half * 128;
-      auto pack_half = [&](int half, const uint32_t (&ra)[32], const uint32_t (&rb)[32]) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const uint32_t* rr = j < 16 ? ra : rb;
-          float v0 = __uint_as_float(rr[(2 * j) & 31]) * alpha;
-          float v1 = __uint_as_float(rr[(2 * j + 1) & 31]) * alpha;
-          if (p.bias) {
-            const int col = col_w + half * 64 + 2 * j;
-            if (col < p.N) {
-              v0 += __bfloat162float(p.bias[col]);
-              v1 += __bfloat162float(p.bias[col + 1]);
-            }
-          }
-          __nv_bfloat162 hh = __floats2bfloat162_rn(v0, v1);
-          pk[half * 32 + j] = *reinterpret_cast<uint32_t*>(&hh);
-        }
-      };
-      {
-        uint32_t ra[32], rb[32];
-        tc_ld_32x32b_x32(tsrc, ra);
-        tc_ld_32x32b_x32(tsrc + 32, rb);
-        tc_wait_ld();
-        pack_half(0, ra, rb);
-      }
-      uint32_t rc[32], rd[32];
-      tc_ld_32x32b_x32(tsrc + 64, rc);
-      tc_ld_32x32b_x32(tsrc + 96, rd);
+      const int col_w = n_blk * BN + col_q * 64;               // first of my 64 columns
+      const uint32_t tsrc = tmem_base + ((uint32_t)(quarter * 32) << 16) + col_q * 64;
+      uint32_t ra[32], rb[32];
+      tc_ld_32x32b_x32(tsrc, ra);
+      tc_ld_32x32b_x32(tsrc + 32, rb);
       tc_wait_ld();
       e_ld0 += tick<PROF>() - t1;
       // 2) hand the accumulator back: the next tile's MMAs may start while we convert and write out
@@ -399,51 +376,74 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
       long long t2 = tick<PROF>();
       e_drain += t2 - t1;
-      pack_half(1, rc, rd);
-      // 3) write out through shared memory: each warp owns a 32-row x 128-byte staging box (128-byte
-      //    swizzle, so the 16-byte row pieces of the 32 lanes spread over all banks) and sends it with
-      //    one TMA store per 64 columns; the store clips rows >= M and columns >= N.  Direct 16-byte
-      //    stores from 32 different rows per instruction kept the load/store path busy for ~7000
-      //    cycles per tile and slowed the MMA issue in that time.
-      const uint32_t stage_out = sbase + L::OFF_OUT + (uint32_t)(col_half * 4 + quarter) * L::OUT_BOX_BYTES;
+      // 3) wait for this warp's slot.  All sixteen warps converting and storing at once costs the next
+      //    tile about 1400 cycles: the four warps that share the MMA thread's scheduler take its issue
+      //    slots just when the tensor pipe is empty, and sixteen 4 KiB TMA stores in one burst hold up the
+      //    operand loads behind them.  Spread over the next tile's main loop both disappear in its slack.
+      if (tile + num_pairs < p.num_tiles) {          // not after the last tile: there is nothing left to protect
+        const long long due = clock64() + p.stagger_base + (long long)(col_q * 4 + quarter) * p.stagger_step;
+        while (clock64() < due) __nanosleep(64);
+      }
+      uint32_t pk[32];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (lane == 0) bulk_wait_group_read0();      // the previous store has read the box
-        __syncwarp();
-#pragma unroll
-        for (int q = 0; q < 8; ++q)
-          st_shared_v4(stage_out + (uint32_t)lane * 128u + (uint32_t)((q ^ (lane & 7)) * 16), pk[h * 32 + 4 * q],
-                       pk[h * 32 + 4 * q + 1], pk[h * 32 + 4 * q + 2], pk[h * 32 + 4 * q + 3]);
-        fence_proxy_async();
-        __syncwarp();
-        const int colh = col_w + h * 64;
-        if (lane == 0 && row0 < p.M && colh < p.N) {
-          tma_store_2d(&tmap_out, stage_out, colh, row0);
-          bulk_commit_group();
+      for (int j = 0; j < 32; ++j) {
+        const uint32_t* rr = j < 16 ? ra : rb;
+        if (PROF && (p.tune_skip & 1)) { pk[j] = rr[(2 * j) & 31]; continue; }
+        float v0 = __uint_as_float(rr[(2 * j) & 31]) * alpha;
+        float v1 = __uint_as_float(rr[(2 * j + 1) & 31]) * alpha;
+        if (p.bias) {
+          const int col = col_w + 2 * j;
+          if (col < p.N) {
+            v0 += __bfloat162float(p.bias[col]);
+            v1 += __bfloat162float(p.bias[col + 1]);
+          }
         }
-        if (PUSH && push.n > 0) {
-          // Same box to the peers with ordinary 16-byte stores over NVLink: eight lanes cover the 128 bytes
-          // of one row, so every instruction writes four full lines (the box is read back un-swizzled).
-          const int rsub = lane >> 3, chunk = lane & 7;
-          const int col = colh + chunk * 8;
+        __nv_bfloat162 hh = __floats2bfloat162_rn(v0, v1);
+        pk[j] = *reinterpret_cast<uint32_t*>(&hh);
+      }
+      // 4) write out through shared memory: each warp owns a 32-row x 128-byte staging box (128-byte
+      //    swizzle, so the 16-byte row pieces of the 32 lanes spread over all banks) and sends it with
+      //    one TMA store; the store clips rows >= M and columns >= N.  Direct 16-byte stores from 32
+      //    different rows per instruction kept the load/store path busy for ~7000 cycles per tile and
+      //    slowed the MMA issue in that time.
+      const uint32_t box_off = (uint32_t)(L::OFF_OUT + (col_q * 4 + quarter) * L::OUT_BOX_BYTES);
+      const uint32_t stage_out = sbase + box_off;
+      if (PROF && (p.tune_skip & 2)) {
+        if (pk[0] == 0x12345678u && pk[31] == 0x9abcdef0u) *abort_flag = 2;   // keeps the values alive
+        continue;
+      }
+      if (lane == 0) bulk_wait_group_read0();      // the previous store has read the box
+      __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int r = rsub + 4 * i;
-            const uint4 v = *reinterpret_cast<const uint4*>(smem + L::OFF_OUT +
-                                                             (col_half * 4 + quarter) * L::OUT_BOX_BYTES + r * 128 +
-                                                             ((chunk ^ (r & 7)) * 16));
-            if (row0 + r < p.M && col < p.N) {
+      for (int q = 0; q < 8; ++q)
+        st_shared_v4(stage_out + (uint32_t)lane * 128u + (uint32_t)((q ^ (lane & 7)) * 16), pk[4 * q], pk[4 * q + 1],
+                     pk[4 * q + 2], pk[4 * q + 3]);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0 && row0 < p.M && col_w < p.N) {
+        tma_store_2d(&tmap_out, stage_out, col_w, row0);
+        bulk_commit_group();
+      }
+      if (PUSH && push.n > 0) {
+        // Same box to the peers with ordinary 16-byte stores over NVLink: eight lanes cover the 128 bytes
+        // of one row, so every instruction writes four full lines (the box is read back un-swizzled).
+        const int rsub = lane >> 3, chunk = lane & 7;
+        const int col = col_w + chunk * 8;
 #pragma unroll
-              for (int pr = 0; pr < 7; ++pr)
-                if (pr < push.n) *reinterpret_cast<uint4*>(push.out[pr] + (long long)(row0 + r) * push.ld + col) = v;
-            }
+        for (int i = 0; i < 8; ++i) {
+          const int r = rsub + 4 * i;
+          const uint4 v = *reinterpret_cast<const uint4*>(smem + box_off + r * 128 + ((chunk ^ (r & 7)) * 16));
+          if (row0 + r < p.M && col < p.N) {
+#pragma unroll
+            for (int pr = 0; pr < 7; ++pr)
+              if (pr < push.n) *reinterpret_cast<uint4*>(push.out[pr] + (long long)(row0 + r) * push.ld + col) = v;
           }
         }
       }
       e_store += tick<PROF>() - t2;
     }
     if (lane == 0) bulk_wait_group0();   // my stores are complete before the CTA may exit
-    if (PROF && p.profile && warp == 2 && lane == 0) {
+    if (PROF && p.profile && warp == 6 && lane == 0) {
       long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
       o[10] = e_wait; o[11] = e_drain; o[12] = e_store; o[13] = e_ld0;
     }
@@ -538,6 +538,16 @@ int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const 
   {
     const char* tn = getenv("FPQ_GEMM_TUNE_N");
     p.tune_n = tn ? atoi(tn) : 0;
+    // the sixteen slots cover at most 60 % of a tile's main loop (740 cycles per K stage)
+    p.stagger_base = 0;
+    p.stagger_step = (int)(p.num_k_stages * 740 * 6 / 10 / 16);
+    if (p.stagger_step > 300) p.stagger_step = 300;
+    if (const char* sg = getenv("FPQ_GEMM_STAGGER")) {   // tuning aid: "base,step" in cycles
+      int b0 = 0, s0 = 0;
+      if (sscanf(sg, "%d,%d", &b0, &s0) == 2) { p.stagger_base = b0; p.stagger_step = s0; }
+    }
+    const char* ts = getenv("FPQ_GEMM_TUNE_SKIP");
+    p.tune_skip = ts ? atoi(ts) : 0;
   }
   const char* e = getenv("FPQ_GEMM_RASTER");
   p.raster_group = e ? atoi(e) : 8;
