@@ -350,11 +350,16 @@ __device__ __forceinline__ uint32_t e2m1_code_hw(float v, float& value) {
   return code;
 }
 
+// G = 16 / 32: column c uses scale group c / G.  G = 1: activation order -- the columns were permuted
+// beforehand and column c uses group gidx[c] of the n_groups static groups (gptq.py:146-148, 170-171);
+// every thread then keeps one scale per column, so blocks are limited to 256 threads.
 template <int G>
-__global__ void __launch_bounds__(512) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C, int64_t c1,
-                                                         const float* __restrict__ scales,
-                                                         const float* __restrict__ U, float* __restrict__ Err,
-                                                         uint8_t* __restrict__ codes) {
+__global__ void __launch_bounds__(G == 1 ? 256 : 512) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C,
+                                                                        int64_t c1, const float* __restrict__ scales,
+                                                                        const float* __restrict__ U,
+                                                                        float* __restrict__ Err,
+                                                                        uint8_t* __restrict__ codes,
+                                                                        const int32_t* __restrict__ gidx, int n_groups) {
   extern __shared__ float Us[];   // NB rows of US_LD floats, then the reciprocals of the diagonal
   float* rdiag = Us + NB * US_LD;
   for (int idx = threadIdx.x; idx < NB * NB / 4; idx += blockDim.x) {
@@ -373,11 +378,15 @@ __global__ void __launch_bounds__(512) gptq_block_kernel(float* __restrict__ W, 
   if (!live) row = rows - 1;                   // keep the quad's shuffles uniform; nothing is stored
 
   constexpr int NGRP = SUB / G;
-  float sc[NGRP], rsc[NGRP];
+  float sc[NGRP], rsc[G == 1 ? 1 : NGRP];
 #pragma unroll
   for (int g = 0; g < NGRP; ++g) {
-    sc[g] = scales[row * (C / G) + (c1 + SUB * q) / G + g];
-    rsc[g] = rcp_safe(sc[g]) ? __frcp_rn(sc[g]) : 0.0f;
+    if (G == 1) {
+      sc[g] = scales[row * n_groups + gidx[c1 + SUB * q + g]];
+    } else {
+      sc[g] = scales[row * (C / G) + (c1 + SUB * q) / G + g];
+      rsc[g] = rcp_safe(sc[g]) ? __frcp_rn(sc[g]) : 0.0f;
+    }
   }
   float w[SUB], err[SUB];
   {
@@ -403,7 +412,8 @@ __global__ void __launch_bounds__(512) gptq_block_kernel(float* __restrict__ W, 
       float e = 0.0f;
       if (owner) {
         // w / s and (w - wq) / U[i,i] as IEEE divisions (the reference's), computed from reciprocals
-        const float s = sc[ii / G], rs = rsc[ii / G];
+        const float s = sc[ii / G];
+        const float rs = G == 1 ? (rcp_safe(s) ? __frcp_rn(s) : 0.0f) : rsc[G == 1 ? 0 : ii / G];
         const float qv = rs != 0.0f ? div_by(w[ii], s, rs) : __fdiv_rn(w[ii], s);
         float gv;
         const uint32_t code = e2m1_code_hw(qv, gv);
@@ -604,6 +614,12 @@ extern "C" int64_t fpq_gptq_workspace_bytes(int64_t rows, int64_t cols) {
 extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const float* scales, int group,
                                  const float* U, uint8_t* codes, void* workspace, int32_t* error_flag,
                                  fpq_stream_t stream) {
+  return fpq_gptq_quantize_ordered(W, rows, cols, scales, group, nullptr, U, codes, workspace, error_flag, stream);
+}
+
+extern "C" int fpq_gptq_quantize_ordered(float* W, int64_t rows, int64_t cols, const float* scales, int group,
+                                         const int32_t* group_index, const float* U, uint8_t* codes, void* workspace,
+                                         int32_t* error_flag, fpq_stream_t stream) {
   FPQ_CHECK_ARG(W && scales && U && workspace && error_flag, "NULL pointer");
   FPQ_CHECK_ARG(group == 16 || group == 32, "group must be 16 (NVFP4) or 32 (MXFP4)");
   FPQ_CHECK_ARG(rows > 0 && cols > 0 && cols % NB == 0, "cols (%lld) must be a multiple of %d", (long long)cols, NB);
@@ -618,6 +634,7 @@ extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const flo
   if (dev < 64 && !configured[dev]) {
     FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev] = true;
   }
   // workspace: block errors (fp32) | their transposed three-term bf16 split | three-term bf16 split of U
@@ -641,14 +658,18 @@ extern "C" int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const flo
   // handful of blocks for a second pass.
   const int64_t units = (rows + 7) / 8;
   int wpb = (int)((units + sm_count() - 1) / sm_count());
-  wpb = wpb < 4 ? 4 : (wpb > 16 ? 16 : wpb);
+  const int wpb_max = group_index ? 8 : 16;
+  wpb = wpb < 4 ? 4 : (wpb > wpb_max ? wpb_max : wpb);
   const unsigned threads = (unsigned)wpb * 32;
   const unsigned grid = (unsigned)((units + wpb - 1) / wpb);
   for (int64_t c1 = 0; c1 < cols; c1 += NB) {
-    if (group == 16)
-      gptq_block_kernel<16><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
+    const int n_groups = (int)(cols / group);
+    if (group_index)
+      gptq_block_kernel<1><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes, group_index, n_groups);
+    else if (group == 16)
+      gptq_block_kernel<16><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes, nullptr, n_groups);
     else
-      gptq_block_kernel<32><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes);
+      gptq_block_kernel<32><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes, nullptr, n_groups);
     FPQ_CHECK_LAUNCH();
     const int64_t c2 = c1 + NB;
     if (c2 >= cols) break;

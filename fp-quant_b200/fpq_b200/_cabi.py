@@ -44,6 +44,8 @@ _SIGNATURES = {
     "fpq_cholesky_inverse_upper": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     "fpq_gptq_quantize": [c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p],
+    "fpq_gptq_quantize_ordered": [c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p],
     "fpq_gptq_workspace_bytes": [c_int64, c_int64],
     "fpq_relative_mse": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     "fpq_relative_mse_tc": [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -309,15 +309,22 @@ def cholesky_inverse_upper(H: torch.Tensor):
     return U, status
 
 
-def gptq_quantize(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group: int, want_codes: bool = True):
-    """Runs the GPTQ column loop on W in place (W becomes the dequantised weight).  Returns packed codes or None."""
+def gptq_quantize(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group: int, want_codes: bool = True,
+                  group_index: Optional[torch.Tensor] = None):
+    """Runs the GPTQ column loop on W in place (W becomes the dequantised weight).  Returns packed codes or None.
+    `group_index` (int32 [cols]): activation order -- W's columns are already permuted and column c takes
+    the static scale of group group_index[c]; W and the codes stay in the permuted order."""
     W, scales, U = _f32(W, "W", inplace=True), _f32(scales, "scales"), _f32(U, "U")
     rows, cols = W.shape
+    if group_index is not None:
+        if group_index.dtype != torch.int32 or not group_index.is_contiguous() or group_index.numel() != cols \
+                or group_index.device != W.device:
+            raise ValueError("group_index must be a contiguous int32 tensor of cols entries on W's device")
     codes = torch.empty(rows, cols // 2, dtype=torch.uint8, device=W.device) if want_codes else None
     ws = torch.empty(int(C.lib().fpq_gptq_workspace_bytes(rows, cols)), dtype=torch.uint8, device=W.device)
     with _guard(W.device):
-        C.call("fpq_gptq_quantize", W.data_ptr(), rows, cols, scales.data_ptr(), group, U.data_ptr(), _ptr(codes),
-               ws.data_ptr(), device_error_flag(W.device).data_ptr(), _stream(W))
+        C.call("fpq_gptq_quantize_ordered", W.data_ptr(), rows, cols, scales.data_ptr(), group, _ptr(group_index),
+               U.data_ptr(), _ptr(codes), ws.data_ptr(), device_error_flag(W.device).data_ptr(), _stream(W))
     return codes
 
 

@@ -29,7 +29,7 @@ from .. import dist as fdist
 from .. import ops
 from ..transforms.transforms import build_transform, get_transform_matrix
 from .gptq import GPTQ, get_relative_mse_error
-from .quant_args import ScalePrecision
+from .quant_args import QuantizationOrder, ScalePrecision
 from .quant_ops import cast_scales_to_eXmY
 from .quantizer import Quantizer
 
@@ -412,7 +412,11 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
         group_members: Dict[str, List[str]] = {}
         for name in handles:
             group_members.setdefault(_input_group(name.split(".")[-1]), []).append(name)
-        share_ok = {grp: not any(bool((handles[n].layer.weight == 0).all(dim=0).any().item()) for n in names)
+        # (In activation order every layer permutes, damps and factors its own copy of the Hessian inside
+        # `GPTQ.step`: no sharing.)
+        act_order = QuantizationOrder(args.quantization_order) == QuantizationOrder.ACTIVATION
+        share_ok = {grp: not act_order and
+                    not any(bool((handles[n].layer.weight == 0).all(dim=0).any().item()) for n in names)
                     for grp, names in group_members.items()}
         group_order, group_owner, layer_owner = plan_ranks(
             group_members, {g: handles[leaders[g]].d_col for g in group_members}, world_size)

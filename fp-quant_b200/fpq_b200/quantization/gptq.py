@@ -32,8 +32,6 @@ class GPTQ:
         self.d_row, self.d_col = layer.weight.shape
         self.quantizer = quantizer
         self.quantization_order = QuantizationOrder(quantization_order)
-        if self.quantization_order != QuantizationOrder.DEFAULT:
-            raise NotImplementedError("activation-order GPTQ is not built yet")
         self.block_size, self.rel_damp = block_size, rel_damp
         self.W_device, self.W_dtype, self.W_shape = self.W.device, self.W.dtype, self.W.shape
         self.H: Optional[torch.Tensor] = None
@@ -82,18 +80,40 @@ class GPTQ:
 
         group = self.quantizer.group_size
         scales, _ = self.quantizer.get_quantization_params(self.W)        # static scales, gptq.py:142
+        act_order = self.quantization_order == QuantizationOrder.ACTIVATION
+        group_index = perm_inv = None
+        W = self.W
+        if act_order:
+            # gptq.py:146-155: columns by falling diag(H); the Hessian is permuted before it is damped and
+            # inverted (the dead-column test still reads the unpermuted weight, as in the reference), and a
+            # permuted column keeps the static scale of the group it came from
+            if U is not None:
+                raise ValueError("activation order derives the factor from the permuted Hessian: do not pass U")
+            perm = torch.argsort(self.H.diag(), descending=True)
+            perm_inv = torch.argsort(perm)
+            group_index = (perm // group).to(torch.int32).contiguous()
+            self.H = self.H[perm][:, perm].contiguous()
+            W = self.W[:, perm].contiguous()
         if U is None:
             U = self._get_hessian_inverse()
         rank, ws = fdist.world(process_group)
+        sc = scales.float().contiguous()
         if shard_rows and ws > 1 and self.d_row >= 128 * ws:
             lo, hi = fdist.shard_bounds(self.d_row, ws, rank, multiple=128)
-            w_loc = self.W[lo:hi].clone()
-            codes_loc = ops.gptq_quantize(w_loc, scales[lo:hi].float().contiguous(), U, group, want_codes=True)
+            w_loc = W[lo:hi].clone()
+            codes_loc = ops.gptq_quantize(w_loc, sc[lo:hi].contiguous(), U, group, want_codes=True, group_index=group_index)
             w = fdist.allgather_rows(w_loc, self.d_row, 128, process_group)
             self.packed_codes = fdist.allgather_rows(codes_loc, self.d_row, 128, process_group)
         else:
-            w = self.W.clone()
-            self.packed_codes = ops.gptq_quantize(w, scales.float().contiguous(), U, group, want_codes=True)
+            w = W.clone()
+            self.packed_codes = ops.gptq_quantize(w, sc, U, group, want_codes=True, group_index=group_index)
+        if act_order:
+            # gptq.py:190-193: back to the original column order (weights, codes, Hessian)
+            w = w[:, perm_inv].contiguous()
+            nib = torch.stack((self.packed_codes & 0xF, self.packed_codes >> 4), dim=-1).reshape(self.d_row, self.d_col)
+            nib = nib[:, perm_inv]
+            self.packed_codes = (nib[:, 0::2] | (nib[:, 1::2] << 4)).contiguous()
+            self.H = self.H[perm_inv][:, perm_inv].contiguous()
         qweight = None
         if self.export_quantized_model and want_grid_values:
             # grid values of both nibbles of a byte from one 256-entry table

@@ -247,6 +247,17 @@ int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, float* works
 int fpq_gptq_quantize(float* W, int64_t rows, int64_t cols, const float* scales, int group,
                       const float* U, uint8_t* codes, void* workspace, int32_t* error_flag, fpq_stream_t stream);
 
+/*
+ * The same loop in activation order (quantization_order = "activation", gptq.py:146-155, 170-171): the
+ * caller has permuted the columns of W (and the Hessian behind U) by falling diag(H); group_index
+ * (device int32 [cols]) names, for every permuted column, which of the cols/group static scale groups
+ * of the unpermuted W it belongs to.  W and codes come back in the permuted order (gptq.py:190-192
+ * undoes it).  group_index == NULL is fpq_gptq_quantize.
+ */
+int fpq_gptq_quantize_ordered(float* W, int64_t rows, int64_t cols, const float* scales, int group,
+                              const int32_t* group_index, const float* U, uint8_t* codes, void* workspace,
+                              int32_t* error_flag, fpq_stream_t stream);
+
 /* Bytes of workspace fpq_gptq_quantize needs for a [rows, cols] weight (sizing helper for the call above;
  * the reference allocates its temporaries implicitly, gptq.py:159-187). */
 int64_t fpq_gptq_workspace_bytes(int64_t rows, int64_t cols);

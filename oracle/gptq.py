@@ -73,8 +73,10 @@ def cholesky_inverse_upper(Hd: torch.Tensor) -> Tuple[torch.Tensor, bool]:
 
 
 def gptq_column_loop(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group: int,
-                     block_size: int = 128):
-    """The hot loop of `GPTQ.step` (gptq.py:159-187), export path, default order.
+                     block_size: int = 128, group_index: torch.Tensor = None):
+    """The hot loop of `GPTQ.step` (gptq.py:159-187), export path.  Default order: column i uses the
+    scale of group i // group; with `group_index` (activation order, gptq.py:146-148, 170-171) W's columns
+    are already permuted and column i uses the scale of group group_index[i].
 
     W [R, C] fp32 (rotated), scales fp32 [R, C/group] fixed beforehand from the
     unmodified W (gptq.py:142), U from `cholesky_inverse_upper`.
@@ -92,7 +94,7 @@ def gptq_column_loop(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, gro
         Ub = U[c1:c2, c1:c2]
         for i in range(c2 - c1):
             col = blk[:, i]
-            s = scales[:, (c1 + i) // group]
+            s = scales[:, (c1 + i) // group] if group_index is None else scales[:, int(group_index[c1 + i])]
             c = fp4.e2m1_codes(col.unsqueeze(-1), s.unsqueeze(-1), 1).squeeze(-1)
             wq = fp4.code_values(c) * s
             codes[:, c1 + i] = c
@@ -110,3 +112,12 @@ def relative_mse(Wq: torch.Tensor, W: torch.Tensor, H: torch.Tensor) -> float:
     Hd = H.to(torch.float64)
     Wd = W.to(torch.float64)
     return float((d @ Hd).mul(d).mean() / ((Wd @ Hd).mul(Wd).mean() + 1e-6))
+
+
+def activation_order(H: torch.Tensor, group: int):
+    """gptq.py:146-152: columns sorted by falling diag(H); returns (perm, perm_inv, group_index) where
+    group_index[i] is the scale group of the column that lands at position i."""
+    perm = torch.argsort(torch.diag(H), descending=True)
+    d = H.shape[0]
+    group_index = torch.arange(d // group).repeat_interleave(group)[perm]
+    return perm, torch.argsort(perm), group_index

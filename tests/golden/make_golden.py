@@ -10,6 +10,7 @@ Outputs (a few hundred KB in total):
   edge_<fmt>.npz     the same chain without rotation on rows of ties / zeros / extremes
   log2_probes.npz    cast_to_eBm0 on maxima a few ulps around powers of two
   gptq_<fmt>.npz     GPTQ.quantize (export path) on a 64 x 256 layer with a correlated Hessian
+  gptq_actorder_<fmt>.npz   the same layer with quantization_order="activation"
 The rotation fed to the reference is the oracle's butterfly (the reference's own FWHT is an
 external CUDA kernel whose summation order is unknown), everything downstream is reference code.
 """
@@ -134,6 +135,31 @@ def main():
         assert torch.allclose(Hd, h.H)
         save(f"gptq_{fmt}.npz", weight=wr, hessian=H, damped_hessian=h.H, u=U, scales=scales,
              codes=pack_fp4_to_uint8(qweight), dequantized=wq, relative_mse=rel,
+             global_scale=q.global_scale.clone())
+    # ---- the same layer in activation order (gptq.py:146-155, 190-193)
+    for fmt in specs:
+        name, g, prec = specs[fmt]
+        layer = nn.Linear(C, R, bias=False)
+        layer.weight.data = wr.clone()
+        q = Quantizer(bits=4, format=name, granularity="group", group_size=g, scale_precision=prec)
+        if fmt == "nvfp4":
+            q.get_quantization_params(wr)
+            q._track_global_scale = False
+        h = GPTQ(layer, q, quantization_order="activation", block_size=128, rel_damp=0.01,
+                 export_quantized_model="realquant")
+        h.H, h.num_samples = H.clone(), n
+        wq, qweight, scales = h.quantize()
+        rel = get_relative_mse_error(wq.float(), wr, h.H)
+        perm, perm_inv, gidx = ogptq.activation_order(H, g)
+        Hd = ogptq.prepare_hessian(H[perm][:, perm], wr, 0.01)
+        U, ok = ogptq.cholesky_inverse_upper(Hd)
+        o_wq, o_codes = ogptq.gptq_column_loop(wr[:, perm], scales, U, g, 128, group_index=gidx)
+        o_wq, o_codes = o_wq[:, perm_inv].contiguous(), o_codes[:, perm_inv].contiguous()
+        assert ok and torch.equal(fp4.pack_codes(o_codes), pack_fp4_to_uint8(qweight)) and torch.equal(o_wq, wq), fmt
+        assert torch.allclose(Hd[perm_inv][:, perm_inv], h.H)
+        assert not torch.equal(perm, torch.arange(C))
+        save(f"gptq_actorder_{fmt}.npz", weight=wr, hessian=H, damped_hessian=h.H, u_permuted=U, scales=scales,
+             perm=perm, codes=pack_fp4_to_uint8(qweight), dequantized=wq, relative_mse=rel,
              global_scale=q.global_scale.clone())
     print("oracle pinned against the reference on every case")
 

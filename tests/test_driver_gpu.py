@@ -160,3 +160,37 @@ def test_export_round_trip_runs_as_real_w4a4(fmt, tmp_path):
     print(f"{fmt}: reloaded W4A4 model vs the driver's model: worst layer {worst:.3e}, logits {rel:.3e} (relative MSE)")
     assert worst < 3e-3, worst
     assert rel < 0.08, rel
+
+
+def test_gptq_quantization_in_activation_order():
+    """The driver with quantization_order="activation": every layer permutes and factors its own Hessian;
+    the exported codes x scales still reproduce the weights left in the model, and the result is as good
+    as the default order on the calibration data."""
+    from fpq_b200.quantization.driver import gptq_quantization
+    from fpq_b200.quantization.quant_args import QuantizationOrder
+
+    dev = torch.device("cuda:0")
+    data = _calibration(dev)
+    with torch.no_grad():
+        ref_logits = torch.cat([_tiny_llama(dev)(x.to(dev)).logits.float() for x in data])
+
+    def run(order):
+        model = _tiny_llama(dev)
+        args = _args("nvfp")
+        args.quantization_order = order
+        quantized, _ = gptq_quantization(model, data, args, dev)
+        with torch.no_grad():
+            logits = torch.cat([model(x.to(dev)).logits.float() for x in data])
+        return model, quantized, float(((logits - ref_logits) ** 2).mean() / (ref_logits ** 2).mean())
+
+    model, quantized, err_act = run(QuantizationOrder.ACTIVATION)
+    _, quantized_default, err_default = run(QuantizationOrder.DEFAULT)
+    key = "model.layers.0.mlp.down_proj"
+    e = quantized[key]
+    sc = fp4.decode_scale_bytes(e["scales"].view(torch.uint8), "nvfp4") / e["weight_global_scale"].float().cpu()
+    deq = fp4.dequantize(fp4.unpack_codes(e["qweight"]), sc, 16)
+    w = model.model.layers[0].mlp.down_proj.weight.detach().float().cpu()
+    assert torch.allclose(deq, w, rtol=2 ** -7, atol=1e-6)
+    assert not torch.equal(e["qweight"], quantized_default[key]["qweight"])
+    print(f"relative logit error: activation order {err_act:.3e}, default order {err_default:.3e}")
+    assert err_act < 1.5 * err_default + 1e-3

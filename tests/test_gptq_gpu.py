@@ -161,3 +161,58 @@ def test_gptq_end_to_end_beats_rtn(cuda_device, fmt):
     assert agree >= 0.97
     assert abs(rel - rel_ref) <= 0.02 * rel_ref
     assert rel < 0.5 * rel_rtn
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_activation_order_column_loop_matches_golden(cuda_device, fmt):
+    """fpq_gptq_quantize_ordered with the reference's permuted U and static scales handed in."""
+    from fpq_b200 import ops
+
+    g = load(f"gptq_actorder_{fmt}.npz")
+    group = GROUP[fmt]
+    perm = g["perm"].long()
+    perm_inv = torch.argsort(perm)
+    gidx = (perm // group).to(torch.int32)
+    W = g["weight"][:, perm].contiguous().to(cuda_device)
+    codes = ops.gptq_quantize(W, g["scales"].to(cuda_device), g["u_permuted"].to(cuda_device), group,
+                              group_index=gidx.to(cuda_device))
+    got = fp4.unpack_codes(codes.cpu())[:, perm_inv]
+    want = fp4.unpack_codes(g["codes"])
+    agree = (got == want).float().mean().item()
+    print(f"{fmt} activation order: code agreement with the reference {agree:.5f}")
+    assert agree >= 0.99
+    wq = W.cpu()[:, perm_inv]
+    rel = ogptq.relative_mse(wq, g["weight"], g["damped_hessian"])
+    assert abs(rel - g["relative_mse"].item()) <= 0.01 * g["relative_mse"].item()
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_gptq_class_in_activation_order(cuda_device, fmt):
+    """GPTQ(quantization_order="activation").quantize(): permutation, damping and factor of the permuted
+    Hessian, ordered column loop, un-permutation -- against the reference's result for the same layer."""
+    import torch.nn as nn
+
+    from fpq_b200.quantization import GPTQ, Quantizer, get_relative_mse_error
+
+    g = load(f"gptq_actorder_{fmt}.npz")
+    name, prec = ("nvfp", "e4m3") if fmt == "nvfp4" else ("mxfp", "e8m0")
+    layer = nn.Linear(256, 64, bias=False, device=cuda_device)
+    layer.weight.data = g["weight"].to(cuda_device)
+    q = Quantizer(bits=4, format=name, granularity="group", group_size=GROUP[fmt], scale_precision=prec)
+    if fmt == "nvfp4":
+        q.get_quantization_params(layer.weight.data)
+        q._track_global_scale = False
+    h = GPTQ(layer, q, quantization_order="activation", block_size=128, rel_damp=0.01, export_quantized_model="realquant")
+    h.H, h.num_samples = g["hessian"].clone().to(cuda_device), 4
+    wq, qweight, scales = h.quantize()
+    assert torch.equal(scales.float().cpu(), g["scales"])
+    assert torch.allclose(h.H.cpu(), g["damped_hessian"], rtol=1e-6, atol=1e-9)      # back in the original order
+    got = fp4.unpack_codes(h.packed_codes.cpu())
+    want = fp4.unpack_codes(g["codes"])
+    agree = (got == want).float().mean().item()
+    print(f"{fmt} GPTQ class, activation order: code agreement {agree:.5f}")
+    assert agree >= 0.99
+    assert torch.equal(qweight.float().cpu(), fp4.code_values(got))
+    assert torch.equal(wq.float().cpu(), fp4.dequantize(got, g["scales"], GROUP[fmt]))
+    rel = get_relative_mse_error(wq.float(), layer.weight.data.float(), h.H).item()
+    assert abs(rel - g["relative_mse"].item()) <= 0.01 * g["relative_mse"].item()

@@ -68,6 +68,24 @@ def test_gptq_matches_golden(fmt):
     assert g["relative_mse"].item() < 0.5 * ogptq.relative_mse(rtn, g["weight"], g["damped_hessian"])
 
 
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_gptq_activation_order_matches_golden(fmt):
+    """quantization_order="activation" (gptq.py:146-155, 170-171, 190-193): permute by falling diag(H),
+    keep every column's static scale group, quantise, undo the permutation."""
+    g = load(f"gptq_actorder_{fmt}.npz")
+    group = FORMATS[fmt]
+    perm, perm_inv, gidx = ogptq.activation_order(g["hessian"], group)
+    assert torch.equal(perm, g["perm"].long())
+    Hd = ogptq.prepare_hessian(g["hessian"][perm][:, perm], g["weight"], 0.01)
+    U, ok = ogptq.cholesky_inverse_upper(Hd)
+    assert ok and torch.allclose(U, g["u_permuted"], rtol=1e-4, atol=1e-6)
+    wq, codes = ogptq.gptq_column_loop(g["weight"][:, perm], g["scales"], g["u_permuted"], group, 128, group_index=gidx)
+    assert torch.equal(fp4.pack_codes(codes[:, perm_inv].contiguous()), g["codes"])
+    assert torch.equal(wq[:, perm_inv], g["dequantized"].float())
+    plain = load(f"gptq_{fmt}.npz")
+    assert not torch.equal(g["codes"], plain["codes"])          # the order changes the result
+
+
 def test_rotation_properties():
     x = inputs.normal_weight(16, 256, seed=9, std=1.0, dtype=torch.float32)
     for g in (16, 32, 64, 128):
