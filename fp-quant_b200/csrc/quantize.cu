@@ -771,6 +771,100 @@ __global__ void __launch_bounds__(128) rotate_dense_kernel(const void* x, int in
   }
 }
 
+int grid_for(int64_t work_items, int threads);
+
+// ------------------------------------------------------------------ MSE observer
+// One thread per scale group.  Candidates fl(f_i * s0), f_i = 1 - i * max_shrink / iters evaluated in double
+// and rounded to fp32 as the reference's Python float is by the tensor multiply; error
+// sum_j |x_j - grid(fl(x_j / s)) * s| ^ norm; the first strictly smaller error wins; the winner then goes
+// through the scale-precision chain (src/quantization/quantizer.py:117-134, :143-165).  The candidates are
+// not rounded to E4M3 / E8M0 during the search.
+template <int G, bool NV, bool IN_BF16>
+__global__ void __launch_bounds__(128) mse_scales_kernel(const void* __restrict__ x, int64_t n_groups,
+                                                         const float* __restrict__ gs_ptr, int iters, double max_shrink,
+                                                         float norm, float* __restrict__ scales_out) {
+  float gs = 0.0f, rgs = 0.0f;
+  if (NV) {
+    gs = *gs_ptr;
+    rgs = gs == 0.0f ? 0.0f : __fdiv_rn(1.0f, gs);
+  }
+  for (int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; g < n_groups; g += (int64_t)gridDim.x * blockDim.x) {
+    float v[G];
+    if (IN_BF16) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + g * G);
+#pragma unroll
+      for (int q = 0; q < G / 8; ++q) {
+        const uint4 raw = src[q];
+        const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[8 * q + 2 * j] = __uint_as_float(r[j] << 16);
+          v[8 * q + 2 * j + 1] = __uint_as_float(r[j] & 0xffff0000u);
+        }
+      }
+    } else {
+      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + g * G);
+#pragma unroll
+      for (int q = 0; q < G / 4; ++q) {
+        const float4 t = src[q];
+        v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+      }
+    }
+    float a = 0.0f;
+#pragma unroll
+    for (int j = 0; j < G; ++j) a = fmaxf(a, fabsf(v[j]));
+    const float s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
+    float best = s0, best_err = __int_as_float(0x7f800000);
+    if (s0 != 0.0f) {                         // an all-zero group divides 0 by 0: no candidate is ever "better"
+      for (int i = 0; i < iters; ++i) {
+        const float f = (float)(1.0 - (double)i * max_shrink / (double)iters);
+        const float s = __fmul_rn(f, s0);
+        float err = 0.0f;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          const float gv = e2m1_value(e2m1_code(__fdiv_rn(v[j], s)));
+          const float d = fabsf(__fsub_rn(v[j], __fmul_rn(gv, s)));
+          err = __fadd_rn(err, powf(d, norm));
+        }
+        if (err < best_err) {
+          best_err = err;
+          best = s;
+        }
+      }
+    }
+    uint32_t byte;
+    float out;
+    if (NV) {
+      float t = fminf(fmaxf(__fmul_rn(best, gs), -448.0f), 448.0f);
+      uint16_t u2;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(u2) : "f"(0.0f), "f"(t));
+      const uint32_t u = u2 & 0xffu, ex = u >> 3, ma = u & 7u;
+      const float uf = ex == 0 ? (float)ma * 0.001953125f : __uint_as_float(((ex + 120u) << 23) | (ma << 20));
+      out = __fmul_rn(uf, rgs);
+      byte = u;
+    } else {
+      const float m = fmaxf(__fmul_rn(6.0f, best), 1.17549435e-38f);
+      const int e = mx_exponent(m);
+      out = e >= -124 ? __uint_as_float(((uint32_t)(e + 125) << 23) | 0x2aaaabu) : __fdiv_rn(ldexpf(1.0f, e - 2), 0.75f);
+      byte = (uint32_t)(e + 127);
+    }
+    (void)byte;
+    scales_out[g] = out == 0.0f ? 1.0f : out;
+  }
+}
+
+template <int G, bool NV>
+int launch_mse(const void* x, int dtype, int64_t n_groups, const float* gs, int iters, double max_shrink, float norm,
+               float* out, cudaStream_t st) {
+  const int grid = grid_for(n_groups, 128);
+  if (dtype == FPQ_DT_BF16)
+    mse_scales_kernel<G, NV, true><<<grid, 128, 0, st>>>(x, n_groups, gs, iters, max_shrink, norm, out);
+  else
+    mse_scales_kernel<G, NV, false><<<grid, 128, 0, st>>>(x, n_groups, gs, iters, max_shrink, norm, out);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
+}
+
 int grid_for(int64_t work_items, int threads) {
   int64_t b = ceil_div64(work_items, threads);
   int64_t cap = (int64_t)sm_count() * 16;
@@ -898,6 +992,23 @@ extern "C" int fpq_apply_scales(const void* x, int dtype, int64_t rows, int64_t 
     apply_scales_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(x, n_words, (uint32_t)cols, scales, (uint32_t)group, out_kind, out);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
+}
+
+extern "C" int fpq_mse_scales(const void* x, int dtype, int64_t rows, int64_t cols, int format,
+                              const float* global_scale, int iters, double max_shrink, float error_norm,
+                              float* scales_f32, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(x && scales_f32, "NULL pointer");
+  FPQ_CHECK_ARG(dtype == FPQ_DT_BF16 || dtype == FPQ_DT_F32, "bad dtype");
+  FPQ_CHECK_ARG(format == FPQ_FMT_NVFP4 || format == FPQ_FMT_MXFP4, "bad format");
+  FPQ_CHECK_ARG(format != FPQ_FMT_NVFP4 || global_scale != nullptr, "NVFP4 needs the tensor scale");
+  FPQ_CHECK_ARG(rows >= 0 && cols > 0 && cols % 32 == 0, "cols must be a multiple of 32");
+  FPQ_CHECK_ARG(iters > 0 && iters <= 100000 && max_shrink >= 0.0 && max_shrink < 1.0, "bad search parameters");
+  FPQ_CHECK_ARG(((uintptr_t)x & 15) == 0, "x must be 16-byte aligned");
+  if (rows == 0) return FPQ_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (format == FPQ_FMT_NVFP4)
+    return launch_mse<16, true>(x, dtype, rows * cols / 16, global_scale, iters, max_shrink, error_norm, scales_f32, st);
+  return launch_mse<32, false>(x, dtype, rows * cols / 32, nullptr, iters, max_shrink, error_norm, scales_f32, st);
 }
 
 extern "C" int fpq_pack_grid(const void* q, int dtype, int64_t rows, int64_t cols, uint8_t* packed,

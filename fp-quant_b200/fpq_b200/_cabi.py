@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_int, c_int32, c_int64, c_void_p, c_char_p, c_float
+from ctypes import c_int, c_int32, c_int64, c_void_p, c_char_p, c_double, c_float
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libfpq_b200.so")
@@ -44,6 +44,7 @@ _SIGNATURES = {
     "fpq_cholesky_inverse_upper": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p],
     "fpq_gptq_quantize": [c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                           c_void_p],
+    "fpq_mse_scales": [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_int, c_double, c_float, c_void_p, c_void_p],
     "fpq_gptq_quantize_ordered": [c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p],
     "fpq_gptq_workspace_bytes": [c_int64, c_int64],

@@ -135,6 +135,22 @@ def quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0, global_scale: O
     return q, sb, sf
 
 
+def mse_scales(x: torch.Tensor, fmt: str, global_scale: Optional[torch.Tensor] = None, iters: int = 100,
+               max_shrink: float = 0.80, error_norm: float = 2.4) -> torch.Tensor:
+    """fp32 [rows, cols/g]: the scales the MSE observer picks (quantizer.py:117-134) after the E4M3 / E8M0 chain."""
+    x, rows, cols = _2d(x)
+    out = torch.empty(rows, cols // GROUP_OF[fmt], dtype=torch.float32, device=x.device)
+    if fmt == "nvfp4":
+        if global_scale is None:
+            raise ValueError("nvfp4 needs a global_scale tensor")
+        global_scale = _cuda(global_scale, "global_scale").to(torch.float32)
+    with _guard(x.device):
+        C.call("fpq_mse_scales", x.data_ptr(), _dt(x), rows, cols, FORMATS[fmt],
+               _ptr(global_scale) if fmt == "nvfp4" else None, int(iters), float(max_shrink), float(error_norm),
+               out.data_ptr(), _stream(x))
+    return out
+
+
 def fake_quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0,
                   global_scale: Optional[torch.Tensor] = None, ste: bool = False) -> torch.Tensor:
     shape = x.shape

@@ -2,7 +2,7 @@
 computing on the GPU through the fused CUDA kernels.
 
 Supported: 4-bit NVFP (group 16, E4M3 scales + fp32 tensor scale) and MXFP (group 32, E8M0
-scales), symmetric, group granularity along the last dim, min-max observer -- the
+scales), symmetric, group granularity along the last dim, min-max or MSE observer -- the
 configurations of the MR-GPTQ path.  Everything else raises NotImplementedError.
 """
 from __future__ import annotations
@@ -44,7 +44,7 @@ class Quantizer:
     # ------------------------------------------------------------------ helpers
     def _resolve_kernel_format(self) -> str:
         ok = (self.bits == 4 and self.symmetric and self.granularity == QuantizationGranularity.GROUP
-              and self.observer == QuantizationObserver.MINMAX and self.dim == -1)
+              and self.observer in (QuantizationObserver.MINMAX, QuantizationObserver.MSE) and self.dim == -1)
         if ok and self.format == QuantizationFormat.NVFP and self.scale_precision == ScalePrecision.E4M3 \
                 and self.group_size == 16:
             return "nvfp4"
@@ -53,7 +53,7 @@ class Quantizer:
             return "mxfp4"
         raise NotImplementedError(
             "the B200 path implements 4-bit nvfp (group 16, e4m3 scales) and mxfp (group 32, e8m0 scales) "
-            f"with the min-max observer; got format={self.format} group={self.group_size} "
+            f"with the min-max or MSE observer; got format={self.format} group={self.group_size} "
             f"scales={self.scale_precision} observer={self.observer}")
 
     def _device_global_scale(self, device: torch.device) -> torch.Tensor:
@@ -63,9 +63,12 @@ class Quantizer:
 
     # ------------------------------------------------------------------ API
     @torch.no_grad()
-    def get_quantization_params(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    def get_quantization_params(self, x: torch.Tensor, scale_search_iters: int = 100,
+                                max_scale_shrink_factor: float = 0.80,
+                                error_norm: float = 2.4) -> Tuple[torch.Tensor, torch.Tensor]:
         """Per-group scales (the divisor of the FP4 cast) and zero points (all zero).
-        NVFP also folds max|x| into `global_scale` while `_track_global_scale` is set."""
+        NVFP also folds max|x| into `global_scale` while `_track_global_scale` is set.  The three search
+        parameters only matter for the MSE observer (quantizer.py:117-134)."""
         fmt = self._kernel_format
         gs = None
         if fmt == "nvfp4":
@@ -76,7 +79,10 @@ class Quantizer:
                 ops.global_scale_update(bits, gs, status)
                 if int(status.item()) != 0 or not bool(torch.isfinite(gs).item()):
                     raise ValueError(f"Global scale is not finite: {gs}")
-        _, _, scales = ops.quantize(x, fmt, 0, gs, codes=False, scale_bytes=False, scales_f32=True)
+        if self.observer == QuantizationObserver.MSE:
+            scales = ops.mse_scales(x, fmt, gs, scale_search_iters, max_scale_shrink_factor, error_norm)
+        else:
+            _, _, scales = ops.quantize(x, fmt, 0, gs, codes=False, scale_bytes=False, scales_f32=True)
         scales = scales.view(*x.shape[:-1], x.shape[-1] // self.group_size).to(x.dtype)
         if bool(scales.isnan().any().item()):
             raise ValueError("Scales are not finite.")
@@ -110,8 +116,13 @@ class Quantizer:
     # fused paths the drivers use instead of the three calls above ------------------------
     @torch.no_grad()
     def fused_fake_quantize(self, x: torch.Tensor, hadamard_group: int = 0, ste: bool = True) -> torch.Tensor:
-        """rotate + get_quantization_params + __call__ in one kernel pass."""
+        """rotate + get_quantization_params + __call__ in one kernel pass (min-max observer; the MSE observer
+        takes the three steps one after the other)."""
         fmt = self._kernel_format
+        if self.observer == QuantizationObserver.MSE:
+            xr = ops.rotate_hadamard(x, hadamard_group) if hadamard_group else x
+            scales, _ = self.get_quantization_params(xr)
+            return self._apply(xr, scales.float(), C.OUT_DEQUANT_STE if ste else C.OUT_DEQUANT)
         gs = None
         if fmt == "nvfp4":
             gs = self._device_global_scale(x.device)

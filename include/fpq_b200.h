@@ -124,6 +124,18 @@ int fpq_apply_scales(const void* x, int dtype, int64_t rows, int64_t cols, const
                      int group, int out_kind, void* out, fpq_stream_t stream);
 
 /*
+ * The MSE observer of Quantizer.get_quantization_params (src/quantization/quantizer.py:117-134): per
+ * group, `iters` candidate scales fl(f_i * s0), f_i = 1 - i * max_shrink / iters, s0 = fl(fl(2 absmax)/12);
+ * the one with the smallest sum |x - dequant(quant(x, s))| ^ error_norm (first strictly smaller wins) goes
+ * through the scale-precision chain (E4M3 with the tensor scale, or E8M0).  x [rows, cols] bf16 or fp32
+ * (already rotated), cols % 32 == 0; scales_f32 [rows, cols/g] receives the divisors.  The reference's
+ * defaults are iters 100, max_shrink 0.8, error_norm 2.4.  global_scale: device fp32[1], NVFP4 only.
+ */
+int fpq_mse_scales(const void* x, int dtype, int64_t rows, int64_t cols, int format,
+                   const float* global_scale, int iters, double max_shrink, float error_norm,
+                   float* scales_f32, fpq_stream_t stream);
+
+/*
  * pack_fp4_to_uint8 (src/quantization/quant_ops.py:31-40): tensor of E2M1 grid values ->
  * two 4-bit codes per byte, even element in the low nibble, zeros as 0x8.
  */

@@ -113,9 +113,14 @@ def nvfp4_scales(y: torch.Tensor, global_scale: torch.Tensor) -> Tuple[torch.Ten
     all-zero group stores byte 0 (the reference would store e4m3(gs), which is not
     a usable scale; see the test-suite's note on zero groups).
     """
-    gs = global_scale.to(torch.float32).reshape(())
     a = group_absmax(y.to(torch.float32), NVFP_GROUP)
-    s0 = (2 * a) / 12.0
+    return nvfp4_scales_from_raw((2 * a) / 12.0, global_scale)
+
+
+def nvfp4_scales_from_raw(s0: torch.Tensor, global_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The E4M3 chain of `nvfp4_scales` applied to given unrounded scales (min-max: fl(fl(2a)/12); MSE
+    observer: the best shrunk candidate)."""
+    gs = global_scale.to(torch.float32).reshape(())
     u = _e4m3_round((s0 * gs).clamp(-E4M3_MAX, E4M3_MAX))
     rgs = torch.where(gs == 0, torch.zeros_like(gs), 1.0 / gs)
     s = u.to(torch.float32) * rgs
@@ -144,12 +149,40 @@ def mxfp4_scales(y: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     quantizer.py:64-65).
     """
     a = group_absmax(y.to(torch.float32), MXFP_GROUP)
-    s0 = (2 * a) / 12.0
+    return mxfp4_scales_from_raw((2 * a) / 12.0)
+
+
+def mxfp4_scales_from_raw(s0: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The E8M0 chain of `mxfp4_scales` applied to given unrounded scales."""
     m = (E2M1_MAX * s0).clamp(min=2.0 ** -126)
     e = mx_exponent(m)
     s = torch.pow(torch.tensor(2.0, dtype=torch.float32), e - 2) / 0.75
     s = torch.where(s == 0, torch.ones_like(s), s)
     return (e + 127).to(torch.uint8), s
+
+
+def mse_observer_raw_scales(y: torch.Tensor, group: int, iters: int = 100, max_shrink: float = 0.80,
+                            norm: float = 2.4) -> torch.Tensor:
+    """The MSE observer's search (quantizer.py:117-134): candidates fl(f_i * s0) with
+    f_i = 1 - i * max_shrink / iters (a Python float, rounded to fp32 by the multiply), error
+    sum_j |x_j - grid(fl(x_j / s)) * s| ** norm over the group, the first strictly smaller error wins.
+    The candidate scales are NOT rounded to E4M3 / E8M0 during the search; the chain of the scale
+    precision is applied to the winner afterwards.  Returns fp32 [..., K/group]."""
+    y = y.to(torch.float32)
+    g = y.reshape(*y.shape[:-1], y.shape[-1] // group, group)
+    s0 = (2 * g.abs().amax(dim=-1, keepdim=True)) / 12.0
+    best = s0.clone()
+    best_err = torch.full(g.shape[:-1], float("inf"))
+    for i in range(iters):
+        s = (1 - i * max_shrink / iters) * s0
+        v = g / s                                             # 0 / 0 = NaN for an all-zero group: never "better"
+        q = code_values(e2m1_codes(v, torch.ones(*v.shape[:-1], 1), group))
+        q = torch.where(v.isnan(), v, q)
+        err = (g - q * s).abs_().pow_(norm).sum(dim=-1)
+        better = err < best_err
+        best_err = torch.where(better, err, best_err)
+        best = torch.where(better.unsqueeze(-1), s, best)
+    return best.squeeze(-1)
 
 
 # --------------------------------------------------------------------------- codes

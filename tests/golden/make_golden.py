@@ -10,6 +10,7 @@ Outputs (a few hundred KB in total):
   edge_<fmt>.npz     the same chain without rotation on rows of ties / zeros / extremes
   log2_probes.npz    cast_to_eBm0 on maxima a few ulps around powers of two
   gptq_<fmt>.npz     GPTQ.quantize (export path) on a 64 x 256 layer with a correlated Hessian
+  mse_<fmt>.npz      Quantizer(observer="mse").get_quantization_params on a rotated 64 x 512 weight
   gptq_actorder_<fmt>.npz   the same layer with quantization_order="activation"
 The rotation fed to the reference is the oracle's butterfly (the reference's own FWHT is an
 external CUDA kernel whose summation order is unknown), everything downstream is reference code.
@@ -136,6 +137,21 @@ def main():
         save(f"gptq_{fmt}.npz", weight=wr, hessian=H, damped_hessian=h.H, u=U, scales=scales,
              codes=pack_fp4_to_uint8(qweight), dequantized=wq, relative_mse=rel,
              global_scale=q.global_scale.clone())
+    # ---- MSE observer (quantizer.py:117-134) on the rotated weight, one all-zero group included
+    ym = fp4.fwht_butterfly(inputs.normal_weight(64, 512, seed=0, dtype=torch.float32), 128)
+    ym[3, 32:64] = 0
+    for fmt in specs:
+        name, g, prec = specs[fmt]
+        q = Quantizer(bits=4, format=name, granularity="group", observer="mse", group_size=g, scale_precision=prec)
+        sm, _ = q.get_quantization_params(ym)
+        raw = fp4.mse_observer_raw_scales(ym, g)
+        if fmt == "nvfp4":
+            _, so = fp4.nvfp4_scales_from_raw(raw, fp4.nvfp4_global_scale(ym.abs().max()))
+        else:
+            _, so = fp4.mxfp4_scales_from_raw(raw)
+        assert torch.equal(sm, so), fmt
+        save(f"mse_{fmt}.npz", rotated=ym, scales=sm, global_scale=q.global_scale.clone())
+
     # ---- the same layer in activation order (gptq.py:146-155, 190-193)
     for fmt in specs:
         name, g, prec = specs[fmt]

@@ -166,3 +166,22 @@ def test_oracle_equals_live_reference(fmt, name, prec):
     assert torch.equal(codes, o_codes) and torch.equal(s, o_s)
     keep = o_sb != 0 if fmt == "nvfp4" else torch.ones_like(o_sb, dtype=torch.bool)
     assert torch.equal(sb[keep], o_sb[keep])
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_mse_observer_matches_golden(fmt):
+    """Quantizer(observer="mse") of the reference (quantizer.py:117-134): the restated search picks the same
+    scale for every group, the all-zero group included; and it differs from the min-max scales."""
+    g = load(f"mse_{fmt}.npz")
+    y, group = g["rotated"], FORMATS[fmt]
+    raw = fp4.mse_observer_raw_scales(y, group)
+    if fmt == "nvfp4":
+        gs = fp4.nvfp4_global_scale(y.abs().max())
+        assert torch.equal(gs, g["global_scale"])
+        _, s = fp4.nvfp4_scales_from_raw(raw, gs)
+        _, s_minmax = fp4.nvfp4_scales(y, gs)
+    else:
+        _, s = fp4.mxfp4_scales_from_raw(raw)
+        _, s_minmax = fp4.mxfp4_scales(y)
+    assert torch.equal(s, g["scales"])
+    assert (s != s_minmax).float().mean().item() > 0.03

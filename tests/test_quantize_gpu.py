@@ -1,4 +1,5 @@
 """GPU parity of the fused rotate + FP4 quantise kernels against the CPU oracle (bit-exact)."""
+import os
 import pytest
 import torch
 
@@ -151,3 +152,44 @@ def test_bad_arguments_raise(cuda_device):
         ops.quantize(torch.zeros(4, 64), "mxfp4", 32)
     with pytest.raises(C.FpqError):
         ops.quantize(torch.zeros(4, 64, device=cuda_device), "mxfp4", 24)
+
+
+@pytest.mark.parametrize("fmt", ["nvfp4", "mxfp4"])
+def test_mse_observer_scales_match_the_reference(cuda_device, fmt):
+    """fpq_mse_scales through Quantizer(observer="mse") against the golden scales of the unmodified reference
+    (tests/golden/mse_<fmt>.npz).  The search compares sums of |x - xq| ** 2.4 over 100 candidates; the device
+    powf and the summation order differ from torch-CPU in the last bits, which can only matter between two
+    candidates whose errors agree to ~1e-6: at least 99.5 % of the groups must get the identical scale (all of
+    them do on this tensor; the fraction is printed).  The all-zero group must come out as the reference's."""
+    import numpy as np
+
+    from fpq_b200.quantization import Quantizer
+
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", f"mse_{fmt}.npz"))
+    y, want = torch.from_numpy(d["rotated"]), torch.from_numpy(d["scales"])
+    name, prec, group = ("nvfp", "e4m3", 16) if fmt == "nvfp4" else ("mxfp", "e8m0", 32)
+    q = Quantizer(bits=4, format=name, granularity="group", observer="mse", group_size=group, scale_precision=prec)
+    got, zeros = q.get_quantization_params(y.to(cuda_device))
+    got = got.float().cpu()
+    assert got.shape == want.shape and not bool(zeros.any())
+    if fmt == "nvfp4":
+        assert torch.equal(q.global_scale.cpu(), torch.from_numpy(d["global_scale"]))
+    same = got == want
+    frac = same.float().mean().item()
+    print(f"{fmt}: MSE-observer scales identical to the reference on {frac:.5f} of the groups")
+    assert frac >= 0.995
+    assert torch.equal(got[3, 32 // group:64 // group], want[3, 32 // group:64 // group])       # the all-zero group
+
+    def err(s):
+        g = y.reshape(64, -1, group)
+        codes = fp4.e2m1_codes(y, s, group)
+        return (g - (fp4.code_values(codes).reshape(g.shape) * s.unsqueeze(-1))).abs().pow(2.4).sum(-1)
+
+    e_got = err(got)
+    # the observer must actually lower the error it searches on, against the min-max scales
+    qmm = Quantizer(bits=4, format=name, granularity="group", observer="minmax", group_size=group, scale_precision=prec)
+    mm, _ = qmm.get_quantization_params(y.to(cuda_device))
+    assert e_got.sum() < err(mm.float().cpu()).sum()
+    # and Quantizer.__call__ with those scales works as with any others
+    out = q(y.to(cuda_device), got.to(cuda_device)).cpu()
+    assert torch.allclose(out, fp4.dequantize(fp4.e2m1_codes(y, got, group), got, group), rtol=1e-6, atol=1e-9)
