@@ -102,6 +102,9 @@ __device__ __forceinline__ void load_raw(const void* base, int64_t chunk, bool a
   }
 }
 
+#ifndef FPQ_Q_UNPACK
+#define FPQ_Q_UNPACK 0      // 1: bf16 -> fp32 with cvt instead of shift / mask (measured: see the profile notes)
+#endif
 #ifndef FPQ_Q_MAX3
 #define FPQ_Q_MAX3 1
 #endif
@@ -112,7 +115,15 @@ template <bool STAGE1>
 __device__ __forceinline__ void unpack_chunk(const RawChunk<true>& r, u64 (&P)[16]) {
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
+#if FPQ_Q_UNPACK == 1
+    uint16_t l16, h16;
+    float a, b;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(l16), "=h"(h16) : "r"(r.w[j]));
+    asm("cvt.f32.bf16 %0, %1;" : "=f"(a) : "h"(l16));
+    asm("cvt.f32.bf16 %0, %1;" : "=f"(b) : "h"(h16));
+#else
     const float a = __uint_as_float(r.w[j] << 16), b = __uint_as_float(r.w[j] & 0xffff0000u);
+#endif
     P[j] = STAGE1 ? pack2(__fadd_rn(a, b), __fsub_rn(a, b)) : pack2(a, b);
   }
 }
