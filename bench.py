@@ -346,7 +346,7 @@ def run_ours(args):
         tot_fl = sum(2.0 * M * shapes[i][1] * shapes[i][0] for _, _, i in gemm_events)
         achieved = tot_fl / (tot_ms * 1e-3) / 1e12
         peak = 4.0 * peaks["bf16_tflops"]
-        # DRAM traffic per launch: ncu saw 44.15 MB on the 8192 x 4096 x 4096 launch (93.85 MB algorithmic:
+        # DRAM traffic per launch: ncu saw 45.68 MB on the 8192 x 4096 x 4096 launch (93.85 MB algorithmic:
         # operands that the quantise kernel just wrote are still in L2, part of the output still is when
         # the kernel ends); scaled to the average launch of this run by its algorithmic bytes
         alg = sum(M * shapes[i][0] / 2 + shapes[i][1] * shapes[i][0] / 2 + (M + shapes[i][1]) * shapes[i][0] / g
@@ -355,7 +355,7 @@ def run_ours(args):
                     "unit": "TFLOP/s", "frac": achieved / peak,
                     "peak_source": f"4 x bf16 cuBLAS burst ({peaks['source']}); no FP4 peak was measured on this pool",
                     "frac_of_nominal_9pf": achieved / NOMINAL_FP4_TFLOPS,
-                    "avg_launch_ms": tot_ms / len(gemm_events), "traffic": alg * (44.148e6 / 93.847e6),
+                    "avg_launch_ms": tot_ms / len(gemm_events), "traffic": alg * (45.677e6 / 93.847e6),
                     "traffic_note": "bytes per launch, ncu dram read+write of the 8192x4096x4096 launch scaled by algorithmic bytes"}
     quant_roof = None
     if args.workload in ("linear", "quantize"):
