@@ -9,6 +9,7 @@
 // because H = (J L J)(J L J)^T with J L J upper triangular, hence H^-1 = U^T U with U = (J L J)^-1.
 // One factorisation and one triangular inverse instead of two factorisations and a full inverse.
 
+#include <cstdlib>
 #include "common.cuh"
 #include "sgemm.cuh"
 
@@ -239,8 +240,9 @@ int64_t tc_gemm3_workspace(int64_t M, int64_t N, int64_t K, bool b_is_a_transpos
 }
 
 // C[M, N] (row stride ldc) = beta * C + alpha * A B with fp32-level accuracy on the tensor cores:
-// A [M, K] row-major (lda); B [K, N] row-major (ldb), or B == nullptr for B = A^T (N == M, the symmetric
-// rank-K update; only the tiles touching the lower triangle are then computed).  Both factors are split
+// A [M, K] row-major (lda); B [K, N] row-major (ldb), or B == nullptr for B = (the first N rows of A)^T:
+// with N == M the symmetric rank-K update (only the tiles touching the lower triangle are computed), with
+// N < M its first N columns.  Both factors are split
 // into three bf16 terms and the six leading cross products (hi*hi, hi*mid, mid*hi, hi*lo, lo*hi, mid*mid;
 // the dropped ones are below 2^-24 relative) are accumulated in fp32 in one launch whose K dimension is
 // the concatenation of the six slabs.  K must be a multiple of 64.
@@ -266,13 +268,19 @@ int tc_gemm3(float* C, int64_t ldc, int64_t M, int64_t N, int64_t K, const float
     a_y[t] = (int)(pa[t] * K);
     b_y[t] = (int)(pb[t] * K);
   }
-  return gemm_atb_bf16(C, ldc, M, N, at3, ldat, 3 * K, 0, b3, ldbt, 3 * K, 0, B == nullptr, false, 6, K, a_y, b_y, alpha,
-                       beta, error_flag, st, tri);
+  return gemm_atb_bf16(C, ldc, M, N, at3, ldat, 3 * K, 0, b3, ldbt, 3 * K, 0, B == nullptr && N == M, false, 6, K, a_y,
+                       b_y, alpha, beta, error_flag, st, tri);
 }
 
 // Products at least this large go to the tensor cores; smaller ones stay on the fp32 SIMT kernel, whose
 // launch is cheaper than the two conversion passes.
-bool tc_worthwhile(int64_t M, int64_t N, int64_t K) { return K % 64 == 0 && M * N * K >= (int64_t)512 * 512 * 128; }
+bool tc_worthwhile(int64_t M, int64_t N, int64_t K) {
+  static const int64_t min_macs = [] {
+    const char* e = getenv("FPQ_TC_MIN_MACS_LOG2");       // tuning aid
+    return (int64_t)1 << (e ? atoi(e) : 25);
+  }();
+  return K % 64 == 0 && M * N * K >= min_macs;
+}
 
 // X[lo:hi, lo:hi] = L[lo:hi, lo:hi]^-1 for block indices [lo, hi), given the inverses of the diagonal
 // blocks already in X:  L^-1 = [[X11, 0], [-X22 (L21 X11), X22]].  S = L21 X11 (n2 x n1) goes to `scratch`.
@@ -568,31 +576,67 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
   reverse_copy_kernel<<<grid1d(d * d), 256, 0, st>>>(H, L, d);
   FPQ_CHECK_LAUNCH();
   FPQ_CHECK_CUDA(cudaMemsetAsync(U, 0, (size_t)d * d * sizeof(float), st));
-  for (int k = 0; k < nblk; ++k) {
-    const int64_t r = (int64_t)k * NB;
-    const int nb = (int)((d - r) < NB ? (d - r) : NB);
-    chol_diag_kernel<<<1, 256, 0, st>>>(L + r * d + r, d, U + r * d + r, d, nb, status);
-    FPQ_CHECK_LAUNCH();
-    const int64_t below = d - (r + nb);
-    if (below <= 0) break;
-    SgemmArgs a{};
-    // panel: L21 = A21 * L11^-T  (in place: every CTA reads only the 128 rows it then overwrites)
-    a.A = L + (r + nb) * d + r; a.lda = d;
-    a.B = U + r * d + r; a.ldb = d;
-    a.C = L + (r + nb) * d + r; a.ldc = d;
-    a.M = (int)below; a.N = nb; a.K = nb; a.alpha = 1.0f; a.beta = 0.0f;
-    if (int rc = sgemm(a, true, SGEMM_PLAIN, st)) return rc;
-    // trailing update: A22 -= L21 L21^T (lower tiles only)
-    if (nb == NB && tc_worthwhile(below, below, nb) && 3 * (int64_t)nb * round64(below) <= 6 * half * half) {
-      if (int rc = tc_gemm3(L + (r + nb) * d + (r + nb), d, below, below, nb, L + (r + nb) * d + r, d, nullptr, 0, -1.0f,
-                            1.0f, ws, error_flag, st))
-        return rc;
+  // Right-looking blocked Cholesky in two levels.  Inside an outer block of OB diagonal blocks the rank-128
+  // updates only touch the outer block's own columns (all rows below); the rest of the trailing matrix gets
+  // one rank-(OB*128) update per outer block, which reads and writes it 1/OB as often as a rank-128
+  // update per diagonal block would (those updates are bound by that traffic, not by the tensor pipe).
+  int OB = 4;
+  if (const char* e = getenv("FPQ_CHOL_OB")) {          // tuning aid
+    const int v = atoi(e);
+    if (v >= 1 && v <= 16) OB = v;
+  }
+  const int64_t ws_elems = 6 * half * half;
+  for (int ob = 0; ob < nblk; ob += OB) {
+    const int64_t R = (int64_t)ob * NB;
+    const int64_t Wd = (d - R) < (int64_t)OB * NB ? (d - R) : (int64_t)OB * NB;
+    for (int k = ob; k < nblk && k < ob + OB; ++k) {
+      const int64_t r = (int64_t)k * NB;
+      const int nb = (int)((d - r) < NB ? (d - r) : NB);
+      chol_diag_kernel<<<1, 256, 0, st>>>(L + r * d + r, d, U + r * d + r, d, nb, status);
+      FPQ_CHECK_LAUNCH();
+      const int64_t below = d - (r + nb);
+      if (below <= 0) break;
+      SgemmArgs a{};
+      // panel: L21 = A21 * L11^-T  (in place: every CTA reads only the 128 rows it then overwrites)
+      a.A = L + (r + nb) * d + r; a.lda = d;
+      a.B = U + r * d + r; a.ldb = d;
+      a.C = L + (r + nb) * d + r; a.ldc = d;
+      a.M = (int)below; a.N = nb; a.K = nb; a.alpha = 1.0f; a.beta = 0.0f;
+      if (int rc = sgemm(a, true, SGEMM_PLAIN, st)) return rc;
+      // inner update: columns [r + nb, R + Wd) of the rows below -= L21 * (the first rows of L21)^T
+      const int64_t inner = R + Wd - (r + nb);
+      if (inner <= 0) continue;
+      float* Cin = L + (r + nb) * d + (r + nb);
+      static const int64_t inner_min = [] {
+        const char* e = getenv("FPQ_CHOL_INNER_TC_LOG2");       // tuning aid
+        return (int64_t)1 << (e ? atoi(e) : 25);
+      }();
+      if (nb == NB && tc_worthwhile(below, inner, nb) && below * inner * nb >= inner_min &&
+          3 * (int64_t)nb * round64(below) <= ws_elems) {
+        if (int rc = tc_gemm3(Cin, d, below, inner, nb, L + (r + nb) * d + r, d, nullptr, 0, -1.0f, 1.0f, ws, error_flag, st))
+          return rc;
+        continue;
+      }
+      a.A = L + (r + nb) * d + r; a.lda = d;
+      a.B = L + (r + nb) * d + r; a.ldb = d;
+      a.C = Cin; a.ldc = d;
+      a.M = (int)below; a.N = (int)inner; a.K = nb; a.alpha = -1.0f; a.beta = 1.0f;
+      if (int rc = sgemm(a, true, inner == below ? SGEMM_LOWER : SGEMM_PLAIN, st)) return rc;
+    }
+    // outer update: A22 -= P P^T (lower tiles only), P = the outer block's columns of the rows below it
+    const int64_t below_o = d - (R + Wd);
+    if (below_o <= 0) break;
+    float* C22 = L + (R + Wd) * d + (R + Wd);
+    const float* P = L + (R + Wd) * d + R;
+    if (Wd % 64 == 0 && tc_worthwhile(below_o, below_o, Wd) && 3 * Wd * round64(below_o) <= ws_elems) {
+      if (int rc = tc_gemm3(C22, d, below_o, below_o, Wd, P, d, nullptr, 0, -1.0f, 1.0f, ws, error_flag, st)) return rc;
       continue;
     }
-    a.A = L + (r + nb) * d + r; a.lda = d;
-    a.B = L + (r + nb) * d + r; a.ldb = d;
-    a.C = L + (r + nb) * d + (r + nb); a.ldc = d;
-    a.M = (int)below; a.N = (int)below; a.K = nb; a.alpha = -1.0f; a.beta = 1.0f;
+    SgemmArgs a{};
+    a.A = P; a.lda = d;
+    a.B = P; a.ldb = d;
+    a.C = C22; a.ldc = d;
+    a.M = (int)below_o; a.N = (int)below_o; a.K = (int)Wd; a.alpha = -1.0f; a.beta = 1.0f;
     if (int rc = sgemm(a, true, SGEMM_LOWER, st)) return rc;
   }
   if (int rc = tri_inverse_recursive(L, U, scratch, ws, error_flag, d, 0, nblk, st)) return rc;
