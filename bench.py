@@ -878,13 +878,58 @@ def run_model_forward(args):
     print(json.dumps(line), flush=True)
 
 
+def run_cholesky(args):
+    """Milliseconds per damped-Hessian inverse factor U = chol(H^-1, upper) of a d x d Hessian (d = --gptq-cols),
+    the serial step of MR-GPTQ (src/quantization/gptq.py:200-218)."""
+    from fpq_b200 import ops
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    d = args.gptq_cols
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(2 * d, d, device=dev, generator=g)
+    H = (x.t() @ x).div_(2 * d)              # set-up, not timed
+    H.diagonal().add_(0.01)
+    del x
+    for _ in range(args.warmup):
+        ops.cholesky_inverse_upper(H)
+    torch.cuda.synchronize()
+    times = []
+    with ClockSampler(0) as clocks:
+        for _ in range(args.steps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            U, status = ops.cholesky_inverse_upper(H)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+    ops.check_device_errors(dev)
+    slab = min(256, d)
+    resid = U.t() @ (U @ H[:, :slab])
+    resid[:slab] -= torch.eye(slab, device=dev)
+    ms = sum(times) / len(times)
+    flops = 4.0 / 3.0 * d ** 3
+    line = {
+        "metric": "cholesky_inverse_upper_ms", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (three-term bf16 splits on the tensor cores for the large products)", "data": "synthetic",
+        "config": {"workload": f"U = chol(H^-1, upper) of a damped {d} x {d} Hessian of random activations",
+                   "l2": f"H, L and U are {3 * 4 * d * d / 1e6:.0f} MB"},
+        "status": int(status.item()), "residual_max": float(resid.abs().max()), "best_ms": min(times),
+        "roofline": {"bound": "latency / tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": None, "unit": "TFLOP/s (4/3 d^3 fp32-equivalent)",
+                     "frac": None, "traffic": None},
+        "cpu_baseline": None, "e2e": None, "gpu_launches": None, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model", "tp-linear", "model-forward"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model", "tp-linear", "model-forward", "cholesky"])
     ap.add_argument("--model-layers", type=int, default=2)
     ap.add_argument("--calib-seqs", type=int, default=128)
     ap.add_argument("--tp-fused", action="store_true", help="tp-linear: push output tiles to the peers from the GEMM epilogue")
@@ -910,6 +955,8 @@ def main():
             run_tp_linear(args)
         elif args.workload == "model-forward":
             run_model_forward(args)
+        elif args.workload == "cholesky":
+            run_cholesky(args)
         else:
             run_ours(args)
 
