@@ -10,6 +10,7 @@
 // One factorisation and one triangular inverse instead of two factorisations and a full inverse.
 
 #include <cstdlib>
+#include <vector>
 #include "common.cuh"
 #include "sgemm.cuh"
 
@@ -282,38 +283,79 @@ bool tc_worthwhile(int64_t M, int64_t N, int64_t K) {
   return K % 64 == 0 && M * N * K >= min_macs;
 }
 
-// X[lo:hi, lo:hi] = L[lo:hi, lo:hi]^-1 for block indices [lo, hi), given the inverses of the diagonal
-// blocks already in X:  L^-1 = [[X11, 0], [-X22 (L21 X11), X22]].  S = L21 X11 (n2 x n1) goes to `scratch`.
-int tri_inverse_recursive(const float* L, float* X, float* scratch, __nv_bfloat16* ws, int32_t* error_flag, int64_t d,
-                          int lo, int hi, cudaStream_t st) {
-  if (hi - lo <= 1) return FPQ_OK;
+// X = L^-1 given the inverses of the diagonal blocks already in X.  The block range [lo, hi) is halved
+// recursively: L^-1 = [[X11, 0], [-X22 (L21 X11), X22]], S = L21 X11 (n2 x n1) goes to `scratch`.  The
+// nodes of one depth are independent, so the tree is walked level by level from the leaves: the small
+// nodes of a level share two launches of the batched fp32 kernel (S for all of them, then X21 for all of
+// them), the large ones go to the tensor cores one after the other.
+struct TriNode { int lo, mid, hi; };
+
+void tri_collect(std::vector<std::vector<TriNode>>& levels, int lo, int hi, int depth) {
+  if (hi - lo <= 1) return;
   const int mid = (lo + hi) / 2;
-  if (int rc = tri_inverse_recursive(L, X, scratch, ws, error_flag, d, lo, mid, st)) return rc;
-  if (int rc = tri_inverse_recursive(L, X, scratch, ws, error_flag, d, mid, hi, st)) return rc;
-  const int64_t r0 = (int64_t)lo * NB, r1 = (int64_t)mid * NB;
-  const int64_t n1 = r1 - r0;
-  int64_t n2 = (int64_t)hi * NB - r1;
-  if (r1 + n2 > d) n2 = d - r1;
-  if (tc_worthwhile(n2, n1, n1) && n2 % 64 == 0) {
-    // S = L21 * X11 (X11 lower triangular), then X21 = -X22 * S (X22 lower triangular): the stages that
-    // would only multiply the zero halves are skipped
-    if (int rc = tc_gemm3(scratch, n1, n2, n1, n1, L + r1 * d + r0, d, X + r0 * d + r0, d, 1.0f, 0.0f, ws, error_flag, st, 1))
-      return rc;
-    return tc_gemm3(X + r1 * d + r0, d, n2, n1, n2, X + r1 * d + r1, d, scratch, n1, -1.0f, 0.0f, ws, error_flag, st, 2);
+  if ((int)levels.size() <= depth) levels.resize(depth + 1);
+  levels[depth].push_back({lo, mid, hi});
+  tri_collect(levels, lo, mid, depth + 1);
+  tri_collect(levels, mid, hi, depth + 1);
+}
+
+int tri_inverse_levels(const float* L, float* X, float* scratch, __nv_bfloat16* ws, int32_t* error_flag, int64_t d,
+                       int nblk, cudaStream_t st) {
+  std::vector<std::vector<TriNode>> levels;
+  tri_collect(levels, 0, nblk, 0);
+  for (int depth = (int)levels.size() - 1; depth >= 0; --depth) {
+    std::vector<TriNode> big;
+    SgemmBatch s1{}, s2{};
+    int64_t used = 0;
+    auto flush = [&]() -> int {
+      if (s1.count == 0) return FPQ_OK;
+      if (int rc = sgemm_batched(s1, false, st)) return rc;
+      if (int rc = sgemm_batched(s2, false, st)) return rc;
+      s1.count = s2.count = 0;
+      used = 0;
+      return FPQ_OK;
+    };
+    for (const TriNode& nd : levels[depth]) {
+      const int64_t r0 = (int64_t)nd.lo * NB, r1 = (int64_t)nd.mid * NB;
+      const int64_t n1 = r1 - r0;
+      int64_t n2 = (int64_t)nd.hi * NB - r1;
+      if (r1 + n2 > d) n2 = d - r1;
+      if (tc_worthwhile(n2, n1, n1) && n2 % 64 == 0) {
+        big.push_back(nd);
+        continue;
+      }
+      if (s1.count == SGEMM_MAX_BATCH)
+        if (int rc = flush()) return rc;
+      float* S = scratch + used;
+      used += n1 * n2;
+      SgemmArgs& a = s1.e[s1.count++];          // S = L21 * X11
+      a = SgemmArgs{};
+      a.A = L + r1 * d + r0; a.lda = d;
+      a.B = X + r0 * d + r0; a.ldb = d;
+      a.C = S; a.ldc = n1;
+      a.M = (int)n2; a.N = (int)n1; a.K = (int)n1; a.alpha = 1.0f; a.beta = 0.0f;
+      SgemmArgs& b = s2.e[s2.count++];          // X21 = -X22 * S
+      b = SgemmArgs{};
+      b.A = X + r1 * d + r1; b.lda = d;
+      b.B = S; b.ldb = n1;
+      b.C = X + r1 * d + r0; b.ldc = d;
+      b.M = (int)n2; b.N = (int)n1; b.K = (int)n2; b.alpha = -1.0f; b.beta = 0.0f;
+    }
+    if (int rc = flush()) return rc;
+    for (const TriNode& nd : big) {
+      const int64_t r0 = (int64_t)nd.lo * NB, r1 = (int64_t)nd.mid * NB;
+      const int64_t n1 = r1 - r0;
+      int64_t n2 = (int64_t)nd.hi * NB - r1;
+      if (r1 + n2 > d) n2 = d - r1;
+      // S = L21 * X11 (X11 lower triangular), then X21 = -X22 * S (X22 lower triangular): the stages that
+      // would only multiply the zero halves are skipped
+      if (int rc = tc_gemm3(scratch, n1, n2, n1, n1, L + r1 * d + r0, d, X + r0 * d + r0, d, 1.0f, 0.0f, ws, error_flag, st, 1))
+        return rc;
+      if (int rc = tc_gemm3(X + r1 * d + r0, d, n2, n1, n2, X + r1 * d + r1, d, scratch, n1, -1.0f, 0.0f, ws, error_flag, st, 2))
+        return rc;
+    }
   }
-  SgemmArgs a{};
-  // S = L21 * X11
-  a.A = L + r1 * d + r0; a.lda = d;
-  a.B = X + r0 * d + r0; a.ldb = d;
-  a.C = scratch; a.ldc = n1;
-  a.M = (int)n2; a.N = (int)n1; a.K = (int)n1; a.alpha = 1.0f; a.beta = 0.0f;
-  if (int rc = sgemm(a, false, SGEMM_PLAIN, st)) return rc;
-  // X21 = -X22 * S
-  a.A = X + r1 * d + r1; a.lda = d;
-  a.B = scratch; a.ldb = n1;
-  a.C = X + r1 * d + r0; a.ldc = d;
-  a.M = (int)n2; a.N = (int)n1; a.K = (int)n2; a.alpha = -1.0f; a.beta = 0.0f;
-  return sgemm(a, false, SGEMM_PLAIN, st);
+  return FPQ_OK;
 }
 
 // ------------------------------------------------------------------ GPTQ column block
@@ -639,7 +681,7 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
     a.M = (int)below_o; a.N = (int)below_o; a.K = (int)Wd; a.alpha = -1.0f; a.beta = 1.0f;
     if (int rc = sgemm(a, true, SGEMM_LOWER, st)) return rc;
   }
-  if (int rc = tri_inverse_recursive(L, U, scratch, ws, error_flag, d, 0, nblk, st)) return rc;
+  if (int rc = tri_inverse_levels(L, U, scratch, ws, error_flag, d, nblk, st)) return rc;
   reflect_inplace_kernel<<<grid1d(d * d / 2), 256, 0, st>>>(U, d);   // U <- J X J (upper triangular)
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;

@@ -25,11 +25,12 @@ __device__ __forceinline__ float4 ld4_guard(const float* base, int64_t ld, int r
 }
 
 template <bool B_T, int EPI>
-__global__ void __launch_bounds__(256) sgemm_kernel(const SgemmArgs a) {
+__device__ __forceinline__ void sgemm_body(const SgemmArgs& a) {
   __shared__ __align__(16) float As[2][TK][TM + PAD];
   __shared__ __align__(16) float Bs[2][TK][TN + PAD];
   const int tid = threadIdx.x;
   const int bm = blockIdx.y * TM, bn = blockIdx.x * TN;
+  if (bm >= a.M || bn >= a.N) return;                   // batched launches size the grid for the largest entry
   if (EPI == SGEMM_LOWER && bn > bm + TM - 1) return;   // tile strictly above the diagonal
 
   const int ty = tid >> 4, tx = tid & 15;
@@ -134,6 +135,17 @@ __global__ void __launch_bounds__(256) sgemm_kernel(const SgemmArgs a) {
   }
 }
 
+template <bool B_T, int EPI>
+__global__ void __launch_bounds__(256) sgemm_kernel(const SgemmArgs a) {
+  sgemm_body<B_T, EPI>(a);
+}
+
+// One launch for up to SGEMM_MAX_BATCH independent products (blockIdx.z picks the entry).
+template <bool B_T>
+__global__ void __launch_bounds__(256) sgemm_batched_kernel(const __grid_constant__ SgemmBatch b) {
+  sgemm_body<B_T, SGEMM_PLAIN>(b.e[blockIdx.z]);
+}
+
 template <bool B_T>
 int launch(const SgemmArgs& a, int epi, cudaStream_t stream) {
   dim3 grid((a.N + TN - 1) / TN, (a.M + TM - 1) / TM);
@@ -151,6 +163,24 @@ int sgemm(const SgemmArgs& a, bool b_transposed, int epilogue, cudaStream_t stre
   FPQ_CHECK_ARG(a.K >= 0 && a.A && a.B, "sgemm: bad arguments");
   FPQ_CHECK_ARG((a.N + TN - 1) / TN <= 65535 * 32 && (a.M + TM - 1) / TM <= 65535, "sgemm: matrix too large");
   return b_transposed ? launch<true>(a, epilogue, stream) : launch<false>(a, epilogue, stream);
+}
+
+int sgemm_batched(const SgemmBatch& b, bool b_transposed, cudaStream_t stream) {
+  if (b.count <= 0) return FPQ_OK;
+  FPQ_CHECK_ARG(b.count <= SGEMM_MAX_BATCH, "sgemm_batched: too many entries");
+  int max_m = 0, max_n = 0;
+  for (int i = 0; i < b.count; ++i) {
+    FPQ_CHECK_ARG(b.e[i].K >= 0 && b.e[i].A && b.e[i].B && b.e[i].C, "sgemm_batched: bad arguments");
+    if (b.e[i].M > max_m) max_m = b.e[i].M;
+    if (b.e[i].N > max_n) max_n = b.e[i].N;
+  }
+  if (max_m <= 0 || max_n <= 0) return FPQ_OK;
+  dim3 grid((max_n + TN - 1) / TN, (max_m + TM - 1) / TM, b.count);
+  FPQ_CHECK_ARG(grid.y <= 65535, "sgemm_batched: matrix too large");
+  if (b_transposed) sgemm_batched_kernel<true><<<grid, 256, 0, stream>>>(b);
+  else sgemm_batched_kernel<false><<<grid, 256, 0, stream>>>(b);
+  FPQ_CHECK_LAUNCH();
+  return FPQ_OK;
 }
 
 }  // namespace fpq

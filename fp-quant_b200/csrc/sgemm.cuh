@@ -29,4 +29,12 @@ struct SgemmArgs {
 
 int sgemm(const SgemmArgs& a, bool b_transposed, int epilogue, cudaStream_t stream);
 
+// Independent plain products in one launch (the small nodes of one level of the triangular inverse).
+constexpr int SGEMM_MAX_BATCH = 32;
+struct SgemmBatch {
+  int count;
+  SgemmArgs e[SGEMM_MAX_BATCH];
+};
+int sgemm_batched(const SgemmBatch& b, bool b_transposed, cudaStream_t stream);
+
 }  // namespace fpq
