@@ -60,7 +60,10 @@ def test_unsupported_configurations_raise():
     with pytest.raises(NotImplementedError):
         Quantizer(bits=4, format="int", granularity="group", group_size=128)
     with pytest.raises(NotImplementedError):
-        Quantizer(bits=4, format="nvfp", granularity="group", group_size=16, scale_precision="e4m3", observer="mse")
+        Quantizer(bits=4, format="nvfp", granularity="group", group_size=32, scale_precision="e4m3")
+    with pytest.raises(NotImplementedError):
+        Quantizer(bits=4, format="mxfp", granularity="channel", scale_precision="e8m0")
+    Quantizer(bits=4, format="nvfp", granularity="group", group_size=16, scale_precision="e4m3", observer="mse")
 
 
 @pytest.mark.parametrize("group", [16, 32, 64, 128])
