@@ -194,3 +194,33 @@ def test_gptq_quantization_in_activation_order():
     assert not torch.equal(e["qweight"], quantized_default[key]["qweight"])
     print(f"relative logit error: activation order {err_act:.3e}, default order {err_default:.3e}")
     assert err_act < 1.5 * err_default + 1e-3
+
+
+def test_gptq_quantization_with_the_mse_observer():
+    """w_observer = a_observer = "mse": the scale search replaces the min-max scales for weights (static
+    GPTQ scales) and activations; the model stays usable and the exported scales differ from min-max's."""
+    from fpq_b200.quantization.driver import gptq_quantization
+    from fpq_b200.quantization.quant_args import QuantizationObserver
+
+    dev = torch.device("cuda:0")
+    data = _calibration(dev)
+    with torch.no_grad():
+        ref_logits = torch.cat([_tiny_llama(dev)(x.to(dev)).logits.float() for x in data])
+
+    def run(observer):
+        model = _tiny_llama(dev)
+        args = _args("mxfp")
+        args.w_observer = args.a_observer = observer
+        quantized, _ = gptq_quantization(model, data, args, dev)
+        with torch.no_grad():
+            logits = torch.cat([model(x.to(dev)).logits.float() for x in data])
+        return quantized, float(((logits - ref_logits) ** 2).mean() / (ref_logits ** 2).mean())
+
+    q_mse, err_mse = run(QuantizationObserver.MSE)
+    q_mm, err_mm = run(QuantizationObserver.MINMAX)
+    key = "model.layers.0.self_attn.q_proj"
+    a, b = q_mse[key]["scales"].view(torch.uint8), q_mm[key]["scales"].view(torch.uint8)
+    changed = float((a != b).float().mean())
+    print(f"relative logit error: MSE observer {err_mse:.3e}, min-max {err_mm:.3e}; {changed:.3f} of the q_proj scale bytes differ")
+    assert changed > 0.01
+    assert err_mse < 1.5 * err_mm + 1e-3
