@@ -36,11 +36,23 @@ __global__ void dead_columns_kernel(const float* __restrict__ W, int64_t rows, i
   dead[j] = all_zero ? 1 : 0;
 }
 
-__global__ void mask_dead_kernel(float* H, int64_t d, const uint8_t* __restrict__ dead) {
-  const int64_t n = d * d;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t i = idx / d, j = idx - i * d;
-    if (dead[i] || dead[j]) H[idx] = (i == j) ? 1.0f : 0.0f;
+// Rows and columns of dead input channels become rows / columns of the identity.  A block covers 16 rows x
+// 256 columns and leaves at once when none of its rows and columns is dead (the usual case: nothing is).
+__global__ void __launch_bounds__(256) mask_dead_kernel(float* H, int64_t d, const uint8_t* __restrict__ dead) {
+  __shared__ uint8_t drow[16];
+  const int64_t j = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  const int64_t i0 = (int64_t)blockIdx.y * 16;
+  if (threadIdx.x < 16) drow[threadIdx.x] = (i0 + threadIdx.x < d) ? dead[i0 + threadIdx.x] : 0;
+  const int dj = (j < d && dead[j]) ? 1 : 0;
+  const int any_col = __syncthreads_or(dj);       // also publishes drow
+  int any_row = 0;
+#pragma unroll
+  for (int r = 0; r < 16; ++r) any_row |= drow[r];
+  if (!any_col && !any_row) return;
+  if (j >= d) return;
+  for (int r = 0; r < 16; ++r) {
+    const int64_t i = i0 + r;
+    if (i < d && (drow[r] || dj)) H[i * d + j] = (i == j) ? 1.0f : 0.0f;
   }
 }
 
@@ -548,11 +560,11 @@ using namespace fpq;
 extern "C" int fpq_hessian_prepare(float* H, int64_t d, const float* W, int64_t rows, float rel_damp,
                                    uint8_t* workspace, fpq_stream_t stream) {
   FPQ_CHECK_ARG(H && W && workspace, "NULL pointer");
-  FPQ_CHECK_ARG(d > 0 && rows > 0, "bad shape");
+  FPQ_CHECK_ARG(d > 0 && d <= (1 << 20) && rows > 0, "bad shape");
   cudaStream_t st = (cudaStream_t)stream;
   dead_columns_kernel<<<(unsigned)((d + 255) / 256), 256, 0, st>>>(W, rows, d, workspace);
   FPQ_CHECK_LAUNCH();
-  mask_dead_kernel<<<grid1d(d * d), 256, 0, st>>>(H, d, workspace);
+  mask_dead_kernel<<<dim3((unsigned)((d + 255) / 256), (unsigned)((d + 15) / 16)), 256, 0, st>>>(H, d, workspace);
   FPQ_CHECK_LAUNCH();
   damp_kernel<<<1, 256, 0, st>>>(H, d, rel_damp);
   FPQ_CHECK_LAUNCH();
@@ -588,7 +600,7 @@ extern "C" int fpq_hessian_prepare_noalloc(float* H, int64_t d, const float* W, 
   // Every flag in [0, d) is rewritten before it is read, so nothing needs clearing between calls.
   dead_columns_kernel<<<(unsigned)((d + 255) / 256), 256, 0, st>>>(W, rows, d, scratch);
   FPQ_CHECK_LAUNCH();
-  mask_dead_kernel<<<grid1d(d * d), 256, 0, st>>>(H, d, scratch);
+  mask_dead_kernel<<<dim3((unsigned)((d + 255) / 256), (unsigned)((d + 15) / 16)), 256, 0, st>>>(H, d, scratch);
   FPQ_CHECK_LAUNCH();
   damp_kernel<<<1, 256, 0, st>>>(H, d, rel_damp);
   FPQ_CHECK_LAUNCH();
