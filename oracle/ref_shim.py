@@ -14,7 +14,9 @@ import types
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("FPQ_REFERENCE_ROOT", "/root/reference")
+# FPQ_REFERENCE_ROOT, or a checkout named "reference" beside this repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE_ROOT = os.environ.get("FPQ_REFERENCE_ROOT") or os.path.join(os.path.dirname(_REPO), "reference")
 
 
 def available() -> bool:
