@@ -379,7 +379,7 @@ int tri_inverse_levels(const float* L, float* X, float* scratch, __nv_bfloat16* 
 // four 16-byte pieces of one row per load.  The outer loop over the four 32-column owners is a real
 // loop (the unrolled body of 32 steps stays inside the instruction cache: a fully unrolled
 // thread-per-row version was instruction-fetch bound at three warps per SM).  Afterwards each thread
-// writes its 32 errors to Err[rows, 128] for the trailing update, the dequantised values, rebuilt
+// writes its 32 errors (as the transposed three-term bf16 operand of the trailing update), the dequantised values, rebuilt
 // as grid(code) * scale exactly as they were computed, and its 16 code bytes.
 constexpr int SUB = 32;   // columns per thread
 // Shared-memory image of U's diagonal block: every 32-column piece of a row is shifted by another
@@ -419,7 +419,7 @@ template <int G>
 __global__ void __launch_bounds__(G == 1 ? 256 : 512) gptq_block_kernel(float* __restrict__ W, int64_t rows, int64_t C,
                                                                         int64_t c1, const float* __restrict__ scales,
                                                                         const float* __restrict__ U,
-                                                                        float* __restrict__ Err,
+                                                                        __nv_bfloat16* __restrict__ ErrT3, int64_t lda,
                                                                         uint8_t* __restrict__ codes,
                                                                         const int32_t* __restrict__ gidx, int n_groups) {
   extern __shared__ float Us[];   // NB rows of US_LD floats, then the reciprocals of the diagonal
@@ -500,11 +500,37 @@ __global__ void __launch_bounds__(G == 1 ? 256 : 512) gptq_block_kernel(float* _
       }
     }
   }
+  // The block's errors leave as the operand of the trailing update: three bf16 terms per value, transposed
+  // ([3 * 128, lda], plane p of column c at row p * 128 + c).  They are staged in shared memory (the image
+  // of U is no longer needed) so that the global stores run along the rows.
+  const int rb = (int)(blockDim.x >> 2);            // rows of this block
+  const int es_ld = rb + 1;
+  const int r_local = (int)(threadIdx.x >> 2);
+  __syncthreads();                                  // every warp has finished reading Us
+  float* Es = Us;
+#pragma unroll
+  for (int j = 0; j < SUB; ++j) Es[(SUB * q + j) * es_ld + r_local] = err[j];
+  __syncthreads();
+  {
+    const int64_t row0 = (int64_t)blockIdx.x * rb;
+    const int pairs = rb >> 1;
+    for (int idx = (int)threadIdx.x; idx < NB * pairs; idx += (int)blockDim.x) {
+      const int c = idx / pairs, r0 = 2 * (idx - c * pairs);
+      const int64_t g = row0 + r0;
+      if (g >= lda) continue;                       // lda is even and >= rows: g + 1 < lda as well
+      const float v0 = g < rows ? Es[c * es_ld + r0] : 0.0f;
+      const float v1 = g + 1 < rows ? Es[c * es_ld + r0 + 1] : 0.0f;
+      __nv_bfloat16 h0, m0, l0, h1, m1, l1;
+      split3(v0, h0, m0, l0);
+      split3(v1, h1, m1, l1);
+      __nv_bfloat16* dst = ErrT3 + (int64_t)c * lda + g;
+      *reinterpret_cast<__nv_bfloat162*>(dst) = __halves2bfloat162(h0, h1);
+      *reinterpret_cast<__nv_bfloat162*>(dst + (int64_t)NB * lda) = __halves2bfloat162(m0, m1);
+      *reinterpret_cast<__nv_bfloat162*>(dst + (int64_t)2 * NB * lda) = __halves2bfloat162(l0, l1);
+    }
+  }
   if (!live) return;
 
-  float4* ep = reinterpret_cast<float4*>(Err + row * NB + SUB * q);
-#pragma unroll
-  for (int v = 0; v < SUB / 4; ++v) ep[v] = make_float4(err[4 * v], err[4 * v + 1], err[4 * v + 2], err[4 * v + 3]);
   float4* op = reinterpret_cast<float4*>(W + row * C + c1 + SUB * q);
 #pragma unroll
   for (int v = 0; v < SUB / 4; ++v) {
@@ -735,10 +761,9 @@ extern "C" int fpq_gptq_quantize_ordered(float* W, int64_t rows, int64_t cols, c
     FPQ_CHECK_CUDA(cudaFuncSetAttribute(gptq_block_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured[dev] = true;
   }
-  // workspace: block errors (fp32) | their transposed three-term bf16 split | three-term bf16 split of U
+  // workspace: (unused fp32 slab, kept so that the size helper does not change) | transposed three-term bf16 split of a block's errors | three-term bf16 split of U
   const int64_t lda = gptq_lda(rows);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-  float* err = reinterpret_cast<float*>(ws);
   __nv_bfloat16* errT3 = reinterpret_cast<__nv_bfloat16*>(ws + align256(rows * NB * (int64_t)sizeof(float)));
   __nv_bfloat16* U3 = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(errT3) + align256(3 * NB * lda * 2));
   if (cols > NB) {
@@ -763,17 +788,14 @@ extern "C" int fpq_gptq_quantize_ordered(float* W, int64_t rows, int64_t cols, c
   for (int64_t c1 = 0; c1 < cols; c1 += NB) {
     const int n_groups = (int)(cols / group);
     if (group_index)
-      gptq_block_kernel<1><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes, group_index, n_groups);
+      gptq_block_kernel<1><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, errT3, lda, codes, group_index, n_groups);
     else if (group == 16)
-      gptq_block_kernel<16><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes, nullptr, n_groups);
+      gptq_block_kernel<16><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, errT3, lda, codes, nullptr, n_groups);
     else
-      gptq_block_kernel<32><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, err, codes, nullptr, n_groups);
+      gptq_block_kernel<32><<<grid, threads, smem, st>>>(W, rows, cols, c1, scales, U, errT3, lda, codes, nullptr, n_groups);
     FPQ_CHECK_LAUNCH();
     const int64_t c2 = c1 + NB;
     if (c2 >= cols) break;
-    dim3 tgrid((unsigned)((lda + 31) / 32), NB / 32);
-    transpose_split3_kernel<<<tgrid, 256, 0, st>>>(err, NB, rows, NB, errT3, lda);
-    FPQ_CHECK_LAUNCH();
     int a_y[6], b_y[6];
     for (int t = 0; t < 6; ++t) {
       a_y[t] = pa[t] * NB;
