@@ -158,6 +158,11 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  // Barriers, tensor memory and descriptors touched nothing another kernel wrote: with a programmatic
+  // dependent launch all of the above overlaps the tail of the previous kernel; operands and the output
+  // (read-modify-write) are only touched from here on.
+  launch_dependents();
+  grid_dependency_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -368,11 +373,21 @@ int gemm_atb_bf16(float* out, int64_t ldc, int64_t d1, int64_t d2, const void* A
   int grid = sm_count();
   if (grid > p.num_tiles) grid = p.num_tiles;
   if (grid < 1) return FPQ_OK;
-  if (big)
-    hessian_kernel<true><<<grid, NUM_THREADS, Shape<true>::DYN_BYTES, stream>>>(ta, tb, p);
-  else
-    hessian_kernel<false><<<grid, NUM_THREADS, Shape<false>::DYN_BYTES, stream>>>(ta, tb, p);
-  FPQ_CHECK_LAUNCH();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = big ? Shape<true>::DYN_BYTES : Shape<false>::DYN_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_dependent_launch() ? 1 : 0;
+  if (big) {
+    FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, hessian_kernel<true>, ta, tb, p));
+  } else {
+    FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, hessian_kernel<false>, ta, tb, p));
+  }
   return FPQ_OK;
 }
 
