@@ -29,7 +29,9 @@ struct QuantParams {
   void* y;              // dequantised / rotated output
   const float* gs;      // NVFP4 tensor scale
   uint32_t* absmax_bits;
+  uint8_t* mask;        // QuEST clip mask: one bit per element (codes) or one byte per element (dequantised output)
   uint32_t sf_tiles_per_row_block;  // ceil((cols/g)/4)
+  uint32_t rows, pad_rows;          // swizzled scale layout: rows of the tensor and rows up to the next multiple of 128
   int layout;
   int out_bf16;
   int ste;
@@ -263,6 +265,35 @@ __device__ __forceinline__ float mx_scale(float a, uint32_t& byte, int& e) {
   return s;
 }
 
+// Third value of the FMT template parameter (not part of the C ABI's format numbers): MXFP4 codes and
+// E8M0 scale bytes with the QuEST scale rule instead of the group maximum.
+constexpr int FMT_MXQUEST = 2;
+
+// QuEST scale of one 32-element group (inference_lib/src/fp_quant/module/triton/mxfp4.py:51-59):
+// std = sqrt(mean(x^2) - mean(x)^2), scale = fl(fl(c * std) + 1e-8) with c = fl32(2.92247856 / 6)
+// (pseudoquant_linear_fns.py:20), divisor 2^floor(log2(scale)), stored byte = that exponent + 127.
+// The sums run over the sixteen register pairs in order, even and odd elements separately (one packed
+// add per pair), then even + odd; squares are rounded products (no fused multiply-add), so a CPU
+// reproduces every bit.  A variance that rounds below zero counts as zero.  scale >= 1e-8 is a normal
+// number, so the exponent field is floor(log2(scale)) exactly.
+__device__ __forceinline__ float quest_scale(const u64* P, uint32_t& byte) {
+  u64 acc = P[0], acc2 = mul2(P[0], P[0]);
+#pragma unroll
+  for (int j = 1; j < 16; ++j) {
+    acc = add2(acc, P[j]);
+    acc2 = add2(acc2, mul2(P[j], P[j]));
+  }
+  float a0, a1, q0, q1;
+  unpack2(acc, a0, a1);
+  unpack2(acc2, q0, q1);
+  const float mean = __fmul_rn(__fadd_rn(a0, a1), 0.03125f);
+  const float mean_sq = __fmul_rn(__fadd_rn(q0, q1), 0.03125f);
+  const float var = fmaxf(__fsub_rn(mean_sq, __fmul_rn(mean, mean)), 0.0f);
+  const float scale = __fadd_rn(__fmul_rn(0.48707976f, __fsqrt_rn(var)), 1e-8f);
+  byte = (__float_as_uint(scale) >> 23) & 0xffu;
+  return __uint_as_float(byte << 23);
+}
+
 // NVFP4 scale of one 16-element group.
 __device__ __forceinline__ float nv_scale(float a, float gs, float rgs, uint32_t& byte) {
   float s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
@@ -410,10 +441,12 @@ __device__ __forceinline__ void process_chunk(const QuantParams& p, const RawChu
     int mx_e = 0;
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
+      if (FMT == FMT_MXQUEST) break;
       float a = absmax_pairs(P + g * PG, PG);
       if (MX_FAST && GH != 0) a = __fmul_rn(a, hadamard_scale<GH>());   // max |t*c| = fl(c * max |t|)
       s[g] = FMT == FPQ_FMT_NVFP4 ? nv_scale(a, gs, rgs, sb[g]) : mx_scale(a, sb[g], mx_e);
     }
+    if (FMT == FMT_MXQUEST) s[0] = quest_scale(P, sb[0]);
     if (MODE == MODE_CODES && active) {
       if (p.sbytes) {
         size_t off = (size_t)c * NG;
@@ -461,6 +494,35 @@ __device__ __forceinline__ void process_chunk(const QuantParams& p, const RawChu
     } else {
 #pragma unroll
       for (int g = 0; g < NG; ++g) divide_pairs(P + g * PG, PG, s[g]);
+    }
+
+    if (FMT == FMT_MXQUEST && p.mask != nullptr) {
+      // bit i set = element i lies inside the grid's range (|x / 2^e| < 6, triton/mxfp4.py:105-110)
+      uint32_t inside = 0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        float a, b;
+        unpack2(P[j], a, b);
+        inside |= (fabsf(a) < 6.0f ? 1u : 0u) << (2 * j);
+        inside |= (fabsf(b) < 6.0f ? 1u : 0u) << (2 * j + 1);
+      }
+      if (active) {
+        if (MODE == MODE_CODES) {
+          reinterpret_cast<uint32_t*>(p.mask)[c] = inside;            // bit i of byte b = element 8 b + i
+        } else {
+          uint4* o = reinterpret_cast<uint4*>(p.mask) + c * 2;        // one bool byte per element
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t nib = (inside >> (16 * h + 4 * q)) & 15u;
+              w[q] = (nib & 1u) | ((nib & 2u) << 7) | ((nib & 4u) << 14) | ((nib & 8u) << 21);
+            }
+            o[h] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
     }
 
     uint32_t cw[4];
@@ -557,6 +619,17 @@ __global__ void __launch_bounds__(256, Prefetches<IN_BF16, MODE>::value ? FPQ_Q_
     }
   }
 
+  if (MODE == MODE_CODES && p.pad_rows != 0) {
+    // swizzled scale bytes of the rows between the tensor's last row and the end of its 128-row block: zero
+    // (the GEMM's TMA loads whole 512-byte tiles, and a defined value keeps its pad rows finite)
+    const int64_t n_words = (int64_t)p.pad_rows * p.sf_tiles_per_row_block;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+      const uint32_t r = p.rows + (uint32_t)(w / p.sf_tiles_per_row_block);
+      const uint32_t kb = (uint32_t)(w % p.sf_tiles_per_row_block);
+      *reinterpret_cast<uint32_t*>(p.sbytes + swizzled_offset(r, kb * 4u, p.sf_tiles_per_row_block)) = 0u;
+    }
+  }
+
   if (MODE == MODE_ABSMAX) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1)
@@ -617,6 +690,9 @@ int launch_mode(int gh, int fmt, int dtype, const QuantParams& p, cudaStream_t s
     return dtype == FPQ_DT_BF16 ? launch_gh<FPQ_FMT_MXFP4, true, MODE>(gh, p, stream)
                                 : launch_gh<FPQ_FMT_MXFP4, false, MODE>(gh, p, stream);
   } else {
+    if (fmt == FMT_MXQUEST)
+      return dtype == FPQ_DT_BF16 ? launch_gh<FMT_MXQUEST, true, MODE>(gh, p, stream)
+                                  : launch_gh<FMT_MXQUEST, false, MODE>(gh, p, stream);
     if (fmt == FPQ_FMT_MXFP4)
       return dtype == FPQ_DT_BF16 ? launch_gh<FPQ_FMT_MXFP4, true, MODE>(gh, p, stream)
                                   : launch_gh<FPQ_FMT_MXFP4, false, MODE>(gh, p, stream);
@@ -964,6 +1040,11 @@ extern "C" int fpq_quantize(const void* x, int dtype, int64_t rows, int64_t cols
   p.gs = global_scale;
   p.sf_tiles_per_row_block = (uint32_t)ceil_div64(cols / g, 4);
   p.layout = scale_layout;
+  if (scale_bytes && scale_layout == FPQ_SCALES_SWIZZLED) {
+    FPQ_CHECK_ARG(rows < ((int64_t)1 << 31), "too many rows for the swizzled scale layout");
+    p.rows = (uint32_t)rows;
+    p.pad_rows = (uint32_t)(ceil_div64(rows, 128) * 128 - rows);
+  }
   return launch_mode<MODE_CODES>(hadamard_group, format, dtype, p, (cudaStream_t)stream);
 }
 
@@ -983,6 +1064,48 @@ extern "C" int fpq_fake_quantize(const void* x, int dtype, int64_t rows, int64_t
   p.out_bf16 = dtype == FPQ_DT_BF16;
   p.ste = ste;
   return launch_mode<MODE_DEQUANT>(hadamard_group, format, dtype, p, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_quantize_quest(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+                                  uint8_t* codes, uint8_t* scale_bytes, int scale_layout, uint8_t* clip_mask,
+                                  fpq_stream_t stream) {
+  if (int rc = check_common(x, dtype, rows, cols, hadamard_group)) return rc;
+  FPQ_CHECK_ARG(scale_layout == FPQ_SCALES_ROWMAJOR || scale_layout == FPQ_SCALES_SWIZZLED, "bad scale_layout");
+  FPQ_CHECK_ARG(codes != nullptr, "codes is NULL");
+  FPQ_CHECK_ARG(((uintptr_t)codes & 15) == 0 && ((uintptr_t)scale_bytes & 15) == 0 && ((uintptr_t)clip_mask & 3) == 0,
+                "codes and scale_bytes must be 16-byte aligned, clip_mask 4-byte aligned");
+  if (rows == 0) return FPQ_OK;
+  QuantParams p{};
+  p.x = x;
+  p.n_chunks = rows * cols / 32;
+  p.chunks_per_row = (uint32_t)(cols / 32);
+  p.codes = codes;
+  p.sbytes = scale_bytes;
+  p.mask = clip_mask;
+  p.sf_tiles_per_row_block = (uint32_t)ceil_div64(cols / 32, 4);
+  p.layout = scale_layout;
+  if (scale_bytes && scale_layout == FPQ_SCALES_SWIZZLED) {
+    FPQ_CHECK_ARG(rows < ((int64_t)1 << 31), "too many rows for the swizzled scale layout");
+    p.rows = (uint32_t)rows;
+    p.pad_rows = (uint32_t)(ceil_div64(rows, 128) * 128 - rows);
+  }
+  return launch_mode<MODE_CODES>(hadamard_group, FMT_MXQUEST, dtype, p, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_fake_quantize_quest(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
+                                       void* y, uint8_t* clip_mask, fpq_stream_t stream) {
+  if (int rc = check_common(x, dtype, rows, cols, hadamard_group)) return rc;
+  FPQ_CHECK_ARG(y != nullptr && ((uintptr_t)y & 15) == 0, "y must be non-NULL and 16-byte aligned");
+  FPQ_CHECK_ARG(((uintptr_t)clip_mask & 15) == 0, "clip_mask must be 16-byte aligned");
+  if (rows == 0) return FPQ_OK;
+  QuantParams p{};
+  p.x = x;
+  p.n_chunks = rows * cols / 32;
+  p.chunks_per_row = (uint32_t)(cols / 32);
+  p.y = y;
+  p.mask = clip_mask;
+  p.out_bf16 = dtype == FPQ_DT_BF16;
+  return launch_mode<MODE_DEQUANT>(hadamard_group, FMT_MXQUEST, dtype, p, (cudaStream_t)stream);
 }
 
 extern "C" int fpq_apply_scales(const void* x, int dtype, int64_t rows, int64_t cols, const float* scales,

@@ -32,6 +32,8 @@ _SIGNATURES = {
     "fpq_quantize": [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                      c_int, c_void_p, c_void_p],
     "fpq_fake_quantize": [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "fpq_quantize_quest": [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "fpq_fake_quantize_quest": [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p],
     "fpq_apply_scales": [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "fpq_pack_grid": [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p],
     "fpq_swizzle_scales": [c_void_p, c_int64, c_int64, c_void_p, c_void_p],

@@ -13,9 +13,9 @@ from torch import nn
 from ... import ops
 from ...rotation import sylvester
 from ..utils.config import FPQuantConfig, FPQuantDtype, validate_config
-from .linear_fns import FPQuant4x16MasterFn, FPQuant4x16NoMasterFn, forward_quantize
+from .linear_fns import FPQuant4x16MasterFn, FPQuant4x16NoMasterFn, forward_quantize, gemm_alpha
 from .pseudoquant_linear_fns import PseudoQuant4x16MasterFn, PseudoQuant4x16NoMasterFn, forward_pseudoquantize
-from .qutlass_ops import HAS_QUTLASS  # noqa: F401  (kept for API compatibility)
+from .qutlass_ops import HAS_QUTLASS, swizzle_scales_op  # noqa: F401  (HAS_QUTLASS kept for API compatibility)
 
 
 def get_hadamard_matrix(group_size: int, dtype: torch.dtype, device: torch.device):
@@ -62,6 +62,8 @@ class FPQuantLinear(nn.Module):
         self.register_buffer("backward_hadamard_matrix", torch.empty(hg, hg, **kw))
         self._scales_blocked = None
         self._scales_blocked_key = None
+        self._alpha = None
+        self._alpha_key = None
 
     # ------------------------------------------------------------------ load-time step
     @torch.no_grad()
@@ -106,14 +108,32 @@ class FPQuantLinear(nn.Module):
         self._scales_blocked = None
 
     def _blocked_weight_scales(self) -> torch.Tensor:
-        """Weight scale bytes in the swizzled layout, built once per `scales` tensor."""
+        """Weight scale bytes in the swizzled layout, built once per `scales` tensor.  While torch.compile
+        traces the module the cache check (addresses and version counters, which a tracer cannot see) is left
+        out: a cache filled by an earlier eager call is used as it is, otherwise the re-layout becomes an op of
+        the graph."""
+        g = _SCALE_GROUP[self.config.forward_dtype]
+        if torch.compiler.is_compiling():
+            if self._scales_blocked is not None:
+                return self._scales_blocked
+            return swizzle_scales_op(self.scales.view(torch.uint8)[: self.out_features, : self.in_features // g].contiguous())
         key = (self.scales.data_ptr(), self.scales._version, tuple(self.scales.shape))
         if self._scales_blocked is None or self._scales_blocked_key != key:
-            g = _SCALE_GROUP[self.config.forward_dtype]
             rowmajor = self.scales.view(torch.uint8)[: self.out_features, : self.in_features // g]
             self._scales_blocked = ops.swizzle_scales(rowmajor.contiguous())
             self._scales_blocked_key = key
         return self._scales_blocked
+
+    def _gemm_alpha(self) -> torch.Tensor:
+        """1 / (weight_global_scale * act_global_scale) as fp32 [1], recomputed only when a tensor scale changed
+        (three small kernels per forward otherwise: the decode path is bound by launches)."""
+        w, a = self.weight_global_scale, self.act_global_scale
+        if torch.compiler.is_compiling():
+            return gemm_alpha(w, a)
+        key = (w.data_ptr(), w._version, a.data_ptr(), a._version)
+        if self._alpha is None or self._alpha_key != key:
+            self._alpha, self._alpha_key = gemm_alpha(w, a), key
+        return self._alpha
 
     # ------------------------------------------------------------------ forward
     def forward(self, x) -> torch.Tensor:
@@ -128,7 +148,8 @@ class FPQuantLinear(nn.Module):
                 return PseudoQuant4x16NoMasterFn.apply(x, self.dqweight, *common)
             if cfg.store_master_weights:
                 return FPQuant4x16MasterFn.apply(x, self.weight, *common)
-            return FPQuant4x16NoMasterFn.apply(x, self.qweight, self._blocked_weight_scales(), *common)
+            return FPQuant4x16NoMasterFn.apply(x, self.qweight, self._blocked_weight_scales(), *common,
+                                               self._gemm_alpha())
         if cfg.forward_dtype == FPQuantDtype.MXFP4 and cfg.backward_dtype in (FPQuantDtype.MXFP4, FPQuantDtype.MXFP8) \
                 and not cfg.pseudoquantization:
             raise NotImplementedError("quantised backward passes (MXFP4 / MXFP8 QAT) are outside the B200 hot path")

@@ -42,27 +42,39 @@ def forward_quantize_blocked(x, hadamard_matrix, global_scale, dtype: FPQuantDty
     """Fast path of `forward_quantize`: scales come out in the layout the matmul reads."""
     if dtype not in (FPQuantDtype.MXFP4, FPQuantDtype.NVFP4):
         raise ValueError(f"Unsupported forward dtype: {dtype}")
-    if dtype == FPQuantDtype.MXFP4 and forward_method != "abs_max":
-        raise NotImplementedError("only the abs_max method is on the B200 path (QuEST scales are not built)")
+    if forward_method not in ("abs_max", "quest"):
+        raise ValueError(f"Unsupported forward method: {forward_method}")
     return fused_quantize_blocked_op(x.to(torch.bfloat16), hadamard_matrix.to(torch.bfloat16), global_scale.float(),
-                                     dtype == FPQuantDtype.NVFP4, rotation)
+                                     dtype == FPQuantDtype.NVFP4, rotation, forward_method == "quest")
 
 
-def forward_gemm_blocked(x_q, w_q, x_scales_blocked, w_scales_blocked, alpha, dtype: FPQuantDtype):
+def forward_gemm_blocked(x_q, w_q, x_scales_blocked, w_scales_blocked, alpha, dtype: FPQuantDtype, bias=None):
     if dtype not in (FPQuantDtype.MXFP4, FPQuantDtype.NVFP4):
         raise ValueError(f"Unsupported dtype: {dtype}")
     return matmul_fp4_bf16_tn_blocked_op(x_q, w_q, x_scales_blocked, w_scales_blocked, alpha.float(),
-                                         dtype == FPQuantDtype.NVFP4)
+                                         dtype == FPQuantDtype.NVFP4, bias)
+
+
+def gemm_alpha(weight_global_scale: torch.Tensor, act_global_scale: torch.Tensor) -> torch.Tensor:
+    """fp32 [1]: 1 / (weight_global_scale * act_global_scale) with the reference's rounding order -- product
+    and reciprocal in the dtype of the buffers (bf16 once `pre_forward` made them), then the cast to fp32
+    (linear_fns.py:433, :505 and `alpha.float()` at :57-62).  For the abs_max default 3 * 3 this is
+    bf16(1/9) = 0.111328, not 0.111111."""
+    return (1.0 / (weight_global_scale * act_global_scale)).float().reshape(1)
 
 
 def _linear_forward(x, weight_q, weight_scales_blocked, weight_global_scale, act_global_scale, bias,
-                    hadamard_matrix, dtype, forward_method):
+                    hadamard_matrix, dtype, forward_method, alpha=None):
     x_flat = x.contiguous().flatten(end_dim=-2)
     x_q, x_scales = forward_quantize_blocked(x_flat, hadamard_matrix, act_global_scale, dtype, forward_method)
-    alpha = 1.0 / (weight_global_scale.float() * act_global_scale.float())
-    y = forward_gemm_blocked(x_q, weight_q, x_scales, weight_scales_blocked, alpha, dtype)
+    if alpha is None:
+        alpha = gemm_alpha(weight_global_scale, act_global_scale)
+    # the bias is added in the GEMM's epilogue (fp32 accumulator + bias, one rounding to bf16) instead of
+    # the reference's separate bf16 add (linear_fns.py:514-515)
+    fused_bias = bias if bias is not None and bias.dtype == torch.bfloat16 else None
+    y = forward_gemm_blocked(x_q, weight_q, x_scales, weight_scales_blocked, alpha, dtype, fused_bias)
     y = y.unflatten(dim=0, sizes=x.shape[:-1])
-    if bias is not None:
+    if bias is not None and fused_bias is None:
         y = y + bias
     return y
 
@@ -73,9 +85,10 @@ class FPQuant4x16NoMasterFn(Function):
 
     @staticmethod
     def forward(ctx, x, weight_q, weight_scales, weight_global_scale, act_global_scale, bias,
-                forward_hadamard_matrix, dtype, forward_method):
+                forward_hadamard_matrix, dtype, forward_method, alpha=None):
+        """`alpha` (optional, fp32 [1]): the module's cached `gemm_alpha` of the two tensor scales."""
         return _linear_forward(x, weight_q, weight_scales, weight_global_scale, act_global_scale, bias,
-                               forward_hadamard_matrix, dtype, forward_method)
+                               forward_hadamard_matrix, dtype, forward_method, alpha)
 
     @staticmethod
     def backward(ctx, grad_output):

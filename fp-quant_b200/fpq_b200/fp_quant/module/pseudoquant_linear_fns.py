@@ -16,16 +16,16 @@ from ..utils.config import FPQuantDtype
 
 def forward_pseudoquantize(x: torch.Tensor, hadamard_matrix: torch.Tensor, global_scale: torch.Tensor,
                            dtype: FPQuantDtype, forward_method: str) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Dequantised rotate+quantise of x and the clip mask (all ones for abs_max)
-    (pseudoquant_linear_fns.py:12-48)."""
+    """Dequantised rotate+quantise of x and the clip mask (all ones for abs_max; for quest the elements
+    with |x / divisor| < 6) (pseudoquant_linear_fns.py:12-48)."""
     if dtype not in (FPQuantDtype.MXFP4, FPQuantDtype.NVFP4):
         if dtype == FPQuantDtype.MXFP8:
             raise NotImplementedError("MXFP8 is not supported for forward quantization yet")
         raise ValueError(f"Unsupported forward dtype: {dtype}")
-    if forward_method != "abs_max":
-        if dtype == FPQuantDtype.NVFP4:
-            raise AssertionError("NVFP4 only supports abs_max method")
-        raise NotImplementedError("only the abs_max method is on the B200 path (QuEST scales are not built)")
+    if forward_method not in ("abs_max", "quest"):
+        raise ValueError(f"Unsupported forward method: {forward_method}")
+    if forward_method == "quest" and dtype == FPQuantDtype.NVFP4:
+        raise AssertionError("NVFP4 only supports abs_max method")
     fmt = "nvfp4" if dtype == FPQuantDtype.NVFP4 else "mxfp4"
     kind, group = classify_rotation(hadamard_matrix)
     xin = x if x.dtype in (torch.bfloat16, torch.float32) else x.to(torch.bfloat16)
@@ -33,6 +33,9 @@ def forward_pseudoquantize(x: torch.Tensor, hadamard_matrix: torch.Tensor, globa
         xin, group = ops.rotate_dense(xin.reshape(-1, x.shape[-1]), hadamard_matrix).view(x.shape), 0
     elif kind == "identity":
         group = 0
+    if forward_method == "quest":          # std-based scales; the mask marks the elements inside the grid's range
+        y, mask = ops.fake_quantize_quest(xin, group, return_mask=True)
+        return y.to(x.dtype), mask
     gs = global_scale.float() if fmt == "nvfp4" else None
     y = ops.fake_quantize(xin, fmt, group, gs).to(x.dtype)
     return y, torch.ones_like(y, dtype=torch.bool)

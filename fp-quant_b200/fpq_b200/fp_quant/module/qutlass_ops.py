@@ -8,8 +8,11 @@ Two families:
     scale tensors out on every call;
   * the `*_blocked` ops are the fast path: quantise writes the swizzled layout directly and the
     matmul consumes it, so nothing is re-laid out per call.
-All are registered as torch custom ops (namespace fpq_b200::) with fake implementations so that
-torch.compile(fullgraph=True) can trace through them.
+All are registered as torch custom ops with fake implementations so that torch.compile(fullgraph=True)
+can trace through them.  The reference names live in the reference's own namespace `fp_quant::`
+(qutlass_ops.py:36, :54, :111 register `fp_quant::fused_quantize_mx_op` etc.), so code that reaches
+them through `torch.ops.fp_quant` keeps working; when the reference package was imported first and owns
+that namespace already, they fall back to `fpq_b200::`.  The `*_blocked` ops are always `fpq_b200::`.
 """
 from __future__ import annotations
 
@@ -21,6 +24,16 @@ from ... import ops
 from ...rotation import kind_of
 
 HAS_QUTLASS = True  # the CUDA library plays QuTLASS' part
+
+
+def _reference_namespace_free() -> bool:
+    try:
+        return not hasattr(torch.ops.fp_quant, "fused_quantize_mx_op")
+    except Exception:
+        return True
+
+
+NAMESPACE = "fp_quant" if _reference_namespace_free() else "fpq_b200"
 
 
 def _padded(rows: int, cols: int) -> Tuple[int, int]:
@@ -37,25 +50,46 @@ def _rotate_then(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, rotation: 
     return ops.rotate_dense(x_flat, hadamard_matrix, out_dtype=torch.float32), 0
 
 
+def _pad_rowmajor(sb: torch.Tensor, rows: int, sf_cols: int) -> torch.Tensor:
+    pr, pc = _padded(rows, sf_cols)
+    if (pr, pc) == (rows, sf_cols):
+        return sb
+    padded = torch.zeros(pr, pc, dtype=torch.uint8, device=sb.device)
+    padded[:rows, :sf_cols] = sb
+    return padded
+
+
 def _quantize(x_flat, hadamard_matrix, fmt, global_scale, swizzled, rotation=0):
     x, group = _rotate_then(x_flat, hadamard_matrix, rotation)
     q, sb, _ = ops.quantize(x, fmt, group, global_scale, swizzled=swizzled)
-    rows, sf_cols = x.shape[0], x.shape[1] // ops.GROUP_OF[fmt]
     if not swizzled:
-        pr, pc = _padded(rows, sf_cols)
-        if (pr, pc) != (rows, sf_cols):
-            padded = torch.zeros(pr, pc, dtype=torch.uint8, device=sb.device)
-            padded[:rows, :sf_cols] = sb
-            sb = padded
+        sb = _pad_rowmajor(sb, x.shape[0], x.shape[1] // ops.GROUP_OF[fmt])
     return q, sb
 
 
+def _quantize_quest(x_flat, hadamard_matrix, swizzled, return_mask, rotation=0):
+    x, group = _rotate_then(x_flat, hadamard_matrix, rotation)
+    q, sb, mask = ops.quantize_quest(x, group, swizzled=swizzled, return_mask=return_mask)
+    if not swizzled:
+        sb = _pad_rowmajor(sb, x.shape[0], x.shape[1] // 32)
+    return q, sb, mask
+
+
+def _check_method(forward_method: str) -> None:
+    if forward_method not in ("abs_max", "quest"):
+        raise ValueError(f"Unsupported forward method: {forward_method}")
+
+
 # --------------------------------------------------------------------------- quantise
-@torch.library.custom_op("fpq_b200::fused_quantize_mx", mutates_args=())
+@torch.library.custom_op(f"{NAMESPACE}::fused_quantize_mx_op", mutates_args=())
 def _fused_quantize_mx(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, forward_method: str,
                        return_mask: bool) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    if forward_method != "abs_max":
-        raise NotImplementedError("only the abs_max method is on the B200 path (QuEST scales are not built)")
+    _check_method(forward_method)
+    if forward_method == "quest":
+        q, sb, mask = _quantize_quest(x_flat, hadamard_matrix, swizzled=False, return_mask=return_mask)
+        if mask is None:
+            mask = torch.empty((x_flat.shape[0], 0), dtype=torch.uint8, device=x_flat.device)
+        return q, sb.view(torch.float8_e8m0fnu), mask
     q, sb = _quantize(x_flat, hadamard_matrix, "mxfp4", None, swizzled=False)
     # abs_max never clips, so the mask (one bit per element, [rows, cols/8]) is all ones
     mask = torch.full((x_flat.shape[0], x_flat.shape[1] // 8 if return_mask else 0), 0xFF, dtype=torch.uint8,
@@ -80,7 +114,7 @@ def fused_quantize_mx_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, fo
     return q, s, (m if return_mask else None)
 
 
-@torch.library.custom_op("fpq_b200::fused_quantize_nv_op", mutates_args=())
+@torch.library.custom_op(f"{NAMESPACE}::fused_quantize_nv_op", mutates_args=())
 def fused_quantize_nv_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor,
                          global_scale: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     q, sb = _quantize(x_flat, hadamard_matrix, "nvfp4", global_scale, swizzled=False)
@@ -97,17 +131,23 @@ def _(x_flat, hadamard_matrix, global_scale):
 
 @torch.library.custom_op("fpq_b200::fused_quantize_blocked_op", mutates_args=())
 def fused_quantize_blocked_op(x_flat: torch.Tensor, hadamard_matrix: torch.Tensor, global_scale: torch.Tensor,
-                              nvfp4: bool, rotation: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+                              nvfp4: bool, rotation: int = 0, quest: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Fast path: packed codes + scale bytes already in the swizzled layout (uint8).
     `rotation`: 0 = inspect the matrix, 1 = Hadamard butterfly, 2 = identity, 3 = dense product
-    (callers that classified the matrix once pass the verdict and skip the inspection)."""
+    (callers that classified the matrix once pass the verdict and skip the inspection).
+    `quest`: MXFP4 with the QuEST scale rule instead of the group maximum."""
+    if quest:
+        if nvfp4:
+            raise ValueError("NVFP4 can only be used with abs_max method")
+        q, sb, _ = _quantize_quest(x_flat, hadamard_matrix, swizzled=True, return_mask=False, rotation=rotation)
+        return q, sb
     q, sb = _quantize(x_flat, hadamard_matrix, "nvfp4" if nvfp4 else "mxfp4", global_scale if nvfp4 else None,
                       swizzled=True, rotation=rotation)
     return q, sb
 
 
 @fused_quantize_blocked_op.register_fake
-def _(x_flat, hadamard_matrix, global_scale, nvfp4, rotation=0):
+def _(x_flat, hadamard_matrix, global_scale, nvfp4, rotation=0, quest=False):
     rows, cols = x_flat.size(0), x_flat.size(1) // (16 if nvfp4 else 32)
     pr, pc = _padded(rows, cols)
     q = torch.empty(rows, x_flat.size(1) // 2, dtype=torch.uint8, device=x_flat.device)
@@ -115,25 +155,37 @@ def _(x_flat, hadamard_matrix, global_scale, nvfp4, rotation=0):
 
 
 # --------------------------------------------------------------------------- matmul
+@torch.library.custom_op("fpq_b200::swizzle_scales_op", mutates_args=())
+def swizzle_scales_op(rowmajor: torch.Tensor) -> torch.Tensor:
+    """uint8 [rows, sf_cols] row-major -> the padded 128x4-tile layout, as a traceable op."""
+    return ops.swizzle_scales(rowmajor)
+
+
+@swizzle_scales_op.register_fake
+def _(rowmajor):
+    pr, pc = _padded(rowmajor.size(0), rowmajor.size(1))
+    return torch.empty(pr, pc, dtype=torch.uint8, device=rowmajor.device)
+
+
 def to_blocked(x: torch.Tensor) -> torch.Tensor:
     """Row-major scale matrix -> 128x4-tile swizzled layout (flat, like the reference helper)."""
     return ops.swizzle_scales(x.view(torch.uint8) if x.dtype != torch.uint8 else x).flatten()
 
 
-def _matmul(x, w, xs_blocked, ws_blocked, alpha, fmt):
+def _matmul(x, w, xs_blocked, ws_blocked, alpha, fmt, bias=None):
     lead = x.shape[:-1]
-    y = ops.gemm_fp4(x.reshape(-1, x.shape[-1]), w, xs_blocked, ws_blocked, alpha, fmt)
+    y = ops.gemm_fp4(x.reshape(-1, x.shape[-1]), w, xs_blocked, ws_blocked, alpha, fmt, bias=bias)
     return y.view(*lead, w.shape[0])
 
 
-@torch.library.custom_op("fpq_b200::matmul_mxf4_bf16_tn_op", mutates_args=())
+@torch.library.custom_op(f"{NAMESPACE}::matmul_mxf4_bf16_tn_op", mutates_args=())
 def matmul_mxf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
                            alpha: torch.Tensor) -> torch.Tensor:
     return _matmul(x, w, ops.swizzle_scales(xs.view(torch.uint8)), ops.swizzle_scales(ws.view(torch.uint8)),
                    alpha, "mxfp4")
 
 
-@torch.library.custom_op("fpq_b200::matmul_nvf4_bf16_tn_op", mutates_args=())
+@torch.library.custom_op(f"{NAMESPACE}::matmul_nvf4_bf16_tn_op", mutates_args=())
 def matmul_nvf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
                            alpha: torch.Tensor) -> torch.Tensor:
     return _matmul(x, w, ops.swizzle_scales(xs.view(torch.uint8)), ops.swizzle_scales(ws.view(torch.uint8)),
@@ -142,8 +194,10 @@ def matmul_nvf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, w
 
 @torch.library.custom_op("fpq_b200::matmul_fp4_bf16_tn_blocked_op", mutates_args=())
 def matmul_fp4_bf16_tn_blocked_op(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tensor,
-                                  ws_blocked: torch.Tensor, alpha: torch.Tensor, nvfp4: bool) -> torch.Tensor:
-    return _matmul(x, w, xs_blocked, ws_blocked, alpha, "nvfp4" if nvfp4 else "mxfp4")
+                                  ws_blocked: torch.Tensor, alpha: torch.Tensor, nvfp4: bool,
+                                  bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bias (optional, bf16 [N]) is added to the fp32 accumulator in the kernel's epilogue."""
+    return _matmul(x, w, xs_blocked, ws_blocked, alpha, "nvfp4" if nvfp4 else "mxfp4", bias)
 
 
 def _fake_mm(x, w, *rest):
@@ -152,4 +206,4 @@ def _fake_mm(x, w, *rest):
 
 matmul_mxf4_bf16_tn_op.register_fake(lambda x, w, xs, ws, alpha: _fake_mm(x, w))
 matmul_nvf4_bf16_tn_op.register_fake(lambda x, w, xs, ws, alpha: _fake_mm(x, w))
-matmul_fp4_bf16_tn_blocked_op.register_fake(lambda x, w, xs, ws, alpha, nvfp4: _fake_mm(x, w))
+matmul_fp4_bf16_tn_blocked_op.register_fake(lambda x, w, xs, ws, alpha, nvfp4, bias=None: _fake_mm(x, w))

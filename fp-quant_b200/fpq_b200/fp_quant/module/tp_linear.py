@@ -24,9 +24,16 @@ from ... import dist as fdist
 from ... import ops
 from ..utils.config import FPQuantDtype
 from .linear import FPQuantLinear
-from .linear_fns import forward_gemm_blocked, forward_quantize_blocked
+from .linear_fns import forward_gemm_blocked, forward_quantize_blocked, gemm_alpha
 
 _SCALE_GROUP = {FPQuantDtype.MXFP4: 32, FPQuantDtype.NVFP4: 16}
+BARRIER_TIMEOUT_MS = 10_000
+
+
+def fused_path_allowed(out_features: int, world_size: int) -> bool:
+    """True when every rank's slice of `out_features` is at least 256 rows (what the epilogue-push kernel
+    needs).  Depends on nothing rank-local, so all ranks agree."""
+    return min(hi - lo for lo, hi in fdist.all_bounds(out_features, world_size, 128)) >= 256
 
 
 class ColumnParallelFPQuantLinear(nn.Module):
@@ -46,6 +53,10 @@ class ColumnParallelFPQuantLinear(nn.Module):
         self.rank, self.world_size = fdist.world(process_group)
         self.in_features, self.out_features = full.in_features, full.out_features
         self.lo, self.hi = fdist.shard_bounds(self.out_features, self.world_size, self.rank, multiple=128)
+        # Shares differ by one 128-row unit, so "my slice is wide enough for the large-M kernel" is not the same
+        # on every rank.  The fused path is a collective (symmetric-memory barriers on all ranks): it is taken
+        # only when EVERY rank's slice qualifies, a decision all ranks reach identically.
+        self.fused_ok = fused_path_allowed(self.out_features, self.world_size)
         g = _SCALE_GROUP[cfg.forward_dtype]
         self.register_buffer("qweight", full.qweight[self.lo:self.hi].contiguous())
         rowmajor = full.scales.view(torch.uint8)[self.lo:self.hi, : self.in_features // g].contiguous()
@@ -63,12 +74,12 @@ class ColumnParallelFPQuantLinear(nn.Module):
         x_flat = x.contiguous().flatten(end_dim=-2)
         m = x_flat.shape[0]
         n_loc = self.hi - self.lo
-        if self.fused and self.world_size > 1 and m > 128 and n_loc >= 256:
+        if self.fused and self.world_size > 1 and m > 128 and self.fused_ok:
             return self._forward_fused(x_flat, m).unflatten(dim=0, sizes=x.shape[:-1])
         if n_loc > 0:
             x_q, x_scales = forward_quantize_blocked(x_flat, self.forward_hadamard_matrix, self.act_global_scale,
                                                      cfg.forward_dtype, cfg.forward_method)
-            alpha = 1.0 / (self.weight_global_scale.float() * self.act_global_scale.float())
+            alpha = gemm_alpha(self.weight_global_scale, self.act_global_scale)
             y = forward_gemm_blocked(x_q, self.qweight, x_scales, self.scales_blocked, alpha, cfg.forward_dtype)
             if self.bias is not None:
                 y = y + self.bias
@@ -93,15 +104,16 @@ class ColumnParallelFPQuantLinear(nn.Module):
         buf, hdl = self._symmetric_buffer(m, x_flat.device)
         x_q, x_scales = forward_quantize_blocked(x_flat, self.forward_hadamard_matrix, self.act_global_scale,
                                                  cfg.forward_dtype, cfg.forward_method)
-        alpha = 1.0 / (self.weight_global_scale.float() * self.act_global_scale.float())
-        hdl.barrier(channel=0)           # every rank is done with the previous contents of all buffers
+        alpha = gemm_alpha(self.weight_global_scale, self.act_global_scale)
+        # bounded: a rank that never arrives ends the wait with an error instead of a stuck kernel
+        hdl.barrier(channel=0, timeout_ms=BARRIER_TIMEOUT_MS)    # every rank is done with the previous contents
         # the tensor may sit at an offset inside the symmetric allocation; the offset is the same on every rank
         off = buf.data_ptr() - int(hdl.buffer_ptrs[self.rank])
         if off < 0 or off + buf.numel() * 2 > int(hdl.buffer_size):
             raise RuntimeError("symmetric buffer does not contain the output tensor")
         peers = [int(hdl.buffer_ptrs[r]) + off for r in range(self.world_size) if r != self.rank]
         ops.gemm_fp4_push(x_q, self.qweight, x_scales, self.scales_blocked, alpha, fmt, buf, peers, self.lo, None)
-        hdl.barrier(channel=1)           # every rank's slice has landed everywhere
+        hdl.barrier(channel=1, timeout_ms=BARRIER_TIMEOUT_MS)    # every rank's slice has landed everywhere
         return buf.clone() if self.bias_full is None else buf + self.bias_full
 
     def _gather_columns(self, y: torch.Tensor, m: int) -> torch.Tensor:

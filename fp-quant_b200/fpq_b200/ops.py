@@ -119,7 +119,7 @@ def quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0, global_scale: O
     if scale_bytes:
         if swizzled:
             pr, pc = padded_scale_shape(rows, sf_cols)
-            alloc = torch.zeros if (pr != rows or pc != sf_cols) else torch.empty
+            alloc = torch.zeros if pc != sf_cols else torch.empty       # pad rows are zeroed by the kernel
             sb = alloc(pr, pc, dtype=torch.uint8, device=dev)
         else:
             sb = torch.empty(rows, sf_cols, dtype=torch.uint8, device=dev)
@@ -133,6 +133,36 @@ def quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0, global_scale: O
                _ptr(global_scale) if fmt == "nvfp4" else None, _ptr(q), _ptr(sb),
                C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _ptr(sf), _stream(x))
     return q, sb, sf
+
+
+def quantize_quest(x: torch.Tensor, hadamard_group: int = 0, swizzled: bool = False, return_mask: bool = False):
+    """MXFP4 with the QuEST scale rule: (codes u8 [rows, cols/2], E8M0 scale bytes, clip mask u8 [rows, cols/8] | None)."""
+    x, rows, cols = _2d(x)
+    sf_cols = cols // 32
+    dev = x.device
+    q = torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev)
+    if swizzled:
+        pr, pc = padded_scale_shape(rows, sf_cols)
+        sb = (torch.zeros if pc != sf_cols else torch.empty)(pr, pc, dtype=torch.uint8, device=dev)
+    else:
+        sb = torch.empty(rows, sf_cols, dtype=torch.uint8, device=dev)
+    mask = torch.empty(rows, cols // 8, dtype=torch.uint8, device=dev) if return_mask else None
+    with _guard(dev):
+        C.call("fpq_quantize_quest", x.data_ptr(), _dt(x), rows, cols, hadamard_group, q.data_ptr(), sb.data_ptr(),
+               C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _ptr(mask), _stream(x))
+    return q, sb, mask
+
+
+def fake_quantize_quest(x: torch.Tensor, hadamard_group: int = 0, return_mask: bool = True):
+    """Quantise-dequantise with the QuEST scale rule: (y like x, bool clip mask like x | None)."""
+    shape = x.shape
+    x, rows, cols = _2d(x)
+    y = torch.empty_like(x)
+    mask = torch.empty(rows, cols, dtype=torch.bool, device=x.device) if return_mask else None
+    with _guard(x.device):
+        C.call("fpq_fake_quantize_quest", x.data_ptr(), _dt(x), rows, cols, hadamard_group, y.data_ptr(), _ptr(mask),
+               _stream(x))
+    return y.view(shape), (mask.view(shape) if mask is not None else None)
 
 
 def mse_scales(x: torch.Tensor, fmt: str, global_scale: Optional[torch.Tensor] = None, iters: int = 100,

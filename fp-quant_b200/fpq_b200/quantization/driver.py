@@ -13,8 +13,8 @@ Differences in structure (same mathematics):
   * when torch.distributed is initialised with several ranks (one per GPU, every rank holding the same
     model), the calibration sequences are split over the ranks, the Hessians are all-reduced, the
     Cholesky-inverse chains of a block's distinct Hessians run on different ranks and their factors are
-    broadcast, and the rows of every weight are split for the column loop and gathered.  Every rank
-    returns the full result.
+    broadcast, and every linear is quantised, whole, by one rank (`plan_ranks`) that broadcasts the
+    result.  Every rank returns the full result.
 """
 from __future__ import annotations
 
@@ -25,6 +25,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .. import _cabi as C
 from .. import dist as fdist
 from .. import ops
 from ..transforms.transforms import build_transform, get_transform_matrix
@@ -58,6 +59,7 @@ class _Phases:
 
 
 last_phases: Optional[_Phases] = None     # phases of the most recent gptq_quantization call
+last_relative_mse: Dict[str, float] = {}  # "model.layers.<i>.<linear>" -> relative MSE of the most recent call (rank 0 prints them)
 
 
 class _HessianSink:
@@ -333,6 +335,8 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
     wkw = _quantizer_kwargs(args, "w")
     global last_phases
     ph = last_phases = _Phases()
+    last_relative_mse.clear()
+    pending_mse: Dict[str, torch.Tensor] = {}
     copies = _HostCopies(device)
     ph.mark("start")
     rank, world_size = fdist.world()
@@ -362,12 +366,7 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                 leaders[grp] = name
                 layer.group_state["sink"] = _HessianSink(handles[name])
         if getattr(args, "fuse_global_scale", False) and args.scale_precision == ScalePrecision.E4M3:
-            for pat in (r"(q|k|v)_proj$", r"(gate|up)_proj$"):       # gptq.py:367-383
-                names = [n for n in handles if re.search(pat, n)]
-                if names:
-                    fused = torch.stack([handles[n].quantizer.global_scale.to(device) for n in names]).min(dim=0).values
-                    for n in names:
-                        handles[n].quantizer.global_scale = fused.clone()
+            _fuse_weight_global_scales({n: h.quantizer for n, h in handles.items()}, device)
 
         ph.mark("setup")
         _run_block(block, input_args, input_kwargs, device, args, keep_outputs=False, offload_device=offload)   # Hessians
@@ -474,8 +473,7 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             if world_size > 1:
                 for t in (wq, codes, scales, rel):
                     torch.distributed.broadcast(t, src=layer_owner[name])
-            if rank == 0:
-                print(f"[{name:16}]: Relative MSE error: {rel.item():.2e}")
+            pending_mse[f"model.layers.{block_idx}.{name}"] = rel
             handle.layer.weight.data = wq
             if args.export_quantized_model:
                 wgs = handle.quantizer.global_scale.to(device)
@@ -487,6 +485,14 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                 else:
                     quantized[key] = _export_entry(copies, args, orig_dtype, device, wgs, ags, dqweight=wq)
         results.clear()
+        # one host read per block for the log line of every layer (gptq.py:414-415), not one per layer
+        names = [k for k in pending_mse if k not in last_relative_mse]
+        if names:
+            values = torch.cat([pending_mse[k] for k in names]).tolist()
+            for k, v in zip(names, values):
+                last_relative_mse[k] = v
+                if rank == 0:
+                    print(f"[{k.split('.', 3)[3]:16}]: Relative MSE error: {v:.2e}")
 
         ph.mark("column_loops")
         _release_group_states(layers)
@@ -500,36 +506,94 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
     return quantized, non_quantized
 
 
+def _fuse_weight_global_scales(quantizers: Dict[str, Quantizer], device) -> None:
+    """q/k/v and gate/up share the smallest of their weight tensor scales (gptq.py:367-383, rtn.py:134-150)."""
+    for pat in (r"(q|k|v)_proj$", r"(gate|up)_proj$"):
+        names = [n for n in quantizers if re.search(pat, n)]
+        if names:
+            fused = torch.stack([quantizers[n].global_scale.to(device) for n in names]).min(dim=0).values
+            for n in names:
+                quantizers[n].global_scale = fused.clone()
+
+
 @torch.no_grad()
 def rtn_quantization(model, calibration_data: List[torch.Tensor], args, device) -> Tuple[dict, dict]:
-    """Round-to-nearest over all blocks (rtn.py:17-237): rotate each weight, quantise it with the
-    fused kernel, keep the dequantised weight in the model and the packed form in the export dict."""
+    """Round-to-nearest over all blocks (rtn.py:17-237).  Per block: fix (and optionally fuse) the weight
+    tensor scales, quantise every rotated weight with its quantiser (min-max or MSE observer), and -- when
+    the scales are E4M3, i.e. the format has an activation tensor scale that must be settled on data
+    (rtn.py:26) -- run the calibration sequences through the block once so that the activation quantisers
+    see every input (rtn.py:152-156), freeze them, export, and run the sequences again to produce the next
+    block's inputs (rtn.py:216-228).
+
+    The reference's first pass computes with the fake-quantised rotated weight rebuilt on the fly and
+    `fix_parametrization` stores that same weight afterwards (qlinear.py:36-47, :52-76); here the weight is
+    quantised once, before the first pass, which feeds both passes the identical matrix."""
     print("RTN quantization...")
     orig_dtype = model.config.torch_dtype if args.dtype == "auto" else args.dtype
+    offload = "cpu" if args.cpu_offload_activations else device
+    need_calibration = args.scale_precision == ScalePrecision.E4M3
     quantized, non_quantized = {}, {}
     copies = _HostCopies(device)
     wkw = _quantizer_kwargs(args, "w")
-    fmt = {"nvfp": "nvfp4", "mxfp": "mxfp4"}[str(args.format)]
+    input_args = input_kwargs = None
+    if need_calibration:
+        input_args, input_kwargs = _collect_block_inputs(model, calibration_data, args, device)
     for block_idx, block in enumerate(model.model.layers):
+        print(f"Processing block {block_idx}...")
         block.to(device=device, dtype=orig_dtype).requires_grad_(False)
         layers = _wrap_block(block, args, device)
+        rotated = {name: layer.transform(layer.weight, inv_t=True) for name, layer in layers.items()}
+        wq: Dict[str, Quantizer] = {}
+        if wkw:
+            wq = {name: Quantizer(**wkw) for name in layers}
+            if need_calibration:                                   # rtn.py:116-131: set and freeze the tensor scales
+                for name, q in wq.items():
+                    q.get_quantization_params(rotated[name].float())
+                    q._track_global_scale = False
+                if getattr(args, "fuse_global_scale", False):
+                    _fuse_weight_global_scales(wq, device)
+        exports = {}
         for name, layer in layers.items():
-            q = Quantizer(**wkw)
-            w = layer.transform(layer.weight, inv_t=True)
-            gs = None
-            if fmt == "nvfp4":
-                q.get_quantization_params(w.float())               # sets the tensor scale
-                gs = q.global_scale
-            codes, sbytes, _ = ops.quantize(w, fmt, 0, gs)
-            wq = ops.fake_quantize(w, fmt, 0, gs)
-            layer.weight.data = wq
+            w = rotated[name]
+            if name in wq:
+                q = wq[name]
+                group = q.group_size
+                scales, _ = q.get_quantization_params(w.float())             # honours the observer (rtn.py:175)
+                scales = scales.float().contiguous()
+                codes = ops.apply_scales(w.float(), scales, group, C.OUT_CODES)
+                layer.weight.data = ops.apply_scales(w.float(), scales, group, C.OUT_DEQUANT).to(w.dtype)
+                exports[name] = (codes, scales, q.global_scale.to(device))
+            else:
+                layer.weight.data = w
+            layer._rotated = None
             layer._train_mode = False
-            if args.export_quantized_model:
+        del rotated
+
+        if need_calibration:
+            _run_block(block, input_args, input_kwargs, device, args, keep_outputs=False, offload_device=offload)
+            _release_group_states(layers)
+        for layer in layers.values():
+            if layer.act_quantizer is not None:
+                layer.act_quantizer._track_global_scale = False
+
+        if args.export_quantized_model:
+            for name, layer in layers.items():
+                if name not in exports:
+                    continue
+                codes, scales, wgs = exports[name]
                 ags = layer.act_quantizer.global_scale if layer.act_quantizer is not None else torch.ones(1)
                 key = f"model.layers.{block_idx}.{name}"
                 if args.export_quantized_model == "realquant":
-                    quantized[key] = _export_entry(copies, args, orig_dtype, device, q.global_scale, ags, qweight=codes, scales=sbytes)
+                    quantized[key] = _export_entry(copies, args, orig_dtype, device, wgs, ags, qweight=codes,
+                                                   scales=cast_scales_to_eXmY(scales * wgs, args.scale_precision))
                 else:
-                    quantized[key] = _export_entry(copies, args, orig_dtype, device, q.global_scale, ags, dqweight=wq)
+                    quantized[key] = _export_entry(copies, args, orig_dtype, device, wgs, ags, dqweight=layer.weight.data)
+        exports.clear()
+
+        if need_calibration:
+            _run_block(block, input_args, input_kwargs, device, args, keep_outputs=True, offload_device=offload)
+            _release_group_states(layers)
+        if getattr(args, "cpu_offload_modules", False):
+            block.cpu()
     copies.finish()
     return quantized, non_quantized

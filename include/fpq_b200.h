@@ -96,8 +96,9 @@ int fpq_global_scale_update(const uint32_t* absmax_bits, float* global_scale, in
  *   hadamard_group 0 (none), 16, 32, 64 or 128
  *   global_scale device fp32[1], NVFP4 only (NULL for MXFP4)
  *   codes        uint8 [rows, cols/2] or NULL
- *   scale_bytes  uint8 in `scale_layout` or NULL; swizzled buffers must be zero-filled by
- *                the caller when rows % 128 != 0 or (cols/g) % 4 != 0
+ *   scale_bytes  uint8 in `scale_layout` or NULL; in the swizzled layout the kernel also zeroes the
+ *                bytes of the pad rows (rows .. next multiple of 128); the caller zero-fills the
+ *                buffer only when (cols/g) % 4 != 0 (pad columns)
  *   scales_f32   fp32 [rows, cols/g] (the divisor actually used) or NULL
  */
 int fpq_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
@@ -114,6 +115,29 @@ int fpq_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadam
 int fpq_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,
                       int format, const float* global_scale, void* y, int ste,
                       fpq_stream_t stream);
+
+/*
+ * The forward_method = "quest" variant of the MXFP4 quantise (the default method of FPQuantConfig,
+ * inference_lib/src/fp_quant/utils/config.py:20; qutlass.fusedQuantizeMx(method="quest"),
+ * inference_lib/src/fp_quant/module/qutlass_ops.py:36-71; its only in-tree statement is the Triton kernel
+ * inference_lib/src/fp_quant/module/triton/mxfp4.py:51-59, :105-110).  Per group of 32 rotated values:
+ * std = sqrt(mean(x^2) - mean(x)^2), scale = (2.92247856 / 6) * std + 1e-8, divisor 2^floor(log2(scale)),
+ * stored E8M0 byte = that exponent + 127 (the tensor scale of this method is 1, linear.py:190-196); codes are
+ * E2M1 round-to-nearest-even of x / divisor, saturating at +-6.  clip_mask (optional): uint8 [rows, cols/8],
+ * bit i of byte b set when element 8 b + i was inside the grid's range (|x / divisor| < 6), the packing
+ * `_unpack_mask` reads (linear_fns.py:66-76).  Other arguments as for fpq_quantize.
+ */
+int fpq_quantize_quest(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group, uint8_t* codes,
+                       uint8_t* scale_bytes, int scale_layout, uint8_t* clip_mask, fpq_stream_t stream);
+
+/*
+ * Pseudo-quantisation with the QuEST scale rule: y = grid(code) * divisor in the dtype of x, clip_mask
+ * (optional) one byte per element, 1 = inside the range.  Replaces mxfp4_forward_kernel with quest=True
+ * (inference_lib/src/fp_quant/module/triton/mxfp4.py:19-119; pseudoquant_linear_fns.py:19-34) up to its
+ * rounding of exact ties (the Triton kernel rounds them toward zero, this rounds to even).
+ */
+int fpq_fake_quantize_quest(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group, void* y,
+                            uint8_t* clip_mask, fpq_stream_t stream);
 
 /*
  * Quantise with scales given by the caller: Quantizer.quantize / dequantize / __call__
@@ -194,6 +218,8 @@ int fpq_sgemm(const float* A, int64_t lda, const float* B, int64_t ldb, int b_tr
  * mirrored, as accumulate_hessian does (src/quantization/accumulate_hessian.py:20-148); alpha and beta
  * carry the running-mean factors of GPTQ.update (src/quantization/gptq.py:94-102), so the input is
  * not rescaled.  xa, xb: bf16 [tokens, d] row-major, d % 8 == 0.  error_flag as in fpq_gemm_fp4.
+ * Tokens are processed in slabs of 4096 (one launch each) because the tensor core's accumulator truncates:
+ * 4.5e-6 relative Frobenius error against fp64 for any number of tokens.
  */
 int fpq_hessian_accumulate(float* H, int64_t d, const void* xa_bf16, const void* xb_bf16, int64_t tokens,
                            float alpha, float beta, int32_t* error_flag, fpq_stream_t stream);

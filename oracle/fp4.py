@@ -161,6 +161,52 @@ def mxfp4_scales_from_raw(s0: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]
     return (e + 127).to(torch.uint8), s
 
 
+QUEST_GAUSSIAN_SCALE = 2.92247856 / 6.0      # inference_lib/src/fp_quant/module/pseudoquant_linear_fns.py:20
+
+
+def quest_scales(y: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-32 scales of the "quest" forward method, the default of FPQuantConfig
+    (inference_lib/src/fp_quant/utils/config.py:20).  Its only statement in the reference tree is the Triton
+    pseudo-quantisation kernel (inference_lib/src/fp_quant/module/triton/mxfp4.py:51-59):
+        std = sqrt(mean(x^2) - mean(x)^2); scale = c * std + 1e-8; divisor = 2^floor(log2(scale))
+    with c = 2.92247856 / 6 as an fp32 constant.  Triton does not define the order of its sums; it is fixed
+    here (and in the CUDA kernel) as: even and odd elements of the group accumulated separately in index
+    order, then even + odd; squares are rounded products added to their accumulator (no fused multiply-add);
+    a variance that rounds below zero counts as zero; floor(log2) is the exponent field (scale >= 1e-8 is a
+    normal number).  Returns (stored E8M0 byte = exponent + 127, fp32 divisors)."""
+    g = y.to(torch.float32).reshape(*y.shape[:-1], y.shape[-1] // MXFP_GROUP, MXFP_GROUP // 2, 2)
+    acc = g[..., 0, :].clone()
+    acc2 = g[..., 0, :] * g[..., 0, :]
+    for j in range(1, MXFP_GROUP // 2):
+        acc = acc + g[..., j, :]
+        acc2 = acc2 + g[..., j, :] * g[..., j, :]
+    mean = (acc[..., 0] + acc[..., 1]) * 0.03125
+    mean_sq = (acc2[..., 0] + acc2[..., 1]) * 0.03125
+    var = (mean_sq - mean * mean).clamp(min=0.0)
+    scale = torch.tensor(QUEST_GAUSSIAN_SCALE, dtype=torch.float32) * var.sqrt() + torch.tensor(1e-8, dtype=torch.float32)
+    byte = (scale.view(torch.int32) >> 23) & 0xFF
+    divisor = (byte << 23).to(torch.int32).view(torch.float32)
+    return byte.to(torch.uint8), divisor
+
+
+def quest_quantize(y: torch.Tensor):
+    """Rotated fp32 tensor -> (packed codes, E8M0 scale bytes, fp32 divisors, clip mask bool): E2M1
+    round-to-nearest-even of y / divisor saturating at +-6, zeros packed as 0x8 like every code in this
+    package; mask = |y / divisor| < 6 (triton/mxfp4.py:105-110)."""
+    sb, s = quest_scales(y)
+    codes = e2m1_codes(y, s, MXFP_GROUP)
+    v = y.to(torch.float32).reshape(*y.shape[:-1], -1, MXFP_GROUP) / s.unsqueeze(-1)
+    return pack_codes(codes), sb, s, (v.abs() < E2M1_MAX).reshape(y.shape)
+
+
+def pack_clip_mask(mask: torch.Tensor) -> torch.Tensor:
+    """bool [.., K] -> uint8 [.., K/8], bit i of byte b = element 8 b + i: the layout `_unpack_mask` reads
+    (inference_lib/src/fp_quant/module/linear_fns.py:66-76)."""
+    m = mask.reshape(*mask.shape[:-1], mask.shape[-1] // 8, 8).to(torch.int32)
+    w = torch.tensor([1, 2, 4, 8, 16, 32, 64, 128], dtype=torch.int32)
+    return (m * w).sum(dim=-1).to(torch.uint8)
+
+
 def mse_observer_raw_scales(y: torch.Tensor, group: int, iters: int = 100, max_shrink: float = 0.80,
                             norm: float = 2.4) -> torch.Tensor:
     """The MSE observer's search (quantizer.py:117-134): candidates fl(f_i * s0) with

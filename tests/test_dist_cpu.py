@@ -81,3 +81,21 @@ def test_shard_bounds_cover_everything():
                 assert b[0][0] == 0 and b[-1][1] == n
                 assert all(b[i][1] == b[i + 1][0] for i in range(ws - 1))
                 assert all((lo % mult == 0) for lo, hi in b if lo < n)
+
+
+@pytest.mark.parametrize("out_features,world_size,expect", [(1536, 8, False), (384, 2, False), (640, 4, False),
+                                                             (2048, 8, True), (17408, 8, True), (512, 2, True)])
+def test_fused_tensor_parallel_path_is_chosen_identically_on_all_ranks(out_features, world_size, expect):
+    """The epilogue-push path of the column-parallel linear is a collective: either every rank takes it or none.
+    Shares of uneven splits differ by 128 rows (1536 over 8 ranks: 256 x 4 + 128 x 4), so a rank-local test
+    ("my slice has >= 256 rows") would split the ranks; the decision must come out of the split alone."""
+    for p in (ROOT, os.path.join(ROOT, "fp-quant_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from fpq_b200 import dist as fdist
+    from fpq_b200.fp_quant.module.tp_linear import fused_path_allowed
+
+    verdict = fused_path_allowed(out_features, world_size)
+    assert verdict == expect
+    local = [hi - lo >= 256 for lo, hi in fdist.all_bounds(out_features, world_size, 128)]
+    assert verdict == all(local)          # and it is the conjunction of what each rank would have said

@@ -48,6 +48,32 @@ def test_gemm_random_codes_and_scales(cuda_device, fmt, shape):
     _check(got.cpu(), want)
 
 
+# The W4A4 linear shapes of a Qwen3-8B block (K, N) at the token counts where the entry point leaves the
+# large-M kernel: M = 1 and 16 take the swap-AB split-K kernel (the cluster size and the K depth per CTA
+# change with K = 12288), M = 128 the single-CTA or the CTA-pair kernel depending on N.
+QWEN3_8B_LINEARS = [(4096, 4096), (4096, 12288), (12288, 4096), (4096, 1024)]
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("kn", QWEN3_8B_LINEARS)
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_gemm_small_m_at_model_shapes(cuda_device, fmt, kn, M):
+    from fpq_b200 import ops
+
+    K, N = kn
+    a, b, sa, sb = _random_operands(M, N, K, fmt, seed=M + 3 * N + 5 * K)
+    d = cuda_device
+    got = ops.gemm_fp4(a.to(d), b.to(d), ops.swizzle_scales(sa.to(d)), ops.swizzle_scales(sb.to(d)),
+                       torch.tensor([0.25], device=d), fmt)
+    ops.check_device_errors(d)
+    assert got.shape == (M, N)
+    # every row, a sample of the output features (first and last tile included)
+    gen = torch.Generator().manual_seed(N + K)
+    cols = torch.cat([torch.arange(0, 64), torch.arange(N - 64, N), torch.randperm(N, generator=gen)[:256]]).unique()
+    want = fp4.fp4_matmul(a, b[cols], sa, sb[cols], 0.25, fmt)
+    _check(got[:, cols.to(d)].cpu(), want)
+
+
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 def test_gemm_with_bias(cuda_device, fmt):
     from fpq_b200 import ops

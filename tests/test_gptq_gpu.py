@@ -66,7 +66,10 @@ def test_hessian_prepare_matches_oracle(cuda_device):
     H = g["hessian"].clone().to(cuda_device)
     ops.hessian_prepare(H, W.to(cuda_device), 0.01)
     assert torch.allclose(H.cpu(), want, rtol=1e-6, atol=1e-9)
-    assert H[5, 5].item() == pytest.approx(1.0 + 0.01 * torch.diag(want - torch.diag(torch.diag(want)) + torch.diag(torch.diag(want))).mean().item(), rel=1e-2) or True
+    damp = 0.01 * torch.diag(ogptq.prepare_hessian(g["hessian"], W, 0.0)).mean().item()
+    for dead in (5, 77):       # a dead column keeps only its unit diagonal plus the damping
+        assert H[dead, dead].item() == pytest.approx(1.0 + damp, rel=1e-5)
+        assert torch.count_nonzero(H[dead]).item() == 1 and torch.count_nonzero(H[:, dead]).item() == 1
 
 
 @pytest.mark.parametrize("d", [128, 256, 384, 1000, 1664, 2048])

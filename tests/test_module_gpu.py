@@ -107,7 +107,10 @@ def test_fpquant_linear_forward(cuda_device, dtype_name, hgroup, bias):
     assert torch.equal(layer.qweight.cpu(), wq)
     g = 16 if dtype_name == "nvfp4" else 32
     assert torch.equal(layer.scales.view(torch.uint8).cpu()[:N, : K // g], ws)
-    want = fp4.fp4_matmul(xq, wq, xs, ws, 1.0 / 9.0, dtype_name).float()
+    # alpha with the reference's rounding order: 1 / (3 * 3) in the bf16 of the buffers, then fp32
+    alpha = float((1.0 / (torch.tensor([3.0]).bfloat16() * torch.tensor([3.0]).bfloat16())).float())
+    assert alpha == 0.111328125 and float(layer._gemm_alpha()) == alpha
+    want = fp4.fp4_matmul(xq, wq, xs, ws, alpha, dtype_name).float()
     if bias:
         want = (want.bfloat16() + b).float()
     got = y.cpu().float().view(-1, N)
@@ -176,3 +179,104 @@ def test_pseudoquant_linear(cuda_device):
     y = layer(x.to(cuda_device))
     exact = x.float() @ w.float().t()
     assert (y.cpu().float() - exact).norm() / exact.norm() < 0.25
+
+
+@pytest.mark.parametrize("bias", [False, True])
+def test_fpquant_linear_with_the_default_quest_method(cuda_device, bias):
+    """FPQuantConfig's defaults (MXFP4, forward_method = "quest", Hadamard 32) with a bf16 backward: the
+    configuration a user gets without arguments (inference_lib/src/fp_quant/utils/config.py:17-27).  Weight
+    codes and scale bytes bit-exact against the oracle's QuEST rule, tensor scales 1.0 (linear.py:190-196),
+    output within bf16 rounding of the fp64 product of the decoded operands."""
+    from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype, FPQuantLinear
+
+    K, N = 512, 384
+    cfg = FPQuantConfig(backward_dtype=FPQuantDtype.BF16)
+    assert cfg.forward_method == "quest" and cfg.forward_dtype == FPQuantDtype.MXFP4 and cfg.hadamard_group_size == 32
+    layer = FPQuantLinear(K, N, cfg, bias=bias, device=cuda_device, dtype=torch.bfloat16)
+    w = inputs.normal_weight(N, K, seed=3)
+    b = inputs.normal_weight(1, N, seed=8, std=0.1)[0]
+    layer.weight.data.copy_(w)
+    if bias:
+        layer.bias.data.copy_(b)
+    layer.pre_forward()
+    assert float(layer.weight_global_scale) == 1.0 and float(layer.act_global_scale) == 1.0
+    wq, ws, _, _ = fp4.quest_quantize(fp4.fwht_butterfly(w, 32))
+    assert torch.equal(layer.qweight.cpu(), wq)
+    assert torch.equal(layer.scales.view(torch.uint8).cpu()[:N, : K // 32], ws)
+    x = inputs.outlier_activations(2 * 37, K, seed=1).view(2, 37, K)
+    y = layer(x.to(cuda_device))
+    xq, xs, _, _ = fp4.quest_quantize(fp4.fwht_butterfly(x.view(-1, K), 32))
+    want = fp4.fp4_matmul(xq, wq, xs, ws, 1.0, "mxfp4").float()
+    if bias:
+        want = (want.bfloat16() + b).float()
+    got = y.cpu().float().view(-1, N)
+    tol = 2.0 ** -6 * want.abs() + 2.0 ** -9 * want.abs().max()
+    assert not ((got - want).abs() > tol).any()
+    exact = x.view(-1, K).float() @ w.float().t() + (b.float() if bias else 0.0)
+    assert (got - exact).norm() / exact.norm() < 0.3
+
+
+def test_quest_mask_and_pseudoquant_through_the_reference_api(cuda_device):
+    """`forward_quantize(..., "quest")` hands back the packed clip mask when the input requires grad
+    (linear_fns.py:34-40), and `forward_pseudoquantize` returns the element-wise one (pseudoquant_linear_fns.py:
+    19-34); both are the oracle's."""
+    from fpq_b200.fp_quant import FPQuantDtype
+    from fpq_b200.fp_quant.module.linear import get_hadamard_matrix
+    from fpq_b200.fp_quant.module.linear_fns import forward_quantize
+    from fpq_b200.fp_quant.module.pseudoquant_linear_fns import forward_pseudoquantize
+
+    M, K = 70, 256
+    x = inputs.outlier_activations(M, K, seed=5)
+    h = get_hadamard_matrix(64, torch.bfloat16, cuda_device)
+    gs = torch.tensor([1.0], device=cuda_device)
+    want_codes, want_sb, want_s, want_mask = fp4.quest_quantize(fp4.fwht_butterfly(x, 64))
+    q, s, mask = forward_quantize(x.to(cuda_device).requires_grad_(True), h, gs, FPQuantDtype.MXFP4, "quest")
+    assert s.dtype == torch.float8_e8m0fnu and s.shape == (128, 8) and mask.shape == (M, K // 8)
+    assert torch.equal(q.cpu(), want_codes) and torch.equal(s.view(torch.uint8).cpu()[:M], want_sb)
+    assert torch.equal(mask.cpu(), fp4.pack_clip_mask(want_mask))
+    _, _, none = forward_quantize(x.to(cuda_device), h, gs, FPQuantDtype.MXFP4, "quest")
+    assert none is None
+    y, m = forward_pseudoquantize(x.to(cuda_device), h, gs, FPQuantDtype.MXFP4, "quest")
+    assert torch.equal(y.cpu().float(), fp4.dequantize(fp4.unpack_codes(want_codes), want_s, 32).bfloat16().float())
+    assert torch.equal(m.cpu(), want_mask)
+    with pytest.raises(AssertionError):
+        forward_pseudoquantize(x.to(cuda_device), h, gs, FPQuantDtype.NVFP4, "quest")
+
+
+def test_ops_live_in_the_reference_namespace_and_trace_under_torch_compile(cuda_device):
+    """The reference registers its operators as torch custom ops `fp_quant::*` with fake implementations so that
+    torch.compile(fullgraph=True) traces through a quantised layer (README.md:39; qutlass_ops.py:36, :54, :111).
+    Same names here; `torch.library.opcheck` validates schema and fake kernels, and a layer compiled with
+    fullgraph=True (graph capture and fake-tensor propagation; backend aot_eager, so no code generator is
+    involved) returns what the eager layer returns."""
+    from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype, FPQuantLinear
+    from fpq_b200.fp_quant.module import qutlass_ops
+    from fpq_b200.fp_quant.module.linear import get_hadamard_matrix
+
+    assert qutlass_ops.NAMESPACE == "fp_quant"
+    for name in ("fused_quantize_mx_op", "fused_quantize_nv_op", "matmul_mxf4_bf16_tn_op", "matmul_nvf4_bf16_tn_op"):
+        assert hasattr(torch.ops.fp_quant, name), name
+    x = inputs.outlier_activations(70, 256, seed=5).to(cuda_device)
+    h = get_hadamard_matrix(32, torch.bfloat16, cuda_device)
+    gs = torch.tensor([3.0], device=cuda_device)
+    checks = ("test_schema", "test_faketensor", "test_autograd_registration")
+    torch.library.opcheck(torch.ops.fp_quant.fused_quantize_mx_op.default, (x, h, "abs_max", False), test_utils=checks)
+    torch.library.opcheck(torch.ops.fp_quant.fused_quantize_mx_op.default, (x, h, "quest", True), test_utils=checks)
+    torch.library.opcheck(torch.ops.fp_quant.fused_quantize_nv_op.default, (x, h, gs), test_utils=checks)
+    torch.library.opcheck(torch.ops.fpq_b200.fused_quantize_blocked_op.default, (x, h, gs, False, 0, False), test_utils=checks)
+    q, s, _ = torch.ops.fp_quant.fused_quantize_mx_op(x, h, "abs_max", False)
+    wq, ws, _ = torch.ops.fp_quant.fused_quantize_mx_op(inputs.normal_weight(128, 256, seed=3).to(cuda_device), h, "abs_max", False)
+    alpha = torch.tensor([1 / 9.0], device=cuda_device)
+    # (the schema check perturbs its inputs with arithmetic that torch does not implement for float8_e8m0fnu)
+    torch.library.opcheck(torch.ops.fp_quant.matmul_mxf4_bf16_tn_op.default, (q, wq, s, ws, alpha), test_utils=checks[1:])
+
+    for method in ("abs_max", "quest"):
+        cfg = FPQuantConfig(forward_method=method, backward_dtype=FPQuantDtype.BF16)
+        layer = FPQuantLinear(256, 128, cfg, bias=True, device=cuda_device, dtype=torch.bfloat16)
+        layer.weight.data.copy_(inputs.normal_weight(128, 256, seed=3))
+        layer.bias.data.copy_(inputs.normal_weight(1, 128, seed=8, std=0.1)[0])
+        layer.pre_forward()
+        with torch.no_grad():
+            eager = layer(x)
+            compiled = torch.compile(layer, fullgraph=True, backend="aot_eager")(x)
+        assert torch.equal(eager, compiled)

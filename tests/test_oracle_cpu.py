@@ -185,3 +185,53 @@ def test_mse_observer_matches_golden(fmt):
         _, s_minmax = fp4.mxfp4_scales(y)
     assert torch.equal(s, g["scales"])
     assert (s != s_minmax).float().mean().item() > 0.03
+
+
+def test_quest_restatement_matches_the_reference_triton_kernel():
+    """oracle/fp4.py::quest_quantize against the UNMODIFIED Triton kernel of the reference run by Triton's
+    interpreter (tests/golden/quest_triton.npz, made by tests/golden/make_quest_golden.py): the scale rule,
+    the divisor, the clip mask and the rounding must agree on every element except exact ties, which the
+    Triton kernel's strict `>` thresholds send toward zero (inference_lib/src/fp_quant/module/triton/mxfp4.py:
+    70-104) and this package, like the reference's Quantizer, rounds to even."""
+    import numpy as np
+
+    d = np.load(os.path.join(GOLDEN, "quest_triton.npz"))
+    x = torch.from_numpy(d["x"])
+    want, want_mask = torch.from_numpy(d["quest_dequantized"]), torch.from_numpy(d["quest_mask"])
+    codes, sb, s, mask = fp4.quest_quantize(x)
+    got = fp4.dequantize(fp4.unpack_codes(codes), s, 32)
+    assert torch.equal(mask, want_mask)
+    assert torch.equal(sb.to(torch.float32) - 127, torch.log2(s))                  # stored byte = exponent + 127
+    v = (x.reshape(64, -1, 32) / s.unsqueeze(-1)).reshape(x.shape)
+    tie = torch.zeros_like(v, dtype=torch.bool)
+    for t in (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0):
+        tie |= v.abs() == t
+    differ = got != want
+    assert int(tie.sum()) > 100 and not bool((differ & ~tie).any())
+    assert bool((got[differ].abs() > want[differ].abs()).all())                    # on ties the kernel goes down, we go to even
+    # the all-zero group and the constant group (zero variance: divisor 2^floor(log2(1e-8)) = 2^-27)
+    assert float(s[3, 1]) == 2.0 ** -27 and float(s[5, 0]) == 2.0 ** -27
+    assert torch.equal(got[5, :32], torch.full((32,), 6 * 2.0 ** -27))
+    # packed mask layout
+    packed = fp4.pack_clip_mask(mask)
+    for i in range(8):
+        assert torch.equal(((packed >> i) & 1).bool(), mask[:, i::8])
+
+
+def test_abs_max_triton_kernel_agrees_with_the_quantizer_rule_off_ties():
+    """The same golden file holds the Triton kernel's abs_max branch: away from exact ties and all-zero groups
+    (where it divides by zero) it must give what the Quantizer chain gives -- the basis for comparing the
+    pseudo-quantised forward against the Quantizer rather than bit for bit against Triton."""
+    import numpy as np
+
+    d = np.load(os.path.join(GOLDEN, "quest_triton.npz"))
+    x = torch.from_numpy(d["x"])
+    want = torch.from_numpy(d["absmax_dequantized"])
+    codes, _, s = fp4.quantize(x, "mxfp4")
+    got = fp4.dequantize(fp4.unpack_codes(codes), s, 32)
+    v = (x.reshape(64, -1, 32) / s.unsqueeze(-1)).reshape(x.shape)
+    tie = torch.zeros_like(v, dtype=torch.bool)
+    for t in (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0):
+        tie |= v.abs() == t
+    ok = (got == want) | tie | want.isnan()
+    assert bool(ok.all()), int((~ok).sum())

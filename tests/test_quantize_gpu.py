@@ -80,6 +80,32 @@ def test_quantize_edge_cases(cuda_device, fmt):
     assert torch.equal(q.cpu(), want_codes)
 
 
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("hgroup", [16, 32, 64, 128])
+def test_rounding_boundaries_through_the_rotation(cuda_device, fmt, hgroup):
+    """The edge rows above reach the quantiser unrotated.  These rows are built backwards from the rotated
+    values (tests/inputs.py::rotation_boundary_probes), so the rotation is exact and every probe lands on or
+    within a few grid steps of one of the seven E2M1 rounding boundaries after the kernel's own butterfly:
+    this is where the MXFP4 single-multiply path (multiplier not a power of two for groups 32 and 128) could
+    differ from the reference's division."""
+    from fpq_b200 import ops
+
+    x, t = inputs.rotation_boundary_probes(hgroup)
+    y = fp4.fwht_butterfly(x, hgroup)
+    assert torch.equal(y, t * torch.tensor(hgroup ** -0.5, dtype=torch.float32))      # the construction holds
+    assert torch.equal(ops.rotate_hadamard(x.to(cuda_device), hgroup).cpu(), y)
+    gs = _global_scale(y) if fmt == "nvfp4" else None
+    want_codes, want_sb, want_s = _oracle_quant(y, fmt, gs)
+    q, sb, sf = ops.quantize(x.to(cuda_device), fmt, hgroup, None if gs is None else gs.to(cuda_device),
+                             scales_f32=True)
+    assert torch.equal(sf.cpu(), want_s)
+    assert torch.equal(sb.cpu(), want_sb)
+    assert torch.equal(q.cpu(), want_codes)
+    if fmt == "mxfp4":      # every code of the grid is hit, so both sides of every boundary were probed
+        seen = set(fp4.unpack_codes(want_codes).flatten().tolist())
+        assert seen >= set(range(1, 8)) | set(range(8, 16))
+
+
 @pytest.mark.parametrize("fmt,hgroup", [("nvfp4", 128), ("mxfp4", 128), ("mxfp4", 32)])
 def test_weight_round_trip_4096(cuda_device, fmt, hgroup):
     """The 4096 x 4096 N(0, 0.02^2) weight: codes, scales, global scale and MSE."""
@@ -193,3 +219,52 @@ def test_mse_observer_scales_match_the_reference(cuda_device, fmt):
     # and Quantizer.__call__ with those scales works as with any others
     out = q(y.to(cuda_device), got.to(cuda_device)).cpu()
     assert torch.allclose(out, fp4.dequantize(fp4.e2m1_codes(y, got, group), got, group), rtol=1e-6, atol=1e-9)
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("rows", [1, 64, 130])
+def test_swizzled_pad_rows_are_written_by_the_kernel(cuda_device, fmt, rows):
+    """The scale bytes of the rows between the tensor's end and the next multiple of 128 are zeroed by the
+    quantise kernel itself: a buffer pre-filled with 0xFF comes back identical to the oracle's zero-padded
+    layout, so callers need no memset before a launch."""
+    from fpq_b200 import _cabi as C
+
+    K = 512
+    x = inputs.outlier_activations(rows, K, seed=51).to(cuda_device)
+    g = 16 if fmt == "nvfp4" else 32
+    gs = torch.tensor([5.0], device=cuda_device) if fmt == "nvfp4" else None
+    pr = (rows + 127) // 128 * 128
+    sb = torch.full((pr, K // g), 0xFF, dtype=torch.uint8, device=cuda_device)
+    codes = torch.empty(rows, K // 2, dtype=torch.uint8, device=cuda_device)
+    C.call("fpq_quantize", x.data_ptr(), C.DT_BF16, rows, K, 32, C.FMT_NVFP4 if fmt == "nvfp4" else C.FMT_MXFP4,
+           None if gs is None else gs.data_ptr(), codes.data_ptr(), sb.data_ptr(), C.SCALES_SWIZZLED, None,
+           torch.cuda.current_stream().cuda_stream)
+    _, want_sb, _ = _oracle_quant(fp4.fwht_butterfly(x.cpu(), 32), fmt, None if gs is None else gs.cpu())
+    assert torch.equal(sb.cpu(), fp4.swizzle_scales(want_sb))
+
+
+@pytest.mark.parametrize("hgroup", [0, 32, 64, 128])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_quest_quantize_bit_exact(cuda_device, hgroup, dtype):
+    """forward_method = "quest": codes, E8M0 bytes (row-major and swizzled), the packed clip mask and the
+    pseudo-quantised output against the oracle's restatement, which tests/test_oracle_cpu.py pins to the
+    reference's Triton kernel."""
+    from fpq_b200 import ops
+
+    x = inputs.outlier_activations(130, 512, seed=61, dtype=dtype)
+    x[3, 32:64] = 0
+    x[5, :32] = 1.0
+    y = fp4.fwht_butterfly(x, hgroup) if hgroup else x.float()
+    want_codes, want_sb, want_s, want_mask = fp4.quest_quantize(y)
+    q, sb, mask = ops.quantize_quest(x.to(cuda_device), hgroup, swizzled=False, return_mask=True)
+    assert torch.equal(sb.cpu(), want_sb)
+    assert torch.equal(q.cpu(), want_codes)
+    assert torch.equal(mask.cpu(), fp4.pack_clip_mask(want_mask))
+    q2, sbz, none = ops.quantize_quest(x.to(cuda_device), hgroup, swizzled=True)
+    assert none is None and torch.equal(q2.cpu(), want_codes)
+    assert torch.equal(sbz.cpu(), fp4.swizzle_scales(want_sb))
+    dq, m2 = ops.fake_quantize_quest(x.to(cuda_device), hgroup)
+    want_dq = fp4.dequantize(fp4.unpack_codes(want_codes), want_s, 32)
+    assert torch.equal(dq.cpu().float(), want_dq.to(dtype).float())
+    assert m2.dtype == torch.bool and torch.equal(m2.cpu(), want_mask)
+    assert 0.5 < want_mask.float().mean().item() < 1.0          # the rule does clip: that is its point
