@@ -15,6 +15,12 @@ buffers (pinned H2D of X and D2H of Y inside the timed region).
 With --gpus N (launched by torchrun, one rank per GPU) every rank processes its own M tokens
 (weak scaling, no collective on the data path); the time is the max over ranks.
 
+The default line also carries `mr_gptq` (second half of the metric): MR-GPTQ of one 14336 x 4096 linear
+(seconds per layer) and of a Llama-3.1-8B-shaped model through the driver (seconds per transformer block),
+both partitioned over the N ranks with their NCCL all-reduce of the Hessians (strong scaling); and, for the
+two hot kernels, a sustained figure from a loop of at least two seconds beside the burst figure of the timed
+steps, with the SM clock sampled during each.
+
 --impl reference times the CPU restatement of the reference algorithm (the oracle) on the
 host cores for a bounded sample of the same workload.  It is the only mode that touches
 `oracle/`, besides the `cpu_baseline` leg of the default mode.
@@ -46,8 +52,20 @@ def load_peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def load_traffic():
+    """DRAM bytes per launch that ncu measured for the two hot kernels, with the algorithmic bytes of the captured
+    launch, the commit and the command of the capture (profiles/dram_traffic.json).  The bench scales the measured
+    bytes to its own launches by algorithmic bytes; without the file `traffic` is null."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {}
 
 
 # ------------------------------------------------------------------------------ inputs
@@ -256,6 +274,120 @@ def workload_config(args):
             "l2": "per-step working set ~0.8 GB (activations, weights, outputs of four shapes) > 126 MB L2"}
 
 
+def library_gemm(args, layers, xs_dev, gs, wscales, outs, flops_step, dev):
+    """cuBLASLt's block-scaled FP4 GEMM through torch on this run's operands: same codes, same swizzled scale
+    bytes, so equal results also pin the scale layout.  MXFP4 goes through torch.nn.functional.scaled_mm
+    (BlockWise1x32, SWIZZLE_32_4_4); when this torch build rejects it the comparison is made in NVFP4 on
+    operands quantised here (same shapes and flops), and says so.  Comparison only, never on the product path."""
+    import torch.nn.functional as F
+
+    from fpq_b200 import ops
+    from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype, FPQuantLinear
+
+    def mx_call(a4, b4t, sa, sbw):
+        return F.scaled_mm(a4, b4t, sa, F.ScalingType.BlockWise1x32, sbw, F.ScalingType.BlockWise1x32,
+                           swizzle_a=F.SwizzleType.SWIZZLE_32_4_4, swizzle_b=F.SwizzleType.SWIZZLE_32_4_4,
+                           output_dtype=torch.bfloat16)
+
+    def nv_call(a4, b4t, sa, sbw):
+        return torch._scaled_mm(a4, b4t, sa, sbw, out_dtype=torch.bfloat16)
+
+    def operands(fmt, weights):
+        sdt = torch.float8_e8m0fnu if fmt == "mxfp4" else torch.float8_e4m3fn
+        one = torch.ones(1, device=dev)
+        out = []
+        for i, (wq, wsb) in enumerate(weights):
+            q, sb, _ = ops.quantize(xs_dev[i], fmt, HADAMARD_GROUP[fmt], one if fmt == "nvfp4" else None, swizzled=True)
+            out.append((q.view(torch.float4_e2m1fn_x2), wq.view(torch.float4_e2m1fn_x2).t(), sb.flatten().view(sdt),
+                        wsb.flatten().view(sdt), q, sb, wq, wsb))
+        return out
+
+    def measure(fmt, call, ops_l):
+        one = torch.ones(1, device=dev)
+        same = True
+        for a4, b4t, sa, sbw, q, sb, wq, wsb in ops_l:
+            y = call(a4, b4t, sa, sbw).float()
+            ours = ops.gemm_fp4(q, wq, sb, wsb, one, fmt).float()
+            same = same and bool(torch.allclose(y, ours, rtol=2e-2, atol=1e-2 * float(ours.abs().max())))
+        res = {}
+        for name, fn in (("tflops", lambda o: call(o[0], o[1], o[2], o[3])),
+                         ("ours_same_loop_tflops", lambda o: ops.gemm_fp4(o[4], o[6], o[5], o[7], one, fmt))):
+            for _ in range(3):
+                for o in ops_l:
+                    fn(o)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                for o in ops_l:
+                    fn(o)
+            e1.record()
+            torch.cuda.synchronize()
+            res[name] = flops_step / (e0.elapsed_time(e1) / args.steps * 1e-3) / 1e12
+        res["time_ratio_ours_over_library"] = res["tflops"] / res["ours_same_loop_tflops"]
+        res["results_agree"] = same
+        return res
+
+    fmt = args.format
+    attempts = []
+    try:
+        if fmt == "mxfp4":
+            weights = [(l.qweight, wscales[i]) for i, l in enumerate(layers)]
+            try:
+                r = measure("mxfp4", mx_call, operands("mxfp4", weights))
+                return {"name": "cuBLASLt block-scaled MXFP4 via torch.nn.functional.scaled_mm (comparison only)", "format": "mxfp4", **r}
+            except Exception as exc:
+                attempts.append("mxfp4: " + repr(exc)[:160])
+        # NVFP4: weights re-quantised here with tensor scale 1 (only the comparison needs them)
+        weights = []
+        for i, l in enumerate(layers):
+            K, N = l.in_features, l.out_features
+            w = make_weight(N, K, seed=3 + 10 * i).to(dev)
+            wq, wsb, _ = ops.quantize(w, "nvfp4", HADAMARD_GROUP["nvfp4"], torch.ones(1, device=dev), swizzled=True)
+            weights.append((wq, wsb))
+        r = measure("nvfp4", nv_call, operands("nvfp4", weights))
+        out = {"name": "cuBLASLt block-scaled NVFP4 via torch._scaled_mm (comparison only)", "format": "nvfp4", **r}
+        if attempts:
+            out["note"] = "the headline format is mxfp4, which this torch build rejects (" + "; ".join(attempts) + \
+                          "): both arms of this comparison run NVFP4 on the same shapes"
+        return out
+    except Exception as exc:  # the comparison is optional
+        return {"unavailable": "; ".join(attempts + [repr(exc)[:200]])}
+
+
+def sustained(fn, dev_index, seconds=2.0):
+    """Runs fn() back to back for at least `seconds` of device time (after a short calibration) with the SM
+    clock sampled meanwhile.  Returns (device seconds per call, calls, clock summary)."""
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    per = max(e0.elapsed_time(e1) / 3 * 1e-3, 1e-6)
+    n = max(3, int(seconds / per) + 1)
+    with ClockSampler(dev_index) as clk:
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e-3 / n, n, clk.summary()
+
+
+def rank_stats(ms, world, dev):
+    """min / median / max over the ranks of a per-rank time (ms)."""
+    import torch.distributed as dist
+
+    if world == 1:
+        return {"min": ms, "median": ms, "max": ms}
+    t = torch.zeros(world, device=dev)
+    dist.all_gather_into_tensor(t, torch.tensor([ms], device=dev))
+    v = sorted(t.tolist())
+    return {"min": v[0], "median": v[len(v) // 2], "max": v[-1], "per_rank": t.tolist()}
+
+
 # ------------------------------------------------------------------------------ GPU arm
 def run_ours(args):
     import torch.distributed as dist
@@ -293,6 +425,7 @@ def run_ours(args):
     wscales = [l._blocked_weight_scales() for l in layers]
     outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for (K, N) in shapes]
     flops_step = sum(2.0 * M * N * K for (K, N) in shapes)
+    n_layers_linear = len(layers)
 
     gemm_events = []
 
@@ -331,12 +464,22 @@ def run_ours(args):
         stop.record()
         barrier()
     ops.check_device_errors(dev)
-    ms = start.elapsed_time(stop)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms_rank = start.elapsed_time(stop)
+    per_rank_ms = rank_stats(ms_rank / args.steps, world, dev)
+    ms = per_rank_ms["max"] * args.steps
     value = flops_step * world * args.steps / (ms * 1e-3) / 1e12 if args.workload != "quantize" else None
+    traffic = load_traffic()
+
+    def scaled_traffic(kernel, alg_bytes_per_launch):
+        t = traffic.get(kernel)
+        if not t:
+            return None, "no ncu capture on file (profiles/dram_traffic.json)"
+        return (alg_bytes_per_launch * t["dram_bytes"] / t["algorithmic_bytes"],
+                f"bytes per launch: ncu dram read+write of {t['launch']} (commit {t['commit']}) scaled by algorithmic bytes")
+
+    def quantize_all(f):
+        for i in range(len(layers)):
+            ops.quantize(xs_dev[i], f, HADAMARD_GROUP[f], gs[i] if f == "nvfp4" else None, swizzled=True)
 
     # ---- roofline of the dominant kernel
     roofline = None
@@ -346,84 +489,70 @@ def run_ours(args):
         tot_fl = sum(2.0 * M * shapes[i][1] * shapes[i][0] for _, _, i in gemm_events)
         achieved = tot_fl / (tot_ms * 1e-3) / 1e12
         peak = 4.0 * peaks["bf16_tflops"]
-        # DRAM traffic per launch: ncu saw 45.68 MB on the 8192 x 4096 x 4096 launch (93.85 MB algorithmic:
-        # operands that the quantise kernel just wrote are still in L2, part of the output still is when
-        # the kernel ends); scaled to the average launch of this run by its algorithmic bytes
         alg = sum(M * shapes[i][0] / 2 + shapes[i][1] * shapes[i][0] / 2 + (M + shapes[i][1]) * shapes[i][0] / g
                   + 2.0 * M * shapes[i][1] for _, _, i in gemm_events) / len(gemm_events)
+        tr, tr_note = scaled_traffic("gemm_fp4_pair_kernel", alg)
         roofline = {"kernel": "gemm_fp4_pair_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
                     "unit": "TFLOP/s", "frac": achieved / peak,
                     "peak_source": f"4 x bf16 cuBLAS burst ({peaks['source']}); no FP4 peak was measured on this pool",
                     "frac_of_nominal_9pf": achieved / NOMINAL_FP4_TFLOPS,
-                    "avg_launch_ms": tot_ms / len(gemm_events), "traffic": alg * (45.677e6 / 93.847e6),
-                    "traffic_note": "bytes per launch, ncu dram read+write of the 8192x4096x4096 launch scaled by algorithmic bytes"}
+                    "avg_launch_ms": tot_ms / len(gemm_events), "traffic": tr, "traffic_note": tr_note}
+        # sustained: the same GEMMs (operands quantised once) back to back for >= 2 s, clocks sampled meanwhile
+        pre = [ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)[:2]
+               for i in range(len(layers))]
+
+        def gemm_pass():
+            for i, layer in enumerate(layers):
+                ops.gemm_fp4(pre[i][0], layer.qweight, pre[i][1], wscales[i], alphas[i], fmt, out=outs[i])
+
+        sec, n, clk = sustained(gemm_pass, local)
+        sus = flops_step / sec / 1e12
+        sus_peak = 4.0 * peaks["bf16_tflops_sustained"]
+        roofline["sustained"] = {"achieved": sus, "peak": sus_peak, "frac": sus / sus_peak, "seconds": sec * n,
+                                 "frac_of_nominal_9pf": sus / NOMINAL_FP4_TFLOPS, "clocks": clk,
+                                 "ms_x_mhz_per_pass": sec * 1e3 * (clk["sm_mhz"] or 0),
+                                 "peak_source": f"4 x bf16 cuBLAS sustained ({peaks['source']})",
+                                 "note": "GEMM launches only, all shapes of the step in turn"}
+        del pre
     quant_roof = None
     if args.workload in ("linear", "quantize"):
-        # time the quantise launches alone (same inputs, back to back; 0.4 GB of input per pass > L2)
-        for _ in range(2):
-            for i in range(len(layers)):
-                ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(3, args.steps)
-        e0.record()
-        for _ in range(reps):
-            for i in range(len(layers)):
-                ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)
-        e1.record()
-        torch.cuda.synchronize()
-        qms = e0.elapsed_time(e1) / reps
-        qbytes = sum(M * K * (2 + 0.5 + 1.0 / g) for (K, N) in shapes)
-        quant_roof = {"kernel": "quant_kernel", "bound": "hbm", "achieved": qbytes / (qms * 1e-3) / 1e9,
-                      "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                      "peak_source": f"copy bandwidth ({peaks['source']})",
-                      "frac_of_nominal_8tbs": qbytes / (qms * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
-                      # ncu: 324.4 MB read+write on a [32768, 4096] launch whose algorithmic bytes are 339.7 MB
-                      "traffic": qbytes / len(shapes) * (324.366e6 / 339.739e6),
-                      "traffic_note": "bytes per launch, ncu dram read+write of a [32768,4096] launch scaled by elements"}
+        quant_roof = {}
+        for f in ("mxfp4", "nvfp4"):
+            # the quantise launches alone (same inputs, back to back; 0.4 GB of input per pass > L2)
+            gq = SCALE_GROUP[f]
+            for _ in range(2):
+                quantize_all(f)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(3, args.steps)
+            e0.record()
+            for _ in range(reps):
+                quantize_all(f)
+            e1.record()
+            torch.cuda.synchronize()
+            qms = e0.elapsed_time(e1) / reps
+            qbytes = sum(M * K * (2 + 0.5 + 1.0 / gq) for (K, N) in shapes)
+            tr, tr_note = scaled_traffic(f"quant_kernel_{f}", qbytes / len(shapes))
+            sec, n, clk = sustained(lambda: quantize_all(f), local)
+            entry = {"kernel": "quant_kernel", "format": f, "bound": "hbm", "achieved": qbytes / (qms * 1e-3) / 1e9,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     "peak_source": f"copy bandwidth ({peaks['source']})",
+                     "frac_of_nominal_8tbs": qbytes / (qms * 1e-3) / 1e9 / NOMINAL_HBM_GBS,
+                     "traffic": tr, "traffic_note": tr_note,
+                     "sustained": {"achieved": qbytes / sec / 1e9, "frac": qbytes / sec / 1e9 / peaks["hbm_gbs"],
+                                   "seconds": sec * n, "clocks": clk}}
+            if f == fmt:
+                quant_roof.update(entry)          # the headline format at the top level, as before
+            else:
+                quant_roof[f] = entry
         if args.workload == "quantize":
             roofline = quant_roof
 
     # ---- the vendor library on the same operands, for orientation only (never on the product path):
-    # cuBLASLt block-scaled FP4 through torch._scaled_mm, same codes, same swizzled scale bytes
+    # cuBLASLt block-scaled FP4 through torch, same codes, same swizzled scale bytes
     library = None
     if args.workload in ("linear", "gemm") and rank == 0 and not args.no_library_gemm:
-        try:
-            sdt = torch.float8_e8m0fnu if fmt == "mxfp4" else torch.float8_e4m3fn
-            ops_l = []
-            for i, layer in enumerate(layers):
-                q, sb, _ = ops.quantize(xs_dev[i], fmt, hgroup, gs[i] if fmt == "nvfp4" else None, swizzled=True)
-                ops_l.append((q.view(torch.float4_e2m1fn_x2), layer.qweight.view(torch.float4_e2m1fn_x2).t(),
-                              sb.flatten().view(sdt), wscales[i].flatten().view(sdt), q, sb, i))
-            same = True
-            for a4, b4t, sa, sbw, q, sb, i in ops_l:
-                y = torch._scaled_mm(a4, b4t, sa, sbw, out_dtype=torch.bfloat16).float()
-                ours = ops.gemm_fp4(q, layers[i].qweight, sb, wscales[i], torch.ones(1, device=dev), fmt).float()
-                same = same and bool(torch.allclose(y, ours, rtol=2e-2, atol=1e-2 * float(ours.abs().max())))
-            for _ in range(3):
-                for a4, b4t, sa, sbw, *_ in ops_l:
-                    torch._scaled_mm(a4, b4t, sa, sbw, out_dtype=torch.bfloat16)
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(args.steps):
-                for a4, b4t, sa, sbw, *_ in ops_l:
-                    torch._scaled_mm(a4, b4t, sa, sbw, out_dtype=torch.bfloat16)
-            e1.record()
-            torch.cuda.synchronize()
-            lms = e0.elapsed_time(e1) / args.steps
-            e0.record()
-            for _ in range(args.steps):
-                for a4, b4t, sa, sbw, q, sb, i in ops_l:
-                    ops.gemm_fp4(q, layers[i].qweight, sb, wscales[i], alphas[i], fmt, out=outs[i])
-            e1.record()
-            torch.cuda.synchronize()
-            oms = e0.elapsed_time(e1) / args.steps
-            library = {"name": "cuBLASLt block-scaled FP4 via torch._scaled_mm (comparison only)",
-                       "tflops": flops_step / (lms * 1e-3) / 1e12, "ours_same_loop_tflops": flops_step / (oms * 1e-3) / 1e12,
-                       "results_agree": same}
-        except Exception as exc:  # the comparison is optional
-            library = {"unavailable": repr(exc)[:200]}
+        library = library_gemm(args, layers, xs_dev, gs, wscales, outs, flops_step, dev)
 
     # ---- end to end through FPQuantLinear.forward with host buffers
     e2e = None
@@ -486,8 +615,20 @@ def run_ours(args):
         cpu = {"value": f / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                "sample": f"{args.cpu_rows} of {M} token rows per shape, all four shapes, full N and K"}
 
+    # ---- second half of the metric: MR-GPTQ seconds per layer and per transformer block, partitioned over the ranks
+    mr_gptq = None
+    if args.workload == "linear" and not args.no_mr_gptq:
+        del xs_dev, outs, layers, wscales
+        torch.cuda.empty_cache()
+        lay = measure_gptq_layer(args, world, rank, local, dev, steps=3, warmup=1)
+        mod = measure_gptq_model(args, world, rank, local, dev, steps=1, warmup=1, n_layers=2, n_seq=128)
+        if rank == 0:
+            mr_gptq = {"s_per_layer": lay["value"], "s_per_block": mod["value"],
+                       "layer": {k: lay[k] for k in ("config", "breakdown_s", "relative_mse", "comm", "per_rank_ms", "roofline", "clocks")},
+                       "model": {k: mod[k] for k in ("config", "phases_s", "comm", "per_rank_ms", "relative_mse_first_block", "clocks")}}
+
     if rank == 0:
-        n_launch = len(gemm_events) + (args.steps * len(layers) if args.workload in ("linear", "quantize") else 0)
+        n_launch = len(gemm_events) + (args.steps * n_layers_linear if args.workload in ("linear", "quantize") else 0)
         line = {
             "metric": "w4a4_linear_tflops" if args.workload != "quantize" else "quantize_gbs",
             "value": value if value is not None else (quant_roof["achieved"] if quant_roof else None),
@@ -495,12 +636,26 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp4(e2m1)xfp4->f32->bf16", "data": "synthetic", "config": workload_config(args),
+            "per_rank_ms_per_step": per_rank_ms,
             "roofline": roofline, "quantize_roofline": quant_roof, "library_gemm": library, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": n_launch, "clocks": clocks.summary(),
+            "mr_gptq": mr_gptq, "gpu_launches": n_launch, "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def dist_setup():
+    """(world, rank, local rank, device); initialises NCCL once when launched by torchrun."""
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    return world, rank, local, torch.device("cuda", local)
 
 
 # ------------------------------------------------------------------------------ MR-GPTQ of one layer
@@ -511,15 +666,20 @@ def run_gptq(args):
     rows of the weight are sharded for the column loop (results all-gathered)."""
     import torch.distributed as dist
 
+    world, rank, local, dev = dist_setup()
+    line = measure_gptq_layer(args, world, rank, local, dev, args.steps, args.warmup, cpu_baseline=not args.no_cpu_baseline)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_gptq_layer(args, world, rank, local, dev, steps, warmup, cpu_baseline=False):
+    """The JSON object of `--workload gptq` (None on ranks other than 0).  A collective: every rank calls it."""
+    import torch.distributed as dist
+
     from fpq_b200 import dist as fdist, ops
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
     R, C, n_seq, T, hg = args.gptq_rows, args.gptq_cols, 128, 2048, 128
     fmt, group = "nvfp4", 16
     peaks = load_peaks()
@@ -584,51 +744,48 @@ def run_gptq(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         layer(False)
     barrier()
     with ClockSampler(local) as clocks:
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             status = layer(True)
         stop.record()
         barrier()
     ops.check_device_errors(dev)
-    ms = start.elapsed_time(stop)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    per_rank_ms = rank_stats(start.elapsed_time(stop) / steps, world, dev)
+    ms = per_rank_ms["max"] * steps
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and cpu_baseline:
         threads = os.cpu_count() or 1
         torch.set_num_threads(threads)
         csec, cparts = cpu_gptq_sample(C, R, n_seq * T)
         cpu = {"value": csec, "unit": "s/layer", "cores": threads, "kind": "port", "breakdown_s": cparts,
                "sample": f"8192 of {n_seq * T} calibration tokens, 2048 of {R} weight rows, full-size Cholesky; parts scaled linearly"}
-    if rank == 0:
-        sec = ms * 1e-3 / args.steps
-        hess_flops = float((hi - lo) * T) * C * (C + 1)
-        hess_t = times["hessian"] / args.steps
-        line = {
-            "metric": "mr_gptq_s_per_layer", "value": sec, "unit": "s/layer", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16 Hessian products, fp32 factorisation and column loop", "data": "synthetic",
-            "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4) of one linear {R}x{C}, {n_seq}x{T} calibration tokens, "
-                                   f"damp 0.01, block 128; sequences and weight rows sharded over {world} GPU(s)",
-                       "l2": "calibration activations 2 GB per pass > 126 MB L2"},
-            "breakdown_s": {k: v / args.steps for k, v in times.items()},
-            "relative_mse": float(rel_mse.item()), "cholesky_failed": int(status.item()),
-            "roofline": {"kernel": "hessian_kernel", "bound": "tensor", "achieved": hess_flops / hess_t / 1e12,
-                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": hess_flops / hess_t / 1e12 / peaks["bf16_tflops"],
-                         "peak_source": f"bf16 cuBLAS burst ({peaks['source']})",
-                         "note": "time includes the Hadamard rotation of the activations; flops = T*d*(d+1)", "traffic": None},
-            "cpu_baseline": cpu, "e2e": None, "clocks": clocks.summary(),
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    sec = ms * 1e-3 / steps
+    hess_flops = float((hi - lo) * T) * C * (C + 1)
+    hess_t = times["hessian"] / steps
+    return {
+        "metric": "mr_gptq_s_per_layer", "value": sec, "unit": "s/layer", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 Hessian products, fp32 factorisation and column loop", "data": "synthetic",
+        "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4) of one linear {R}x{C}, {n_seq}x{T} calibration tokens, "
+                               f"damp 0.01, block 128; sequences and weight rows sharded over {world} GPU(s)",
+                   "l2": "calibration activations 2 GB per pass > 126 MB L2"},
+        "breakdown_s": {k: v / steps for k, v in times.items()}, "per_rank_ms": per_rank_ms,
+        "comm": {"collective": "NCCL all-reduce(sum) of the fp32 Hessian" if world > 1 else None,
+                 "allreduce_bytes_per_gpu": int(2 * (world - 1) / world * 4 * C * C), "allreduce_s": times["allreduce"] / steps},
+        "relative_mse": float(rel_mse.item()), "cholesky_failed": int(status.item()),
+        "roofline": {"kernel": "hessian_kernel", "bound": "tensor", "achieved": hess_flops / hess_t / 1e12,
+                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": hess_flops / hess_t / 1e12 / peaks["bf16_tflops"],
+                     "peak_source": f"bf16 cuBLAS burst ({peaks['source']})",
+                     "note": "time includes the Hadamard rotation of the activations; flops = T*d*(d+1)", "traffic": None},
+        "cpu_baseline": cpu, "e2e": None, "clocks": clocks.summary(),
+    }
 
 
 # ------------------------------------------------------------------------------ MR-GPTQ of a model
@@ -636,26 +793,34 @@ def run_gptq_model(args):
     """Model-level MR-GPTQ through the public driver (`gptq_quantization`) on a randomly initialised Llama-3.1-8B
     shaped model (hidden 4096, MLP 14336, 32/8 heads, vocab 128256) truncated to `--model-layers` blocks, with
     `--calib-seqs` x 2048 uniformly random token ids, NVFP4 W4A4, Hadamard 128.  Multi-GPU: sequences, Cholesky
-    chains and weight rows are partitioned over the ranks inside the driver.  Reports seconds per transformer
+    chains and column loops are partitioned over the ranks inside the driver.  Reports seconds per transformer
     block (7 linears: 4 distinct Hessians, 4 Cholesky chains, 7 column loops, two passes over the calibration set)."""
+    import torch.distributed as dist
+
+    world, rank, local, dev = dist_setup()
+    line = measure_gptq_model(args, world, rank, local, dev, args.steps, args.warmup, args.model_layers, args.calib_seqs)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_gptq_model(args, world, rank, local, dev, steps, warmup, n_layers, n_seq):
+    """The JSON object of `--workload gptq-model` (None on ranks other than 0).  A collective."""
+    import contextlib
+    import io
     import types
 
     import torch.distributed as dist
     from transformers import LlamaConfig, LlamaForCausalLM
 
     from fpq_b200 import ops
+    from fpq_b200.quantization import driver as _drv
     from fpq_b200.quantization.driver import gptq_quantization
     from fpq_b200.quantization.quant_args import (QuantizationFormat, QuantizationGranularity, QuantizationObserver,
                                                   QuantizationOrder, ScalePrecision)
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    n_layers, n_seq, T = args.model_layers, args.calib_seqs, 2048
+    T = 2048
     cfg = LlamaConfig(hidden_size=4096, intermediate_size=14336, num_hidden_layers=n_layers, num_attention_heads=32,
                       num_key_value_heads=8, vocab_size=128256, max_position_embeddings=T)
     qargs = types.SimpleNamespace(
@@ -680,12 +845,9 @@ def run_gptq_model(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    import contextlib
-    import io
-
-    times = []
+    times, per_rank = [], None
     with ClockSampler(local) as clocks:
-        for it in range(args.warmup + args.steps):
+        for it in range(warmup + steps):
             model = build()
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -694,35 +856,37 @@ def run_gptq_model(args):
                 quantized, _ = gptq_quantization(model, data, qargs, dev)
             e1.record()
             barrier()
-            ms = e0.elapsed_time(e1)
-            if world > 1:
-                t = torch.tensor([ms], device=dev)
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                ms = float(t.item())
-            if it >= args.warmup:
-                times.append(ms)
+            stats = rank_stats(e0.elapsed_time(e1), world, dev)
+            if it >= warmup:
+                times.append(stats["max"])
+                per_rank = stats
             n_keys = len(quantized)
-            from fpq_b200.quantization import driver as _drv
             phases = _drv.last_phases.summary()
+            rel = dict(_drv.last_relative_mse)
             del model, quantized
             torch.cuda.empty_cache()
     ops.check_device_errors(dev)
-    if rank == 0:
-        ms = sum(times) / len(times)
-        line = {
-            "metric": "mr_gptq_model_s_per_block", "value": ms * 1e-3 / n_layers, "unit": "s/block", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16 forward and Hessian products, fp32-accurate factorisation and column loop",
-            "data": "synthetic",
-            "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4 W4A4) of a random-init Llama-3.1-8B-shaped model truncated to "
-                                   f"{n_layers} blocks, {n_seq}x{T} random token ids ({args.calib_batch} per block call), through gptq_quantization(); sequences, "
-                                   f"Cholesky chains and weight rows partitioned over {world} GPU(s)",
-                       "l2": "calibration activations of a block (2 GB) > 126 MB L2"},
-            "exported_layers": n_keys, "phases_s": phases, "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if rank != 0:
+        return None
+    ms = sum(times) / len(times)
+    hessian_bytes = 4 * (3 * 4096 * 4096 + 14336 * 14336)       # the four distinct Hessians of a block, fp32
+    return {
+        "metric": "mr_gptq_model_s_per_block", "value": ms * 1e-3 / n_layers, "unit": "s/block", "n_gpus": world,
+        "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 forward and Hessian products, fp32-accurate factorisation and column loop",
+        "data": "synthetic",
+        "config": {"workload": f"MR-GPTQ (Hadamard 128 + NVFP4 W4A4) of a random-init Llama-3.1-8B-shaped model truncated to "
+                               f"{n_layers} blocks, {n_seq}x{T} random token ids ({args.calib_batch} per block call), through gptq_quantization(); sequences, "
+                               f"Cholesky chains and column loops partitioned over {world} GPU(s)",
+                   "l2": "calibration activations of a block (2 GB) > 126 MB L2"},
+        "exported_layers": n_keys, "phases_s": phases, "per_rank_ms": per_rank,
+        "comm": {"collective": "NCCL all-reduce(sum) of the block's four fp32 Hessians, all-reduce(min) of the activation "
+                               "tensor scales, broadcasts of factors and results" if world > 1 else None,
+                 "allreduce_bytes_per_gpu_per_block": int(2 * (world - 1) / world * hessian_bytes),
+                 "allreduce_s_per_block": phases.get("allreduce", 0.0) / n_layers},
+        "relative_mse_first_block": {k.split(".", 3)[3]: v for k, v in rel.items() if k.startswith("model.layers.0.")},
+        "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
+    }
 
 
 # ------------------------------------------------------------------------------ column-parallel W4A4 linear
@@ -941,6 +1105,7 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-library-gemm", action="store_true", help="skip the cuBLASLt comparison line")
+    ap.add_argument("--no-mr-gptq", action="store_true", help="linear workload: skip the MR-GPTQ part of the line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

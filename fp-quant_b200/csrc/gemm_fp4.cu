@@ -93,7 +93,11 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
 
-  const int warp = threadIdx.x >> 5;
+  // warp index through a shuffle (known to be the same in all lanes) and single-thread roles through
+  // elect.sync: the role code then runs on the uniform datapath, where the operands of tcgen05 / TMA
+  // instructions live; with `threadIdx.x >> 5` and `lane == 0` every such instruction cost its thread
+  // 75-150 cycles of register moves
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -122,7 +126,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t it = 0;   // global stage counter
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
@@ -167,7 +171,7 @@ gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t it = 0;
       uint32_t tile_count = 0;
       bool ok = true;

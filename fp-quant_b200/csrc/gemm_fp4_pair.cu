@@ -4,33 +4,35 @@
 // A pair of CTAs (cluster of 2, two neighbouring SMs) owns a 256 x 256 output tile.  Each CTA loads
 // its own 128 rows of A and its own 128 of the 256 rows of B, so every byte of the operands is fetched
 // from L2 once per pair; one thread of the leader CTA issues MMAs that span both SMs (M = 256), each
-// SM accumulating its 128 x 256 half in its own tensor memory.  Measured on B200: a single CTA cannot
-// issue FP4 MMAs faster than one per ~180 cycles whatever their N, about half the tensor pipe; a pair
-// does twice the work per instruction.
+// SM accumulating its 128 x 256 half in its own tensor memory.
 //
-// Warps per CTA: 0 TMA producer, 1 MMA issuer (leader CTA only) and tensor-memory owner, 2-5 epilogue,
-// 6-9 scale-factor movers.  Scale tiles go shared -> registers -> tensor memory (tcgen05.st, each of
-// the four warps filling its own 32-lane quarter) so that the MMA queue carries nothing but MMAs; a
-// tcgen05.cp per 512-byte tile in that queue cost 20-35 % of the run time.  The epilogue first drains
-// the whole accumulator into registers (packed bf16), hands it back, and only then writes to global
-// memory, so the stores overlap the next tile's MMAs.
+// Warps per CTA (22): 0 TMA producer, 1 MMA issuer (leader CTA only) and tensor-memory owner, 2-5
+// scale-factor movers, 6-21 epilogue (one per 32 rows x 64 columns of the CTA's half tile).  Scale tiles
+// go shared -> registers -> tensor memory (tcgen05.st, each of the four mover warps filling its own
+// 32-lane quarter) so that the MMA queue carries nothing but MMAs.  The epilogue first drains the whole
+// accumulator into registers in one round of loads, hands it back, and only then converts and writes
+// to global memory, so conversion and stores overlap the next tile's MMAs.
 //
 // Barriers: the "full" barrier of a stage lives in the leader and collects everything the MMAs of that
 // stage need: the operand bytes of both CTAs (both producers announce theirs on it) and one arrival
 // per scale-mover warp of both CTAs once the stage's scales sit in tensor memory.  Scale tiles land on
-// a per-CTA "sf_full" barrier that only the movers watch.  The issuing thread pays 75-150 cycles for
-// every tcgen05 instruction and ~100 for every barrier wait, more than the tensor pipe needs for the
-// four MMAs of a stage, so its loop is kept to one wait, four MMAs and one commit per stage: the
-// commit frees the stage in the leader, whose producer passes the news on to the follower's "empty"
-// barrier.  "accumulator full" exists in both CTAs (one commit each per tile), "accumulator empty"
-// lives in the leader and collects the epilogue warps of both CTAs.  Every wait is bounded.  Nothing
-// is broadcast between the CTAs.
+// a per-CTA "sf_full" barrier that only the movers watch.  The issuing thread's loop is one wait, four
+// MMAs and one commit per stage; the commit frees the stage in both CTAs at once (tcgen05.commit with
+// a CTA mask: a signal, no data).  "accumulator full" exists in both CTAs (one commit each per tile),
+// "accumulator empty" lives in the leader and collects the epilogue warps of both CTAs.  Every wait is
+// bounded.  No load is broadcast between the CTAs.
+//
+// What limits it (measured on B200 with timing-only variants of this kernel, 8192 x 4096 x K): MMAs alone,
+// without operand traffic, take 0.28 us per stage of four; the full loop 0.39 us; with half-width MMAs
+// (N = 128) still 0.33 us.  The three fit one model: per stage a CTA's shared memory takes 35 KB of TMA
+// writes and gives 48 KB of operand reads (A, its half of B for itself and again for the peer), 83 KB at
+// 128 bytes per cycle.  cuBLASLt's kernel for the same problem (a CUTLASS 256 x 256 x 64 block-scaled
+// 2-SM kernel, by its name in the profiler) runs within 2 % of this one.
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
-#include <cstdio>
-#include <cstdlib>
+#include <atomic>
 
 namespace fpq {
 namespace {
@@ -47,6 +49,8 @@ constexpr int TMEM_COLS = 512;
 constexpr int SF_TMEM_BASE = 256;
 
 
+
+
 struct PairParams {
   int M, N, K;
   int num_m_pairs, num_n_blocks, num_tiles;
@@ -57,10 +61,7 @@ struct PairParams {
   __nv_bfloat16* out;
   int* error_flag;
   int raster_group;
-  int stagger_base, stagger_step;   // cycles after the accumulator release before epilogue warp i converts and stores: base + i * step
-  int tune_skip;           // tuning aid (tuning instantiation only): 1 = no conversion math, 2 = no staging and store
-  int tune_n;              // tuning aid: issue the MMAs with this N instead of 256 (timing only, results are wrong)
-  long long* profile;      // optional: per-pair cycle counters for tuning (NULL in normal use)
+  int stagger_step;        // cycles between the time slots in which the epilogue warps convert and store (see the epilogue)
 };
 
 // Tensor-parallel push: the tile also goes to the same place of up to seven other GPUs' output buffers
@@ -71,9 +72,15 @@ struct PushParams {
   long long ld;
 };
 
+// Operand ring and epilogue staging.  What bounds the main loop is how many operand bytes are in flight
+// between L2 and shared memory: a stage is refilled ~1.5 us after it was consumed, the tensor pipe consumes
+// one (32 KiB of operands per CTA) every ~0.28 us, so four stages (measured: 0.405 us per stage) starve it and
+// six do not.  Shared memory is therefore spent on stages, and the sixteen epilogue warps share a few
+// staging boxes in turn (a barrier per box) instead of owning one each.
 template <bool NVFP4>
 struct PairSmem {
-  static constexpr int STAGES = 4;
+  static constexpr int STAGES = NVFP4 ? 5 : 6;                // NVFP4: 5 x 48 tensor-memory columns of scales is all that fits
+  static constexpr int NBOX = NVFP4 ? 8 : 4;                  // 32-row x 128-byte staging boxes of the epilogue
   static constexpr int SFBLK = NVFP4 ? 4 : 2;                 // 512-byte scale tiles per 128 rows per stage
   static constexpr int SFA_COLS = 4 * SFBLK;                  // tensor-memory columns of one stage's A scales
   static constexpr int SF_TMEM_BUF = 12 * SFBLK;              // A scales + B scales (256 rows) of one stage
@@ -87,13 +94,15 @@ struct PairSmem {
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_SFA = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_SFB = OFF_SFA + STAGES * SFA_BYTES;
-  static constexpr int OFF_OUT = OFF_SFB + STAGES * SFB_BYTES;  // sixteen 32-row x 128-byte staging boxes (epilogue)
+  static constexpr int OFF_OUT = OFF_SFB + STAGES * SFB_BYTES;
   static constexpr int OUT_BOX_BYTES = 32 * 128;
-  // full[S], empty[S], sf_full[S], acc_full, acc_empty
-  static constexpr int OFF_BAR = OFF_OUT + 16 * OUT_BOX_BYTES;
-  static constexpr int OFF_MISC = OFF_BAR + (3 * STAGES + 2) * 8;
+  // full[S], empty[S], sf_full[S], acc_full, acc_empty, box_read[16]
+  static constexpr int OFF_BAR = OFF_OUT + NBOX * OUT_BOX_BYTES;
+  static constexpr int OFF_MISC = OFF_BAR + (3 * STAGES + 2 + 16) * 8;
   static constexpr int TOTAL = OFF_MISC + 16;
-  static constexpr int DYN_BYTES = TOTAL + 1024;
+  static constexpr int DYN_BYTES = TOTAL;                      // the dynamic shared memory is declared 1024-byte aligned
+  static_assert(DYN_BYTES <= 227 * 1024, "stages and staging boxes exceed the shared memory of an SM");
+  static_assert(SF_TMEM_BASE + STAGES * SF_TMEM_BUF <= TMEM_COLS, "scale buffers exceed tensor memory");
 };
 
 __device__ __forceinline__ void pair_tile_coords(const PairParams& p, int tile, int& m_pair, int& n_blk) {
@@ -107,11 +116,7 @@ __device__ __forceinline__ void pair_tile_coords(const PairParams& p, int tile, 
   n_blk = in_band / rows;
 }
 
-// Cycle counter for the tuning counters; compiled out (constant 0) in the normal instantiation.
-template <bool PROF>
-__device__ __forceinline__ long long tick() { return PROF ? clock64() : 0ll; }
-
-template <bool NVFP4, bool PROF, bool PUSH>
+template <bool NVFP4, bool PUSH>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -119,20 +124,30 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   using L = PairSmem<NVFP4>;
   constexpr int STAGES = L::STAGES;
   constexpr int SFBLK = L::SFBLK;
-  unsigned long long ns_entry = 0;
-  if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_entry));
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];      // 128-byte-swizzled TMA boxes need 1024-byte alignment
+  uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
+  if ((sbase & 1023u) != 0) {                                 // same in both CTAs of the pair: nobody waits for anybody
+    if (threadIdx.x == 0) atomicExch(p.error_flag, 1);
+    return;
+  }
   const uint32_t bar_full = sbase + L::OFF_BAR;
   const uint32_t bar_empty = bar_full + STAGES * 8;
   const uint32_t bar_sf_full = bar_empty + STAGES * 8;
   const uint32_t bar_acc_full = bar_sf_full + STAGES * 8;
   const uint32_t bar_acc_empty = bar_acc_full + 8;
+  const uint32_t bar_box = bar_acc_empty + 8;
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The warp index goes through a shuffle so that the compiler knows it is the same in all lanes, and the
+  // single-thread roles are chosen with elect.sync: both keep the role code on the uniform datapath, where
+  // the descriptors and addresses of the tcgen05 / TMA instructions have to live anyway.  With
+  // `threadIdx.x >> 5` and `lane == 0` every tcgen05.mma cost its issuing thread 75-150 cycles (operands
+  // moved from vector to uniform registers one by one) and the loop ran at 755 cycles per stage of four
+  // MMAs; like this it runs at the rate shared memory sustains (see PairSmem).
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+  const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();        // 0 = leader
   const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
@@ -144,6 +159,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     mbar_init(bar_acc_full, 1);
     mbar_init(bar_acc_empty, 32);          // sixteen epilogue warps per CTA (used in the leader)
+    for (int b = 0; b < 16; ++b) mbar_init(bar_box + 8 * b, 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tensormap(&tmap_a);
@@ -165,8 +181,6 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   // may overlap the tail of the previous kernel; from here on operands and outputs are accessed.
   launch_dependents();
   grid_dependency_wait();
-  unsigned long long ns_setup = 0;
-  if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_setup));
 
   // addresses of the leader's barriers as seen from this CTA
   const uint32_t lead_full = map_to_cta(bar_full, 0);
@@ -174,8 +188,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   if (warp == 0) {
     // ------------------------------------------------------------- TMA producer (both CTAs)
-    if (lane == 0) {
-      const uint32_t peer_empty = map_to_cta(bar_empty, 1);
+    if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs) {
@@ -185,11 +198,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const int n_row = n_blk * BN + (int)rank * BN_CTA;              // my rows of B
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
           const int s = it % STAGES;
-          const long long pt0 = tick<PROF>();
           if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          // the MMA thread frees a stage in the leader only; the leader tells the follower
-          if (rank == 0 && it >= (uint32_t)STAGES) mbar_arrive_cluster(peer_empty + 8 * s);
-          const long long pt1 = tick<PROF>();
           const uint32_t full = lead_full + 8 * s;
           // scale tiles first (the movers need them earliest): 64 eight-byte words per 512-byte tile,
           // rows of the map are 128-row blocks; they complete on this CTA's own barrier
@@ -200,10 +209,6 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           mbar_arrive_expect_tx_cluster(full, L::STAGE_TX);
           tma_load_2d_pair(sbase + L::OFF_A + s * L::A_BYTES, &tmap_a, ks * BK_BYTES, m_row, full);
           tma_load_2d_pair(sbase + L::OFF_B + s * L::B_BYTES, &tmap_b, ks * BK_BYTES, n_row, full);
-          if (PROF && p.profile && pair_id == 0 && it < 512) {
-            long long* o = p.profile + 74 * 64 + 2048 + (size_t)rank * 2048 + (size_t)it * 4;
-            o[0] = pt0; o[1] = pt1; o[2] = tick<PROF>();
-          }
         }
       }
       if (!ok) {
@@ -211,42 +216,33 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         atomicExch(p.error_flag, 1);
       }
       // Drain: my loads complete on the leader's barrier, which I cannot poll from the follower; a stage
-      // is freed only after it was complete, so waiting for my last min(it, STAGES) stages to be freed
-      // proves that every load has landed.  The leader keeps passing the news on.
+      // is freed (in both CTAs, by the MMA thread's commit) only after it was complete, so waiting for my
+      // last min(it, STAGES) stages to be freed proves that every load has landed.
       const uint32_t first = it > STAGES ? it - STAGES : 0;
       volatile int never = 0;
       for (uint32_t j = first; j < it; ++j) {
-        const bool freed = mbar_wait_bounded(bar_empty + 8 * (j % STAGES), (j / STAGES) & 1, &never, 400000000LL);
-        if (rank == 0 && freed) mbar_arrive_cluster(peer_empty + 8 * (j % STAGES));
+        (void)mbar_wait_bounded(bar_empty + 8 * (j % STAGES), (j / STAGES) & 1, &never, 400000000LL);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------- MMA issuer (leader only)
-    if (lane == 0 && rank == 0) {
+    if (rank == 0 && elect_one()) {
       const uint32_t peer_acc_full = map_to_cta(bar_acc_full, 1);
       uint32_t idesc_k[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const uint32_t sf_id = NVFP4 ? 0u : (uint32_t)((k & 1) * 2);
-        idesc_k[k] = make_idesc_fp4(256, p.tune_n ? p.tune_n : BN, !NVFP4, sf_id, sf_id);
+        idesc_k[k] = make_idesc_fp4(256, BN, !NVFP4, sf_id, sf_id);
       }
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
-      long long t_acc = 0, t_full = 0;
-      const long long t_begin = tick<PROF>();
-      unsigned long long ns_begin = 0;
-      if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_begin));
       for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs, ++tile_count) {
-        long long t0 = tick<PROF>();
         if (!mbar_wait_bounded_spin(bar_acc_empty, (tile_count & 1) ^ 1, abort_flag)) { ok = false; break; }
-        t_acc += tick<PROF>() - t0;
         tc_fence_after();
+        // per stage: one barrier wait, four MMAs, one commit; everything else is uniform address arithmetic
         for (int ks = 0; ks < p.num_k_stages; ++ks, ++it) {
-          const int s = it % STAGES;
-          t0 = tick<PROF>();
+          const uint32_t s = it % STAGES;
           if (!mbar_wait_bounded_spin(bar_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
-          const long long t1 = tick<PROF>();
-          t_full += t1 - t0;
           tc_fence_after();
           const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + s * L::SF_TMEM_BUF;
           const uint32_t sfa_t = sf_buf, sfb_t = sf_buf + L::SFA_COLS;
@@ -262,30 +258,21 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             }
           } else {
             const int kmma = (k_left + 63) / 64;
-            for (int k = 0; k < kmma; ++k) {
-              const uint32_t blk = NVFP4 ? (uint32_t)k : (uint32_t)(k >> 1);
-              tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k & 3],
-                                                  sfa_t + 4 * blk, sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              if (k < kmma) {
+                const uint32_t blk = NVFP4 ? (uint32_t)k : (uint32_t)(k >> 1);
+                tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k], sfa_t + 4 * blk,
+                                                    sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+              }
             }
           }
-          tc_commit_pair(bar_empty + 8 * s);          // frees the stage (the leader's producer tells the follower)
-          if (PROF && p.profile && pair_id == 0 && it < 512) {
-            long long* o = p.profile + 74 * 64 + (size_t)it * 4;
-            o[0] = t0 - t_begin; o[1] = t1 - t_begin; o[2] = tick<PROF>() - t_begin; o[3] = 0;
-          }
+          tc_commit_pair_multicast(bar_empty + 8 * s, 3);   // frees the stage in both CTAs
         }
         if (ok) {
           tc_commit_pair(bar_acc_full);
           tc_commit_pair(peer_acc_full);
         }
-      }
-      if (PROF && p.profile) {
-        long long* o = p.profile + (size_t)pair_id * 64;
-        unsigned long long ns_end = 0;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_end));
-        o[0] = tick<PROF>() - t_begin; o[1] = t_acc; o[2] = t_full; o[3] = 0; o[4] = it; o[14] = t_begin;
-        o[15] = (long long)(ns_end - ns_begin);
-        o[16] = (long long)ns_entry; o[17] = (long long)ns_setup; o[18] = (long long)ns_begin; o[19] = (long long)ns_end;
       }
       if (!ok) {
         *abort_flag = 1;
@@ -305,14 +292,9 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int my_tiles = pair_id < p.num_tiles ? (p.num_tiles - pair_id + num_pairs - 1) / num_pairs : 0;
     const uint32_t n_it = (uint32_t)my_tiles * (uint32_t)p.num_k_stages;
     bool ok = true;
-    long long m_sf = 0, m_st = 0, m_arr = 0;
-    const long long m_begin = tick<PROF>();
     for (uint32_t it = 0; it < n_it && ok; ++it) {
       const int s = it % STAGES;
-      long long t0 = tick<PROF>();
       if (!mbar_wait_bounded(bar_sf_full + 8 * s, (it / STAGES) & 1, abort_flag)) { ok = false; break; }
-      long long t1 = tick<PROF>();
-      m_sf += t1 - t0;
       tc_fence_after();
       const uint32_t sf_buf = tmem_base + SF_TMEM_BASE + s * L::SF_TMEM_BUF + lane_base;
       const uint8_t* sfa_s = smem + L::OFF_SFA + s * L::SFA_BYTES + lane * 16;
@@ -327,18 +309,10 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           tc_st_32x32b_x4(sf_buf + L::SFA_COLS + 8 * j + 4 * h, b.x, b.y, b.z, b.w);
         }
       }
-      long long t2 = tick<PROF>();
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      long long t3 = tick<PROF>();
-      m_st += t3 - t2;
       if (lane == 0) mbar_arrive_cluster(lead_full + 8 * s);
-      m_arr += tick<PROF>() - t3;
-    }
-    if (PROF && p.profile && warp == 2 && lane == 0) {
-      long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
-      o[5] = m_sf; o[6] = 0; o[7] = m_st; o[8] = m_arr; o[9] = tick<PROF>() - m_begin;
     }
     if (!ok && lane == 0) {
       *abort_flag = 1;
@@ -351,14 +325,10 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const float alpha = *p.alpha;
     uint32_t tile_count = 0;
     bool ok = true;
-    long long e_wait = 0, e_drain = 0, e_store = 0, e_ld0 = 0;
     for (int tile = pair_id; tile < p.num_tiles && ok; tile += num_pairs, ++tile_count) {
       int m_pair, n_blk;
       pair_tile_coords(p, tile, m_pair, n_blk);
-      long long t0 = tick<PROF>();
       if (!mbar_wait_bounded(bar_acc_full, tile_count & 1, abort_flag)) { ok = false; break; }
-      long long t1 = tick<PROF>();
-      e_wait += t1 - t0;
       tc_fence_after();
       // 1) drain this warp's 64 fp32 columns in one round (two 32-column loads in flight): with sixteen
       //    warps the whole accumulator is in registers after a single load latency
@@ -369,26 +339,22 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       tc_ld_32x32b_x32(tsrc, ra);
       tc_ld_32x32b_x32(tsrc + 32, rb);
       tc_wait_ld();
-      e_ld0 += tick<PROF>() - t1;
       // 2) hand the accumulator back: the next tile's MMAs may start while we convert and write out
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
-      long long t2 = tick<PROF>();
-      e_drain += t2 - t1;
       // 3) wait for this warp's slot.  All sixteen warps converting and storing at once costs the next
       //    tile about 1400 cycles: the four warps that share the MMA thread's scheduler take its issue
       //    slots just when the tensor pipe is empty, and sixteen 4 KiB TMA stores in one burst hold up the
       //    operand loads behind them.  Spread over the next tile's main loop both disappear in its slack.
       if (tile + num_pairs < p.num_tiles) {          // not after the last tile: there is nothing left to protect
-        const long long due = clock64() + p.stagger_base + (long long)(col_q * 4 + quarter) * p.stagger_step;
+        const long long due = clock64() + (long long)(col_q * 4 + quarter) * p.stagger_step;
         while (clock64() < due) __nanosleep(64);
       }
       uint32_t pk[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const uint32_t* rr = j < 16 ? ra : rb;
-        if (PROF && (p.tune_skip & 1)) { pk[j] = rr[(2 * j) & 31]; continue; }
         float v0 = __uint_as_float(rr[(2 * j) & 31]) * alpha;
         float v1 = __uint_as_float(rr[(2 * j + 1) & 31]) * alpha;
         if (p.bias) {
@@ -401,19 +367,21 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         __nv_bfloat162 hh = __floats2bfloat162_rn(v0, v1);
         pk[j] = *reinterpret_cast<uint32_t*>(&hh);
       }
-      // 4) write out through shared memory: each warp owns a 32-row x 128-byte staging box (128-byte
-      //    swizzle, so the 16-byte row pieces of the 32 lanes spread over all banks) and sends it with
-      //    one TMA store; the store clips rows >= M and columns >= N.  Direct 16-byte stores from 32
-      //    different rows per instruction kept the load/store path busy for ~7000 cycles per tile and
-      //    slowed the MMA issue in that time.
-      const uint32_t box_off = (uint32_t)(L::OFF_OUT + (col_q * 4 + quarter) * L::OUT_BOX_BYTES);
+      // 4) write out through shared memory: a 32-row x 128-byte staging box (128-byte swizzle, so the
+      //    16-byte row pieces of the 32 lanes spread over all banks) sent with one TMA store, which clips
+      //    rows >= M and columns >= N.
+      //    The boxes are shared: slot i uses box i % NBOX after slot i - NBOX (the last user of the previous
+      //    tile for the first NBOX slots).  Every slot has a barrier of its own on which it announces that
+      //    its store has read the box, once per tile, and the next user of the box waits for exactly that
+      //    phase (one arriving and one waiting warp per barrier, never more than a phase apart).
+      const int slot = col_q * 4 + quarter;
+      const uint32_t box_off = (uint32_t)(L::OFF_OUT + (slot % L::NBOX) * L::OUT_BOX_BYTES);
       const uint32_t stage_out = sbase + box_off;
-      if (PROF && (p.tune_skip & 2)) {
-        if (pk[0] == 0x12345678u && pk[31] == 0x9abcdef0u) *abort_flag = 2;   // keeps the values alive
-        continue;
+      if (slot >= L::NBOX) {
+        if (!mbar_wait_bounded(bar_box + 8 * (slot - L::NBOX), tile_count & 1, abort_flag)) { ok = false; break; }
+      } else if (tile_count > 0) {
+        if (!mbar_wait_bounded(bar_box + 8 * (slot + 16 - L::NBOX), (tile_count - 1) & 1, abort_flag)) { ok = false; break; }
       }
-      if (lane == 0) bulk_wait_group_read0();      // the previous store has read the box
-      __syncwarp();
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         st_shared_v4(stage_out + (uint32_t)lane * 128u + (uint32_t)((q ^ (lane & 7)) * 16), pk[4 * q], pk[4 * q + 1],
@@ -439,14 +407,14 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               if (pr < push.n) *reinterpret_cast<uint4*>(push.out[pr] + (long long)(row0 + r) * push.ld + col) = v;
           }
         }
+        __syncwarp();
       }
-      e_store += tick<PROF>() - t2;
+      if (lane == 0) {
+        bulk_wait_group_read0();                   // the store has read the box: the next user may overwrite it
+        mbar_arrive(bar_box + 8 * slot);
+      }
     }
     if (lane == 0) bulk_wait_group0();   // my stores are complete before the CTA may exit
-    if (PROF && p.profile && warp == 6 && lane == 0) {
-      long long* o = p.profile + (size_t)pair_id * 64 + rank * 32;
-      o[10] = e_wait; o[11] = e_drain; o[12] = e_store; o[13] = e_ld0;
-    }
     if (!ok && lane == 0) {
       *abort_flag = 1;
       atomicExch(p.error_flag, 1);
@@ -455,11 +423,6 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   tc_fence_before();
   __syncthreads();
-  if (PROF && p.profile && threadIdx.x == 0 && rank == 0) {
-    unsigned long long ns_done = 0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_done));
-    p.profile[(size_t)pair_id * 64 + 20] = (long long)ns_done;
-  }
   cluster_sync_all();          // neither CTA leaves while its peer may still signal its barriers
   if (warp == 1) {
     __syncwarp();
@@ -472,17 +435,15 @@ template <bool NVFP4>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                 const CUtensorMap& tout, PairParams p, const PushParams& push, cudaStream_t stream) {
   using L = PairSmem<NVFP4>;
-  auto kern = push.n > 0 ? gemm_fp4_pair_kernel<NVFP4, false, true>
-              : p.profile   ? gemm_fp4_pair_kernel<NVFP4, true, false>
-                            : gemm_fp4_pair_kernel<NVFP4, false, false>;
-  static bool configured[64] = {};
+  auto kern = push.n > 0 ? gemm_fp4_pair_kernel<NVFP4, true> : gemm_fp4_pair_kernel<NVFP4, false>;
+  // one-time per device (idempotent: concurrent first calls set the same attribute)
+  static std::atomic<bool> configured[64];
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-    configured[dev] = true;
+  if (dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    configured[dev].store(true, std::memory_order_release);
   }
   int pairs = sm_count() / 2;
   if (pairs > p.num_tiles) pairs = p.num_tiles;
@@ -531,27 +492,11 @@ int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const 
   push.n = n_peers;
   push.ld = ldc;
   for (int i = 0; i < n_peers && i < 7; ++i) push.out[i] = reinterpret_cast<__nv_bfloat16*>(peers[i]);
-  {
-    const char* pe = getenv("FPQ_GEMM_PROFILE_PTR");   // tuning aid: address of a device buffer of 8 int64 per pair
-    p.profile = pe ? reinterpret_cast<long long*>(strtoull(pe, nullptr, 0)) : nullptr;
-  }
-  {
-    const char* tn = getenv("FPQ_GEMM_TUNE_N");
-    p.tune_n = tn ? atoi(tn) : 0;
-    // the sixteen slots cover at most 60 % of a tile's main loop (740 cycles per K stage)
-    p.stagger_base = 0;
-    p.stagger_step = (int)(p.num_k_stages * 740 * 6 / 10 / 16);
-    if (p.stagger_step > 300) p.stagger_step = 300;
-    if (const char* sg = getenv("FPQ_GEMM_STAGGER")) {   // tuning aid: "base,step" in cycles
-      int b0 = 0, s0 = 0;
-      if (sscanf(sg, "%d,%d", &b0, &s0) == 2) { p.stagger_base = b0; p.stagger_step = s0; }
-    }
-    const char* ts = getenv("FPQ_GEMM_TUNE_SKIP");
-    p.tune_skip = ts ? atoi(ts) : 0;
-  }
-  const char* e = getenv("FPQ_GEMM_RASTER");
-  p.raster_group = e ? atoi(e) : 8;
-  if (p.raster_group < 1) p.raster_group = 1;
+  // Time slots of the sixteen epilogue warps: together at most 60 % of a tile's main loop (~740 cycles per
+  // K stage), and never more than 300 cycles apart (larger steps delay the next tile's drain).
+  p.stagger_step = (int)(p.num_k_stages * 740 * 6 / 10 / 16);
+  if (p.stagger_step > 300) p.stagger_step = 300;
+  p.raster_group = 8;
   CUtensorMap ta, tb, tsa, tsb, tout;
   // output as 64-column x 32-row boxes of bf16 (128 bytes per box row, 128-byte swizzle)
   if (int rc = make_tensor_map_2d(&tout, out, 2, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 32, 1)) return rc;

@@ -87,7 +87,11 @@ gemm_fp4_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + L::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::OFF_MISC + 4);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // warp index through a shuffle (known to be the same in all lanes) and single-thread roles through
+  // elect.sync: the role code then runs on the uniform datapath, where the operands of tcgen05 / TMA
+  // instructions live; with `threadIdx.x >> 5` and `lane == 0` every such instruction cost its thread
+  // 75-150 cycles of register moves
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank(), csize = cluster_nctarank();
   const int n_blk = blockIdx.x / csize;                       // 128 weight rows per cluster
   const int ks_begin = (int)rank * p.stages_per_cta;
@@ -118,7 +122,7 @@ gemm_fp4_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
   const uint32_t tmem_base = *tmem_base_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       bool ok = true;
       for (int i = 0; i < my_stages; ++i) {
         const int ks = ks_begin + i, s = i % STAGES;
@@ -140,7 +144,7 @@ gemm_fp4_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
         (void)mbar_wait_bounded(bar_full + 8 * (j % STAGES), (j / STAGES) & 1, &never, 200000000LL);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {
       bool ok = true;
       for (int i = 0; i < my_stages; ++i) {
         const int ks = ks_begin + i, s = i % STAGES;

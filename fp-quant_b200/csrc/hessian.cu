@@ -134,7 +134,11 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const uint32_t bar_acc_empty = bar_acc_full + 16;       // [2]
   volatile uint32_t* tmem_base_slot = reinterpret_cast<volatile uint32_t*>(smem + Smem::OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::OFF_MISC + 4);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // warp index through a shuffle (known to be the same in all lanes) and single-thread roles through
+  // elect.sync: the role code then runs on the uniform datapath, where the operands of tcgen05 / TMA
+  // instructions live; with `threadIdx.x >> 5` and `lane == 0` every such instruction cost its thread
+  // 75-150 cycles of register moves
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -165,7 +169,7 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   grid_dependency_wait();
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
@@ -201,7 +205,7 @@ hessian_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         (void)mbar_wait_bounded(bar_full + 8 * (j % STAGES), (j / STAGES) & 1, &never, 200000000LL);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (elect_one()) {
       const uint32_t idesc = make_idesc_bf16(TILE, TILE_N, true, true);   // per 128-row half
       uint32_t it = 0, tile_count = 0;
       bool ok = true;

@@ -265,6 +265,14 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
 __device__ __forceinline__ void tc_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
+// The same arrival delivered to the barrier at this shared-memory offset in every CTA of `cta_mask` (a signal
+// between the CTAs of the pair; no data is moved).
+__device__ __forceinline__ void tc_commit_pair_multicast(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(cta_mask)
+      : "memory");
+}
 template <bool NVFP4>
 __device__ __forceinline__ void tc_mma_fp4_block_scaled_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                              uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
