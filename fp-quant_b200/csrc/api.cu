@@ -32,7 +32,7 @@ int sm_count() {
 
 }  // namespace fpq
 
-extern "C" int fpq_version(void) { return 104; }
+extern "C" int fpq_version(void) { return 105; }
 
 extern "C" const char* fpq_last_error(void) { return fpq::get_error(); }
 

@@ -291,11 +291,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cuda
   }
   p.num_n_blocks = (p.N + BN - 1) / BN;
   p.num_tiles = p.num_m_blocks * p.num_n_blocks;
-  {
-    const char* e = getenv("FPQ_GEMM_RASTER");
-    p.raster_group = e ? atoi(e) : 8;
-    if (p.raster_group < 1) p.raster_group = 1;
-  }
+  p.raster_group = 8;
   int grid = sm_count();
   if (grid > p.num_tiles) grid = p.num_tiles;
   kern<<<grid, NUM_THREADS, L::DYN_BYTES, stream>>>(ta, tb, p);
@@ -439,17 +435,14 @@ extern "C" int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, cons
   if (M == 0) return FPQ_OK;
   {
     // Large M: CTA pairs (256 x 256 tiles).  Small M streams the weights once and stays on single CTAs.
-    const char* e = getenv("FPQ_GEMM_PAIR");
-    const bool use_pair = e ? atoi(e) != 0 : true;
-    const char* sm = getenv("FPQ_GEMM_SMALLM");
     // Up to 64 tokens the swap-AB kernel always wins; up to 128 it wins when the 128-row weight blocks
     // leave SMs free for split-K (measured under graph replay: 9.6 vs 18.4 us at N = K = 4096,
     // 14.4 vs 39.0 us at K = 12288, but 25.1 vs 20.0 us at N = 12288).
     const bool small = M <= 64 || (M <= 128 && (N + 127) / 128 <= sm_count() / 2);
-    if ((sm ? atoi(sm) != 0 : true) && small)
+    if (small)
       return gemm_fp4_smallm(a_codes, b_codes, a_scales_swizzled, b_scales_swizzled, alpha, bias_bf16, out_bf16, M, N,
                              K, format, error_flag, (cudaStream_t)stream);
-    if (use_pair && M > 128 && N >= 256)
+    if (M > 128 && N >= 256)
       return gemm_fp4_pair(a_codes, b_codes, a_scales_swizzled, b_scales_swizzled, alpha, bias_bf16, out_bf16, M, N, K,
                            format, error_flag, (cudaStream_t)stream);
   }

@@ -12,6 +12,8 @@
 #include <cstdlib>
 #include <vector>
 #include "common.cuh"
+
+#include <atomic>
 #include "sgemm.cuh"
 
 namespace fpq {
@@ -288,11 +290,7 @@ int tc_gemm3(float* C, int64_t ldc, int64_t M, int64_t N, int64_t K, const float
 // Products at least this large go to the tensor cores; smaller ones stay on the fp32 SIMT kernel, whose
 // launch is cheaper than the two conversion passes.
 bool tc_worthwhile(int64_t M, int64_t N, int64_t K) {
-  static const int64_t min_macs = [] {
-    const char* e = getenv("FPQ_TC_MIN_MACS_LOG2");       // tuning aid
-    return (int64_t)1 << (e ? atoi(e) : 25);
-  }();
-  return K % 64 == 0 && M * N * K >= min_macs;
+  return K % 64 == 0 && M * N * K >= ((int64_t)1 << 25);
 }
 
 // X = L^-1 given the inverses of the diagonal blocks already in X.  The block range [lo, hi) is halved
@@ -562,20 +560,43 @@ __global__ void split_bf16_kernel(const float* __restrict__ x, const float* __re
   }
 }
 
-// acc[0] += weight * sum(a .* b)
-__global__ void frobenius_dot_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t n, double weight,
-                                     double* acc) {
+// Deterministic reductions of the relative-MSE metric: every CTA writes the sum of its part to a slot of
+// its own (nothing is added atomically), and one warp adds the slots in a fixed order at the end.
+constexpr int MSE_DOT_BLOCKS = 1024;      // CTAs (and slots) of one frobenius_dot_kernel launch
+constexpr int MSE_REGION = FPQ_RELATIVE_MSE_ACC_DOUBLES / 2;   // slots per quantity (numerator / denominator)
+
+// partial[blockIdx.x] = weight * sum over this CTA's elements of a .* b
+__global__ void __launch_bounds__(256) frobenius_dot_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                            int64_t n, double weight, double* partial) {
+  __shared__ double warp_sum[8];
   double s = 0.0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
     s += (double)a[i] * (double)b[i];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if ((threadIdx.x & 31) == 0) atomicAdd(acc, weight * s);
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += warp_sum[w];
+    partial[blockIdx.x] = weight * t;
+  }
 }
 
-__global__ void ratio_kernel(const double* acc, float* out, double count) {
-  // mean(num) / (mean(den) + 1e-6), src/quantization/gptq.py:28-30
-  out[0] = (float)((acc[0] / count) / (acc[1] / count + 1e-6));
+// out = mean(num) / (mean(den) + 1e-6), src/quantization/gptq.py:28-30; num / den = the sums of the first
+// n_slots slots of the two regions, each lane adding its slots in index order, then a fixed shuffle tree.
+__global__ void ratio_kernel(const double* acc, int n_slots, float* out, double count) {
+  double v[2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    double s = 0.0;
+    for (int i = threadIdx.x; i < n_slots; i += 32) s += acc[(size_t)q * MSE_REGION + i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    v[q] = s;
+  }
+  if (threadIdx.x == 0) out[0] = (float)((v[0] / count) / (v[1] / count + 1e-6));
 }
 
 }  // namespace
@@ -611,17 +632,22 @@ extern "C" int fpq_hessian_prepare_noalloc(float* H, int64_t d, const float* W, 
                 (long long)d, FPQ_PREPARE_NOALLOC_MAX_D);
   // The array's name is only a host-side handle; kernels need its device address, which differs per
   // GPU.  Resolve it once per device, with that device current.
-  static uint8_t* scratch_of_device[64] = {};
+  static std::atomic<uint8_t*> scratch_of_device[64];      // two threads making the first call store the same address
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
   FPQ_CHECK_ARG(dev >= 0 && dev < 64, "device index %d out of range", dev);
-  if (scratch_of_device[dev] == nullptr) {
-    uint8_t* ptr = nullptr;
-    FPQ_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_prepare_scratch));
-    FPQ_CHECK_ARG(ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
-    scratch_of_device[dev] = ptr;
+  // The scratch is the current device's copy of the array, so H, W and the stream must belong to the
+  // current device: a Hessian on another GPU would be masked with flags this GPU never wrote.
+  cudaPointerAttributes attr{};
+  FPQ_CHECK_CUDA(cudaPointerGetAttributes(&attr, H));
+  FPQ_CHECK_ARG(attr.type != cudaMemoryTypeDevice || attr.device == dev,
+                "H lives on device %d but the current device is %d: make the device that owns H current", attr.device, dev);
+  uint8_t* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    FPQ_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_prepare_scratch));
+    FPQ_CHECK_ARG(scratch != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    scratch_of_device[dev].store(scratch, std::memory_order_release);
   }
-  uint8_t* scratch = scratch_of_device[dev];
   cudaStream_t st = (cudaStream_t)stream;
   // Every flag in [0, d) is rewritten before it is read, so nothing needs clearing between calls.
   dead_columns_kernel<<<(unsigned)((d + 255) / 256), 256, 0, st>>>(W, rows, d, scratch);
@@ -660,11 +686,7 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
   // updates only touch the outer block's own columns (all rows below); the rest of the trailing matrix gets
   // one rank-(OB*128) update per outer block, which reads and writes it 1/OB as often as a rank-128
   // update per diagonal block would (those updates are bound by that traffic, not by the tensor pipe).
-  int OB = 4;
-  if (const char* e = getenv("FPQ_CHOL_OB")) {          // tuning aid
-    const int v = atoi(e);
-    if (v >= 1 && v <= 16) OB = v;
-  }
+  constexpr int OB = 4;
   const int64_t ws_elems = 6 * half * half;
   for (int ob = 0; ob < nblk; ob += OB) {
     const int64_t R = (int64_t)ob * NB;
@@ -687,11 +709,7 @@ extern "C" int fpq_cholesky_inverse_upper(const float* H, float* U, int64_t d, f
       const int64_t inner = R + Wd - (r + nb);
       if (inner <= 0) continue;
       float* Cin = L + (r + nb) * d + (r + nb);
-      static const int64_t inner_min = [] {
-        const char* e = getenv("FPQ_CHOL_INNER_TC_LOG2");       // tuning aid
-        return (int64_t)1 << (e ? atoi(e) : 25);
-      }();
-      if (nb == NB && tc_worthwhile(below, inner, nb) && below * inner * nb >= inner_min &&
+      if (nb == NB && tc_worthwhile(below, inner, nb) &&
           3 * (int64_t)nb * round64(below) <= ws_elems) {
         if (int rc = tc_gemm3(Cin, d, below, inner, nb, L + (r + nb) * d + r, d, nullptr, 0, -1.0f, 1.0f, ws, error_flag, st))
           return rc;
@@ -811,17 +829,18 @@ extern "C" int fpq_gptq_quantize_ordered(float* W, int64_t rows, int64_t cols, c
 extern "C" int fpq_relative_mse(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
                                 float* diff_workspace, double* acc_workspace, float* out, fpq_stream_t stream) {
   FPQ_CHECK_ARG(Wq && W && H && diff_workspace && acc_workspace && out, "NULL pointer");
+  const int64_t tiles = ((rows + 127) / 128) * ((d + 127) / 128);      // CTAs of one fp32 product = partial sums
+  FPQ_CHECK_ARG(tiles <= MSE_REGION, "matrix too large for the %d partial-sum slots of the workspace", MSE_REGION);
   cudaStream_t st = (cudaStream_t)stream;
-  FPQ_CHECK_CUDA(cudaMemsetAsync(acc_workspace, 0, 2 * sizeof(double), st));
   diff_kernel<<<grid1d(rows * d), 256, 0, st>>>(Wq, W, diff_workspace, rows * d);
   FPQ_CHECK_LAUNCH();
   SgemmArgs a{};
   a.lda = d; a.B = H; a.ldb = d; a.M = (int)rows; a.N = (int)d; a.K = (int)d; a.alpha = 1.0f; a.ldd = d;
   a.A = diff_workspace; a.D = diff_workspace; a.dot_out = acc_workspace;
   if (int rc = sgemm(a, false, SGEMM_DOT, st)) return rc;
-  a.A = W; a.D = W; a.dot_out = acc_workspace + 1;
+  a.A = W; a.D = W; a.dot_out = acc_workspace + MSE_REGION;
   if (int rc = sgemm(a, false, SGEMM_DOT, st)) return rc;
-  ratio_kernel<<<1, 1, 0, st>>>(acc_workspace, out, (double)rows * (double)d);
+  ratio_kernel<<<1, 32, 0, st>>>(acc_workspace, (int)tiles, out, (double)rows * (double)d);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
 }
@@ -840,18 +859,19 @@ extern "C" int fpq_relative_mse_tc(const float* Wq, const float* W, const float*
   cudaStream_t st = (cudaStream_t)stream;
   __nv_bfloat16* hi = reinterpret_cast<__nv_bfloat16*>(bf16_workspace);
   __nv_bfloat16* lo = hi + rows * d;
-  FPQ_CHECK_CUDA(cudaMemsetAsync(acc_workspace, 0, 2 * sizeof(double), st));
+  // slots [0, 1024) and [1024, 2048) of a region take the two terms of a quantity
   for (int which = 0; which < 2; ++which) {
+    double* region = acc_workspace + (size_t)which * MSE_REGION;
     split_bf16_kernel<<<grid1d(rows * d), 256, 0, st>>>(which == 0 ? Wq : W, which == 0 ? W : nullptr, hi, lo, rows * d);
     FPQ_CHECK_LAUNCH();
     if (int rc = fpq_hessian_accumulate(gram_workspace, d, hi, nullptr, rows, 1.0f, 0.0f, error_flag, stream)) return rc;
-    frobenius_dot_kernel<<<grid1d(d * d), 256, 0, st>>>(H, gram_workspace, d * d, 1.0, acc_workspace + which);
+    frobenius_dot_kernel<<<MSE_DOT_BLOCKS, 256, 0, st>>>(H, gram_workspace, d * d, 1.0, region);
     FPQ_CHECK_LAUNCH();
     if (int rc = fpq_hessian_accumulate(gram_workspace, d, hi, lo, rows, 1.0f, 0.0f, error_flag, stream)) return rc;
-    frobenius_dot_kernel<<<grid1d(d * d), 256, 0, st>>>(H, gram_workspace, d * d, 2.0, acc_workspace + which);
+    frobenius_dot_kernel<<<MSE_DOT_BLOCKS, 256, 0, st>>>(H, gram_workspace, d * d, 2.0, region + MSE_DOT_BLOCKS);
     FPQ_CHECK_LAUNCH();
   }
-  ratio_kernel<<<1, 1, 0, st>>>(acc_workspace, out, (double)rows * (double)d);
+  ratio_kernel<<<1, 32, 0, st>>>(acc_workspace, 2 * MSE_DOT_BLOCKS, out, (double)rows * (double)d);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
 }

@@ -638,6 +638,95 @@ __global__ void __launch_bounds__(256, Prefetches<IN_BF16, MODE>::value ? FPQ_Q_
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// SiLU(gate) * up fused in front of the rotate + quantise pass: the input of an MLP's down-projection
+// (src/utils/llama_utils.py:62-70 of IST-DASLab/FP-Quant computes `act_fn(gate) * up`, rotates it and
+// quantises it in three passes over memory).  The activation keeps the reference's rounding points: it is
+// what torch computes for bf16 tensors, silu in fp32 rounded to bf16, then the product rounded to bf16;
+// from there on the chunk goes through process_chunk like any bf16 input.
+__device__ __forceinline__ uint32_t silu_mul_word(uint32_t g2, uint32_t u2) {
+  const float g0 = __uint_as_float(g2 << 16), g1 = __uint_as_float(g2 & 0xffff0000u);
+  const float u0 = __uint_as_float(u2 << 16), u1 = __uint_as_float(u2 & 0xffff0000u);
+  // x / (1 + exp(-x)) with the library exponential and an IEEE division, as torch evaluates silu
+  const float s0 = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(g0, __fadd_rn(1.0f, expf(-g0)))));
+  const float s1 = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(g1, __fadd_rn(1.0f, expf(-g1)))));
+  const __nv_bfloat162 h = __floats2bfloat162_rn(__fmul_rn(s0, u0), __fmul_rn(s1, u1));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int GH, int FMT>
+__global__ void __launch_bounds__(256, 2) quant_silu_mul_kernel(const QuantParams p, const void* up) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t stride = (((int64_t)gridDim.x * blockDim.x) >> 5) * 32;
+  launch_dependents();
+  grid_dependency_wait();
+  float gs = 0.0f, rgs = 0.0f;
+  if (FMT == FPQ_FMT_NVFP4) {
+    gs = *p.gs;
+    rgs = gs == 0.0f ? 0.0f : __frcp_rn(gs);
+  }
+  float unused_max = 0.0f;
+  int64_t cb = warp * 32;
+  RawChunk<true> g, u;
+  if (cb < p.n_chunks) {
+    load_raw(p.x, cb + lane, cb + lane < p.n_chunks, g);
+    load_raw(up, cb + lane, cb + lane < p.n_chunks, u);
+  }
+  while (cb < p.n_chunks) {
+    RawChunk<true> h;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) h.w[j] = silu_mul_word(g.w[j], u.w[j]);
+    const int64_t nx = cb + stride + lane;          // the next chunk's loads fly while this one is quantised
+    load_raw(p.x, nx, nx < p.n_chunks, g);
+    load_raw(up, nx, nx < p.n_chunks, u);
+    process_chunk<GH, FMT, true, MODE_CODES>(p, h, cb + lane, cb + lane < p.n_chunks, lane, gs, rgs, unused_max);
+    cb += stride;
+  }
+  if (p.pad_rows != 0) {
+    const int64_t n_words = (int64_t)p.pad_rows * p.sf_tiles_per_row_block;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+      const uint32_t r = p.rows + (uint32_t)(w / p.sf_tiles_per_row_block);
+      const uint32_t kb = (uint32_t)(w % p.sf_tiles_per_row_block);
+      *reinterpret_cast<uint32_t*>(p.sbytes + swizzled_offset(r, kb * 4u, p.sf_tiles_per_row_block)) = 0u;
+    }
+  }
+}
+
+template <int GH, int FMT>
+int launch_silu_mul(const QuantParams& params, const void* up, cudaStream_t stream) {
+  QuantParams p = params;
+  p.row_magic = (p.chunks_per_row >= 2 && p.n_chunks < (1ll << 32)) ? ~0ull / p.chunks_per_row + 1 : 0;
+  const int64_t blocks_needed = ceil_div64(ceil_div64(p.n_chunks, 32), 8);
+  int64_t blocks = (int64_t)sm_count() * 2;          // persistent: the two resident blocks per SM
+  if (blocks > blocks_needed) blocks = blocks_needed;
+  if (blocks < 1) blocks = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_dependent_launch() ? 1 : 0;
+  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, quant_silu_mul_kernel<GH, FMT>, p, up));
+  return FPQ_OK;
+}
+
+template <int FMT>
+int launch_silu_mul_gh(int gh, const QuantParams& p, const void* up, cudaStream_t stream) {
+  switch (gh) {
+    case 0: return launch_silu_mul<0, FMT>(p, up, stream);
+    case 16: return launch_silu_mul<16, FMT>(p, up, stream);
+    case 32: return launch_silu_mul<32, FMT>(p, up, stream);
+    case 64: return launch_silu_mul<64, FMT>(p, up, stream);
+    case 128: return launch_silu_mul<128, FMT>(p, up, stream);
+  }
+  set_error("hadamard_group must be 0, 16, 32, 64 or 128 (got %d)", gh);
+  return FPQ_ERR_INVALID_ARGUMENT;
+}
+
 template <int GH, int FMT, bool IN_BF16, int MODE>
 int launch_one(const QuantParams& params, cudaStream_t stream) {
   QuantParams p = params;
@@ -1046,6 +1135,36 @@ extern "C" int fpq_quantize(const void* x, int dtype, int64_t rows, int64_t cols
     p.pad_rows = (uint32_t)(ceil_div64(rows, 128) * 128 - rows);
   }
   return launch_mode<MODE_CODES>(hadamard_group, format, dtype, p, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_quantize_silu_mul(const void* gate_bf16, const void* up_bf16, int64_t rows, int64_t cols,
+                                     int hadamard_group, int format, const float* global_scale, uint8_t* codes,
+                                     uint8_t* scale_bytes, int scale_layout, fpq_stream_t stream) {
+  if (int rc = check_common(gate_bf16, FPQ_DT_BF16, rows, cols, hadamard_group)) return rc;
+  FPQ_CHECK_ARG(up_bf16 != nullptr && ((uintptr_t)up_bf16 & 31) == 0, "up must be non-NULL and 32-byte aligned");
+  FPQ_CHECK_ARG(format == FPQ_FMT_MXFP4 || format == FPQ_FMT_NVFP4, "format must be FPQ_FMT_MXFP4 or FPQ_FMT_NVFP4");
+  FPQ_CHECK_ARG(format != FPQ_FMT_NVFP4 || global_scale != nullptr, "NVFP4 needs a global_scale pointer");
+  FPQ_CHECK_ARG(scale_layout == FPQ_SCALES_ROWMAJOR || scale_layout == FPQ_SCALES_SWIZZLED, "bad scale_layout");
+  FPQ_CHECK_ARG(codes != nullptr && scale_bytes != nullptr, "codes and scale_bytes are required");
+  FPQ_CHECK_ARG(((uintptr_t)codes & 15) == 0 && ((uintptr_t)scale_bytes & 15) == 0, "outputs must be 16-byte aligned");
+  if (rows == 0) return FPQ_OK;
+  const int g = format == FPQ_FMT_NVFP4 ? 16 : 32;
+  QuantParams p{};
+  p.x = gate_bf16;
+  p.n_chunks = rows * cols / 32;
+  p.chunks_per_row = (uint32_t)(cols / 32);
+  p.codes = codes;
+  p.sbytes = scale_bytes;
+  p.gs = global_scale;
+  p.sf_tiles_per_row_block = (uint32_t)ceil_div64(cols / g, 4);
+  p.layout = scale_layout;
+  if (scale_layout == FPQ_SCALES_SWIZZLED) {
+    FPQ_CHECK_ARG(rows < ((int64_t)1 << 31), "too many rows for the swizzled scale layout");
+    p.rows = (uint32_t)rows;
+    p.pad_rows = (uint32_t)(ceil_div64(rows, 128) * 128 - rows);
+  }
+  return format == FPQ_FMT_NVFP4 ? launch_silu_mul_gh<FPQ_FMT_NVFP4>(hadamard_group, p, up_bf16, (cudaStream_t)stream)
+                                 : launch_silu_mul_gh<FPQ_FMT_MXFP4>(hadamard_group, p, up_bf16, (cudaStream_t)stream);
 }
 
 extern "C" int fpq_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,

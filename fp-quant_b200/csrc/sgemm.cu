@@ -31,6 +31,7 @@ __device__ __forceinline__ void sgemm_body(const SgemmArgs& a) {
   const int tid = threadIdx.x;
   const int bm = blockIdx.y * TM, bn = blockIdx.x * TN;
   if (bm >= a.M || bn >= a.N) return;                   // batched launches size the grid for the largest entry
+                                                        // (SGEMM_DOT is never batched: its grid covers the matrix exactly)
   if (EPI == SGEMM_LOWER && bn > bm + TM - 1) return;   // tile strictly above the diagonal
 
   const int ty = tid >> 4, tx = tid & 15;
@@ -129,9 +130,19 @@ __device__ __forceinline__ void sgemm_body(const SgemmArgs& a) {
     }
   }
   if (EPI == SGEMM_DOT) {
+    // one partial sum per CTA, written (not added) to its own slot: the caller sums the slots in a fixed
+    // order, so the result does not depend on the order in which CTAs finish
+    __shared__ double warp_sum[8];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
-    if ((tid & 31) == 0) atomicAdd(a.dot_out, local);
+    if ((tid & 31) == 0) warp_sum[tid >> 5] = local;
+    __syncthreads();
+    if (tid == 0) {
+      double t = 0.0;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += warp_sum[w];
+      a.dot_out[(size_t)blockIdx.y * gridDim.x + blockIdx.x] = t;
+    }
   }
 }
 

@@ -24,7 +24,7 @@ struct SgemmArgs {
   int M, N, K;
   float alpha, beta;
   const float* D; int64_t ldd;   // SGEMM_DOT: elementwise partner
-  double* dot_out;               // SGEMM_DOT: atomically accumulated sum
+  double* dot_out;               // SGEMM_DOT: one partial sum per CTA, slot blockIdx.y * gridDim.x + blockIdx.x
 };
 
 int sgemm(const SgemmArgs& a, bool b_transposed, int epilogue, cudaStream_t stream);

@@ -17,6 +17,7 @@ FMT_MXFP4, FMT_NVFP4 = 0, 1
 DT_BF16, DT_F32 = 0, 1
 SCALES_ROWMAJOR, SCALES_SWIZZLED = 0, 1
 OUT_CODES, OUT_GRID, OUT_DEQUANT, OUT_DEQUANT_STE = 0, 1, 2, 3
+RELATIVE_MSE_ACC_DOUBLES = 32768
 ERR_DEVICE_TIMEOUT = -4
 ERR_NOT_POSITIVE_DEFINITE = -5
 
@@ -31,6 +32,7 @@ _SIGNATURES = {
     "fpq_global_scale_update": [c_void_p, c_void_p, c_void_p, c_void_p],
     "fpq_quantize": [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                      c_int, c_void_p, c_void_p],
+    "fpq_quantize_silu_mul": [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "fpq_fake_quantize": [c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "fpq_quantize_quest": [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "fpq_fake_quantize_quest": [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p],

@@ -13,9 +13,11 @@ from torch import nn
 from ... import ops
 from ...rotation import sylvester
 from ..utils.config import FPQuantConfig, FPQuantDtype, validate_config
-from .linear_fns import FPQuant4x16MasterFn, FPQuant4x16NoMasterFn, forward_quantize, gemm_alpha
+from .linear_fns import (FPQuant4x16MasterFn, FPQuant4x16NoMasterFn, forward_gemm_blocked, forward_quantize,
+                         gemm_alpha)
 from .pseudoquant_linear_fns import PseudoQuant4x16MasterFn, PseudoQuant4x16NoMasterFn, forward_pseudoquantize
-from .qutlass_ops import HAS_QUTLASS, swizzle_scales_op  # noqa: F401  (HAS_QUTLASS kept for API compatibility)
+from .qutlass_ops import (HAS_QUTLASS, fused_silu_mul_quantize_blocked_op,  # noqa: F401  (HAS_QUTLASS: API compatibility)
+                          swizzle_scales_op)
 
 
 def get_hadamard_matrix(group_size: int, dtype: torch.dtype, device: torch.device):
@@ -134,6 +136,31 @@ class FPQuantLinear(nn.Module):
         if self._alpha is None or self._alpha_key != key:
             self._alpha, self._alpha_key = gemm_alpha(w, a), key
         return self._alpha
+
+    def forward_silu_mul(self, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+        """`self(silu(gate) * up)` for the down-projection of a gated MLP, with the activation computed inside
+        the quantise kernel (one pass over gate and up instead of three passes over memory; same rounding
+        points as the unfused computation).  Falls back to the plain forward for configurations the fused
+        kernel does not cover (pseudo-quantisation, master weights, QuEST scales, dense rotations, non-bf16)."""
+        cfg = self.config
+        fused = (cfg.forward_dtype in _SCALE_GROUP and cfg.backward_dtype == FPQuantDtype.BF16
+                 and not cfg.pseudoquantization and not cfg.store_master_weights and cfg.forward_method == "abs_max"
+                 and cfg.transform_init in ("hadamard", "identity")
+                 and gate.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and gate.is_cuda)
+        if not fused:
+            return self.forward(torch.nn.functional.silu(gate) * up)
+        lead = gate.shape[:-1]
+        g2, u2 = gate.contiguous().flatten(end_dim=-2), up.contiguous().flatten(end_dim=-2)
+        nv = cfg.forward_dtype == FPQuantDtype.NVFP4
+        rotation = 1 if cfg.transform_init == "hadamard" else 2
+        x_q, x_scales = fused_silu_mul_quantize_blocked_op(g2, u2, self.forward_hadamard_matrix,
+                                                           self.act_global_scale.float(), nv, rotation)
+        bias = self.bias if self.bias is not None and self.bias.dtype == torch.bfloat16 else None
+        y = forward_gemm_blocked(x_q, self.qweight, x_scales, self._blocked_weight_scales(), self._gemm_alpha(),
+                                 cfg.forward_dtype, bias)
+        if self.bias is not None and bias is None:
+            y = y + self.bias
+        return y.unflatten(dim=0, sizes=lead)
 
     # ------------------------------------------------------------------ forward
     def forward(self, x) -> torch.Tensor:

@@ -154,6 +154,29 @@ def _(x_flat, hadamard_matrix, global_scale, nvfp4, rotation=0, quest=False):
     return q, torch.empty(pr, pc, dtype=torch.uint8, device=x_flat.device)
 
 
+@torch.library.custom_op("fpq_b200::fused_silu_mul_quantize_blocked_op", mutates_args=())
+def fused_silu_mul_quantize_blocked_op(gate: torch.Tensor, up: torch.Tensor, hadamard_matrix: torch.Tensor,
+                                       global_scale: torch.Tensor, nvfp4: bool, rotation: int = 0
+                                       ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """`fused_quantize_blocked_op(silu(gate) * up, ...)` (abs_max scales) without writing the product to memory:
+    the step between an MLP's gate / up projections and its down projection (src/utils/llama_utils.py:62-70).
+    gate, up: bf16 [M, K]; Hadamard or identity rotation (other matrices take the unfused path)."""
+    kind, group = kind_of(rotation, hadamard_matrix)
+    if kind == "dense":
+        raise ValueError("the fused SiLU path supports the Hadamard and identity rotations")
+    fmt = "nvfp4" if nvfp4 else "mxfp4"
+    return ops.quantize_silu_mul(gate, up, fmt, group if kind == "hadamard" else 0, global_scale if nvfp4 else None,
+                                 swizzled=True)
+
+
+@fused_silu_mul_quantize_blocked_op.register_fake
+def _(gate, up, hadamard_matrix, global_scale, nvfp4, rotation=0):
+    rows, cols = gate.size(0), gate.size(1) // (16 if nvfp4 else 32)
+    pr, pc = _padded(rows, cols)
+    q = torch.empty(rows, gate.size(1) // 2, dtype=torch.uint8, device=gate.device)
+    return q, torch.empty(pr, pc, dtype=torch.uint8, device=gate.device)
+
+
 # --------------------------------------------------------------------------- matmul
 @torch.library.custom_op("fpq_b200::swizzle_scales_op", mutates_args=())
 def swizzle_scales_op(rowmajor: torch.Tensor) -> torch.Tensor:

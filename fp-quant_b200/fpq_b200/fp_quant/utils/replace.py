@@ -77,3 +77,29 @@ def finalize_master_weights(model: nn.Module, current_key_name=None) -> None:
                 module.config.store_master_weights = False
             if module.weight is not None:
                 module.pre_forward()
+
+
+def fuse_gated_mlp_activation(model: nn.Module) -> int:
+    """Route `down_proj(act_fn(gate_proj(x)) * up_proj(x))` of every gated-SiLU MLP whose down-projection is an
+    FPQuantLinear through `FPQuantLinear.forward_silu_mul`, which evaluates SiLU(gate) * up inside the quantise
+    kernel of the down-projection.  The reference leaves that product to a separate elementwise kernel followed
+    by the rotation and the quantiser (src/utils/llama_utils.py:62-70); this helper is an addition of this
+    package, not part of the reference's interface.  Modules are recognised by their attributes (`gate_proj`,
+    `up_proj`, `down_proj`, `act_fn` = SiLU), as the Llama / Qwen / Mistral MLP classes of transformers have them.
+    Returns the number of modules patched."""
+    import types
+
+    from ..module.linear import FPQuantLinear
+
+    def forward(self, x):
+        return self.down_proj.forward_silu_mul(self.gate_proj(x), self.up_proj(x))
+
+    patched = 0
+    for module in model.modules():
+        act = getattr(module, "act_fn", None)
+        is_silu = isinstance(act, nn.SiLU) or type(act).__name__ in ("SiLUActivation", "SiLU") or act is torch.nn.functional.silu
+        if (is_silu and isinstance(getattr(module, "down_proj", None), FPQuantLinear)
+                and hasattr(module, "gate_proj") and hasattr(module, "up_proj")):
+            module.forward = types.MethodType(forward, module)
+            patched += 1
+    return patched

@@ -135,6 +135,32 @@ def quantize(x: torch.Tensor, fmt: str, hadamard_group: int = 0, global_scale: O
     return q, sb, sf
 
 
+def quantize_silu_mul(gate: torch.Tensor, up: torch.Tensor, fmt: str, hadamard_group: int = 0,
+                      global_scale: Optional[torch.Tensor] = None, swizzled: bool = True):
+    """quantize(silu(gate) * up) in one pass: (codes u8 [rows, cols/2], scale bytes).  gate, up: bf16 [.., cols]."""
+    gate, rows, cols = _2d(gate)
+    up = _cuda(up, "up").contiguous()
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or up.numel() != gate.numel():
+        raise ValueError("gate and up must be bfloat16 tensors of the same shape")
+    sf_cols = cols // GROUP_OF[fmt]
+    dev = gate.device
+    q = torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev)
+    if swizzled:
+        pr, pc = padded_scale_shape(rows, sf_cols)
+        sb = (torch.zeros if pc != sf_cols else torch.empty)(pr, pc, dtype=torch.uint8, device=dev)
+    else:
+        sb = torch.empty(rows, sf_cols, dtype=torch.uint8, device=dev)
+    if fmt == "nvfp4":
+        if global_scale is None:
+            raise ValueError("nvfp4 needs a global_scale tensor")
+        global_scale = _cuda(global_scale, "global_scale").to(torch.float32)
+    with _guard(dev):
+        C.call("fpq_quantize_silu_mul", gate.data_ptr(), up.data_ptr(), rows, cols, hadamard_group, FORMATS[fmt],
+               _ptr(global_scale) if fmt == "nvfp4" else None, q.data_ptr(), sb.data_ptr(),
+               C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _stream(gate))
+    return q, sb
+
+
 def quantize_quest(x: torch.Tensor, hadamard_group: int = 0, swizzled: bool = False, return_mask: bool = False):
     """MXFP4 with the QuEST scale rule: (codes u8 [rows, cols/2], E8M0 scale bytes, clip mask u8 [rows, cols/8] | None)."""
     x, rows, cols = _2d(x)
@@ -382,14 +408,14 @@ def relative_mse(Wq: torch.Tensor, W: torch.Tensor, H: torch.Tensor, exact_fp32:
     if not exact_fp32 and d % 8 == 0:
         bf = torch.empty(2 * rows * d, dtype=torch.bfloat16, device=W.device)
         gram = torch.empty(d, d, dtype=torch.float32, device=W.device)
-        acc = torch.zeros(2, dtype=torch.float64, device=W.device)
+        acc = torch.empty(C.RELATIVE_MSE_ACC_DOUBLES, dtype=torch.float64, device=W.device)
         out = torch.empty(1, dtype=torch.float32, device=W.device)
         with _guard(W.device):
             C.call("fpq_relative_mse_tc", Wq.data_ptr(), W.data_ptr(), H.data_ptr(), rows, d, bf.data_ptr(),
                    gram.data_ptr(), acc.data_ptr(), out.data_ptr(), device_error_flag(W.device).data_ptr(), _stream(W))
         return out
     diff = torch.empty_like(W)
-    acc = torch.zeros(2, dtype=torch.float64, device=W.device)
+    acc = torch.empty(C.RELATIVE_MSE_ACC_DOUBLES, dtype=torch.float64, device=W.device)
     out = torch.empty(1, dtype=torch.float32, device=W.device)
     with _guard(W.device):
         C.call("fpq_relative_mse", Wq.data_ptr(), W.data_ptr(), H.data_ptr(), rows, d, diff.data_ptr(),

@@ -106,6 +106,20 @@ int fpq_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadam
                  int scale_layout, float* scales_f32, fpq_stream_t stream);
 
 /*
+ * fpq_quantize of the tensor `silu(gate) * up` without materialising it: the input of an MLP's down-projection,
+ * which the reference computes, rotates and quantises in separate passes over memory
+ * (src/utils/llama_utils.py:62-70: `x = self.act_fn(gate) * up`, `down_in_transform(x)`, then the activation
+ * quantiser of `down_proj`; in the inference library the same tensor reaches FPQuantLinear.forward of the
+ * down-projection, inference_lib/src/fp_quant/module/linear.py:250-368).  The reference's rounding points are
+ * kept: silu evaluated in fp32 as x / (1 + exp(-x)) and rounded to bf16, the product rounded to bf16, then
+ * rotation and quantisation in fp32 as in fpq_quantize.  gate, up: bf16 [rows, cols]; other arguments and
+ * constraints as for fpq_quantize (codes and scale_bytes are both required).
+ */
+int fpq_quantize_silu_mul(const void* gate_bf16, const void* up_bf16, int64_t rows, int64_t cols, int hadamard_group,
+                          int format, const float* global_scale, uint8_t* codes, uint8_t* scale_bytes,
+                          int scale_layout, fpq_stream_t stream);
+
+/*
  * Fused rotate + quantise + dequantise ("pseudo-quantisation"): y = grid(code) * scale
  * (or the straight-through form when ste != 0), same dtype as x.  Replaces the Triton
  * kernels mxfp4_forward_kernel / nvfp4_forward_kernel
@@ -245,6 +259,8 @@ int fpq_hessian_prepare(float* H, int64_t d, const float* W, int64_t rows, float
  *   - d must not exceed FPQ_PREPARE_NOALLOC_MAX_D; larger d is rejected with FPQ_ERR_INVALID_ARGUMENT.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current).  Make that first call before any stream capture begins.
+ *   - The scratch used is the CURRENT device's copy of the array: make the GPU that owns H, W and the
+ *     stream current before the call (a Hessian on another device is rejected).
  *   - All calls on one GPU share the array: calls whose kernels may overlap on the GPU (different
  *     streams without ordering between them) race on it.  Serialise them, or use fpq_hessian_prepare.
  *     The array keeps the last call's flags; every flag the next call reads is rewritten first, so no
@@ -303,15 +319,19 @@ int64_t fpq_gptq_workspace_bytes(int64_t rows, int64_t cols);
 /*
  * get_relative_mse_error (src/quantization/gptq.py:28-30):
  * out[0] = mean(((Wq - W) H) * (Wq - W)) / (mean((W H) * W) + 1e-6).  Wq, W [rows, d], H [d, d] fp32;
- * diff_workspace: rows * d floats; acc_workspace: 2 doubles; out: device fp32[1].
+ * diff_workspace: rows * d floats; acc_workspace: FPQ_RELATIVE_MSE_ACC_DOUBLES doubles (one slot per CTA:
+ * partial sums are written, never added atomically, and summed in a fixed order, so the result is the same
+ * bit pattern on every run); out: device fp32[1].
  */
+#define FPQ_RELATIVE_MSE_ACC_DOUBLES 32768
 int fpq_relative_mse(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
                      float* diff_workspace, double* acc_workspace, float* out, fpq_stream_t stream);
 
 /*
  * The same metric (src/quantization/gptq.py:28-30) on the tensor cores: sum((A H) .* A) = <H, A^T A>, with
  * A^T A computed like a Hessian from a two-term bf16 split of A (~1e-5 relative accuracy).
- * bf16_workspace: 2 * rows * d bf16; gram_workspace: d * d floats; acc_workspace: 2 doubles; d % 8 == 0.
+ * bf16_workspace: 2 * rows * d bf16; gram_workspace: d * d floats; acc_workspace:
+ * FPQ_RELATIVE_MSE_ACC_DOUBLES doubles (deterministic reduction as above); d % 8 == 0.
  */
 int fpq_relative_mse_tc(const float* Wq, const float* W, const float* H, int64_t rows, int64_t d,
                         void* bf16_workspace, float* gram_workspace, double* acc_workspace, float* out,

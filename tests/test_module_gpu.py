@@ -280,3 +280,38 @@ def test_ops_live_in_the_reference_namespace_and_trace_under_torch_compile(cuda_
             eager = layer(x)
             compiled = torch.compile(layer, fullgraph=True, backend="aot_eager")(x)
         assert torch.equal(eager, compiled)
+
+
+@pytest.mark.parametrize("dtype_name,hgroup", [("mxfp4", 32), ("nvfp4", 128)])
+def test_gated_mlp_with_fused_activation(cuda_device, dtype_name, hgroup):
+    """`fuse_gated_mlp_activation` on a Llama-style MLP whose linears are real-quantised FPQuantLinear layers:
+    the patched module returns bit for bit what the unpatched one (separate SiLU * up kernel, then the
+    down-projection's own rotate + quantise) returns."""
+    import torch.nn as nn
+
+    from fpq_b200.fp_quant import (FPQuantConfig, FPQuantDtype, fuse_gated_mlp_activation,
+                                   replace_quantize_with_fp_quant_linear)
+
+    class MLP(nn.Module):
+        def __init__(self, d, f):
+            super().__init__()
+            self.gate_proj, self.up_proj = nn.Linear(d, f, bias=False), nn.Linear(d, f, bias=False)
+            self.down_proj = nn.Linear(f, d, bias=True)
+            self.act_fn = nn.SiLU()
+
+        def forward(self, x):
+            return self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))
+
+    torch.manual_seed(0)
+    mlp = MLP(256, 512).to(device=cuda_device, dtype=torch.bfloat16)
+    fd = FPQuantDtype.MXFP4 if dtype_name == "mxfp4" else FPQuantDtype.NVFP4
+    cfg = FPQuantConfig(forward_dtype=fd, forward_method="abs_max", backward_dtype=FPQuantDtype.BF16,
+                        hadamard_group_size=hgroup, modules_to_not_convert=[])
+    replace_quantize_with_fp_quant_linear(mlp, cfg)
+    x = inputs.outlier_activations(2 * 70, 256, seed=1).view(2, 70, 256).to(cuda_device)
+    with torch.no_grad():
+        want = mlp(x)
+        assert fuse_gated_mlp_activation(mlp) == 1
+        got = mlp(x)
+        compiled = torch.compile(mlp, fullgraph=True, backend="aot_eager")(x)
+    assert torch.equal(got, want) and torch.equal(compiled, want)

@@ -268,3 +268,37 @@ def test_quest_quantize_bit_exact(cuda_device, hgroup, dtype):
     assert torch.equal(dq.cpu().float(), want_dq.to(dtype).float())
     assert m2.dtype == torch.bool and torch.equal(m2.cpu(), want_mask)
     assert 0.5 < want_mask.float().mean().item() < 1.0          # the rule does clip: that is its point
+
+
+@pytest.mark.parametrize("fmt,hgroup", [("mxfp4", 32), ("nvfp4", 16), ("nvfp4", 128), ("mxfp4", 0)])
+@pytest.mark.parametrize("shape", [(3, 256), (130, 1024), (512, 4096)])
+def test_fused_silu_mul_quantize(cuda_device, fmt, hgroup, shape):
+    """fpq_quantize_silu_mul = fpq_quantize of bf16(bf16(silu(gate)) * up).  Two checks:
+      * bit-exact against the two-step device computation (torch's silu and product on the GPU, then the
+        quantise kernel): the fused kernel evaluates the activation with the same operations;
+      * against the CPU oracle fed torch-CPU's bf16 activation: the two exponentials can differ in the last
+        fp32 bit, which moves a bf16 rounding of the activation for a few elements in 10^5; every differing
+        code must sit in a scale group whose activation input differs, and such groups must be rare."""
+    from fpq_b200 import ops
+
+    gate = inputs.outlier_activations(*shape, seed=71) * 4
+    up = inputs.outlier_activations(*shape, seed=73)
+    gs = torch.tensor([2.5]) if fmt == "nvfp4" else None
+    gs_d = None if gs is None else gs.to(cuda_device)
+    q, sb = ops.quantize_silu_mul(gate.to(cuda_device), up.to(cuda_device), fmt, hgroup, gs_d, swizzled=True)
+    h_dev = torch.nn.functional.silu(gate.to(cuda_device)) * up.to(cuda_device)
+    q2, sb2, _ = ops.quantize(h_dev, fmt, hgroup, gs_d, swizzled=True)
+    assert torch.equal(q, q2) and torch.equal(sb, sb2)
+    qr, sbr = ops.quantize_silu_mul(gate.to(cuda_device), up.to(cuda_device), fmt, hgroup, gs_d, swizzled=False)
+    assert torch.equal(qr, q) and torch.equal(ops.swizzle_scales(sbr), sb)
+
+    h_cpu = torch.nn.functional.silu(gate) * up                                  # bf16 on the CPU
+    y = fp4.fwht_butterfly(h_cpu, hgroup) if hgroup else h_cpu.float()
+    want_codes, want_sb, _ = _oracle_quant(y, fmt, gs)
+    g = 16 if fmt == "nvfp4" else 32
+    rot = max(hgroup, g)                      # an input element reaches every output of its rotation group
+    in_diff = (h_cpu != h_dev.cpu()).reshape(shape[0], -1, rot).any(-1)
+    code_diff = (fp4.unpack_codes(qr.cpu()) != fp4.unpack_codes(want_codes)).reshape(shape[0], -1, rot).any(-1)
+    scale_diff = (sbr.cpu() != want_sb).reshape(shape[0], -1, rot // g).any(-1)
+    assert not bool(((code_diff | scale_diff) & ~in_diff).any())
+    assert in_diff.float().mean().item() < 2e-3

@@ -64,3 +64,28 @@ def test_noalloc_rejects_sizes_beyond_its_scratch(cuda_device):
                                          torch.cuda.current_stream().cuda_stream)
     assert rc == -1
     assert b"exceeds the built-in scratch" in lib.fpq_last_error()
+
+
+def test_noalloc_at_its_size_limit(cuda_device):
+    """d = FPQ_PREPARE_NOALLOC_MAX_D uses the whole built-in array: dead columns in the first and in the last
+    256-column tile, compared with the workspace variant on the diagonal and on the dead rows / columns
+    (the full 4 GiB matrices are compared on the device)."""
+    from fpq_b200 import _cabi
+
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    d, rows, dead = 32768, 8, (7, 32768 - 200, 32768 - 1)
+    g = torch.Generator(device=cuda_device).manual_seed(3)
+    H = torch.rand(d, d, device=cuda_device, generator=g)
+    W = torch.rand(rows, d, device=cuda_device, generator=g) + 0.5
+    for j in dead:
+        W[:, j] = 0
+    H_ref = H.clone()
+    ws = torch.empty(d, dtype=torch.uint8, device=cuda_device)
+    _cabi.check(lib.fpq_hessian_prepare(H_ref.data_ptr(), d, W.data_ptr(), rows, ctypes.c_float(0.01), ws.data_ptr(), stream))
+    _cabi.check(lib.fpq_hessian_prepare_noalloc(H.data_ptr(), d, W.data_ptr(), rows, ctypes.c_float(0.01), stream))
+    torch.cuda.synchronize()
+    assert torch.equal(H, H_ref)
+    for j in dead:
+        assert torch.count_nonzero(H[j]).item() == 1 and torch.count_nonzero(H[:, j]).item() == 1
+    assert H[5, 5].item() != H_ref[7, 7].item()      # a live diagonal entry kept its own value plus the damping
