@@ -970,8 +970,11 @@ def run_model_forward(args):
     from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype, fuse_gated_mlp_activation
     from fpq_b200.fp_quant.utils.replace import replace_quantize_with_fp_quant_linear
 
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
+    import torch.distributed as dist
+
+    from fpq_b200.fp_quant.module.tp_linear import tensor_parallelize
+
+    world, rank, local, dev = dist_setup()
     n_layers = args.model_layers
     cfg = Qwen3Config(hidden_size=5120, intermediate_size=17408, num_hidden_layers=n_layers, num_attention_heads=40,
                       num_key_value_heads=8, head_dim=128, vocab_size=151936, max_position_embeddings=4096)
@@ -1002,39 +1005,90 @@ def run_model_forward(args):
 
     @torch.no_grad()
     def decode_rate(steps, warmup):
-        out = body(input_ids=decode_prompt, use_cache=True)
-        cache = out.past_key_values
-        for _ in range(warmup):
-            cache = body(input_ids=decode_ids, past_key_values=cache, use_cache=True).past_key_values
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            cache = body(input_ids=decode_ids, past_key_values=cache, use_cache=True).past_key_values
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) * 1e-3 / steps
+        """Seconds per decode step.  The loop is run twice from the same prompt and the second run is timed:
+        torch's attention backend prepares a plan for every new (heads, cache length) shape (about 10 ms each,
+        measured with cProfile), which would otherwise be charged to whichever model decodes first."""
+        def run():
+            cache = body(input_ids=decode_prompt, use_cache=True).past_key_values
+            for _ in range(warmup):
+                cache = body(input_ids=decode_ids, past_key_values=cache, use_cache=True).past_key_values
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                cache = body(input_ids=decode_ids, past_key_values=cache, use_cache=True).past_key_values
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) * 1e-3 / steps
 
-    with ClockSampler(0) as clocks:
-        bf16_prefill = timed(prefill, args.steps, args.warmup)
+        run()
+        return run()
+
+    def block_linears_graph_us(block):
+        """Device time of the seven linears of one decoder block at the decode batch (64 tokens), replayed from a
+        CUDA graph: what the layers cost once the Python and launch overhead that bounds the eager decode loop
+        is out of the way (a serving stack replays graphs).  Inputs are random tensors of each layer's width."""
+        lins = [block.self_attn.q_proj, block.self_attn.k_proj, block.self_attn.v_proj, block.self_attn.o_proj,
+                block.mlp.gate_proj, block.mlp.up_proj, block.mlp.down_proj]
+        xs = [torch.randn(64, l.in_features, device=dev, dtype=torch.bfloat16) for l in lins]
+
+        def run():
+            return [l(x) for l, x in zip(lins, xs)]
+
+        with torch.no_grad():
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                run()
+            for _ in range(3):
+                gr.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(50):
+                gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+        del gr
+        return e0.elapsed_time(e1) / 50 * 1e3
+
+    with ClockSampler(local) as clocks:
+        bf16_prefill = timed(prefill, args.steps, args.warmup)        # every rank: the whole bf16 model
         bf16_decode = decode_rate(16, 4)
+        bf16_graph_us = block_linears_graph_us(body.layers[0])
         qcfg = FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, forward_method="abs_max", backward_dtype=FPQuantDtype.BF16,
                              hadamard_group_size=32, modules_to_not_convert=["lm_head"])
         replace_quantize_with_fp_quant_linear(model, qcfg)
         torch.cuda.empty_cache()
         unfused_prefill = timed(prefill, args.steps, args.warmup)
         unfused_decode = decode_rate(16, 4)
+        fp4_graph_us = block_linears_graph_us(body.layers[0])
         fused_mlps = fuse_gated_mlp_activation(model)        # SiLU(gate) * up inside the down-projection's quantise kernel
+        tp_blocks = tensor_parallelize(model, None)          # several ranks: column-parallel -> row-parallel pairs, NCCL all-reduce
+        torch.cuda.empty_cache()
         fp4_prefill = timed(prefill, args.steps, args.warmup)
         fp4_decode = decode_rate(16, 4)
+    if world > 1:
+        t = torch.tensor([fp4_prefill, fp4_decode], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        fp4_prefill, fp4_decode = float(t[0]), float(t[1])
     ops.check_device_errors(dev)
     tokens = prefill_ids.numel()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
     line = {
-        "metric": "w4a4_model_prefill_tokens_per_s", "value": tokens / fp4_prefill, "unit": "tokens/s", "n_gpus": 1,
+        "metric": "w4a4_model_prefill_tokens_per_s", "value": tokens / fp4_prefill, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": fp4_prefill * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp4(e2m1)xfp4->f32->bf16 linears, bf16 attention", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp4(e2m1)xfp4->f32->bf16 linears, bf16 attention", "data": "synthetic",
         "config": {"workload": f"forward of {n_layers} Qwen3-14B-shaped decoder blocks, all linears W4A4 MXFP4 FPQuantLinear "
-                               f"(Hadamard 32), prefill 8x2048 tokens, decode batch 64 on a 128-token cache, HF eager modules",
+                               f"(Hadamard 32), prefill 8x2048 tokens, decode batch 64 on a 128-token cache, HF eager modules; "
+                               f"tensor-parallel over {world} GPU(s): q/k/v and gate/up column-parallel, o_proj and down_proj "
+                               f"row-parallel with one NCCL all-reduce each ({tp_blocks} blocks converted)",
+                   "allreduce_bytes_per_block_prefill": 2 * 2 * tokens * 5120 if world > 1 else 0,
                    "l2": "weights of a block (0.6 GB bf16, 0.17 GB FP4) and activations exceed the 126 MB L2"},
         "prefill": {"w4a4_tokens_per_s": tokens / fp4_prefill, "bf16_tokens_per_s": tokens / bf16_prefill,
                     "speedup_vs_bf16": bf16_prefill / fp4_prefill,
@@ -1042,11 +1096,16 @@ def run_model_forward(args):
                     "ms_saved_per_block_by_fused_silu_mul": (unfused_prefill - fp4_prefill) * 1e3 / n_layers},
         "decode": {"w4a4_tokens_per_s": 64 / fp4_decode, "bf16_tokens_per_s": 64 / bf16_decode,
                    "speedup_vs_bf16": bf16_decode / fp4_decode, "ms_per_step_w4a4": fp4_decode * 1e3,
-                   "w4a4_tokens_per_s_separate_silu_mul": 64 / unfused_decode},
+                   "w4a4_tokens_per_s_separate_silu_mul": 64 / unfused_decode,
+                   "note": "the eager loop is bound by Python and launch overhead on both sides",
+                   "block_linears_cuda_graph_us": {"w4a4": fp4_graph_us, "bf16": bf16_graph_us,
+                                                   "what": "the seven linears of a block at 64 tokens, one rank's full-width layers, replayed from a CUDA graph"}},
         "fused_mlp_modules": fused_mlps,
         "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
     }
     print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_cholesky(args):

@@ -13,8 +13,8 @@ from torch import nn
 from ... import ops
 from ...rotation import sylvester
 from ..utils.config import FPQuantConfig, FPQuantDtype, validate_config
-from .linear_fns import (FPQuant4x16MasterFn, FPQuant4x16NoMasterFn, forward_gemm_blocked, forward_quantize,
-                         gemm_alpha)
+from .linear_fns import (FPQuant4x16MasterFn, FPQuant4x16NoMasterFn, _linear_forward, forward_gemm_blocked,
+                         forward_quantize, gemm_alpha)
 from .pseudoquant_linear_fns import PseudoQuant4x16MasterFn, PseudoQuant4x16NoMasterFn, forward_pseudoquantize
 from .qutlass_ops import (HAS_QUTLASS, fused_silu_mul_quantize_blocked_op,  # noqa: F401  (HAS_QUTLASS: API compatibility)
                           swizzle_scales_op)
@@ -175,6 +175,9 @@ class FPQuantLinear(nn.Module):
                 return PseudoQuant4x16NoMasterFn.apply(x, self.dqweight, *common)
             if cfg.store_master_weights:
                 return FPQuant4x16MasterFn.apply(x, self.weight, *common)
+            if not (torch.is_grad_enabled() and x.requires_grad):
+                # inference: the function body without the autograd.Function wrapper (its backward only raises)
+                return _linear_forward(x, self.qweight, self._blocked_weight_scales(), *common, self._gemm_alpha())
             return FPQuant4x16NoMasterFn.apply(x, self.qweight, self._blocked_weight_scales(), *common,
                                                self._gemm_alpha())
         if cfg.forward_dtype == FPQuantDtype.MXFP4 and cfg.backward_dtype in (FPQuantDtype.MXFP4, FPQuantDtype.MXFP8) \

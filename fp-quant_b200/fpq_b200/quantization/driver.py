@@ -18,6 +18,7 @@ Differences in structure (same mathematics):
 """
 from __future__ import annotations
 
+import contextlib
 import re
 from typing import Dict, List, Optional, Tuple
 
@@ -60,6 +61,7 @@ class _Phases:
 
 last_phases: Optional[_Phases] = None     # phases of the most recent gptq_quantization call
 last_relative_mse: Dict[str, float] = {}  # "model.layers.<i>.<linear>" -> relative MSE of the most recent call (rank 0 prints them)
+_split_state: dict = {}                   # per process: side stream of the split second pass; whether the split is exact for this model
 
 
 class _HessianSink:
@@ -136,6 +138,7 @@ class RotatedLinear(nn.Module):
         self.input_sink = None          # called with the rotated, unquantised input (Hessian accumulation)
         self.group_state = group_state if group_state is not None else {}
         self._rotated = None            # (weight version, rotated weight) while the weight is still the original
+        self.deferred_inputs = None     # a list: forward() stores its prepared input there and returns zeros
 
     def _prepared_input(self, x: torch.Tensor) -> torch.Tensor:
         st = self.group_state
@@ -154,6 +157,9 @@ class RotatedLinear(nn.Module):
         if self.input_sink is not None:          # legacy hook of a stand-alone module
             self.group_state["sink"] = self.input_sink
         xq = self._prepared_input(x)
+        if self.deferred_inputs is not None:      # first half of a split pass: the product is added later
+            self.deferred_inputs.append(xq)
+            return xq.new_zeros(*xq.shape[:-1], self.out_features)
         if self._train_mode:
             # the same weight is rotated for every calibration sequence: keep the result until the weight changes
             if self._rotated is None or self._rotated[0] != self.weight._version:
@@ -305,6 +311,50 @@ def _run_block(block, input_args, input_kwargs, device, args, keep_outputs: bool
                     input_kwargs[i]["hidden_states"] = piece
 
 
+def _split_pass_first_half(block, input_args, input_kwargs, device, args, last_linear: "RotatedLinear"):
+    """The second pass over the calibration sequences (gptq.py:446-457) up to the input of `last_linear`, the
+    block's final linear (an MLP's down-projection): every sequence goes through the block with that layer
+    returning zeros, so what comes out is the residual stream the layer's output is added to.  Returns the
+    per-sequence pairs (block output without the layer, the layer's prepared input).  Used on several GPUs,
+    where the final linear's weight arrives last: everything that does not need it is done while its owner
+    still works on it."""
+    parts = []
+    last_linear.deferred_inputs = []
+    try:
+        for a, kw in zip(input_args, input_kwargs):
+            with torch.no_grad(), torch.amp.autocast(device_type="cuda", enabled=getattr(args, "amp", False)):
+                out = _first(block(*_to(a, device), **_to(kw, device)))
+            assert len(last_linear.deferred_inputs) == 1, "the deferred linear must run exactly once per block call"
+            parts.append((out, last_linear.deferred_inputs.pop()))
+    finally:
+        last_linear.deferred_inputs = None
+    return parts
+
+
+def _split_pass_second_half(parts, input_args, input_kwargs, last_linear: "RotatedLinear", offload_device) -> None:
+    """Adds the final linear's product to the stored residual streams and writes the block outputs where
+    `_run_block(keep_outputs=True)` writes them.  bf16(residual + bf16(linear)) is the operation the block
+    itself performs, so the result is bit-identical to the unsplit pass for blocks that end in
+    `residual + down_proj(...)` (`_split_pass_is_exact` checks that on the first sequence)."""
+    for (out, xq), a, kw in zip(parts, input_args, input_kwargs):
+        y = out + F.linear(xq, last_linear.weight, last_linear.bias)
+        y = y.to(offload_device)
+        if len(a) > 0:
+            a[0].data = y
+        elif "hidden_states" in kw:
+            kw["hidden_states"] = y
+        else:
+            raise ValueError("Unsupported block input format.")
+
+
+def _split_pass_is_exact(block, parts, input_args, input_kwargs, device, args, last_linear) -> bool:
+    """Whether the split pass reproduces the block on the first sequence bit for bit (weights final)."""
+    with torch.no_grad(), torch.amp.autocast(device_type="cuda", enabled=getattr(args, "amp", False)):
+        want = _first(block(*_to(input_args[0], device), **_to(input_kwargs[0], device)))
+    out, xq = parts[0]
+    return bool(torch.equal(want, out + F.linear(xq, last_linear.weight, last_linear.bias)))
+
+
 def plan_ranks(group_members: Dict[str, List[str]], group_cols: Dict[str, int], world_size: int):
     """Which rank factors which Hessian and quantises which linear of a block.
 
@@ -420,6 +470,36 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
         group_order, group_owner, layer_owner = plan_ranks(
             group_members, {g: handles[leaders[g]].d_col for g in group_members}, world_size)
 
+        # ---- the block's final linear on several GPUs.  `down_proj` has the widest Hessian (its chain and its
+        # column loop take longer than everything else in the block together) and nothing else waits for it
+        # but the end of the second pass.  Its owner therefore works on it on a side stream while all ranks
+        # (the owner included, on its main stream, for the cheap parts) exchange the other six linears and run
+        # the second pass up to the input of down_proj; the product with the finished weight is added last.
+        deferred = None
+        if world_size > 1 and max(1, int(getattr(args, "calibration_batch", 1))) == 1 and getattr(args, "split_second_pass", True) \
+                and _split_state.get("exact", True):
+            lasts = [n for n in handles if re.search(r"down_proj$", n)]
+            if len(lasts) == 1 and len(group_members[_input_group(lasts[0].split(".")[-1])]) == 1:
+                deferred = lasts[0]
+        main_stream = torch.cuda.current_stream(device)
+        side_stream = None
+        if deferred is not None and layer_owner[deferred] == rank:
+            if "stream" not in _split_state:
+                _split_state["stream"] = torch.cuda.Stream(device=device)
+            side_stream = _split_state["stream"]
+
+        @contextlib.contextmanager
+        def on_stream_of(name):
+            """The side stream for the deferred linear on its owner (ordered after everything queued on the main
+            stream so far), the current stream otherwise."""
+            if name == deferred and side_stream is not None:
+                side_stream.wait_stream(main_stream)
+                with torch.cuda.stream(side_stream):
+                    yield
+            else:
+                yield
+
+        checks: List[torch.Tensor] = []
         shared_U: Dict[str, torch.Tensor] = {}
         for g in group_order:
             lead = handles[leaders[g]]
@@ -429,11 +509,13 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             owner = group_owner[g]
             elsewhere = any(layer_owner[n] != owner for n in group_members[g])
             if rank == owner:
-                lead.quantization_pre_step()
-                lead.prepare_hessian()
-                ph.mark("factor_prepare")
-                shared_U[g] = lead._get_hessian_inverse(prepared=True)
-                ph.mark("factor_chain")
+                with on_stream_of(leaders[g]):
+                    lead.defer_host_syncs = world_size > 1
+                    lead.quantization_pre_step()
+                    lead.prepare_hessian()
+                    ph.mark("factor_prepare")
+                    shared_U[g] = lead._get_hessian_inverse(prepared=True)
+                    ph.mark("factor_chain")
             elif elsewhere:
                 shared_U[g] = torch.empty((lead.d_col, lead.d_col), device=device, dtype=torch.float32)
         for g in group_order:                       # after all chains were queued: they overlap across ranks
@@ -442,26 +524,37 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
 
         ph.mark("factor")
         results = {}
+        originals = {}
         for name, handle in handles.items():
             if layer_owner[name] != rank:
                 continue
             grp = _input_group(name.split(".")[-1])
             leader = handles[leaders[grp]]
-            if grp in shared_U and share_ok[grp]:
-                if not (handle is leader and rank == group_owner[grp]):     # the factoring rank's leader is prepared
-                    handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
-                    handle.quantization_pre_step()
-                    handle.prepare_hessian()       # same damping as the leader's: leaves the damped H for the MSE
-                wq, qweight, scales = handle.step(shared_U[grp], want_grid_values=False)   # the packed codes are exported
-            else:
-                if handle is not leader:
-                    handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
-                wq, qweight, scales = handle.quantize(want_grid_values=False)
-            rel = get_relative_mse_error(wq.float(), handle.layer.weight.float(), handle.H)
-            results[name] = (wq, handle.packed_codes, scales.float().contiguous(), rel.reshape(1))
+            with on_stream_of(name):
+                if world_size > 1:
+                    handle.defer_host_syncs = True
+                    handle.quantizer.deferred_checks = checks
+                if grp in shared_U and share_ok[grp]:
+                    if not (handle is leader and rank == group_owner[grp]):     # the factoring rank's leader is prepared
+                        handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
+                        handle.quantization_pre_step()
+                        handle.prepare_hessian()       # same damping as the leader's: leaves the damped H for the MSE
+                    wq, qweight, scales = handle.step(shared_U[grp], want_grid_values=False)   # the packed codes are exported
+                else:
+                    if handle is not leader:
+                        handle.H, handle.num_samples = leader.H_undamped.clone(), leader.num_samples
+                    wq, qweight, scales = handle.quantize(want_grid_values=False)
+                if name == deferred:
+                    rel = None                        # measured after the second pass, off the other ranks' path
+                    originals[name] = handle.layer.weight.data
+                else:
+                    rel = get_relative_mse_error(wq.float(), handle.layer.weight.float(), handle.H).reshape(1)
+                results[name] = (wq, handle.packed_codes, scales.float().contiguous(), rel)
         shared_U.clear()
 
-        for name, handle in handles.items():        # same order on every rank: one broadcast group per linear
+        def exchange(name):
+            """Broadcast of one linear's result from its owner (same order on every rank), weight swap, export."""
+            handle = handles[name]
             rows, cols = handle.d_row, handle.d_col
             if name in results:
                 wq, codes, scales, rel = results[name]
@@ -471,9 +564,10 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                 scales = torch.empty((rows, cols // handle.quantizer.group_size), device=device, dtype=torch.float32)
                 rel = torch.empty(1, device=device, dtype=torch.float32)
             if world_size > 1:
-                for t in (wq, codes, scales, rel):
+                for t in ((wq, codes, scales) if name == deferred else (wq, codes, scales, rel)):
                     torch.distributed.broadcast(t, src=layer_owner[name])
-            pending_mse[f"model.layers.{block_idx}.{name}"] = rel
+            if rel is not None:
+                pending_mse[f"model.layers.{block_idx}.{name}"] = rel
             handle.layer.weight.data = wq
             if args.export_quantized_model:
                 wgs = handle.quantizer.global_scale.to(device)
@@ -484,8 +578,43 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                                                    scales=cast_scales_to_eXmY(scales * wgs, args.scale_precision))
                 else:
                     quantized[key] = _export_entry(copies, args, orig_dtype, device, wgs, ags, dqweight=wq)
+
+        for name in handles:                        # same order on every rank: one broadcast group per linear
+            if name != deferred:
+                exchange(name)
+        ph.mark("column_loops")
+        _release_group_states(layers)
+        if deferred is None:
+            _run_block(block, input_args, input_kwargs, device, args, keep_outputs=True, offload_device=offload)
+        else:
+            last = handles[deferred].layer
+            if side_stream is not None:
+                # the owner's own sequences wait for its side stream: its forward kernels would only slow the
+                # chain and the loop down, and the other ranks wait for those, not for this
+                main_stream.wait_stream(side_stream)
+            parts = _split_pass_first_half(block, input_args, input_kwargs, device, args, last)
+            ph.mark("update_pass_first_half")
+            exchange(deferred)
+            if "exact" not in _split_state:      # once per process: does this architecture end in residual + down_proj?
+                _split_state["exact"] = _split_pass_is_exact(block, parts, input_args, input_kwargs, device, args, last)
+            if _split_state["exact"]:
+                _split_pass_second_half(parts, input_args, input_kwargs, last, offload)
+            else:
+                _run_block(block, input_args, input_kwargs, device, args, keep_outputs=True, offload_device=offload)
+            del parts
+            if deferred in results:              # the owner measures its layer now that nobody waits for it
+                handle = handles[deferred]
+                pending_mse[f"model.layers.{block_idx}.{deferred}"] = get_relative_mse_error(
+                    results[deferred][0].float(), originals[deferred].float(), handle.H).reshape(1)
+            elif rank == 0:
+                pending_mse[f"model.layers.{block_idx}.{deferred}"] = torch.full((1,), float("nan"), device=device)
         results.clear()
-        # one host read per block for the log line of every layer (gptq.py:414-415), not one per layer
+        originals.clear()
+        _release_group_states(layers)
+        ph.mark("update_pass")
+        # one host read per block: finiteness checks of the quantisers and the log line of every layer (gptq.py:414-415)
+        if checks and bool(torch.stack([c.reshape(()) for c in checks]).any().item()):
+            raise ValueError("Scales or global scale are not finite.")
         names = [k for k in pending_mse if k not in last_relative_mse]
         if names:
             values = torch.cat([pending_mse[k] for k in names]).tolist()
@@ -493,12 +622,6 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                 last_relative_mse[k] = v
                 if rank == 0:
                     print(f"[{k.split('.', 3)[3]:16}]: Relative MSE error: {v:.2e}")
-
-        ph.mark("column_loops")
-        _release_group_states(layers)
-        _run_block(block, input_args, input_kwargs, device, args, keep_outputs=True, offload_device=offload)
-        _release_group_states(layers)
-        ph.mark("update_pass")
         if getattr(args, "cpu_offload_modules", False):
             block.cpu()
         del handles

@@ -39,6 +39,8 @@ class GPTQ:
         self.export_quantized_model = export_quantized_model
         self.packed_codes: Optional[torch.Tensor] = None     # uint8 [rows, cols/2] of the last `step`
         self.used_identity_fallback = False
+        self.defer_host_syncs = False     # True: nothing in quantize() waits for the device (multi-GPU driver's critical path)
+        self.fallback_status: Optional[torch.Tensor] = None
 
     @torch.no_grad()
     def update(self, input: torch.Tensor) -> None:
@@ -133,6 +135,14 @@ class GPTQ:
         if not prepared:
             self.prepare_hessian()
         U, status = ops.cholesky_inverse_upper(self.H)
+        if self.defer_host_syncs:
+            # the reference's `except:` branch (gptq.py:216-217) without reading the status on the host:
+            # U becomes the identity on the device when the factorisation failed
+            failed = (status != 0).to(torch.float32)
+            U.mul_(1.0 - failed)
+            U.diagonal().add_(failed)
+            self.fallback_status = status
+            return U
         self.used_identity_fallback = bool(status.item())
         if self.used_identity_fallback:      # the reference's `except:` branch (gptq.py:216-217)
             U = torch.eye(self.d_col, device=self.H.device, dtype=torch.float32)

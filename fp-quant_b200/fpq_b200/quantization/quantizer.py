@@ -40,6 +40,10 @@ class Quantizer:
         self.global_scale = torch.tensor([first], dtype=torch.float32)
         self._track_global_scale = self.scale_precision == ScalePrecision.E4M3
         self._kernel_format = self._resolve_kernel_format()
+        # None: the finiteness checks of `get_quantization_params` synchronise and raise at once, like the
+        # reference's.  A list: the checks are appended as device booleans ("something is wrong") and the
+        # caller raises later with `raise_deferred_checks` -- for drivers that must not stall the host.
+        self.deferred_checks = None
 
     # ------------------------------------------------------------------ helpers
     def _resolve_kernel_format(self) -> str:
@@ -77,16 +81,30 @@ class Quantizer:
                 bits = ops.absmax_bits(x, 0)
                 status = torch.zeros(1, dtype=torch.int32, device=x.device)
                 ops.global_scale_update(bits, gs, status)
-                if int(status.item()) != 0 or not bool(torch.isfinite(gs).item()):
+                bad = (status != 0) | ~torch.isfinite(gs)
+                if self.deferred_checks is not None:
+                    self.deferred_checks.append(bad.reshape(()))
+                elif bool(bad.item()):
                     raise ValueError(f"Global scale is not finite: {gs}")
         if self.observer == QuantizationObserver.MSE:
             scales = ops.mse_scales(x, fmt, gs, scale_search_iters, max_scale_shrink_factor, error_norm)
         else:
             _, _, scales = ops.quantize(x, fmt, 0, gs, codes=False, scale_bytes=False, scales_f32=True)
         scales = scales.view(*x.shape[:-1], x.shape[-1] // self.group_size).to(x.dtype)
-        if bool(scales.isnan().any().item()):
+        bad = scales.isnan().any()
+        if self.deferred_checks is not None:
+            self.deferred_checks.append(bad)
+        elif bool(bad.item()):
             raise ValueError("Scales are not finite.")
         return scales, torch.zeros_like(scales)
+
+    def raise_deferred_checks(self) -> None:
+        """One synchronisation for all checks collected since `deferred_checks` was set to a list."""
+        if self.deferred_checks:
+            bad = bool(torch.stack(self.deferred_checks).any().item())
+            self.deferred_checks.clear()
+            if bad:
+                raise ValueError("Scales or global scale are not finite.")
 
     def _apply(self, x: torch.Tensor, scales: torch.Tensor, kind: int) -> torch.Tensor:
         group = self.group_size

@@ -35,9 +35,22 @@ def _worker(rank, world, port, out_path):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     data = _calibration(dev)
     model = _tiny_llama(dev)
+    from fpq_b200.quantization import driver as drv
+
     quantized, _ = gptq_quantization(model, data, _args("nvfp"), dev)
     with torch.no_grad():
         logits = torch.cat([model(x.to(dev)).logits.float() for x in data]).cpu()
+    split_exact = drv._split_state.get("exact")
+    # the same two-rank run with the second pass in one piece (the down-projection not deferred): the split
+    # pass adds the same two bf16 tensors the block adds, so codes and logits must be identical
+    plain_args = _args("nvfp")
+    plain_args.split_second_pass = False
+    model_p = _tiny_llama(dev)
+    quantized_p, _ = gptq_quantization(model_p, data, plain_args, dev)
+    with torch.no_grad():
+        logits_p = torch.cat([model_p(x.to(dev)).logits.float() for x in data]).cpu()
+    same_as_plain = all(torch.equal(quantized[k]["qweight"], quantized_p[k]["qweight"]) for k in quantized) \
+        and torch.equal(logits, logits_p)
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
@@ -56,7 +69,8 @@ def _worker(rank, world, port, out_path):
 
         first = [f"model.layers.0.self_attn.{n}_proj" for n in "qkv"]
         torch.save({"agree": agreement(list(quantized1)), "agree_first": agreement(first),
-                    "keys": sorted(quantized) == sorted(quantized1),
+                    "keys": sorted(quantized) == sorted(quantized1), "split_exact": split_exact,
+                    "same_as_plain": same_as_plain,
                     "logit_diff": float(((logits - logits1) ** 2).mean() / (logits1 ** 2).mean())}, out_path)
 
 
@@ -69,6 +83,7 @@ def test_two_rank_driver_matches_single_gpu(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     r = torch.load(out)
     assert r["keys"]
+    assert r["split_exact"] is True and r["same_as_plain"], r
     # q/k/v of the first block see identical inputs on both runs: only the order of the Hessian sum differs
     assert r["agree_first"] > 0.99, r
     # later layers: the activation quantiser's running-minimum tensor scale evolves per rank during the

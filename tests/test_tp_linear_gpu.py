@@ -55,10 +55,56 @@ def _worker(rank, world, port, out_path):
                 print(f"rank {rank} {fmt} fused call {it} differs: {int(bad.sum())} elements, columns "
                       f"{bad.any(dim=0).nonzero().flatten()[:4].tolist()}..{bad.any(dim=0).nonzero().flatten()[-4:].tolist()} "
                       f"rows {bad.any(dim=1).nonzero().flatten()[:4].tolist()}", flush=True)
+    # ---- row-parallel: input features split, partial products summed by one all-reduce
+    from fpq_b200.fp_quant.module.tp_linear import RowParallelFPQuantLinear, tensor_parallelize
+    from fpq_b200 import dist as fdist
+
+    row_err = 0.0
+    for fmt, hg in ((FPQuantDtype.MXFP4, 32), (FPQuantDtype.NVFP4, 128)):
+        cfg = FPQuantConfig(forward_dtype=fmt, forward_method="abs_max", backward_dtype=FPQuantDtype.BF16, hadamard_group_size=hg)
+        layer = FPQuantLinear(1024, 384, cfg, bias=True, device=dev, dtype=torch.bfloat16)
+        layer.weight.data.copy_(inputs.normal_weight(384, 1024, seed=3))
+        layer.bias.data.copy_(torch.linspace(-1, 1, 384))
+        layer.pre_forward()
+        x = inputs.outlier_activations(300, 1024, seed=5).to(dev)
+        want = layer(x).float()
+        rp = RowParallelFPQuantLinear(layer, None)
+        lo, hi = fdist.shard_bounds(1024, world, rank, multiple=128)
+        got = rp(x[:, lo:hi]).float()
+        row_err = max(row_err, float((got - want).abs().max() / want.abs().max()))
+        gate = inputs.outlier_activations(300, 1024, seed=7).to(dev)
+        want2 = layer(torch.nn.functional.silu(gate) * x).float()
+        got2 = rp.forward_silu_mul(gate[:, lo:hi], x[:, lo:hi]).float()
+        row_err = max(row_err, float((got2 - want2).abs().max() / want2.abs().max()))
+
+    # ---- a tiny Qwen3-style model: all linears W4A4, tensor-parallel over the two ranks vs the same model on one
+    from transformers import Qwen3Config, Qwen3ForCausalLM
+    from fpq_b200.fp_quant import fuse_gated_mlp_activation, replace_quantize_with_fp_quant_linear
+
+    def build():
+        torch.manual_seed(0)
+        c = Qwen3Config(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, head_dim=128, vocab_size=160, max_position_embeddings=128)
+        m = Qwen3ForCausalLM(c).to(device=dev, dtype=torch.bfloat16).eval()
+        qc = FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, forward_method="abs_max", backward_dtype=FPQuantDtype.BF16,
+                           hadamard_group_size=32, modules_to_not_convert=["lm_head"])
+        replace_quantize_with_fp_quant_linear(m, qc)
+        return m
+
+    ids = torch.randint(0, 160, (2, 64), generator=torch.Generator().manual_seed(9)).to(dev)
+    single = build()
+    fuse_gated_mlp_activation(single)
+    tp = build()
+    n_blocks = tensor_parallelize(tp, None)
+    with torch.no_grad():
+        want_l = single(ids).logits.float()
+        got_l = tp(ids).logits.float()
+    model_err = float(((got_l - want_l) ** 2).mean() / (want_l ** 2).mean())
+    print(f"rank {rank}: row-parallel max relative deviation {row_err:.3e}; 2-block model, TP vs single: relative MSE of logits {model_err:.3e}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
-        torch.save({"equal": ok}, out_path)
+        torch.save({"equal": ok, "row_err": row_err, "model_err": model_err, "blocks": n_blocks}, out_path)
 
 
 def test_column_parallel_linear_equals_full_layer(tmp_path):
@@ -68,4 +114,11 @@ def test_column_parallel_linear_equals_full_layer(tmp_path):
 
     out = str(tmp_path / "result.pt")
     mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
-    assert torch.load(out)["equal"]
+    r = torch.load(out)
+    assert r["equal"]                       # column-parallel (gathered by NCCL or pushed from the epilogue): bit-identical
+    # row-parallel sums bf16-rounded partial products: within bf16 rounding of the unsplit layer
+    assert r["row_err"] < 2e-2, r
+    # a whole model: the rounding differences above move some 4-bit activation codes in later layers; two W4A4
+    # evaluations of this tiny random model that differ by bf16 rounding agree to a few per cent of the logits'
+    # energy (the reloaded-checkpoint test in test_driver_gpu.py sees the same level)
+    assert r["blocks"] == 2 and r["model_err"] < 0.08, r
