@@ -38,6 +38,25 @@ def shard_bounds(n: int, world_size: int, rank: int, multiple: int = 1) -> Tuple
     return min(lo_u * multiple, n), min(hi_u * multiple, n)
 
 
+def weighted_bounds(n: int, weights: List[float]) -> List[Tuple[int, int]]:
+    """Contiguous shares of n items proportional to `weights` (largest-remainder rounding; every rank with a
+    positive weight gets at least one item when n allows)."""
+    total = float(sum(weights))
+    raw = [n * w / total for w in weights]
+    counts = [int(r) for r in raw]
+    for i in sorted(range(len(weights)), key=lambda i: raw[i] - counts[i], reverse=True)[: n - sum(counts)]:
+        counts[i] += 1
+    for i, w in enumerate(weights):          # nobody with work to do is left empty-handed
+        if w > 0 and counts[i] == 0 and max(counts) > 1:
+            counts[counts.index(max(counts))] -= 1
+            counts[i] = 1
+    out, lo = [], 0
+    for c in counts:
+        out.append((lo, lo + c))
+        lo += c
+    return out
+
+
 def all_bounds(n: int, world_size: int, multiple: int = 1) -> List[Tuple[int, int]]:
     return [shard_bounds(n, world_size, r, multiple) for r in range(world_size)]
 

@@ -381,6 +381,88 @@ def cholesky_inverse_upper(H: torch.Tensor):
     return U, status
 
 
+# --------------------------------------------------------------------------- CUDA-graph replays of the two long launch chains
+# The Cholesky-inverse chain (786 dependent launches at d = 14336) and the column loop (two launches per 128
+# columns) are bound by how fast the host issues small kernels: the same binary needed 0.08 s or 0.27 s per
+# two transformer blocks for the chains depending on the host it ran on.  Both are static given their shapes,
+# so each shape is captured once into a CUDA graph over buffers of its own and replayed afterwards.
+_graphs: dict = {}
+
+
+def _capture(key, build):
+    """(graph, statics) for `key`; `build()` allocates the static buffers and returns (statics, run) where run()
+    issues the launches on the current stream."""
+    entry = _graphs.get(key)
+    if entry is None:
+        statics, run = build()
+        run()                                   # first run outside the capture: one-time initialisation, warm caches
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        # thread-local: other threads of the process (NCCL's watchdog) may call into CUDA during the capture
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            run()
+        entry = _graphs[key] = (graph, statics)
+    return entry
+
+
+def cholesky_inverse_upper_graphed(H: torch.Tensor):
+    """`cholesky_inverse_upper` replayed from a CUDA graph captured per (device, d).  Same result; costs one
+    copy of H in and one of U out, and holds H, U and the workspace of every d it has seen."""
+    H = _f32(H, "H")
+    d = H.shape[0]
+
+    def build():
+        st = {"H": torch.empty_like(H), "U": torch.empty_like(H),
+              "ws": torch.empty(int(C.lib().fpq_cholesky_workspace_floats(d)), dtype=torch.float32, device=H.device),
+              "status": torch.zeros(1, dtype=torch.int32, device=H.device)}
+        flag = device_error_flag(H.device).data_ptr()
+
+        def run():
+            with _guard(H.device):
+                C.call("fpq_cholesky_inverse_upper", st["H"].data_ptr(), st["U"].data_ptr(), d, st["ws"].data_ptr(),
+                       st["status"].data_ptr(), flag, _stream(H))
+        st["H"].copy_(H)
+        return st, run
+
+    graph, st = _capture(("chol", H.device.index, d), build)
+    st["H"].copy_(H)
+    graph.replay()
+    return st["U"].clone(), st["status"].clone()
+
+
+def gptq_quantize_graphed(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group: int,
+                          group_index: Optional[torch.Tensor] = None):
+    """`gptq_quantize` (codes wanted) replayed from a CUDA graph captured per shape; W is updated in place."""
+    W, scales, U = _f32(W, "W", inplace=True), _f32(scales, "scales"), _f32(U, "U")
+    rows, cols = W.shape
+    ordered = group_index is not None
+
+    def build():
+        dev = W.device
+        st = {"W": torch.empty_like(W), "scales": torch.empty_like(scales), "U": torch.empty_like(U),
+              "codes": torch.empty(rows, cols // 2, dtype=torch.uint8, device=dev),
+              "ws": torch.empty(int(C.lib().fpq_gptq_workspace_bytes(rows, cols)), dtype=torch.uint8, device=dev),
+              "gidx": torch.empty(cols, dtype=torch.int32, device=dev) if ordered else None}
+        flag = device_error_flag(dev).data_ptr()
+
+        def run():
+            with _guard(dev):
+                C.call("fpq_gptq_quantize_ordered", st["W"].data_ptr(), rows, cols, st["scales"].data_ptr(), group,
+                       _ptr(st["gidx"]), st["U"].data_ptr(), st["codes"].data_ptr(), st["ws"].data_ptr(), flag, _stream(W))
+        st["W"].copy_(W); st["scales"].copy_(scales); st["U"].copy_(U)
+        if ordered:
+            st["gidx"].copy_(group_index)
+        return st, run
+
+    graph, st = _capture(("gptq", W.device.index, rows, cols, group, ordered), build)
+    st["W"].copy_(W); st["scales"].copy_(scales); st["U"].copy_(U)
+    if ordered:
+        st["gidx"].copy_(group_index)
+    graph.replay()
+    W.copy_(st["W"])
+    return st["codes"].clone()
+
+
 def gptq_quantize(W: torch.Tensor, scales: torch.Tensor, U: torch.Tensor, group: int, want_codes: bool = True,
                   group_index: Optional[torch.Tensor] = None):
     """Runs the GPTQ column loop on W in place (W becomes the dequantised weight).  Returns packed codes or None.

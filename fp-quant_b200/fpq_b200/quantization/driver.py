@@ -391,7 +391,19 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
     ph.mark("start")
     rank, world_size = fdist.world()
     n_total = len(calibration_data)
-    lo, hi = fdist.shard_bounds(n_total, world_size, rank)
+    # Rank 0 gets the widest Hessian's chain and column loop (`plan_ranks`), which the other ranks wait for once
+    # they have run the second pass up to that layer.  It is therefore given fewer calibration sequences, so
+    # that its own forward passes fit into the time the others need for theirs.  The shares were balanced on
+    # the phase times of a Llama-3.1-8B block with 128 x 2048 tokens (0.89 / 0.72 / 0.62 of an even share at
+    # 2 / 4 / 8 ranks); `args.owner_share` overrides them, 1.0 is an even split.
+    share = getattr(args, "owner_share", None)
+    if share is None:
+        share = {2: 0.89, 4: 0.72, 8: 0.62}.get(world_size, 1.0 if world_size < 2 else 0.7)
+    if world_size > 1 and getattr(args, "split_second_pass", True):
+        rest = (world_size - share) / (world_size - 1)
+        lo, hi = fdist.weighted_bounds(n_total, [share] + [rest] * (world_size - 1))[rank]
+    else:
+        lo, hi = fdist.shard_bounds(n_total, world_size, rank)
     n_local = hi - lo
     input_args, input_kwargs = _collect_block_inputs(model, calibration_data[lo:hi], args, device)
     ph.mark("collect_inputs")
@@ -408,6 +420,7 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
         for name, layer in layers.items():
             handles[name] = GPTQ(layer, Quantizer(**wkw) if wkw else None, quantization_order=args.quantization_order,
                                  rel_damp=args.rel_damp, export_quantized_model=args.export_quantized_model)
+            handles[name].use_cuda_graphs = bool(getattr(args, "cuda_graphs", True))
             if args.scale_precision == ScalePrecision.E4M3:        # fix the weight global scale now (gptq.py:343-358)
                 handles[name].quantizer.get_quantization_params(layer.transform(layer.weight, inv_t=True).float())
                 handles[name].quantizer._track_global_scale = False
@@ -596,7 +609,10 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             ph.mark("update_pass_first_half")
             exchange(deferred)
             if "exact" not in _split_state:      # once per process: does this architecture end in residual + down_proj?
-                _split_state["exact"] = _split_pass_is_exact(block, parts, input_args, input_kwargs, device, args, last)
+                mine = (not parts) or _split_pass_is_exact(block, parts, input_args, input_kwargs, device, args, last)
+                verdict = torch.tensor([1 if mine else 0], device=device, dtype=torch.int32)
+                torch.distributed.all_reduce(verdict, op=torch.distributed.ReduceOp.MIN)    # one answer for all ranks
+                _split_state["exact"] = bool(verdict.item())
             if _split_state["exact"]:
                 _split_pass_second_half(parts, input_args, input_kwargs, last, offload)
             else:

@@ -40,6 +40,7 @@ class GPTQ:
         self.packed_codes: Optional[torch.Tensor] = None     # uint8 [rows, cols/2] of the last `step`
         self.used_identity_fallback = False
         self.defer_host_syncs = False     # True: nothing in quantize() waits for the device (multi-GPU driver's critical path)
+        self.use_cuda_graphs = False      # True: the Cholesky chain and the column loop are replayed from CUDA graphs (drivers)
         self.fallback_status: Optional[torch.Tensor] = None
 
     @torch.no_grad()
@@ -108,7 +109,10 @@ class GPTQ:
             self.packed_codes = fdist.allgather_rows(codes_loc, self.d_row, 128, process_group)
         else:
             w = W.clone()
-            self.packed_codes = ops.gptq_quantize(w, sc, U, group, want_codes=True, group_index=group_index)
+            if self.use_cuda_graphs:
+                self.packed_codes = ops.gptq_quantize_graphed(w, sc, U, group, group_index=group_index)
+            else:
+                self.packed_codes = ops.gptq_quantize(w, sc, U, group, want_codes=True, group_index=group_index)
         if act_order:
             # gptq.py:190-193: back to the original column order (weights, codes, Hessian)
             w = w[:, perm_inv].contiguous()
@@ -134,7 +138,7 @@ class GPTQ:
     def _get_hessian_inverse(self, prepared: bool = False) -> torch.Tensor:
         if not prepared:
             self.prepare_hessian()
-        U, status = ops.cholesky_inverse_upper(self.H)
+        U, status = (ops.cholesky_inverse_upper_graphed if self.use_cuda_graphs else ops.cholesky_inverse_upper)(self.H)
         if self.defer_host_syncs:
             # the reference's `except:` branch (gptq.py:216-217) without reading the status on the host:
             # U becomes the identity on the device when the factorisation failed

@@ -99,3 +99,17 @@ def test_fused_tensor_parallel_path_is_chosen_identically_on_all_ranks(out_featu
     assert verdict == expect
     local = [hi - lo >= 256 for lo, hi in fdist.all_bounds(out_features, world_size, 128)]
     assert verdict == all(local)          # and it is the conjunction of what each rank would have said
+
+
+def test_weighted_bounds_cover_everything_in_order():
+    for p in (ROOT, os.path.join(ROOT, "fp-quant_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from fpq_b200 import dist as fdist
+
+    for n, weights in ((128, [0.62] + [7.38 / 7] * 7), (128, [0.89, 1.11]), (6, [0.89, 1.11]), (3, [0.62] + [1.05] * 7),
+                       (0, [1.0, 1.0]), (5, [1.0])):
+        b = fdist.weighted_bounds(n, weights)
+        assert len(b) == len(weights) and b[0][0] == 0 and b[-1][1] == n
+        assert all(b[i][1] == b[i + 1][0] for i in range(len(b) - 1)) and all(hi >= lo for lo, hi in b)
+    assert [hi - lo for lo, hi in fdist.weighted_bounds(128, [0.62] + [7.38 / 7] * 7)][0] == 10     # the tail owner's share

@@ -219,3 +219,22 @@ def test_gptq_class_in_activation_order(cuda_device, fmt):
     assert torch.equal(wq.float().cpu(), fp4.dequantize(got, g["scales"], GROUP[fmt]))
     rel = get_relative_mse_error(wq.float(), layer.weight.data.float(), h.H).item()
     assert abs(rel - g["relative_mse"].item()) <= 0.01 * g["relative_mse"].item()
+
+
+def test_graph_replays_match_the_direct_calls(cuda_device):
+    """The CUDA-graph forms the drivers use (one capture per shape, replayed on fresh inputs) return exactly
+    what the direct calls return, also on the second use of a shape with different data."""
+    from fpq_b200 import ops
+
+    for seed in (0, 1):
+        g = load("gptq_nvfp4.npz")
+        H = g["damped_hessian"].to(cuda_device) * (1.0 + 0.1 * seed)
+        U, status = ops.cholesky_inverse_upper(H)
+        U2, status2 = ops.cholesky_inverse_upper_graphed(H)
+        assert torch.equal(U, U2) and int(status2.item()) == int(status.item()) == 0
+        W = (g["weight"] * (1.0 + seed)).to(cuda_device)
+        s = (g["scales"] * (1.0 + seed)).to(cuda_device)
+        W1, W2 = W.clone(), W.clone()
+        c1 = ops.gptq_quantize(W1, s, U, 16)
+        c2 = ops.gptq_quantize_graphed(W2, s, U, 16)
+        assert torch.equal(c1, c2) and torch.equal(W1, W2)
