@@ -355,9 +355,13 @@ def library_gemm(args, layers, xs_dev, gs, wscales, outs, flops_step, dev):
         return {"unavailable": "; ".join(attempts + [repr(exc)[:200]])}
 
 
-def sustained(fn, dev_index, seconds=2.0):
+SUSTAINED_SECONDS = 2.0
+
+
+def sustained(fn, dev_index, seconds=None):
     """Runs fn() back to back for at least `seconds` of device time (after a short calibration) with the SM
     clock sampled meanwhile.  Returns (device seconds per call, calls, clock summary)."""
+    seconds = SUSTAINED_SECONDS if seconds is None else seconds
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -1172,7 +1176,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-library-gemm", action="store_true", help="skip the cuBLASLt comparison line")
     ap.add_argument("--no-mr-gptq", action="store_true", help="linear workload: skip the MR-GPTQ part of the line")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="length of the sustained loops; 0 keeps them to three calls (for profiler captures)")
     args = ap.parse_args()
+    global SUSTAINED_SECONDS
+    SUSTAINED_SECONDS = args.sustained_seconds
     if args.impl == "reference":
         run_reference(args)
     else:

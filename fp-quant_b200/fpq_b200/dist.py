@@ -67,6 +67,13 @@ def allreduce_sum_(t: torch.Tensor, group=None) -> torch.Tensor:
     return t
 
 
+def reduce_sum_(t: torch.Tensor, dst: int, group=None) -> torch.Tensor:
+    """Sum over the ranks, delivered to rank `dst` of the group only; the other ranks' `t` is left undefined."""
+    if world(group)[1] > 1:
+        dist.reduce(t, dst=dst if group is None else dist.get_global_rank(group, dst), op=dist.ReduceOp.SUM, group=group)
+    return t
+
+
 def allreduce_min_(t: torch.Tensor, group=None) -> torch.Tensor:
     """Running-minimum quantities (NVFP4 global scales) across ranks."""
     if world(group)[1] > 1:

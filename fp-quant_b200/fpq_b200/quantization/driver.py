@@ -450,21 +450,6 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             if layer.act_quantizer is not None:
                 layer.act_quantizer._track_global_scale = False
 
-        # ---- multi-GPU: one Hessian per distinct input, summed over the ranks' sequences
-        if world_size > 1:
-            for grp, lname in leaders.items():
-                h = handles[lname]
-                if h.H is None:
-                    h.H = torch.zeros((h.d_col, h.d_col), device=device, dtype=torch.float32)
-                h.H.mul_(float(n_local) / float(n_total))     # local running mean -> this rank's share of the global mean
-                fdist.allreduce_sum_(h.H)
-                h.num_samples = n_total
-            for layer in layers.values():
-                if layer.act_quantizer is not None and layer.act_quantizer.global_scale.numel() == 1:
-                    gs = layer.act_quantizer.global_scale.to(device)
-                    layer.act_quantizer.global_scale = fdist.allreduce_min_(gs)
-
-        ph.mark("allreduce")
         # ---- who does what.  One Cholesky-inverse chain per distinct Hessian when no linear of the group has an
         # all-zero weight column (the dead-column fix of gptq.py:203-208 is then the identity and the damped H,
         # hence U, is the same for all of them).  The chains go to different ranks, largest first; every linear
@@ -514,11 +499,18 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
 
         checks: List[torch.Tensor] = []
         shared_U: Dict[str, torch.Tensor] = {}
-        for g in group_order:
+        chains_queued = set()
+
+        def queue_chain(g):
+            """Queues the Cholesky-inverse chain of group g's Hessian on its owner (once)."""
+            if g in chains_queued:
+                return
+            chains_queued.add(g)
             lead = handles[leaders[g]]
-            lead.H_undamped = lead.H.clone()
+            if any(layer_owner[n] == rank for n in group_members[g]):
+                lead.H_undamped = lead.H.clone()
             if not share_ok[g]:
-                continue
+                return
             owner = group_owner[g]
             elsewhere = any(layer_owner[n] != owner for n in group_members[g])
             if rank == owner:
@@ -531,6 +523,32 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
                     ph.mark("factor_chain")
             elif elsewhere:
                 shared_U[g] = torch.empty((lead.d_col, lead.d_col), device=device, dtype=torch.float32)
+
+        # ---- multi-GPU: one Hessian per distinct input, summed over the ranks' sequences, widest first.  A
+        # Hessian whose linears all stay on the rank that factors it is only needed there: it is reduced to
+        # that rank (half the traffic of an all-reduce), and the deferred linear's chain starts on its owner's
+        # side stream as soon as its sum has arrived, under the remaining collectives.
+        if world_size > 1:
+            for grp in group_order:
+                h = handles[leaders[grp]]
+                if h.H is None:
+                    h.H = torch.zeros((h.d_col, h.d_col), device=device, dtype=torch.float32)
+                h.H.mul_(float(n_local) / float(n_total))     # local running mean -> this rank's share of the global mean
+                if all(layer_owner[n] == group_owner[grp] for n in group_members[grp]):
+                    fdist.reduce_sum_(h.H, group_owner[grp])
+                else:
+                    fdist.allreduce_sum_(h.H)
+                h.num_samples = n_total
+                if deferred is not None and leaders[grp] == deferred:
+                    queue_chain(grp)
+            for layer in layers.values():
+                if layer.act_quantizer is not None and layer.act_quantizer.global_scale.numel() == 1:
+                    gs = layer.act_quantizer.global_scale.to(device)
+                    layer.act_quantizer.global_scale = fdist.allreduce_min_(gs)
+
+        ph.mark("allreduce")
+        for g in group_order:
+            queue_chain(g)
         for g in group_order:                       # after all chains were queued: they overlap across ranks
             if share_ok[g] and world_size > 1 and any(layer_owner[n] != group_owner[g] for n in group_members[g]):
                 torch.distributed.broadcast(shared_U[g], src=group_owner[g])

@@ -59,6 +59,10 @@ def _worker(rank, world_size, port, tmpdir):
         t = torch.tensor([float(rank + 1)])
         assert fdist.allreduce_min_(t.clone()).item() == 1.0
         assert fdist.allreduce_sum_(t.clone()).item() == sum(range(1, world_size + 1))
+        for dst in range(world_size):       # the sum arrives on `dst`; nobody else may rely on its buffer
+            r = fdist.reduce_sum_(t.clone(), dst)
+            if rank == dst:
+                assert r.item() == sum(range(1, world_size + 1))
         open(os.path.join(tmpdir, f"ok{rank}"), "w").write("ok")
     finally:
         dist.destroy_process_group()
