@@ -470,6 +470,25 @@ extern "C" int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, cons
   return bn256 ? launch_gemm<256, false>(ta, tb, p, st) : launch_gemm<128, false>(ta, tb, p, st);
 }
 
+extern "C" int fpq_gemm_mxf8(const uint8_t* a_e4m3, const uint8_t* b_e4m3, const uint8_t* a_scales_swizzled,
+                             const uint8_t* b_scales_swizzled, const float* alpha, void* out_bf16, int64_t M, int64_t N,
+                             int64_t K, int32_t* error_flag, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(a_e4m3 && b_e4m3 && a_scales_swizzled && b_scales_swizzled && alpha && out_bf16 && error_flag,
+                "NULL pointer");
+  FPQ_CHECK_ARG(M >= 0 && N > 0 && K > 0, "bad shape");
+  FPQ_CHECK_ARG(K % 32 == 0, "K (%lld) must be a multiple of 32", (long long)K);
+  FPQ_CHECK_ARG(N % 8 == 0, "N (%lld) must be a multiple of 8", (long long)N);
+  FPQ_CHECK_ARG(M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30), "shape too large");
+  FPQ_CHECK_ARG(((uintptr_t)a_e4m3 & 15) == 0 && ((uintptr_t)b_e4m3 & 15) == 0 &&
+                    ((uintptr_t)a_scales_swizzled & 15) == 0 && ((uintptr_t)b_scales_swizzled & 15) == 0 &&
+                    ((uintptr_t)out_bf16 & 15) == 0,
+                "pointers must be 16-byte aligned");
+  if (M == 0) return FPQ_OK;
+  // one kernel for every shape: rows beyond M or N are zero-filled by the loads and clipped by the stores
+  return gemm_fp4_pair(a_e4m3, b_e4m3, a_scales_swizzled, b_scales_swizzled, alpha, nullptr, out_bf16, M, N, K,
+                       FPQ_FMT_MXFP8, error_flag, (cudaStream_t)stream);
+}
+
 extern "C" int fpq_gemm_fp4_push(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* a_scales_swizzled,
                                  const uint8_t* b_scales_swizzled, const float* alpha, const void* bias_bf16,
                                  void* out_bf16, void* const* peer_outs, int n_peers, int64_t ldc, int64_t col_offset,

@@ -42,8 +42,8 @@ using namespace ptx;
 constexpr int BM_CTA = 128;            // rows of A per CTA
 constexpr int BN = 256;                // columns of the pair tile
 constexpr int BN_CTA = 128;            // rows of B per CTA
-constexpr int BK_BYTES = 128;
-constexpr int BK_ELEMS = 256;
+constexpr int BK_BYTES = 128;           // operand bytes per row and stage: 256 four-bit or 128 eight-bit elements
+constexpr int KIND_MXFP4 = 0, KIND_NVFP4 = 1, KIND_MXFP8 = 2;
 constexpr int NUM_THREADS = 704;       // 22 warps: producer, MMA, 4 scale movers, 16 epilogue (one per 32 rows x 64 columns)
 constexpr int TMEM_COLS = 512;
 constexpr int SF_TMEM_BASE = 256;
@@ -77,11 +77,14 @@ struct PushParams {
 // one (32 KiB of operands per CTA) every ~0.28 us, so four stages (measured: 0.405 us per stage) starve it and
 // six do not.  Shared memory is therefore spent on stages, and the sixteen epilogue warps share a few
 // staging boxes in turn (a barrier per box) instead of owning one each.
-template <bool NVFP4>
+template <int KIND>
 struct PairSmem {
+  static constexpr bool NVFP4 = KIND == KIND_NVFP4;
+  static constexpr int BK_ELEMS = KIND == KIND_MXFP8 ? 128 : 256;   // K elements per stage
+  static constexpr int MMA_K = KIND == KIND_MXFP8 ? 32 : 64;        // K elements per instruction (32 bytes)
   static constexpr int STAGES = NVFP4 ? 5 : 6;                // NVFP4: 5 x 48 tensor-memory columns of scales is all that fits
   static constexpr int NBOX = NVFP4 ? 8 : 4;                  // 32-row x 128-byte staging boxes of the epilogue
-  static constexpr int SFBLK = NVFP4 ? 4 : 2;                 // 512-byte scale tiles per 128 rows per stage
+  static constexpr int SFBLK = NVFP4 ? 4 : KIND == KIND_MXFP8 ? 1 : 2;   // 512-byte scale tiles per 128 rows per stage
   static constexpr int SFA_COLS = 4 * SFBLK;                  // tensor-memory columns of one stage's A scales
   static constexpr int SF_TMEM_BUF = 12 * SFBLK;              // A scales + B scales (256 rows) of one stage
   static constexpr int A_BYTES = BM_CTA * BK_BYTES;           // 16 KiB
@@ -116,14 +119,16 @@ __device__ __forceinline__ void pair_tile_coords(const PairParams& p, int tile, 
   n_blk = in_band / rows;
 }
 
-template <bool NVFP4, bool PUSH>
+template <int KIND, bool PUSH>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                      const __grid_constant__ CUtensorMap tmap_out, const PairParams p, const PushParams push) {
-  using L = PairSmem<NVFP4>;
+  using L = PairSmem<KIND>;
+  constexpr bool NVFP4 = L::NVFP4;
   constexpr int STAGES = L::STAGES;
   constexpr int SFBLK = L::SFBLK;
+  constexpr int BK_ELEMS = L::BK_ELEMS;
   extern __shared__ __align__(1024) uint8_t smem_raw[];      // 128-byte-swizzled TMA boxes need 1024-byte alignment
   uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
@@ -231,8 +236,9 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t idesc_k[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const uint32_t sf_id = NVFP4 ? 0u : (uint32_t)((k & 1) * 2);
-        idesc_k[k] = make_idesc_fp4(256, BN, !NVFP4, sf_id, sf_id);
+        // which of a column's four scale bytes instruction k reads: NVFP4 all four, MXFP4 a pair, MXFP8 one
+        const uint32_t sf_id = NVFP4 ? 0u : KIND == KIND_MXFP8 ? (uint32_t)k : (uint32_t)((k & 1) * 2);
+        idesc_k[k] = KIND == KIND_MXFP8 ? make_idesc_mxf8(256, BN, sf_id, sf_id) : make_idesc_fp4(256, BN, !NVFP4, sf_id, sf_id);
       }
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
@@ -252,18 +258,18 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (k_left >= BK_ELEMS) {
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-              const uint32_t blk = NVFP4 ? (uint32_t)k : (uint32_t)(k >> 1);
-              tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k], sfa_t + 4 * blk,
-                                                  sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+              const uint32_t blk = NVFP4 ? (uint32_t)k : KIND == KIND_MXFP8 ? 0u : (uint32_t)(k >> 1);
+              tc_mma_fp4_block_scaled_pair<KIND>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k], sfa_t + 4 * blk,
+                                                 sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
             }
           } else {
-            const int kmma = (k_left + 63) / 64;
+            const int kmma = (k_left + L::MMA_K - 1) / L::MMA_K;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               if (k < kmma) {
-                const uint32_t blk = NVFP4 ? (uint32_t)k : (uint32_t)(k >> 1);
-                tc_mma_fp4_block_scaled_pair<NVFP4>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k], sfa_t + 4 * blk,
-                                                    sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
+                const uint32_t blk = NVFP4 ? (uint32_t)k : KIND == KIND_MXFP8 ? 0u : (uint32_t)(k >> 1);
+                tc_mma_fp4_block_scaled_pair<KIND>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc_k[k], sfa_t + 4 * blk,
+                                                   sfb_t + 8 * blk, (ks > 0 || k > 0) ? 1u : 0u);
               }
             }
           }
@@ -431,18 +437,18 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   }
 }
 
-template <bool NVFP4>
+template <int KIND>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa, const CUtensorMap& tsb,
                 const CUtensorMap& tout, PairParams p, const PushParams& push, cudaStream_t stream) {
-  using L = PairSmem<NVFP4>;
-  auto kern = push.n > 0 ? gemm_fp4_pair_kernel<NVFP4, true> : gemm_fp4_pair_kernel<NVFP4, false>;
+  using L = PairSmem<KIND>;
+  auto kern = push.n > 0 ? gemm_fp4_pair_kernel<KIND, true> : gemm_fp4_pair_kernel<KIND, false>;
   // one-time per device (idempotent: concurrent first calls set the same attribute)
   static std::atomic<bool> configured[64];
   int dev = 0;
   FPQ_CHECK_CUDA(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev].load(std::memory_order_acquire)) {
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
-    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<NVFP4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<KIND, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
+    FPQ_CHECK_CUDA(cudaFuncSetAttribute(gemm_fp4_pair_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES));
     configured[dev].store(true, std::memory_order_release);
   }
   int pairs = sm_count() / 2;
@@ -470,13 +476,17 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
 int make_tensor_map_2d_u64(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                            uint32_t box_inner, uint32_t box_outer);
 
-// Large-M path of fpq_gemm_fp4.  Shapes and pointers were validated by the caller.
+// Large-M path of fpq_gemm_fp4, and the whole of fpq_gemm_mxf8 (format FPQ_FMT_MXFP8: one byte per element).
+// Shapes and pointers were validated by the caller.
 int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb, const float* alpha,
                   const void* bias, void* out, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
                   cudaStream_t stream, int64_t ldc, void* const* peers, int n_peers) {
   if (ldc <= 0) ldc = N;
+  const bool fp8 = format == FPQ_FMT_MXFP8;
   const int g = format == FPQ_FMT_NVFP4 ? 16 : 32;
-  const int sfblk = format == FPQ_FMT_NVFP4 ? 4 : 2;
+  const int sfblk = format == FPQ_FMT_NVFP4 ? 4 : fp8 ? 1 : 2;
+  const int BK_ELEMS = fp8 ? 128 : 256;
+  const uint64_t row_bytes = fp8 ? (uint64_t)K : (uint64_t)K / 2;
   PairParams p{};
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.num_m_pairs = (int)((M + 255) / 256);
@@ -500,14 +510,15 @@ int gemm_fp4_pair(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const 
   CUtensorMap ta, tb, tsa, tsb, tout;
   // output as 64-column x 32-row boxes of bf16 (128 bytes per box row, 128-byte swizzle)
   if (int rc = make_tensor_map_2d(&tout, out, 2, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 32, 1)) return rc;
-  if (int rc = make_tensor_map_2d(&ta, a, 1, (uint64_t)K / 2, (uint64_t)M, (uint64_t)K / 2, BK_BYTES, BM_CTA, 1)) return rc;
-  if (int rc = make_tensor_map_2d(&tb, b, 1, (uint64_t)K / 2, (uint64_t)N, (uint64_t)K / 2, BK_BYTES, BN_CTA, 1)) return rc;
+  if (int rc = make_tensor_map_2d(&ta, a, 1, row_bytes, (uint64_t)M, row_bytes, BK_BYTES, BM_CTA, 1)) return rc;
+  if (int rc = make_tensor_map_2d(&tb, b, 1, row_bytes, (uint64_t)N, row_bytes, BK_BYTES, BN_CTA, 1)) return rc;
   const uint64_t sf_row_words = (uint64_t)p.sf_blocks_k * 64;      // 8-byte words per 128-row block
   const uint64_t a_blocks = (uint64_t)((M + 127) / 128), b_blocks = (uint64_t)((N + 127) / 128);
   if (int rc = make_tensor_map_2d_u64(&tsa, sfa, sf_row_words, a_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 1)) return rc;
   if (int rc = make_tensor_map_2d_u64(&tsb, sfb, sf_row_words, b_blocks, sf_row_words * 8, (uint32_t)sfblk * 64, 2)) return rc;
-  return format == FPQ_FMT_NVFP4 ? launch_pair<true>(ta, tb, tsa, tsb, tout, p, push, stream)
-                                 : launch_pair<false>(ta, tb, tsa, tsb, tout, p, push, stream);
+  if (fp8) return launch_pair<KIND_MXFP8>(ta, tb, tsa, tsb, tout, p, push, stream);
+  return format == FPQ_FMT_NVFP4 ? launch_pair<KIND_NVFP4>(ta, tb, tsa, tsb, tout, p, push, stream)
+                                 : launch_pair<KIND_MXFP4>(ta, tb, tsa, tsb, tout, p, push, stream);
 }
 
 }  // namespace fpq

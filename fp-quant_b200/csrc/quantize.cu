@@ -296,7 +296,19 @@ __device__ __forceinline__ float quest_scale(const u64* P, uint32_t& byte) {
 
 // NVFP4 scale of one 16-element group.
 __device__ __forceinline__ float nv_scale(float a, float gs, float rgs, uint32_t& byte) {
-  float s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
+  // s0 = fl(fl(2a) / 12) = fl(a / 3) / 2.  With r = fl(1/3), q = fl(a r), e = a - 3 q (exact, fused) the
+  // value fl(q + e r) is the correctly rounded a / 3 for every fp32 mantissa (checked exhaustively on the
+  // CPU); halving is exact while nothing underflows, so the general division is kept for the extremes.
+  float s0;
+  if (a > 7.8886e-31f /* 2^-100 */ && a < 1.3292e36f /* 2^120 */) {
+    const float r = 0.333333343f;             // 0x3eaaaaab
+    float q = __fmul_rn(a, r);
+    const float e = __fmaf_rn(-3.0f, q, a);
+    q = __fmaf_rn(e, r, q);
+    s0 = 0.5f * q;
+  } else {
+    s0 = __fdiv_rn(__fmul_rn(2.0f, a), 12.0f);
+  }
   float t = fminf(fmaxf(__fmul_rn(s0, gs), -448.0f), 448.0f);
   uint16_t u2;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(u2) : "f"(0.0f), "f"(t));
@@ -402,7 +414,10 @@ __device__ __forceinline__ void process_chunk(const QuantParams& p, const RawChu
     // MXFP4 codes take the unscaled butterfly output (the 1/sqrt(g) factor is folded into the
     // code multiplier); every other mode works on the scaled rotation.
     constexpr bool MX_FAST = MODE == MODE_CODES && FMT == FPQ_FMT_MXFP4;
-    rotate_chunk<GH, !MX_FAST>(P, lane);
+    // NVFP4 codes with a rotation whose 1/sqrt(g) is a power of two (g = 16, 64): the factor c goes into the
+    // divisor instead, t / (s / c) = (t c) / s exactly, which saves the sixteen scaling multiplies.
+    constexpr bool NV_FOLD = MODE == MODE_CODES && FMT == FPQ_FMT_NVFP4 && (GH == 16 || GH == 64);
+    rotate_chunk<GH, !(MX_FAST || NV_FOLD)>(P, lane);
 
     if (MODE == MODE_ABSMAX) {
       running_max = fmaxf(running_max, absmax_pairs(P, 16));
@@ -437,13 +452,15 @@ __device__ __forceinline__ void process_chunk(const QuantParams& p, const RawChu
     constexpr int NG = FMT == FPQ_FMT_NVFP4 ? 2 : 1;  // groups per thread
     constexpr int PG = 16 / NG;                       // pairs per group
     float s[NG];
+    float amax_g[NG];
     uint32_t sb[NG];
     int mx_e = 0;
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
       if (FMT == FMT_MXQUEST) break;
       float a = absmax_pairs(P + g * PG, PG);
-      if (MX_FAST && GH != 0) a = __fmul_rn(a, hadamard_scale<GH>());   // max |t*c| = fl(c * max |t|)
+      if ((MX_FAST || NV_FOLD) && GH != 0) a = __fmul_rn(a, hadamard_scale<GH>());   // max |t*c| = fl(c * max |t|)
+      if (NV_FOLD) amax_g[g] = a;
       s[g] = FMT == FPQ_FMT_NVFP4 ? nv_scale(a, gs, rgs, sb[g]) : mx_scale(a, sb[g], mx_e);
     }
     if (FMT == FMT_MXQUEST) s[0] = quest_scale(P, sb[0]);
@@ -490,6 +507,22 @@ __device__ __forceinline__ void process_chunk(const QuantParams& p, const RawChu
           for (int j = 0; j < 16; ++j) P[j] = mul2(P[j], C);
         }
         divide_pairs(P, 16, s[0]);
+      }
+    } else if (NV_FOLD) {
+      constexpr float c = GH == 16 ? 0.25f : 0.125f;
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const float sf = s[g] * (1.0f / c);
+        // Exact while nothing leaves the normal range: then t c is exact for every element that can get a
+        // non-zero code (an element whose t c is subnormal is > 2^20 below the group's scale).
+        if (amax_g[g] > 7.8886e-31f /* 2^-100 */ && sf < 1.2676e30f /* 2^100 */) {
+          divide_pairs(P + g * PG, PG, sf);
+        } else {
+          const u64 C = pack2(c, c);
+#pragma unroll
+          for (int j = 0; j < PG; ++j) P[g * PG + j] = mul2(P[g * PG + j], C);
+          divide_pairs(P + g * PG, PG, s[g]);
+        }
       }
     } else {
 #pragma unroll

@@ -273,11 +273,19 @@ __device__ __forceinline__ void tc_commit_pair_multicast(uint32_t bar, uint16_t 
       "h"(cta_mask)
       : "memory");
 }
-template <bool NVFP4>
+// KIND: 0 = MXFP4 (E8M0 scale per 32 elements, K = 64 per instruction), 1 = NVFP4 (E4M3 per 16, K = 64),
+// 2 = MXFP8 (8-bit operands, E8M0 per 32, K = 32 per instruction).
+template <int KIND>
 __device__ __forceinline__ void tc_mma_fp4_block_scaled_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                              uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
                                                              uint32_t accumulate) {
-  if (NVFP4) {
+  if (KIND == 2) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+  } else if (KIND == 1) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
@@ -323,6 +331,19 @@ __host__ __device__ inline uint32_t make_idesc_fp4(int m, int n, bool ue8m0_scal
   d |= 1u << 10;                      // B format E2M1
   d |= (uint32_t)(n >> 3) << 17;
   d |= (ue8m0_scales ? 1u : 0u) << 23;
+  d |= (uint32_t)(m >> 4) << 24;
+  d |= (a_sf_id & 3u) << 29;
+  return d;
+}
+
+// Instruction descriptor of a block-scaled E4M3 x E4M3 -> fp32 MMA (kind::mxf8f6f4, E8M0 scales), both
+// operands K-major.  The scale ids select one of the four scale bytes a tensor-memory column holds per row.
+__host__ __device__ inline uint32_t make_idesc_mxf8(int m, int n, uint32_t a_sf_id, uint32_t b_sf_id) {
+  uint32_t d = 0;
+  d |= (b_sf_id & 3u) << 4;
+  // A format (bits 7-9) and B format (bits 10-12): 0 = E4M3
+  d |= (uint32_t)(n >> 3) << 17;
+  d |= 1u << 23;                      // scale format UE8M0
   d |= (uint32_t)(m >> 4) << 24;
   d |= (a_sf_id & 3u) << 29;
   return d;

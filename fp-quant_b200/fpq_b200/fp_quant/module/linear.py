@@ -2,8 +2,7 @@
 inference_lib/src/fp_quant/module/linear.py (IST-DASLab/FP-Quant), on the fpq_b200 kernels.
 
 Differences a caller can observe: the weight scales are additionally cached in the swizzled
-layout the matmul reads (`_scales_blocked`, rebuilt when `scales` changes), and the QAT
-configurations (MXFP4/MXFP8 backward) raise, as they are outside the B200 hot path.
+layout the matmul reads (`_scales_blocked`, rebuilt when `scales` changes).
 """
 from __future__ import annotations
 
@@ -13,8 +12,8 @@ from torch import nn
 from ... import ops
 from ...rotation import sylvester
 from ..utils.config import FPQuantConfig, FPQuantDtype, validate_config
-from .linear_fns import (FPQuant4x16MasterFn, FPQuant4x16NoMasterFn, _linear_forward, forward_gemm_blocked,
-                         forward_quantize, gemm_alpha)
+from .linear_fns import (FPQuant4x4MasterFn, FPQuant4x8MasterFn, FPQuant4x8NoMasterFn, FPQuant4x16MasterFn, FPQuant4x16NoMasterFn,
+                         _linear_forward, forward_gemm_blocked, forward_quantize, gemm_alpha)
 from .pseudoquant_linear_fns import PseudoQuant4x16MasterFn, PseudoQuant4x16NoMasterFn, forward_pseudoquantize
 from .qutlass_ops import (HAS_QUTLASS, fused_silu_mul_quantize_blocked_op,  # noqa: F401  (HAS_QUTLASS: API compatibility)
                           swizzle_scales_op)
@@ -180,9 +179,16 @@ class FPQuantLinear(nn.Module):
                 return _linear_forward(x, self.qweight, self._blocked_weight_scales(), *common, self._gemm_alpha())
             return FPQuant4x16NoMasterFn.apply(x, self.qweight, self._blocked_weight_scales(), *common,
                                                self._gemm_alpha())
-        if cfg.forward_dtype == FPQuantDtype.MXFP4 and cfg.backward_dtype in (FPQuantDtype.MXFP4, FPQuantDtype.MXFP8) \
-                and not cfg.pseudoquantization:
-            raise NotImplementedError("quantised backward passes (MXFP4 / MXFP8 QAT) are outside the B200 hot path")
+        if cfg.forward_dtype == FPQuantDtype.MXFP4 and cfg.backward_dtype == FPQuantDtype.MXFP8 and not cfg.pseudoquantization:
+            common = (self.weight_global_scale, self.act_global_scale, self.bias, self.forward_hadamard_matrix,
+                      cfg.forward_dtype, cfg.forward_method)
+            if cfg.store_master_weights:
+                return FPQuant4x8MasterFn.apply(x, self.weight, *common)
+            return FPQuant4x8NoMasterFn.apply(x, self.qweight, self.scales, *common)
+        if cfg.forward_dtype == FPQuantDtype.MXFP4 and cfg.backward_dtype == FPQuantDtype.MXFP4 and not cfg.pseudoquantization \
+                and cfg.store_master_weights:
+            return FPQuant4x4MasterFn.apply(x, self.weight, self.weight_global_scale, self.act_global_scale, self.bias,
+                                            self.forward_hadamard_matrix, cfg.forward_dtype, cfg.forward_method)
         raise ValueError(
             f"Forward dtype: {cfg.forward_dtype}, backward dtype: {cfg.backward_dtype}, store_master_weights: "
             f"{cfg.store_master_weights}, pseudoquantization: {cfg.pseudoquantization} isn't supported yet.")

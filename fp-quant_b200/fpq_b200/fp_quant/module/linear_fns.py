@@ -1,8 +1,8 @@
 """Forward functions of the quantised linear layer, mirroring
 inference_lib/src/fp_quant/module/linear_fns.py (IST-DASLab/FP-Quant): `forward_quantize`,
-`forward_gemm` and the two bf16-backward autograd functions.  Only the forward pass is on the
-B200 path; backward through quantised weights raises like the reference does, and backward
-through master weights is the plain bf16 einsum of the reference.
+`forward_gemm`, the two bf16-backward autograd functions and the MXFP8-backward pair
+(`FPQuant4x8MasterFn`: both gradient GEMMs on MXFP8 operands).  Backward through pre-quantised
+weights raises like the reference does.  `FPQuant4x4MasterFn` runs both gradient GEMMs on MXFP4 operands.
 """
 from __future__ import annotations
 
@@ -12,8 +12,13 @@ import torch
 from torch.autograd import Function
 
 from ..utils.config import FPQuantDtype
-from .qutlass_ops import (fused_quantize_blocked_op, fused_quantize_mx_op, fused_quantize_nv_op,
-                          matmul_fp4_bf16_tn_blocked_op, matmul_mxf4_bf16_tn_op, matmul_nvf4_bf16_tn_op)
+from ... import ops
+from ...rotation import kind_of
+from .qutlass_ops import (backward_bf16_square_double_mxfp8_op, backward_qt_bf16_op, backward_t_bf16_op,
+                          fused_quantize_blocked_op, fused_quantize_mx_op,
+                          fused_quantize_nv_op, matmul_fp4_bf16_tn_blocked_op, matmul_mxf4_bf16_tn_op,
+                          matmul_mxf8_bf16_nn_op, matmul_mxf8_bf16_tn_op, matmul_nvf4_bf16_tn_op,
+                          mxfp4_transpose_mxfp8_op)
 
 
 def forward_quantize(x: torch.Tensor, hadamard_matrix: torch.Tensor, global_scale: torch.Tensor,
@@ -116,5 +121,159 @@ class FPQuant4x16MasterFn(Function):
         g = grad_output.flatten(end_dim=-2)
         grad_input = (g @ weight).view(ctx.x_shape)
         grad_weight = g.t() @ x_flat
+        grad_bias = g.sum(dim=0) if ctx.bias_present else None
+        return grad_input, grad_weight, None, None, grad_bias, None, None, None
+
+
+def _unpack_mask(clip_mask: torch.Tensor) -> torch.Tensor:
+    """[.., K/8] bytes -> [.., K] bool, bit i of byte b = element 8 b + i (linear_fns.py:67-77)."""
+    bits = (clip_mask.unsqueeze(-1) >> torch.arange(8, device=clip_mask.device, dtype=torch.uint8)) & 1
+    return bits.flatten(start_dim=-2).bool()
+
+
+def _unrotate(g: torch.Tensor, hadamard_matrix: torch.Tensor) -> torch.Tensor:
+    """`g.view(-1, h) @ hadamard_matrix.T` in bf16 (linear_fns.py:321-324): gradient with respect to the
+    rotated operand -> gradient with respect to the operand.  The normalised Sylvester matrix is symmetric,
+    so the butterfly kernel does it; any other matrix takes the dense product."""
+    kind, group = kind_of(0, hadamard_matrix)
+    if kind == "identity":
+        return g
+    if kind == "hadamard":
+        return ops.rotate_hadamard(g.contiguous(), group, out_dtype=torch.bfloat16)
+    return ops.rotate_dense(g.contiguous(), hadamard_matrix.t().contiguous(), out_dtype=torch.bfloat16)
+
+
+def _mxfp8_backward(grad_output, x_q, w_q, x_scales, w_scales, act_global_scale, weight_global_scale, x_mask, w_mask,
+                    hadamard_matrix, x_shape, want_weight_grad: bool):
+    """The two gradient GEMMs of linear_fns.py:270-350 on MXFP8 operands.  The saved MXFP4 operands are
+    transposed into MXFP8 (exactly, unless the scales of a 32-row band differ by more than 2^14), the bf16
+    gradient is quantised once with a scale per 32 x 32 square and read along either axis."""
+    g = grad_output.flatten(end_dim=-2).to(torch.bfloat16).contiguous()
+    tokens, out_features = g.shape
+    g_fp8, g_row_scales, g_col_scales = backward_bf16_square_double_mxfp8_op(g)
+    w_t_fp8, w_t_scales = mxfp4_transpose_mxfp8_op(w_q, w_scales)            # [in, out_up128]
+    if w_t_fp8.shape[1] != out_features:
+        w_t_fp8 = w_t_fp8[:, :out_features].contiguous()
+        w_t_scales = w_t_scales[:, : out_features // 32].contiguous()
+    grad_input = matmul_mxf8_bf16_tn_op(g_fp8, w_t_fp8, g_row_scales, w_t_scales,
+                                        (1.0 / weight_global_scale.float()).reshape(1))[:tokens]
+    if x_mask is not None:
+        grad_input = grad_input * _unpack_mask(x_mask).view_as(grad_input).to(grad_input.dtype)
+    grad_input = _unrotate(grad_input, hadamard_matrix).view(x_shape)
+    grad_weight = None
+    if want_weight_grad:
+        x_t_fp8, x_t_scales = mxfp4_transpose_mxfp8_op(x_q, x_scales)        # [in, tokens_up128]
+        grad_weight = matmul_mxf8_bf16_nn_op(g_fp8, x_t_fp8, g_col_scales, x_t_scales,
+                                             (1.0 / act_global_scale.float()).reshape(1))
+        if w_mask is not None:
+            grad_weight = grad_weight * _unpack_mask(w_mask).view_as(grad_weight).to(grad_weight.dtype)
+        grad_weight = _unrotate(grad_weight, hadamard_matrix).view(out_features, w_q.size(-1) * 2)
+    return grad_input, grad_weight
+
+
+class FPQuant4x8MasterFn(Function):
+    """MXFP4 forward from a bf16 master weight, MXFP8 backward (linear_fns.py:232-350)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, weight_global_scale, act_global_scale, bias, forward_hadamard_matrix, dtype,
+                forward_method):
+        x_flat = x.contiguous().flatten(end_dim=-2)
+        x_q, x_scales, x_mask = forward_quantize(x_flat, forward_hadamard_matrix, act_global_scale, dtype, forward_method)
+        w_q, w_scales, w_mask = forward_quantize(weight, forward_hadamard_matrix, weight_global_scale, dtype, forward_method)
+        y = forward_gemm(x_q, w_q, x_scales, w_scales, 1.0 / (weight_global_scale * act_global_scale), dtype)
+        y = y.unflatten(dim=0, sizes=x.shape[:-1])
+        if bias is not None:
+            y = y + bias
+        ctx.x_shape, ctx.bias_present = x.shape, bias is not None
+        ctx.masks = (x_mask, w_mask)
+        ctx.save_for_backward(x_q, w_q, x_scales, w_scales, act_global_scale, weight_global_scale, forward_hadamard_matrix)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x_q, w_q, x_scales, w_scales, act_global_scale, weight_global_scale, hadamard_matrix = ctx.saved_tensors
+        x_mask, w_mask = ctx.masks
+        grad_input, grad_weight = _mxfp8_backward(grad_output, x_q, w_q, x_scales, w_scales, act_global_scale,
+                                                  weight_global_scale, x_mask, w_mask, hadamard_matrix, ctx.x_shape, True)
+        grad_bias = grad_output.flatten(end_dim=-2).sum(dim=0) if ctx.bias_present else None
+        return grad_input, grad_weight, None, None, grad_bias, None, None, None
+
+
+class FPQuant4x8NoMasterFn(Function):
+    """MXFP4 forward from pre-quantised weights (row-major scale bytes as stored in a checkpoint); the
+    backward raises, as the reference's does (linear_fns.py:352-404)."""
+
+    @staticmethod
+    def forward(ctx, x, weight_q, weight_scales, weight_global_scale, act_global_scale, bias, forward_hadamard_matrix,
+                dtype, forward_method):
+        x_flat = x.contiguous().flatten(end_dim=-2)
+        x_q, x_scales, _ = forward_quantize(x_flat, forward_hadamard_matrix, act_global_scale, dtype, forward_method)
+        y = forward_gemm(x_q, weight_q, x_scales, weight_scales, 1.0 / (weight_global_scale * act_global_scale), dtype)
+        y = y.unflatten(dim=0, sizes=x.shape[:-1])
+        if bias is not None:
+            y = y + bias
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        raise NotImplementedError("Backward pass is not implemented for FPQuant4x8NoMasterFn yet")
+
+
+class FPQuant4x4MasterFn(Function):
+    """MXFP4 forward from a bf16 master weight, MXFP4 backward (linear_fns.py:80-230): the gradient and the
+    dequantised, transposed operands are rotated along the contraction axis with a Hadamard matrix whose
+    columns get fresh random signs on every call, quantised to MXFP4 again (abs_max), and both gradient
+    GEMMs run on the FP4 kernel."""
+
+    @staticmethod
+    def forward(ctx, x, weight, weight_global_scale, act_global_scale, bias, forward_hadamard_matrix, dtype,
+                forward_method):
+        x_flat = x.contiguous().flatten(end_dim=-2)
+        x_q, x_scales, x_mask = forward_quantize(x_flat, forward_hadamard_matrix, act_global_scale, dtype, forward_method)
+        w_q, w_scales, w_mask = forward_quantize(weight, forward_hadamard_matrix, weight_global_scale, dtype, forward_method)
+        y = forward_gemm(x_q, w_q, x_scales, w_scales, 1.0 / (weight_global_scale * act_global_scale), dtype)
+        y = y.unflatten(dim=0, sizes=x.shape[:-1])
+        if bias is not None:
+            y = y + bias
+        ctx.x_shape, ctx.bias_present = x.shape, bias is not None
+        ctx.masks = (x_mask, w_mask)
+        ctx.save_for_backward(x_q, w_q, x_scales, w_scales, act_global_scale, weight_global_scale, forward_hadamard_matrix)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x_q, w_q, x_scales, w_scales, act_global_scale, weight_global_scale, hadamard_matrix = ctx.saved_tensors
+        x_mask, w_mask = ctx.masks
+        h = hadamard_matrix.shape[-1]
+        signs = torch.randint(0, 2, (h,), device=hadamard_matrix.device, dtype=torch.bfloat16) * 2.0 - 1.0
+        backward_hadamard_matrix = hadamard_matrix.to(torch.bfloat16) * signs
+        g = grad_output.flatten(end_dim=-2).to(torch.bfloat16).contiguous()
+        tokens, out_features = g.shape
+        # abs_max MXFP4 carries a factor 3 per operand (the scale is a third of the power of two that is stored)
+        ninth = torch.full((1,), 1.0 / 9.0, dtype=torch.float32, device=g.device)
+
+        g_q, g_scales, _ = fused_quantize_mx_op(g, backward_hadamard_matrix, "abs_max", False)
+        wt_q, wt_scales = backward_qt_bf16_op(w_q, w_scales, backward_hadamard_matrix, weight_global_scale.float())
+        grad_input = matmul_mxf4_bf16_tn_op(g_q, wt_q, g_scales, wt_scales, ninth)
+        if x_mask is not None:
+            grad_input = grad_input * _unpack_mask(x_mask).view_as(grad_input).to(grad_input.dtype)
+        grad_input = _unrotate(grad_input, hadamard_matrix).view(ctx.x_shape)
+
+        # the weight gradient contracts over the tokens: pad them to a whole number of K tiles with zero rows
+        pad = (-tokens) % 128
+        g_pad = torch.nn.functional.pad(g, (0, 0, 0, pad)) if pad else g
+        gt_q, gt_scales = backward_t_bf16_op(g_pad, backward_hadamard_matrix)
+        if pad:
+            zero_codes = torch.full((pad, x_q.shape[1]), 0x88, dtype=torch.uint8, device=x_q.device)
+            x_q_pad = torch.cat([x_q.view(torch.uint8), zero_codes])
+            xs = x_scales.view(torch.uint8)[:tokens, : x_q.shape[1] // 16]
+            xs_pad = torch.cat([xs, torch.full((pad, xs.shape[1]), 127, dtype=torch.uint8, device=xs.device)])
+        else:
+            x_q_pad, xs_pad = x_q, x_scales
+        xt_q, xt_scales = backward_qt_bf16_op(x_q_pad, xs_pad, backward_hadamard_matrix, act_global_scale.float())
+        grad_weight = matmul_mxf4_bf16_tn_op(gt_q, xt_q, gt_scales, xt_scales, ninth)
+        if w_mask is not None:
+            grad_weight = grad_weight * _unpack_mask(w_mask).view_as(grad_weight).to(grad_weight.dtype)
+        grad_weight = _unrotate(grad_weight, hadamard_matrix).view(out_features, w_q.size(-1) * 2)
         grad_bias = g.sum(dim=0) if ctx.bias_present else None
         return grad_input, grad_weight, None, None, grad_bias, None, None, None

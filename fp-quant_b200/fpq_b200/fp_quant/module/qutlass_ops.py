@@ -232,6 +232,101 @@ def matmul_nvf4_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, w
                    alpha, "nvfp4")
 
 
+@torch.library.custom_op(f"{NAMESPACE}::matmul_mxf8_bf16_tn_op", mutates_args=())
+def matmul_mxf8_bf16_tn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
+                           alpha: torch.Tensor) -> torch.Tensor:
+    """MXFP8 GEMM of the quantised backward pass (qutlass_ops.py:171-189): x [M, K] and w [N, K] as E4M3
+    bytes, xs / ws row-major E8M0 scales [rows, K/32]; returns bf16 [M, N] = alpha * dq(x) dq(w)^T."""
+    return ops.gemm_mxf8(x, w, ops.swizzle_scales(xs.view(torch.uint8)), ops.swizzle_scales(ws.view(torch.uint8)), alpha)
+
+
+matmul_mxf8_bf16_tn_op.register_fake(lambda x, w, xs, ws, alpha: x.new_empty(x.shape[0], w.shape[0], dtype=torch.bfloat16))
+
+
+@torch.library.custom_op(f"{NAMESPACE}::matmul_mxf8_bf16_nn_op", mutates_args=())
+def matmul_mxf8_bf16_nn_op(x: torch.Tensor, w: torch.Tensor, xs: torch.Tensor, ws: torch.Tensor,
+                           alpha: torch.Tensor) -> torch.Tensor:
+    """The same product with the first operand stored the other way round (qutlass_ops.py:192-210): x is
+    [K, M] (scales xs [M, K/32] along K), w [N, K]; returns bf16 [M, N].  The operand is transposed to K-major
+    bytes first (one byte per element: a quarter of the bf16 tensor it came from) and takes the tn kernel."""
+    return ops.gemm_mxf8(x.view(torch.uint8).t().contiguous(), w, ops.swizzle_scales(xs.view(torch.uint8)),
+                         ops.swizzle_scales(ws.view(torch.uint8)), alpha)
+
+
+matmul_mxf8_bf16_nn_op.register_fake(lambda x, w, xs, ws, alpha: x.new_empty(x.shape[1], w.shape[0], dtype=torch.bfloat16))
+
+
+@torch.library.custom_op(f"{NAMESPACE}::backward_bf16_square_double_mxfp8", mutates_args=())
+def backward_bf16_square_double_mxfp8_op(x_bf16: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """bf16 [m, n] -> (E4M3 [m_up128, n], row scales e8m0 [m_up128, n/32], column scales e8m0 [n, m_up128/32]):
+    one scale per 32 x 32 square, so the same bytes feed the GEMM over n and the GEMM over m
+    (qutlass_ops.py:277-304)."""
+    out, rs, cs = ops.quantize_mxfp8_square(x_bf16)
+    return out, rs.view(torch.float8_e8m0fnu), cs.view(torch.float8_e8m0fnu)
+
+
+@backward_bf16_square_double_mxfp8_op.register_fake
+def _(x_bf16):
+    m, n = x_bf16.shape
+    mp = (m + 127) // 128 * 128
+    return (torch.empty(mp, n, dtype=torch.float8_e4m3fn, device=x_bf16.device),
+            torch.empty(mp, n // 32, dtype=torch.float8_e8m0fnu, device=x_bf16.device),
+            torch.empty(n, mp // 32, dtype=torch.float8_e8m0fnu, device=x_bf16.device))
+
+
+@torch.library.custom_op(f"{NAMESPACE}::mxfp4_transpose_mxfp8", mutates_args=())
+def mxfp4_transpose_mxfp8_op(x_fp4: torch.Tensor, scales: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """MXFP4 codes [m, n/2] with row-major e8m0 scales (the padded tensor `fused_quantize_mx_op` returns is
+    accepted: its first m rows and n/32 columns are read) -> (E4M3 [n, m_up128], e8m0 [n, m_up128/32]) of the
+    transpose (qutlass_ops.py:307-330)."""
+    m, n = x_fp4.shape[0], x_fp4.shape[1] * 2
+    sb = scales.view(torch.uint8)
+    if tuple(sb.shape) != (m, n // 32):
+        sb = sb[:m, : n // 32].contiguous()
+    out, os_ = ops.mxfp4_transpose_mxfp8(x_fp4.view(torch.uint8), sb)
+    return out, os_.view(torch.float8_e8m0fnu)
+
+
+@mxfp4_transpose_mxfp8_op.register_fake
+def _(x_fp4, scales):
+    m, n = x_fp4.size(0), x_fp4.size(1) * 2
+    mp = (m + 127) // 128 * 128
+    return (torch.empty(n, mp, dtype=torch.float8_e4m3fn, device=x_fp4.device),
+            torch.empty(n, mp // 32, dtype=torch.float8_e8m0fnu, device=x_fp4.device))
+
+
+@torch.library.custom_op(f"{NAMESPACE}::backward_t_bf16", mutates_args=())
+def backward_t_bf16_op(x: torch.Tensor, hadamard_matrix: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [m, n] -> MXFP4 of its transpose, rotated along m: (codes [n, m/2], row-major e8m0 scales, padded
+    like `fused_quantize_mx_op` pads them) (qutlass_ops.py:218-245).  m % 32 == 0."""
+    q, sb = _quantize(x.t().contiguous(), hadamard_matrix, "mxfp4", None, swizzled=False)
+    return q, sb.view(torch.float8_e8m0fnu)
+
+
+@torch.library.custom_op(f"{NAMESPACE}::backward_qt_bf16", mutates_args=())
+def backward_qt_bf16_op(x_e2m1: torch.Tensor, x_e8m0: torch.Tensor, hadamard_matrix: torch.Tensor,
+                        alpha: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """MXFP4 [m, n] quantised under tensor scale alpha -> MXFP4 of (dequantised / alpha)^T rotated along m:
+    (codes [n, m/2], e8m0 scales) (qutlass_ops.py:248-274)."""
+    m, n = x_e2m1.shape[0], x_e2m1.shape[1] * 2
+    sb = x_e8m0.view(torch.uint8)
+    if tuple(sb.shape) != (m, n // 32):
+        sb = sb[:m, : n // 32].contiguous()
+    xt = ops.mxfp4_transpose_dequant(x_e2m1.view(torch.uint8), sb, alpha.float())
+    q, sb2 = _quantize(xt, hadamard_matrix, "mxfp4", None, swizzled=False)
+    return q, sb2.view(torch.float8_e8m0fnu)
+
+
+def _fake_backward_t(rows_out, k, device):
+    pr, pc = _padded(rows_out, k // 32)
+    return (torch.empty(rows_out, k // 2, dtype=torch.uint8, device=device),
+            torch.empty(pr, pc, dtype=torch.float8_e8m0fnu, device=device))
+
+
+backward_t_bf16_op.register_fake(lambda x, h: _fake_backward_t(x.size(-1), x.size(-2), x.device))
+backward_qt_bf16_op.register_fake(lambda q, s, h, alpha: _fake_backward_t(q.size(-1) * 2, q.size(-2), q.device))
+
+
 @torch.library.custom_op("fpq_b200::matmul_fp4_bf16_tn_blocked_op", mutates_args=())
 def matmul_fp4_bf16_tn_blocked_op(x: torch.Tensor, w: torch.Tensor, xs_blocked: torch.Tensor,
                                   ws_blocked: torch.Tensor, alpha: torch.Tensor, nvfp4: bool,

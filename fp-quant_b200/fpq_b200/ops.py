@@ -304,6 +304,85 @@ def gemm_fp4(a_codes: torch.Tensor, b_codes: torch.Tensor, a_scales_swizzled: to
     return out
 
 
+def gemm_mxf8(a_e4m3: torch.Tensor, b_e4m3: torch.Tensor, a_scales_swizzled: torch.Tensor,
+              b_scales_swizzled: torch.Tensor, alpha: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 [M, N] = alpha * dq(A) dq(B)^T for MXFP8 operands: E4M3 bytes [rows, K] (float8_e4m3fn or uint8),
+    one E8M0 scale per 32 elements along K, scales swizzled."""
+    a = _cuda(a_e4m3, "a").contiguous()
+    b = _cuda(b_e4m3, "b").contiguous()
+    for name, t in (("a", a), ("b", b)):
+        if t.dtype not in (torch.float8_e4m3fn, torch.uint8) or t.dim() != 2:
+            raise ValueError(f"{name} must be a 2-D float8_e4m3fn (or uint8) tensor, got {t.dtype} {tuple(t.shape)}")
+    M, K = a.shape
+    N = b.shape[0]
+    if b.shape[1] != K:
+        raise ValueError(f"K mismatch: {tuple(a.shape)} vs {tuple(b.shape)}")
+    sa = _cuda(a_scales_swizzled, "a_scales").contiguous()
+    sb = _cuda(b_scales_swizzled, "b_scales").contiguous()
+    for name, s, rows in (("a_scales", sa, M), ("b_scales", sb, N)):
+        pr, pc = padded_scale_shape(rows, K // 32)
+        if s.numel() != pr * pc:
+            raise ValueError(f"{name} must hold the swizzled layout of [{pr}, {pc}] bytes, got {tuple(s.shape)}")
+    alpha = _cuda(alpha, "alpha").to(torch.float32).reshape(1)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    with _guard(a.device):
+        C.call("fpq_gemm_mxf8", a.data_ptr(), b.data_ptr(), sa.data_ptr(), sb.data_ptr(), alpha.data_ptr(),
+               out.data_ptr(), M, N, K, device_error_flag(a.device).data_ptr(), _stream(a))
+    return out
+
+
+def quantize_mxfp8_square(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """bf16 [rows, cols] -> (E4M3 [rows_pad, cols], row scales u8 [rows_pad, cols/32], column scales u8
+    [cols, rows_pad/32]); one E8M0 byte per 32 x 32 square, rows_pad = rows rounded up to 128 (zero rows)."""
+    x = _cuda(x, "x")
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise ValueError(f"x must be a 2-D bfloat16 tensor, got {x.dtype} {tuple(x.shape)}")
+    x = x.contiguous()
+    rows, cols = x.shape
+    rp = (rows + 127) // 128 * 128
+    out = torch.empty(rp, cols, dtype=torch.float8_e4m3fn, device=x.device)
+    rs = torch.empty(rp, cols // 32, dtype=torch.uint8, device=x.device)
+    cs = torch.empty(cols, rp // 32, dtype=torch.uint8, device=x.device)
+    with _guard(x.device):
+        C.call("fpq_quantize_mxfp8_square", x.data_ptr(), rows, cols, out.data_ptr(), rs.data_ptr(), cs.data_ptr(), _stream(x))
+    return out, rs, cs
+
+
+def mxfp4_transpose_mxfp8(codes: torch.Tensor, scales_rowmajor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """MXFP4 (codes u8 [rows, cols/2], E8M0 bytes [rows, cols/32], row-major, unpadded) -> the transpose as
+    MXFP8: (E4M3 [cols, rows_pad], scales u8 [cols, rows_pad/32])."""
+    codes = _cuda(codes, "codes").contiguous()
+    sc = _cuda(scales_rowmajor, "scales")
+    sc = (sc if sc.dtype == torch.uint8 else sc.view(torch.uint8)).contiguous()
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    if tuple(sc.shape) != (rows, cols // 32):
+        raise ValueError(f"scales must be [{rows}, {cols // 32}] row-major bytes, got {tuple(sc.shape)}")
+    rp = (rows + 127) // 128 * 128
+    out = torch.empty(cols, rp, dtype=torch.float8_e4m3fn, device=codes.device)
+    os_ = torch.empty(cols, rp // 32, dtype=torch.uint8, device=codes.device)
+    with _guard(codes.device):
+        C.call("fpq_mxfp4_transpose_mxfp8", codes.data_ptr(), sc.data_ptr(), rows, cols, out.data_ptr(), os_.data_ptr(),
+               _stream(codes))
+    return out, os_
+
+
+def mxfp4_transpose_dequant(codes: torch.Tensor, scales_rowmajor: torch.Tensor, alpha: torch.Tensor) -> torch.Tensor:
+    """MXFP4 (codes u8 [rows, cols/2], E8M0 bytes [rows, cols/32]) -> bf16 [cols, rows] = dequantised^T / alpha."""
+    codes = _cuda(codes, "codes").contiguous()
+    sc = _cuda(scales_rowmajor, "scales")
+    sc = (sc if sc.dtype == torch.uint8 else sc.view(torch.uint8)).contiguous()
+    rows, cols = codes.shape[0], codes.shape[1] * 2
+    if tuple(sc.shape) != (rows, cols // 32):
+        raise ValueError(f"scales must be [{rows}, {cols // 32}] row-major bytes, got {tuple(sc.shape)}")
+    alpha = _cuda(alpha, "alpha").to(torch.float32).reshape(1)
+    out = torch.empty(cols, rows, dtype=torch.bfloat16, device=codes.device)
+    with _guard(codes.device):
+        C.call("fpq_mxfp4_transpose_dequant", codes.data_ptr(), sc.data_ptr(), rows, cols, alpha.data_ptr(), out.data_ptr(),
+               _stream(codes))
+    return out
+
+
 # --------------------------------------------------------------------------- GPTQ core
 def gemm_fp4_push(a_codes: torch.Tensor, b_codes: torch.Tensor, a_scales_swizzled: torch.Tensor,
                   b_scales_swizzled: torch.Tensor, alpha: torch.Tensor, fmt: str, out: torch.Tensor, peer_ptrs,

@@ -28,6 +28,7 @@ extern "C" {
 /* element formats */
 #define FPQ_FMT_MXFP4 0 /* E2M1 codes, one E8M0 scale per 32 elements */
 #define FPQ_FMT_NVFP4 1 /* E2M1 codes, one E4M3 scale per 16 elements + fp32 tensor scale */
+#define FPQ_FMT_MXFP8 3 /* E4M3 bytes, one E8M0 scale per 32 elements: operands of fpq_gemm_mxf8 only */
 
 /* tensor dtypes */
 #define FPQ_DT_BF16 0
@@ -201,6 +202,51 @@ int fpq_gemm_fp4(const uint8_t* a_codes, const uint8_t* b_codes, const uint8_t* 
                  const uint8_t* b_scales_swizzled, const float* alpha, const void* bias_bf16,
                  void* out_bf16, int64_t M, int64_t N, int64_t K, int format, int32_t* error_flag,
                  fpq_stream_t stream);
+
+/*
+ * Y[M,N] (bf16) = alpha * dq(A)[M,K] * dq(B)[N,K]^T on the tcgen05 tensor cores (kind::mxf8f6f4, CTA pairs),
+ * A and B as E4M3 bytes [rows, K] (K-major), one E8M0 scale per 32 elements along K in the swizzled
+ * layout (as fpq_swizzle_scales writes it).  Replaces matmul_mxf8_bf16_tn_op and its per-call `to_blocked`
+ * (inference_lib/src/fp_quant/module/qutlass_ops.py:171-189), the GEMM of the MXFP8 backward pass
+ * (linear_fns.py:311-318).  alpha: device fp32[1]; K % 32 == 0, K % 16 == 0 bytes, N % 8 == 0.
+ * error_flag as in fpq_gemm_fp4.
+ */
+int fpq_gemm_mxf8(const uint8_t* a_e4m3, const uint8_t* b_e4m3, const uint8_t* a_scales_swizzled,
+                  const uint8_t* b_scales_swizzled, const float* alpha, void* out_bf16, int64_t M, int64_t N,
+                  int64_t K, int32_t* error_flag, fpq_stream_t stream);
+
+/*
+ * bf16 [rows, cols] -> MXFP8 with one E8M0 scale per 32 x 32 square, so that the same E4M3 bytes serve a GEMM
+ * that contracts over the columns (row_scales [rows_pad, cols/32]) and one that contracts over the rows
+ * (col_scales [cols, rows_pad/32]); rows_pad = rows rounded up to 128, the padding rows are written as
+ * zeros.  Stands for backward_bf16_square_double_mxfp8 (qutlass_ops.py:277-304; QuTLASS itself is not
+ * available, so the arithmetic is this library's: scale 2^(floor(log2(max|x|)) - 8), byte 0 for an all-zero
+ * square, x / scale clamped to +-448 and rounded to nearest even).  out_e4m3: [rows_pad, cols] bytes.
+ * cols % 32 == 0.
+ */
+int fpq_quantize_mxfp8_square(const void* x_bf16, int64_t rows, int64_t cols, uint8_t* out_e4m3,
+                              uint8_t* row_scales, uint8_t* col_scales, fpq_stream_t stream);
+
+/*
+ * MXFP4 [rows, cols] (packed codes [rows, cols/2], row-major E8M0 bytes [rows, cols/32]) -> its transpose
+ * as MXFP8: out_e4m3 [cols, rows_pad] bytes, out_scales [cols, rows_pad/32] E8M0 bytes, rows_pad = rows
+ * rounded up to 128 (padding zero).  Stands for mxfp4_transpose_mxfp8 (qutlass_ops.py:307-330; arithmetic
+ * defined here): a 32 x 32 square takes 2^(emax - 6), emax the largest of its 32 source exponents, and an
+ * element becomes fp4 * 2^(e_row - emax + 6), exact unless its row lies more than 2^-14 below the largest
+ * (then rounded to nearest even on the E4M3 grid).  cols % 32 == 0.
+ */
+int fpq_mxfp4_transpose_mxfp8(const uint8_t* codes, const uint8_t* scales_rowmajor, int64_t rows, int64_t cols,
+                              uint8_t* out_e4m3, uint8_t* out_scales, fpq_stream_t stream);
+
+/*
+ * MXFP4 [rows, cols] (packed codes, row-major E8M0 bytes [rows, cols/32]) -> bf16 [cols, rows]: the transpose
+ * of the dequantised tensor, every element divided by *alpha (device fp32[1]: the tensor scale the operand
+ * was quantised under) and rounded once to bf16.  First half of backward_qt_bf16 (qutlass_ops.py:248-274:
+ * dequantise, transpose, rotate, quantise again); the second half is fpq_quantize on the result.
+ * cols % 32 == 0.
+ */
+int fpq_mxfp4_transpose_dequant(const uint8_t* codes, const uint8_t* scales_rowmajor, int64_t rows, int64_t cols,
+                                const float* alpha, void* out_bf16, fpq_stream_t stream);
 
 /*
  * Column-parallel form of fpq_gemm_fp4 for tensor parallelism over NVLink (no counterpart in the reference,

@@ -342,3 +342,17 @@ def fp4_matmul(aq, bq, sa, sb, alpha, fmt: str) -> torch.Tensor:
     b = dequantize(unpack_codes(bq), decode_scale_bytes(sb, fmt), g).to(torch.float64)
     y = (a @ b.t()) * float(alpha)
     return y.to(torch.float32).to(torch.bfloat16)
+
+
+def mxfp8_matmul(a8, b8, sa, sb, alpha) -> torch.Tensor:
+    """Y = alpha * dequant(A) @ dequant(B)^T rounded to bf16 for MXFP8 operands: A [M, K], B [N, K] as E4M3
+    bytes (uint8 or float8_e4m3fn, no NaN patterns), sa / sb row-major E8M0 bytes [rows, K/32], element value
+    = e4m3 * 2^(byte - 127) (contract of `matmul_mxf8_bf16_tn_op`, qutlass_ops.py:171-189).  fp64 throughout.
+    """
+    def dq(x, s):
+        v = x.view(torch.float8_e4m3fn).to(torch.float64)
+        e = torch.pow(torch.tensor(2.0, dtype=torch.float64), s.view(torch.uint8).to(torch.float64) - 127.0)
+        return (v.view(v.shape[0], -1, 32) * e.unsqueeze(-1)).view(v.shape)
+
+    y = (dq(a8, sa) @ dq(b8, sb).t()) * float(alpha)
+    return y.to(torch.float32).to(torch.bfloat16)

@@ -114,3 +114,27 @@ def test_single_product_on_random_inputs(group):
         want = fp4.e2m1_codes(torch.from_numpy((t * c).astype(np.float32)).unsqueeze(-1),
                               torch.full((t.size, 1), float(s)), 1).squeeze(-1).numpy()
         assert np.array_equal(got, want)
+
+
+def test_division_by_three_in_three_instructions():
+    """The NVFP4 scale chain starts with fl(fl(2a) / 12) = fl(a / 3) / 2.  The kernel computes a / 3 as
+    q = fl(a r), e = a - 3 q (fused, exact), fl(q + e r) with r = fl(1/3): correctly rounded for every one of
+    the 2^23 fp32 mantissas (every step below is exact in fp64 before its single rounding to fp32; the
+    exponent does not matter while nothing underflows, which the kernel's range check excludes)."""
+    import re
+
+    import numpy as np
+
+    src = open(os.path.join(ROOT, "fp-quant_b200", "csrc", "quantize.cu")).read()
+    m = re.search(r"const float r = ([0-9.]+)f;\s*// 0x([0-9a-f]{8})", src)
+    assert m, "the reciprocal constant of nv_scale was not found"
+    r = np.float32(float(m.group(1)))
+    assert r.view(np.uint32) == int(m.group(2), 16) == (np.float32(1.0) / np.float32(3.0)).view(np.uint32)
+    for lo in range(1 << 23, 1 << 24, 1 << 21):
+        x = np.arange(lo, lo + (1 << 21), dtype=np.int64).astype(np.float64)
+        q0 = (x * np.float64(r)).astype(np.float32)
+        e64 = x - 3.0 * q0.astype(np.float64)
+        e = e64.astype(np.float32)
+        assert np.array_equal(e.astype(np.float64), e64)                      # the residual is exact in fp32
+        q = (q0.astype(np.float64) + e.astype(np.float64) * np.float64(r)).astype(np.float32)
+        assert np.array_equal(q, (x / 3.0).astype(np.float32))

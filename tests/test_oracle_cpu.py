@@ -235,3 +235,13 @@ def test_abs_max_triton_kernel_agrees_with_the_quantizer_rule_off_ties():
         tie |= v.abs() == t
     ok = (got == want) | tie | want.isnan()
     assert bool(ok.all()), int((~ok).sum())
+
+
+def test_mxfp8_matmul_known_answer():
+    """E4M3 1.0 everywhere, scales (2^0, 2^1) x (2^-1, 2^0) per 32-element group: 32*1*0.5 + 32*2*1 = 80."""
+    a = torch.full((1, 64), 0x38, dtype=torch.uint8)
+    y = fp4.mxfp8_matmul(a, a, torch.tensor([[127, 128]], dtype=torch.uint8), torch.tensor([[126, 127]], dtype=torch.uint8), 1.0)
+    assert y.dtype == torch.bfloat16 and float(y) == 80.0
+    b = torch.tensor([[0x40] * 32 + [0xC4] * 32], dtype=torch.uint8)      # 2.0 and -3.0
+    y = fp4.mxfp8_matmul(a, b, torch.full((1, 2), 127, dtype=torch.uint8), torch.full((1, 2), 127, dtype=torch.uint8), 0.5)
+    assert float(y) == 0.5 * (32 * 2.0 - 32 * 3.0)
