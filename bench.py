@@ -833,7 +833,8 @@ def measure_gptq_model(args, world, rank, local, dev, steps, warmup, n_layers, n
         a_observer=QuantizationObserver.MINMAX, w_group_size=16, a_group_size=16, scale_precision=ScalePrecision.E4M3,
         transform_class="hadamard", hadamard_group_size=128, cpu_offload_activations=False, cpu_offload_modules=False,
         quantization_order=QuantizationOrder.DEFAULT, rel_damp=0.01, export_quantized_model="realquant",
-        dtype=torch.bfloat16, fuse_global_scale=False, amp=False, calibration_batch=args.calib_batch)
+        dtype=torch.bfloat16, fuse_global_scale=False, amp=False, calibration_batch=args.calib_batch,
+        owner_share=getattr(args, "owner_share", None))
     g = torch.Generator().manual_seed(5)
     data = [torch.randint(0, cfg.vocab_size, (1, T), generator=g) for _ in range(n_seq)]
 
@@ -873,7 +874,17 @@ def measure_gptq_model(args, world, rank, local, dev, steps, warmup, n_layers, n
     if rank != 0:
         return None
     ms = sum(times) / len(times)
-    hessian_bytes = 4 * (3 * 4096 * 4096 + 14336 * 14336)       # the four distinct Hessians of a block, fp32
+    # the four distinct Hessians of a block, fp32: those of o_proj and down_proj are needed by one rank only and
+    # are reduced to it (a ring moves (N-1)/N of the buffer per GPU), those of q/k/v and gate/up are all-reduced
+    # (2 (N-1)/N)
+    from fpq_b200.quantization.driver import plan_ranks
+    members = {"qkv": ["q_proj", "k_proj", "v_proj"], "o": ["o_proj"], "gate_up": ["gate_proj", "up_proj"], "down": ["down_proj"]}
+    width = {"qkv": 4096, "o": 4096, "gate_up": 4096, "down": 14336}
+    _, chain_rank, loop_rank = plan_ranks(members, width, world)
+    hessian_traffic = 0.0
+    for grp, names in members.items():
+        spread = any(loop_rank[n] != chain_rank[grp] for n in names)
+        hessian_traffic += (2 if spread else 1) * (world - 1) / world * 4 * width[grp] ** 2
     return {
         "metric": "mr_gptq_model_s_per_block", "value": ms * 1e-3 / n_layers, "unit": "s/block", "n_gpus": world,
         "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong",
@@ -884,10 +895,13 @@ def measure_gptq_model(args, world, rank, local, dev, steps, warmup, n_layers, n
                                f"Cholesky chains and column loops partitioned over {world} GPU(s)",
                    "l2": "calibration activations of a block (2 GB) > 126 MB L2"},
         "exported_layers": n_keys, "phases_s": phases, "per_rank_ms": per_rank,
-        "comm": {"collective": "NCCL all-reduce(sum) of the block's four fp32 Hessians, all-reduce(min) of the activation "
-                               "tensor scales, broadcasts of factors and results" if world > 1 else None,
-                 "allreduce_bytes_per_gpu_per_block": int(2 * (world - 1) / world * hessian_bytes),
-                 "allreduce_s_per_block": phases.get("allreduce", 0.0) / n_layers},
+        "comm": {"collective": "NCCL reduce(sum) of the fp32 Hessians that one rank needs (to that rank) and all-reduce(sum) of "
+                               "those whose linears sit on several ranks, all-reduce(min) of the activation tensor scales, "
+                               "broadcasts of factors and results" if world > 1 else None,
+                 "allreduce_bytes_per_gpu_per_block": int(hessian_traffic),
+                 "allreduce_s_per_block": phases.get("allreduce", 0.0) / n_layers,
+                 "note": "seconds: rank 0's main stream from the end of its calibration pass to the end of the Hessian "
+                         "collectives, so they include waiting for the slowest rank's pass"},
         "relative_mse_first_block": {k.split(".", 3)[3]: v for k, v in rel.items() if k.startswith("model.layers.0.")},
         "roofline": None, "cpu_baseline": None, "e2e": None, "clocks": clocks.summary(),
     }
@@ -1157,13 +1171,144 @@ def run_cholesky(args):
     print(json.dumps(line), flush=True)
 
 
+def run_gemm_mxf8(args):
+    """TFLOP/s of the MXFP8 GEMM of the quantised backward pass (`matmul_mxf8_bf16_tn_op`,
+    inference_lib/src/fp_quant/module/qutlass_ops.py:171-189) on the Qwen3-8B linear shapes at M = --m, with
+    cuBLASLt's block-scaled MXFP8 kernel (through torch) on the same operands beside it."""
+    from fpq_b200 import ops
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    peaks = load_peaks()
+    M = args.m
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def operand(rows, K):
+        x = torch.randint(0, 256, (rows, K), device=dev, dtype=torch.uint8, generator=g)
+        x[(x & 0x7F) == 0x7F] = 0x38                                  # no NaN patterns
+        s = torch.randint(120, 131, (rows, K // 32), device=dev, dtype=torch.uint8, generator=g)
+        return x, ops.swizzle_scales(s)
+
+    alpha = torch.full((1,), 2.0 ** -9, device=dev)
+    ops_ = [(operand(M, K), operand(N, K), torch.empty(M, N, dtype=torch.bfloat16, device=dev)) for (K, N) in SHAPES]
+    flops = sum(2.0 * M * N * K for (K, N) in SHAPES)
+
+    def ours():
+        for (a, sa), (b, sb), out in ops_:
+            ops.gemm_mxf8(a, b, sa, sb, alpha, out=out)
+
+    def library():
+        for (a, sa), (b, sb), out in ops_:
+            torch._scaled_mm(a.view(torch.float8_e4m3fn), b.view(torch.float8_e4m3fn).t(), sa.view(torch.float8_e8m0fnu),
+                             sb.view(torch.float8_e8m0fnu), out_dtype=torch.bfloat16)
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    with ClockSampler(0) as clocks:
+        ms = timed(ours)
+    ops.check_device_errors(dev)
+    lib = None
+    try:
+        lib_ms = timed(library)
+        (a, sa), (b, sb), out = ops_[0]
+        ref = torch._scaled_mm(a.view(torch.float8_e4m3fn), b.view(torch.float8_e4m3fn).t(), sa.view(torch.float8_e8m0fnu),
+                               sb.view(torch.float8_e8m0fnu), out_dtype=torch.bfloat16).float() * float(alpha)
+        got = ops.gemm_mxf8(a, b, sa, sb, alpha).float()
+        agree = bool(((got - ref).abs() <= 2.0 ** -6 * ref.abs() + 2.0 ** -9 * ref.abs().max()).all())
+        lib = {"name": "cuBLASLt block-scaled MXFP8 via torch._scaled_mm (comparison only)", "tflops": flops / (lib_ms * 1e-3) / 1e12,
+               "time_ratio_ours_over_library": ms / lib_ms, "results_agree": agree}
+    except Exception as exc:      # noqa: BLE001
+        lib = {"unavailable": str(exc)[:200]}
+    achieved = flops / (ms * 1e-3) / 1e12
+    peak = 2.0 * peaks["bf16_tflops"]
+    line = {
+        "metric": "mxfp8_gemm_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "e4m3 x e4m3 (e8m0 scale per 32) -> f32 -> bf16", "data": "synthetic",
+        "config": {"workload": f"MXFP8 GEMM, Qwen3-8B shapes (K,N)={SHAPES}, M={M}", "l2": "operands and outputs of the four shapes (1.1 GB at M = 8192) > 126 MB L2"},
+        "roofline": {"kernel": "gemm_fp4_pair_kernel<MXFP8>", "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "peak_source": f"2 x bf16 cuBLAS burst ({peaks['source']}); no FP8 peak was measured on this pool",
+                     "frac_of_nominal_4p5pf": achieved / 4500.0, "traffic": None},
+        "library_gemm": lib, "cpu_baseline": None, "e2e": None, "gpu_launches": args.steps * len(SHAPES), "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_qat_step(args):
+    """Milliseconds per forward + backward of one `FPQuantLinear` with master weights (K = N = 4096, M = --m
+    tokens, MXFP4 forward, Hadamard 32) for the three backward dtypes of the reference (linear.py:244-306):
+    bf16, MXFP8 and MXFP4, with a bf16 `nn.Linear` beside them."""
+    from fpq_b200 import ops
+    from fpq_b200.fp_quant import FPQuantConfig, FPQuantDtype, FPQuantLinear
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    M, K, N = args.m, 4096, 4096
+    x = make_activations(M, K, seed=1).to(dev).requires_grad_(True)
+    gy = (torch.randn(M, N, generator=torch.Generator().manual_seed(2)) * 0.01).bfloat16().to(dev)
+    w = make_weight(N, K, seed=3).to(dev)
+    flops = 3 * 2.0 * M * N * K
+    results = {}
+
+    def timed(layer):
+        def step():
+            x.grad = None
+            layer.weight.grad = None
+            layer(x).backward(gy)
+        for _ in range(max(3, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    with ClockSampler(0) as clocks:
+        for name, bwd in (("bf16", FPQuantDtype.BF16), ("mxfp8", FPQuantDtype.MXFP8), ("mxfp4", FPQuantDtype.MXFP4)):
+            layer = FPQuantLinear(K, N, FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, forward_method="abs_max", backward_dtype=bwd,
+                                                      hadamard_group_size=32, store_master_weights=True),
+                                  bias=False, device=dev, dtype=torch.bfloat16)
+            layer.weight.data.copy_(w)
+            layer.pre_forward()
+            ms = timed(layer)
+            results[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+        plain = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+        plain.weight.data.copy_(w)
+        ms = timed(plain)
+        results["nn.Linear bf16"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+    ops.check_device_errors(dev)
+    best = results["mxfp8"]
+    line = {
+        "metric": "qat_linear_step_ms", "value": best["ms"], "unit": "ms", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": best["ms"], "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "mxfp4 forward, mxfp8 backward", "data": "synthetic",
+        "config": {"workload": f"forward + backward of FPQuantLinear({K}, {N}) with master weights, M={M} tokens, Hadamard 32",
+                   "l2": "activations, gradients and weights of a step (0.3 GB at M = 8192) > 126 MB L2"},
+        "by_backward_dtype": results, "roofline": None, "cpu_baseline": None, "e2e": None, "gpu_launches": None, "clocks": clocks.summary(),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gptq", "gptq-model", "tp-linear", "model-forward", "cholesky"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "quantize", "gemm", "gemm-mxf8", "qat-step", "gptq", "gptq-model", "tp-linear", "model-forward", "cholesky"])
     ap.add_argument("--model-layers", type=int, default=2)
     ap.add_argument("--calib-seqs", type=int, default=128)
     ap.add_argument("--tp-fused", action="store_true", help="tp-linear: push output tiles to the peers from the GEMM epilogue")
@@ -1176,6 +1321,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-library-gemm", action="store_true", help="skip the cuBLASLt comparison line")
     ap.add_argument("--no-mr-gptq", action="store_true", help="linear workload: skip the MR-GPTQ part of the line")
+    ap.add_argument("--owner-share", type=float, default=None,
+                    help="gptq-model on several GPUs: rank 0's share of the calibration sequences, as a fraction of an even share")
     ap.add_argument("--sustained-seconds", type=float, default=2.0,
                     help="length of the sustained loops; 0 keeps them to three calls (for profiler captures)")
     args = ap.parse_args()
@@ -1196,6 +1343,10 @@ def main():
             run_model_forward(args)
         elif args.workload == "cholesky":
             run_cholesky(args)
+        elif args.workload == "gemm-mxf8":
+            run_gemm_mxf8(args)
+        elif args.workload == "qat-step":
+            run_qat_step(args)
         else:
             run_ours(args)
 

@@ -392,13 +392,14 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
     rank, world_size = fdist.world()
     n_total = len(calibration_data)
     # Rank 0 gets the widest Hessian's chain and column loop (`plan_ranks`), which the other ranks wait for once
-    # they have run the second pass up to that layer.  It is therefore given fewer calibration sequences, so
-    # that its own forward passes fit into the time the others need for theirs.  The shares were balanced on
-    # the phase times of a Llama-3.1-8B block with 128 x 2048 tokens (0.89 / 0.72 / 0.62 of an even share at
-    # 2 / 4 / 8 ranks); `args.owner_share` overrides them, 1.0 is an even split.
+    # they have run the second pass up to that layer; its own share of that pass runs after them.  It is
+    # therefore given fewer calibration sequences, so that its forward passes fit into the time the others
+    # need for theirs.  The shares were balanced on a Llama-3.1-8B block with 128 x 2048 tokens (0.89 / 0.55 /
+    # 0.45 of an even share at 2 / 4 / 8 ranks; at 8 ranks 0.25, 0.45 and 0.62 gave 0.111, 0.107 and 0.110 s per
+    # block); `args.owner_share` overrides them, 1.0 is an even split.
     share = getattr(args, "owner_share", None)
     if share is None:
-        share = {2: 0.89, 4: 0.72, 8: 0.62}.get(world_size, 1.0 if world_size < 2 else 0.7)
+        share = {2: 0.89, 4: 0.55, 8: 0.45}.get(world_size, 1.0 if world_size < 2 else 0.6)
     if world_size > 1 and getattr(args, "split_second_pass", True):
         rest = (world_size - share) / (world_size - 1)
         lo, hi = fdist.weighted_bounds(n_total, [share] + [rest] * (world_size - 1))[rank]
@@ -514,13 +515,16 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
             owner = group_owner[g]
             elsewhere = any(layer_owner[n] != owner for n in group_members[g])
             if rank == owner:
+                timed = not (leaders[g] == deferred and side_stream is not None)    # the phase marks follow the main stream
                 with on_stream_of(leaders[g]):
                     lead.defer_host_syncs = world_size > 1
                     lead.quantization_pre_step()
                     lead.prepare_hessian()
-                    ph.mark("factor_prepare")
+                    if timed:
+                        ph.mark("factor_prepare")
                     shared_U[g] = lead._get_hessian_inverse(prepared=True)
-                    ph.mark("factor_chain")
+                    if timed:
+                        ph.mark("factor_chain")
             elif elsewhere:
                 shared_U[g] = torch.empty((lead.d_col, lead.d_col), device=device, dtype=torch.float32)
 
@@ -620,12 +624,17 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
         else:
             last = handles[deferred].layer
             if side_stream is not None:
-                # the owner's own sequences wait for its side stream: its forward kernels would only slow the
-                # chain and the loop down, and the other ranks wait for those, not for this
+                # The owner's own sequences wait for its side stream (its forward kernels would only slow the
+                # chain and the loop down), and the finished weight goes out before they run: the other ranks
+                # wait for the weight, not for the owner's share of the pass.  (Same order of collectives on
+                # every rank; only their place among the local launches differs.)
                 main_stream.wait_stream(side_stream)
-            parts = _split_pass_first_half(block, input_args, input_kwargs, device, args, last)
+                exchange(deferred)
+                parts = _split_pass_first_half(block, input_args, input_kwargs, device, args, last)
+            else:
+                parts = _split_pass_first_half(block, input_args, input_kwargs, device, args, last)
+                exchange(deferred)
             ph.mark("update_pass_first_half")
-            exchange(deferred)
             if "exact" not in _split_state:      # once per process: does this architecture end in residual + down_proj?
                 mine = (not parts) or _split_pass_is_exact(block, parts, input_args, input_kwargs, device, args, last)
                 verdict = torch.tensor([1 if mine else 0], device=device, dtype=torch.int32)
