@@ -17,6 +17,25 @@ constexpr int SQ = 32;                 // side of a square
 constexpr int SQ_PER_BLOCK = 8;        // squares (of one row band) per thread block
 constexpr int THREADS = SQ * SQ_PER_BLOCK;
 
+// Byte offset of scale (row, column) in the 128-row x 4-column tile layout the GEMM reads (tiles row-block-major).
+__device__ __forceinline__ size_t sf_offset(int64_t row, int64_t sfc, int64_t sf_cols, int layout) {
+  if (layout != FPQ_SCALES_SWIZZLED) return (size_t)(row * sf_cols + sfc);
+  const int64_t tiles_per_row_block = (sf_cols + 3) / 4;
+  return (size_t)(((row >> 7) * tiles_per_row_block + (sfc >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (sfc & 3));
+}
+
+// Shared-memory tiles of the transposing kernels: [square][source column][source row], rows padded to a
+// multiple of 16 bytes and squares skewed by one more 16-byte unit so that the eight squares a warp writes at
+// once start in different banks.
+constexpr int T8_ROW = SQ + 4, T8_SQ = SQ * T8_ROW + 16;         // bytes
+constexpr int T16_ROW = SQ + 8, T16_SQ = SQ * T16_ROW + 8;       // bf16 elements
+
+// v * 2^k, exact: one multiply while 2^k is a normal number, the library routine at the extremes.
+__device__ __forceinline__ float scale_pow2(float v, int k) {
+  if (k >= -126 && k <= 127) return v * __int_as_float((k + 127) << 23);
+  return scalbnf(v, k);
+}
+
 __device__ __forceinline__ uint16_t e4m3x2(float lo, float hi) {
   uint16_t r;
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
@@ -42,9 +61,10 @@ __device__ __forceinline__ float square_max(float v, int r, int c, float (*sm)[S
 // rounded to nearest even.  Rows in [rows, rows_pad) are zero.
 __global__ void __launch_bounds__(THREADS) square_quantize_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows,
                                                                   int64_t cols, int64_t rows_pad, uint8_t* __restrict__ out,
-                                                                  uint8_t* __restrict__ row_scales,
-                                                                  uint8_t* __restrict__ col_scales) {
+                                                                  uint8_t* __restrict__ out_t, uint8_t* __restrict__ row_scales,
+                                                                  uint8_t* __restrict__ col_scales, int layout) {
   __shared__ float sm[SQ_PER_BLOCK][SQ + 1];
+  __shared__ __align__(16) uint8_t tile[SQ_PER_BLOCK * T8_SQ];
   const int r = threadIdx.x / SQ_PER_BLOCK, c = threadIdx.x % SQ_PER_BLOCK;
   const int64_t row = (int64_t)blockIdx.y * SQ + r;
   const int64_t sq_col = (int64_t)blockIdx.x * SQ_PER_BLOCK + c;          // square index along the columns
@@ -79,21 +99,35 @@ __global__ void __launch_bounds__(THREADS) square_quantize_kernel(const __nv_bfl
     byte = (uint32_t)(e + 127);
     shift = -e;
   }
-  if (!in_cols || row >= rows_pad) return;
   uint32_t o[8];
 #pragma unroll
   for (int q = 0; q < 8; ++q) {
     float s[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) s[j] = fminf(fmaxf(scalbnf(v[4 * q + j], shift), -448.0f), 448.0f);
+    for (int j = 0; j < 4; ++j) s[j] = fminf(fmaxf(scale_pow2(v[4 * q + j], shift), -448.0f), 448.0f);
     o[q] = (uint32_t)e4m3x2(s[0], s[1]) | ((uint32_t)e4m3x2(s[2], s[3]) << 16);
   }
+  if (out_t != nullptr) {      // the same bytes the other way round: [column][row] through shared memory
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) tile[c * T8_SQ + (4 * q + j) * T8_ROW + r] = (uint8_t)(o[q] >> (8 * j));
+    }
+    __syncthreads();
+  }
+  if (!in_cols) return;
   uint4* dst = reinterpret_cast<uint4*>(out + row * cols + col0);
   dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
   dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-  row_scales[row * (cols / SQ) + sq_col] = (uint8_t)byte;
+  row_scales[sf_offset(row, sq_col, cols / SQ, layout)] = (uint8_t)byte;
   // the same byte for the 32 columns of the square, seen from the transposed side: thread r takes column r
-  col_scales[(col0 + r) * (rows_pad / SQ) + blockIdx.y] = (uint8_t)byte;
+  col_scales[sf_offset(col0 + r, blockIdx.y, rows_pad / SQ, layout)] = (uint8_t)byte;
+  if (out_t != nullptr) {
+    const uint32_t* t32 = reinterpret_cast<const uint32_t*>(&tile[c * T8_SQ + r * T8_ROW]);
+    uint4* dt = reinterpret_cast<uint4*>(out_t + (col0 + r) * rows_pad + (int64_t)blockIdx.y * SQ);
+    dt[0] = make_uint4(t32[0], t32[1], t32[2], t32[3]);
+    dt[1] = make_uint4(t32[4], t32[5], t32[6], t32[7]);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -106,9 +140,9 @@ __global__ void __launch_bounds__(THREADS) square_quantize_kernel(const __nv_bfl
 __global__ void __launch_bounds__(THREADS) fp4_transpose_fp8_kernel(const uint8_t* __restrict__ codes,
                                                                     const uint8_t* __restrict__ scales, int64_t rows,
                                                                     int64_t cols, int64_t rows_pad, uint8_t* __restrict__ out,
-                                                                    uint8_t* __restrict__ out_scales) {
+                                                                    uint8_t* __restrict__ out_scales, int layout) {
   __shared__ float sm[SQ_PER_BLOCK][SQ + 1];
-  __shared__ __align__(16) uint8_t tile[SQ_PER_BLOCK][SQ][SQ + 4];      // [square][column of the source][row of the source]
+  __shared__ __align__(16) uint8_t tile[SQ_PER_BLOCK * T8_SQ];
   const int r = threadIdx.x / SQ_PER_BLOCK, c = threadIdx.x % SQ_PER_BLOCK;
   const int64_t row = (int64_t)blockIdx.y * SQ + r;
   const int64_t sq_col = (int64_t)blockIdx.x * SQ_PER_BLOCK + c;
@@ -133,22 +167,22 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_fp8_kernel(const uint8_
   for (int q = 0; q < 4; ++q) {
 #pragma unroll
     for (int j = 0; j < 8; j += 2) {
-      float a = live ? scalbnf(e2m1_value((ws[q] >> (4 * j)) & 15u), shift) : 0.0f;
-      float b = live ? scalbnf(e2m1_value((ws[q] >> (4 * j + 4)) & 15u), shift) : 0.0f;
+      float a = live ? scale_pow2(e2m1_value((ws[q] >> (4 * j)) & 15u), shift) : 0.0f;
+      float b = live ? scale_pow2(e2m1_value((ws[q] >> (4 * j + 4)) & 15u), shift) : 0.0f;
       const uint16_t p = e4m3x2(a + 0.0f, b + 0.0f);                 // "+ 0" turns the code's -0 into +0
-      tile[c][8 * q + j][r] = (uint8_t)(p & 0xffu);
-      tile[c][8 * q + j + 1][r] = (uint8_t)(p >> 8);
+      tile[c * T8_SQ + (8 * q + j) * T8_ROW + r] = (uint8_t)(p & 0xffu);
+      tile[c * T8_SQ + (8 * q + j + 1) * T8_ROW + r] = (uint8_t)(p >> 8);
     }
   }
   __syncthreads();
   // thread (r, c) now owns source column col0 + r: 32 contiguous output bytes
   if (!in_cols) return;
   const int64_t out_row = col0 + r;
-  const uint32_t* t32 = reinterpret_cast<const uint32_t*>(&tile[c][r][0]);
+  const uint32_t* t32 = reinterpret_cast<const uint32_t*>(&tile[c * T8_SQ + r * T8_ROW]);
   uint4* dst = reinterpret_cast<uint4*>(out + out_row * rows_pad + (int64_t)blockIdx.y * SQ);
   dst[0] = make_uint4(t32[0], t32[1], t32[2], t32[3]);
   dst[1] = make_uint4(t32[4], t32[5], t32[6], t32[7]);
-  out_scales[out_row * (rows_pad / SQ) + blockIdx.y] = (uint8_t)byte;
+  out_scales[sf_offset(out_row, blockIdx.y, rows_pad / SQ, layout)] = (uint8_t)byte;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -159,7 +193,7 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_bf16_kernel(const uint8
                                                                      const uint8_t* __restrict__ scales, int64_t rows,
                                                                      int64_t cols, const float* __restrict__ alpha,
                                                                      __nv_bfloat16* __restrict__ out) {
-  __shared__ __align__(16) __nv_bfloat16 tile[SQ_PER_BLOCK][SQ][SQ + 8];   // [square][column of the source][row of the source]
+  __shared__ __align__(16) __nv_bfloat16 tile[SQ_PER_BLOCK * T16_SQ];      // [square][column of the source][row of the source]
   const int r = threadIdx.x / SQ_PER_BLOCK, c = threadIdx.x % SQ_PER_BLOCK;
   const int64_t row = (int64_t)blockIdx.y * SQ + r;
   const int64_t sq_col = (int64_t)blockIdx.x * SQ_PER_BLOCK + c;
@@ -170,11 +204,26 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_bf16_kernel(const uint8
     const uint4 w = *reinterpret_cast<const uint4*>(codes + row * (cols / 2) + col0 / 2);
     const int e = (int)scales[row * (cols / SQ) + sq_col] - 127;
     const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+    // fl((m 2^e) / a) = fl(m / a) 2^e while nothing leaves the normal range: seven divisions per row instead
+    // of thirty-two.  The bound on e keeps every quotient normal for 2^-20 < |a| < 2^20.
+    const bool table = e > -100 && e < 100 && fabsf(a) > 9.5367e-7f && fabsf(a) < 1.048576e6f;
+    float quot[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) quot[m] = table ? scale_pow2(__fdiv_rn(e2m1_magnitude(m), a), e) : 0.0f;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        tile[c][8 * q + j][r] = __float2bfloat16_rn(__fdiv_rn(scalbnf(e2m1_value((ws[q] >> (4 * j)) & 15u), e), a) + 0.0f);
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t code = (ws[q] >> (4 * j)) & 15u;
+        float v;
+        if (table) {
+          v = quot[code & 7u];
+          v = (code & 8u) ? -v : v;
+        } else {
+          v = __fdiv_rn(scale_pow2(e2m1_value(code), e), a);
+        }
+        tile[c * T16_SQ + (8 * q + j) * T16_ROW + r] = __float2bfloat16_rn(v + 0.0f);
+      }
     }
   }
   __syncthreads();
@@ -184,11 +233,11 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_bf16_kernel(const uint8
   const int64_t m0 = (int64_t)blockIdx.y * SQ;
   __nv_bfloat16* dst = out + out_row * rows + m0;
   if (m0 + SQ <= rows && (rows % 8) == 0) {
-    const uint4* t = reinterpret_cast<const uint4*>(&tile[c][r][0]);
+    const uint4* t = reinterpret_cast<const uint4*>(&tile[c * T16_SQ + r * T16_ROW]);
 #pragma unroll
     for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = t[q];
   } else {
-    for (int i = 0; i < SQ && m0 + i < rows; ++i) dst[i] = tile[c][r][i];
+    for (int i = 0; i < SQ && m0 + i < rows; ++i) dst[i] = tile[c * T16_SQ + r * T16_ROW + i];
   }
 }
 
@@ -212,8 +261,11 @@ extern "C" int fpq_mxfp4_transpose_dequant(const uint8_t* codes, const uint8_t* 
 }
 
 extern "C" int fpq_quantize_mxfp8_square(const void* x_bf16, int64_t rows, int64_t cols, uint8_t* out_e4m3,
-                                         uint8_t* row_scales, uint8_t* col_scales, fpq_stream_t stream) {
+                                         uint8_t* out_t_e4m3, uint8_t* row_scales, uint8_t* col_scales,
+                                         int scale_layout, fpq_stream_t stream) {
   FPQ_CHECK_ARG(x_bf16 && out_e4m3 && row_scales && col_scales, "NULL pointer");
+  FPQ_CHECK_ARG(scale_layout == FPQ_SCALES_ROWMAJOR || scale_layout == FPQ_SCALES_SWIZZLED, "bad scale layout");
+  FPQ_CHECK_ARG(out_t_e4m3 == nullptr || ((uintptr_t)out_t_e4m3 & 15) == 0, "out_t must be 16-byte aligned");
   FPQ_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "cols (%lld) must be a positive multiple of 32", (long long)cols);
   FPQ_CHECK_ARG(rows < (1ll << 31) && cols < (1ll << 31), "shape too large");
   FPQ_CHECK_ARG(((uintptr_t)x_bf16 & 15) == 0 && ((uintptr_t)out_e4m3 & 15) == 0, "x and out must be 16-byte aligned");
@@ -221,14 +273,16 @@ extern "C" int fpq_quantize_mxfp8_square(const void* x_bf16, int64_t rows, int64
   const dim3 grid((unsigned)((cols / SQ + SQ_PER_BLOCK - 1) / SQ_PER_BLOCK), (unsigned)(rows_pad / SQ));
   FPQ_CHECK_ARG(grid.y < 65536, "too many rows for one launch");
   square_quantize_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(reinterpret_cast<const __nv_bfloat16*>(x_bf16), rows,
-                                                                     cols, rows_pad, out_e4m3, row_scales, col_scales);
+                                                                     cols, rows_pad, out_e4m3, out_t_e4m3, row_scales,
+                                                                     col_scales, scale_layout);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
 }
 
 extern "C" int fpq_mxfp4_transpose_mxfp8(const uint8_t* codes, const uint8_t* scales_rowmajor, int64_t rows, int64_t cols,
-                                         uint8_t* out_e4m3, uint8_t* out_scales, fpq_stream_t stream) {
+                                         uint8_t* out_e4m3, uint8_t* out_scales, int scale_layout, fpq_stream_t stream) {
   FPQ_CHECK_ARG(codes && scales_rowmajor && out_e4m3 && out_scales, "NULL pointer");
+  FPQ_CHECK_ARG(scale_layout == FPQ_SCALES_ROWMAJOR || scale_layout == FPQ_SCALES_SWIZZLED, "bad scale layout");
   FPQ_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "cols (%lld) must be a positive multiple of 32", (long long)cols);
   FPQ_CHECK_ARG(rows < (1ll << 31) && cols < (1ll << 31), "shape too large");
   FPQ_CHECK_ARG(((uintptr_t)codes & 15) == 0 && ((uintptr_t)out_e4m3 & 15) == 0, "codes and out must be 16-byte aligned");
@@ -236,7 +290,7 @@ extern "C" int fpq_mxfp4_transpose_mxfp8(const uint8_t* codes, const uint8_t* sc
   const dim3 grid((unsigned)((cols / SQ + SQ_PER_BLOCK - 1) / SQ_PER_BLOCK), (unsigned)(rows_pad / SQ));
   FPQ_CHECK_ARG(grid.y < 65536, "too many rows for one launch");
   fp4_transpose_fp8_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(codes, scales_rowmajor, rows, cols, rows_pad, out_e4m3,
-                                                                       out_scales);
+                                                                       out_scales, scale_layout);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
 }

@@ -143,31 +143,45 @@ def _unrotate(g: torch.Tensor, hadamard_matrix: torch.Tensor) -> torch.Tensor:
     return ops.rotate_dense(g.contiguous(), hadamard_matrix.t().contiguous(), out_dtype=torch.bfloat16)
 
 
+def _row_major_scales(scales: torch.Tensor, rows: int, sf_cols: int) -> torch.Tensor:
+    sb = scales.view(torch.uint8)
+    return sb if tuple(sb.shape) == (rows, sf_cols) else sb[:rows, :sf_cols].contiguous()
+
+
 def _mxfp8_backward(grad_output, x_q, w_q, x_scales, w_scales, act_global_scale, weight_global_scale, x_mask, w_mask,
                     hadamard_matrix, x_shape, want_weight_grad: bool):
     """The two gradient GEMMs of linear_fns.py:270-350 on MXFP8 operands.  The saved MXFP4 operands are
     transposed into MXFP8 (exactly, unless the scales of a 32-row band differ by more than 2^14), the bf16
-    gradient is quantised once with a scale per 32 x 32 square and read along either axis."""
+    gradient is quantised once with a scale per 32 x 32 square and read along either axis.
+
+    Same data flow as the reference's `mxfp4_transpose_mxfp8_op` / `backward_bf16_square_double_mxfp8_op` /
+    `matmul_mxf8_bf16_tn_op` / `..._nn_op` sequence, with the re-layouts folded into the producers: the
+    quantisers write their scales in the layout the GEMM reads, and the gradient's bytes come out in both
+    orientations, so the `nn` product is a `tn` product of the transposed copy."""
     g = grad_output.flatten(end_dim=-2).to(torch.bfloat16).contiguous()
     tokens, out_features = g.shape
-    g_fp8, g_row_scales, g_col_scales = backward_bf16_square_double_mxfp8_op(g)
-    w_t_fp8, w_t_scales = mxfp4_transpose_mxfp8_op(w_q, w_scales)            # [in, out_up128]
-    if w_t_fp8.shape[1] != out_features:
+    in_features = w_q.size(-1) * 2
+    g_fp8, g_row_scales, g_col_scales, g_t_fp8 = ops.quantize_mxfp8_square(g, swizzled=True, transposed=want_weight_grad) \
+        if want_weight_grad else ops.quantize_mxfp8_square(g, swizzled=True) + (None,)
+    if out_features % 128 == 0:
+        w_t_fp8, w_t_scales = ops.mxfp4_transpose_mxfp8(w_q.view(torch.uint8), _row_major_scales(w_scales, out_features, in_features // 32),
+                                                        swizzled=True)
+    else:     # the transposed weight is padded along the contraction axis: cut it back to the gradient's width
+        w_t_fp8, w_t_scales = ops.mxfp4_transpose_mxfp8(w_q.view(torch.uint8), _row_major_scales(w_scales, out_features, in_features // 32))
         w_t_fp8 = w_t_fp8[:, :out_features].contiguous()
-        w_t_scales = w_t_scales[:, : out_features // 32].contiguous()
-    grad_input = matmul_mxf8_bf16_tn_op(g_fp8, w_t_fp8, g_row_scales, w_t_scales,
-                                        (1.0 / weight_global_scale.float()).reshape(1))[:tokens]
+        w_t_scales = ops.swizzle_scales(w_t_scales[:, : out_features // 32].contiguous())
+    grad_input = ops.gemm_mxf8(g_fp8, w_t_fp8, g_row_scales, w_t_scales, (1.0 / weight_global_scale.float()).reshape(1))[:tokens]
     if x_mask is not None:
         grad_input = grad_input * _unpack_mask(x_mask).view_as(grad_input).to(grad_input.dtype)
     grad_input = _unrotate(grad_input, hadamard_matrix).view(x_shape)
     grad_weight = None
     if want_weight_grad:
-        x_t_fp8, x_t_scales = mxfp4_transpose_mxfp8_op(x_q, x_scales)        # [in, tokens_up128]
-        grad_weight = matmul_mxf8_bf16_nn_op(g_fp8, x_t_fp8, g_col_scales, x_t_scales,
-                                             (1.0 / act_global_scale.float()).reshape(1))
+        x_t_fp8, x_t_scales = ops.mxfp4_transpose_mxfp8(x_q.view(torch.uint8), _row_major_scales(x_scales, tokens, in_features // 32),
+                                                        swizzled=True)                       # [in, tokens_up128]
+        grad_weight = ops.gemm_mxf8(g_t_fp8, x_t_fp8, g_col_scales, x_t_scales, (1.0 / act_global_scale.float()).reshape(1))
         if w_mask is not None:
             grad_weight = grad_weight * _unpack_mask(w_mask).view_as(grad_weight).to(grad_weight.dtype)
-        grad_weight = _unrotate(grad_weight, hadamard_matrix).view(out_features, w_q.size(-1) * 2)
+        grad_weight = _unrotate(grad_weight, hadamard_matrix).view(out_features, in_features)
     return grad_input, grad_weight
 
 
@@ -221,9 +235,8 @@ class FPQuant4x8NoMasterFn(Function):
 
 class FPQuant4x4MasterFn(Function):
     """MXFP4 forward from a bf16 master weight, MXFP4 backward (linear_fns.py:80-230): the gradient and the
-    dequantised, transposed operands are rotated along the contraction axis with a Hadamard matrix whose
-    columns get fresh random signs on every call, quantised to MXFP4 again (abs_max), and both gradient
-    GEMMs run on the FP4 kernel."""
+    dequantised, transposed operands are rotated along the contraction axis with the Hadamard matrix,
+    quantised to MXFP4 again (abs_max), and both gradient GEMMs run on the FP4 kernel."""
 
     @staticmethod
     def forward(ctx, x, weight, weight_global_scale, act_global_scale, bias, forward_hadamard_matrix, dtype,
@@ -244,9 +257,12 @@ class FPQuant4x4MasterFn(Function):
     def backward(ctx, grad_output):
         x_q, w_q, x_scales, w_scales, act_global_scale, weight_global_scale, hadamard_matrix = ctx.saved_tensors
         x_mask, w_mask = ctx.masks
-        h = hadamard_matrix.shape[-1]
-        signs = torch.randint(0, 2, (h,), device=hadamard_matrix.device, dtype=torch.bfloat16) * 2.0 - 1.0
-        backward_hadamard_matrix = hadamard_matrix.to(torch.bfloat16) * signs
+        # The reference multiplies the columns of the Hadamard matrix by fresh random signs here
+        # (linear_fns.py:151-158).  With y = x @ (H D) that flips the sign of whole columns of both rotated
+        # operands of a GEMM, which neither the sign-symmetric quantiser nor the product of the two notices:
+        # both gradients are bit-identical with D = I.  The plain matrix is used, so the rotation stays on the
+        # butterfly of the quantise kernel instead of a dense product.
+        backward_hadamard_matrix = hadamard_matrix.to(torch.bfloat16)
         g = grad_output.flatten(end_dim=-2).to(torch.bfloat16).contiguous()
         tokens, out_features = g.shape
         # abs_max MXFP4 carries a factor 3 per operand (the scale is a third of the power of two that is stored)

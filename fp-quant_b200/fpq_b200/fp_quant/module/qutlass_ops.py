@@ -349,3 +349,14 @@ fused_quantize_blocked_op = _eager_bypass(fused_quantize_blocked_op)
 fused_silu_mul_quantize_blocked_op = _eager_bypass(fused_silu_mul_quantize_blocked_op)
 matmul_fp4_bf16_tn_blocked_op = _eager_bypass(matmul_fp4_bf16_tn_blocked_op)
 swizzle_scales_op = _eager_bypass(swizzle_scales_op)
+# ... and the reference-named ops of the training paths (a quantised backward pass calls eight of them per layer)
+_fused_quantize_mx = _eager_bypass(_fused_quantize_mx)
+fused_quantize_nv_op = _eager_bypass(fused_quantize_nv_op)
+matmul_mxf4_bf16_tn_op = _eager_bypass(matmul_mxf4_bf16_tn_op)
+matmul_nvf4_bf16_tn_op = _eager_bypass(matmul_nvf4_bf16_tn_op)
+matmul_mxf8_bf16_tn_op = _eager_bypass(matmul_mxf8_bf16_tn_op)
+matmul_mxf8_bf16_nn_op = _eager_bypass(matmul_mxf8_bf16_nn_op)
+backward_bf16_square_double_mxfp8_op = _eager_bypass(backward_bf16_square_double_mxfp8_op)
+mxfp4_transpose_mxfp8_op = _eager_bypass(mxfp4_transpose_mxfp8_op)
+backward_t_bf16_op = _eager_bypass(backward_t_bf16_op)
+backward_qt_bf16_op = _eager_bypass(backward_qt_bf16_op)

@@ -332,9 +332,20 @@ def gemm_mxf8(a_e4m3: torch.Tensor, b_e4m3: torch.Tensor, a_scales_swizzled: tor
     return out
 
 
-def quantize_mxfp8_square(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def _scale_buffer(rows: int, sf_cols: int, swizzled: bool, device) -> torch.Tensor:
+    """Buffer for [rows, sf_cols] scale bytes: exact when row-major, the padded tile layout (padding zeroed) when swizzled."""
+    if not swizzled:
+        return torch.empty(rows, sf_cols, dtype=torch.uint8, device=device)
+    pr, pc = padded_scale_shape(rows, sf_cols)
+    alloc = torch.empty if (pr, pc) == (rows, sf_cols) else torch.zeros
+    return alloc(pr, pc, dtype=torch.uint8, device=device)
+
+
+def quantize_mxfp8_square(x: torch.Tensor, swizzled: bool = False, transposed: bool = False):
     """bf16 [rows, cols] -> (E4M3 [rows_pad, cols], row scales u8 [rows_pad, cols/32], column scales u8
-    [cols, rows_pad/32]); one E8M0 byte per 32 x 32 square, rows_pad = rows rounded up to 128 (zero rows)."""
+    [cols, rows_pad/32]); one E8M0 byte per 32 x 32 square, rows_pad = rows rounded up to 128 (zero rows).
+    swizzled: both scale tensors in the layout the GEMM reads.  transposed: additionally returns the bytes as
+    [cols, rows_pad] (fourth value)."""
     x = _cuda(x, "x")
     if x.dtype != torch.bfloat16 or x.dim() != 2:
         raise ValueError(f"x must be a 2-D bfloat16 tensor, got {x.dtype} {tuple(x.shape)}")
@@ -342,16 +353,18 @@ def quantize_mxfp8_square(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, 
     rows, cols = x.shape
     rp = (rows + 127) // 128 * 128
     out = torch.empty(rp, cols, dtype=torch.float8_e4m3fn, device=x.device)
-    rs = torch.empty(rp, cols // 32, dtype=torch.uint8, device=x.device)
-    cs = torch.empty(cols, rp // 32, dtype=torch.uint8, device=x.device)
+    out_t = torch.empty(cols, rp, dtype=torch.float8_e4m3fn, device=x.device) if transposed else None
+    rs = _scale_buffer(rp, cols // 32, swizzled, x.device)
+    cs = _scale_buffer(cols, rp // 32, swizzled, x.device)
     with _guard(x.device):
-        C.call("fpq_quantize_mxfp8_square", x.data_ptr(), rows, cols, out.data_ptr(), rs.data_ptr(), cs.data_ptr(), _stream(x))
-    return out, rs, cs
+        C.call("fpq_quantize_mxfp8_square", x.data_ptr(), rows, cols, out.data_ptr(), _ptr(out_t), rs.data_ptr(), cs.data_ptr(),
+               C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _stream(x))
+    return (out, rs, cs, out_t) if transposed else (out, rs, cs)
 
 
-def mxfp4_transpose_mxfp8(codes: torch.Tensor, scales_rowmajor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def mxfp4_transpose_mxfp8(codes: torch.Tensor, scales_rowmajor: torch.Tensor, swizzled: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """MXFP4 (codes u8 [rows, cols/2], E8M0 bytes [rows, cols/32], row-major, unpadded) -> the transpose as
-    MXFP8: (E4M3 [cols, rows_pad], scales u8 [cols, rows_pad/32])."""
+    MXFP8: (E4M3 [cols, rows_pad], scales u8 [cols, rows_pad/32], swizzled for the GEMM on request)."""
     codes = _cuda(codes, "codes").contiguous()
     sc = _cuda(scales_rowmajor, "scales")
     sc = (sc if sc.dtype == torch.uint8 else sc.view(torch.uint8)).contiguous()
@@ -360,10 +373,10 @@ def mxfp4_transpose_mxfp8(codes: torch.Tensor, scales_rowmajor: torch.Tensor) ->
         raise ValueError(f"scales must be [{rows}, {cols // 32}] row-major bytes, got {tuple(sc.shape)}")
     rp = (rows + 127) // 128 * 128
     out = torch.empty(cols, rp, dtype=torch.float8_e4m3fn, device=codes.device)
-    os_ = torch.empty(cols, rp // 32, dtype=torch.uint8, device=codes.device)
+    os_ = _scale_buffer(cols, rp // 32, swizzled, codes.device)
     with _guard(codes.device):
         C.call("fpq_mxfp4_transpose_mxfp8", codes.data_ptr(), sc.data_ptr(), rows, cols, out.data_ptr(), os_.data_ptr(),
-               _stream(codes))
+               C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _stream(codes))
     return out, os_
 
 

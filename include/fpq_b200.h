@@ -221,11 +221,15 @@ int fpq_gemm_mxf8(const uint8_t* a_e4m3, const uint8_t* b_e4m3, const uint8_t* a
  * (col_scales [cols, rows_pad/32]); rows_pad = rows rounded up to 128, the padding rows are written as
  * zeros.  Stands for backward_bf16_square_double_mxfp8 (qutlass_ops.py:277-304; QuTLASS itself is not
  * available, so the arithmetic is this library's: scale 2^(floor(log2(max|x|)) - 8), byte 0 for an all-zero
- * square, x / scale clamped to +-448 and rounded to nearest even).  out_e4m3: [rows_pad, cols] bytes.
- * cols % 32 == 0.
+ * square, x / scale clamped to +-448 and rounded to nearest even).  out_e4m3: [rows_pad, cols] bytes;
+ * out_t_e4m3 (optional, may be NULL): the same bytes transposed, [cols, rows_pad], for the GEMM that
+ * contracts over the rows.  scale_layout: FPQ_SCALES_ROWMAJOR, or FPQ_SCALES_SWIZZLED to write both scale
+ * tensors in the layout the GEMM reads (buffers of the padded size; bytes of the padding are not written:
+ * zero them once).  cols % 32 == 0.
  */
 int fpq_quantize_mxfp8_square(const void* x_bf16, int64_t rows, int64_t cols, uint8_t* out_e4m3,
-                              uint8_t* row_scales, uint8_t* col_scales, fpq_stream_t stream);
+                              uint8_t* out_t_e4m3, uint8_t* row_scales, uint8_t* col_scales, int scale_layout,
+                              fpq_stream_t stream);
 
 /*
  * MXFP4 [rows, cols] (packed codes [rows, cols/2], row-major E8M0 bytes [rows, cols/32]) -> its transpose
@@ -233,10 +237,11 @@ int fpq_quantize_mxfp8_square(const void* x_bf16, int64_t rows, int64_t cols, ui
  * rounded up to 128 (padding zero).  Stands for mxfp4_transpose_mxfp8 (qutlass_ops.py:307-330; arithmetic
  * defined here): a 32 x 32 square takes 2^(emax - 6), emax the largest of its 32 source exponents, and an
  * element becomes fp4 * 2^(e_row - emax + 6), exact unless its row lies more than 2^-14 below the largest
- * (then rounded to nearest even on the E4M3 grid).  cols % 32 == 0.
+ * (then rounded to nearest even on the E4M3 grid).  scale_layout as for fpq_quantize_mxfp8_square (it
+ * applies to out_scales; the input scales are always row-major).  cols % 32 == 0.
  */
 int fpq_mxfp4_transpose_mxfp8(const uint8_t* codes, const uint8_t* scales_rowmajor, int64_t rows, int64_t cols,
-                              uint8_t* out_e4m3, uint8_t* out_scales, fpq_stream_t stream);
+                              uint8_t* out_e4m3, uint8_t* out_scales, int scale_layout, fpq_stream_t stream);
 
 /*
  * MXFP4 [rows, cols] (packed codes, row-major E8M0 bytes [rows, cols/32]) -> bf16 [cols, rows]: the transpose

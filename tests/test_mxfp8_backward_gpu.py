@@ -40,6 +40,11 @@ def test_square_quantize_matches_the_oracle(cuda_device, shape):
     assert torch.equal(a, b)
     ref = x.double()
     assert float((a[:rows] - ref).norm() / ref.norm()) < 0.04
+    # the forms the backward pass uses: scales in the GEMM's tile layout, bytes in both orientations
+    got2, rs2, cs2, got_t = ops.quantize_mxfp8_square(x.to(cuda_device), swizzled=True, transposed=True)
+    assert torch.equal(got2.view(torch.uint8).cpu(), want) and torch.equal(got_t.view(torch.uint8).cpu(), want.t())
+    assert torch.equal(rs2.cpu().flatten(), fp4.swizzle_scales(want_rs).flatten())
+    assert torch.equal(cs2.cpu().flatten(), fp4.swizzle_scales(want_cs).flatten())
 
 
 def test_square_quantize_extremes(cuda_device):
@@ -72,6 +77,9 @@ def test_fp4_transpose_matches_the_oracle(cuda_device, shape):
     got, got_s = ops.mxfp4_transpose_mxfp8(codes.to(cuda_device), sb.to(cuda_device))
     assert torch.equal(got_s.cpu(), want_s)
     assert torch.equal(got.view(torch.uint8).cpu(), want)
+    got2, got_s2 = ops.mxfp4_transpose_mxfp8(codes.to(cuda_device), sb.to(cuda_device), swizzled=True)
+    assert torch.equal(got2.view(torch.uint8).cpu(), want)
+    assert torch.equal(got_s2.cpu().flatten(), fp4.swizzle_scales(want_s).flatten())
 
 
 def test_fp4_transpose_is_exact_for_real_operands(cuda_device):
@@ -209,6 +217,8 @@ def test_fp4_transpose_dequant_matches_the_oracle(cuda_device, shape):
     g = torch.Generator().manual_seed(rows + 5 * cols)
     codes = torch.randint(0, 256, (rows, cols // 2), generator=g, dtype=torch.uint8)
     sb = torch.randint(100, 140, (rows, cols // 32), generator=g, dtype=torch.uint8)
+    sb[::5, 0] = 3                                            # extreme exponents take the kernel's general path
+    sb[1::5, -1] = 250
     for alpha in (3.0, 1.0, 0.37):
         want = mxfp8.fp4_transpose_dequant(codes, sb, alpha)
         got = ops.mxfp4_transpose_dequant(codes.to(cuda_device), sb.to(cuda_device), torch.tensor([alpha], device=cuda_device))
