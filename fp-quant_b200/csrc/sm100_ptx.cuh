@@ -189,6 +189,17 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
       : "memory");
 }
 
+// The same across a CTA pair (M = 256: 128 rows accumulate in each CTA's tensor memory; each CTA holds its rows
+// of A and its half of B at the same shared-memory offsets).  Issued by one thread of the leader CTA.
+__device__ __forceinline__ void tc_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // This warp's 32 lanes x 32 consecutive fp32 columns of tensor memory -> registers.
 __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

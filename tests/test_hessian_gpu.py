@@ -10,7 +10,7 @@ from tests import inputs
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("tokens,d", [(64, 128), (200, 256), (2048, 512), (1000, 1032), (4096, 4096)])
+@pytest.mark.parametrize("tokens,d", [(64, 128), (200, 256), (2048, 512), (1000, 1032), (4096, 4096), (1024, 3080)])   # the last two: 256 x 256 tiles on CTA pairs, the last with ragged edge tiles
 def test_xtx_matches_fp64(cuda_device, tokens, d):
     from fpq_b200 import ops
 
