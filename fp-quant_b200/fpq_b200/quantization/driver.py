@@ -394,12 +394,12 @@ def gptq_quantization(model, calibration_data: List[torch.Tensor], args, device)
     # Rank 0 gets the widest Hessian's chain and column loop (`plan_ranks`), which the other ranks wait for once
     # they have run the second pass up to that layer; its own share of that pass runs after them.  It is
     # therefore given fewer calibration sequences, so that its forward passes fit into the time the others
-    # need for theirs.  The shares were balanced on a Llama-3.1-8B block with 128 x 2048 tokens (0.89 / 0.6 /
+    # need for theirs.  The shares were balanced on a Llama-3.1-8B block with 128 x 2048 tokens (0.82 / 0.6 /
     # 0.45 of an even share at 2 / 4 / 8 ranks; at 8 ranks 0.25, 0.45 and 0.62 gave 0.111, 0.107 and 0.110 s per
     # block); `args.owner_share` overrides them, 1.0 is an even split.
     share = getattr(args, "owner_share", None)
     if share is None:
-        share = {2: 0.89, 4: 0.6, 8: 0.45}.get(world_size, 1.0 if world_size < 2 else 0.6)
+        share = {2: 0.82, 4: 0.6, 8: 0.45}.get(world_size, 1.0 if world_size < 2 else 0.6)
     if world_size > 1 and getattr(args, "split_second_pass", True):
         rest = (world_size - share) / (world_size - 1)
         lo, hi = fdist.weighted_bounds(n_total, [share] + [rest] * (world_size - 1))[rank]

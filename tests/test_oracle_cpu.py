@@ -245,3 +245,47 @@ def test_mxfp8_matmul_known_answer():
     b = torch.tensor([[0x40] * 32 + [0xC4] * 32], dtype=torch.uint8)      # 2.0 and -3.0
     y = fp4.mxfp8_matmul(a, b, torch.full((1, 2), 127, dtype=torch.uint8), torch.full((1, 2), 127, dtype=torch.uint8), 0.5)
     assert float(y) == 0.5 * (32 * 2.0 - 32 * 3.0)
+
+
+def test_mxfp8_square_quantize_known_answers():
+    """One E8M0 byte per 32 x 32 square = floor(log2(max|x|)) - 8 + 127; elements x / 2^(byte - 127) on the E4M3
+    grid; padding rows zero; the same bytes dequantise identically along rows and along columns."""
+    from oracle import mxfp8
+
+    x = torch.zeros(40, 64, dtype=torch.bfloat16)
+    x[:32, :32] = 1.0                   # max 1 -> exponent -8 -> byte 119, elements 256 = 0x78
+    x[0, 0] = 1.5                       # 1.5 * 256 = 384 = 0x7C
+    x[:32, 32:] = 0.0                   # all-zero square: byte 0
+    x[32:, :32] = -448.0                # rows 32..39 of the second band: 448 = 1.75 * 2^8 -> exponent 0 -> byte 127
+    out, rs, cs = mxfp8.square_quantize(x)
+    assert out.shape == (128, 64) and rs.shape == (128, 2) and cs.shape == (64, 4)
+    assert int(rs[0, 0]) == 119 and int(rs[0, 1]) == 0 and int(rs[32, 0]) == 127 and int(rs[64, 0]) == 0
+    assert int(out[1, 1]) == 0x78 and int(out[0, 0]) == 0x7C and int(out[33, 5]) == 0xFE and int(out[50, 5]) == 0
+    assert torch.equal(cs[:32, 0], rs[0, 0].expand(32)) and torch.equal(cs[:32, 1], rs[32, 0].expand(32))
+    a = mxfp8.dequantize_mxfp8(out, rs)
+    b = mxfp8.dequantize_mxfp8(out.t().contiguous(), cs).t()
+    assert torch.equal(a, b) and torch.equal(a[:40], x.double())
+    # a value just below a power of two saturates instead of overflowing: 511 / 2 = 255.5 -> scaled past 448
+    y = torch.full((32, 32), 0.001, dtype=torch.bfloat16)
+    y[3, 3] = 510.0
+    out, rs, _ = mxfp8.square_quantize(y)
+    assert int(rs[0, 0]) == 127 and int(out[3, 3]) == 0x7E
+
+
+def test_mxfp4_transposes_are_exact_on_real_operands():
+    """MXFP4 -> transposed MXFP8 keeps every value exactly while the exponents of a 32-row band lie within 2^14,
+    and the transposing dequantiser returns fp4 * 2^e / alpha rounded once to bf16."""
+    from oracle import mxfp8
+
+    y = fp4.fwht_butterfly(torch.randn(70, 128, generator=torch.Generator().manual_seed(4)), 32)
+    q, sb, _ = fp4.quantize(y, "mxfp4")
+    want = fp4.dequantize(fp4.unpack_codes(q), fp4.decode_scale_bytes(sb, "mxfp4"), 32).double()
+    out, os_ = mxfp8.fp4_transpose_fp8(q, sb)
+    assert out.shape == (128, 128) and os_.shape == (128, 4)
+    got = mxfp8.dequantize_mxfp8(out, os_)
+    assert torch.equal(got[:, :70], want.t()) and float(got[:, 70:].abs().max()) == 0.0
+    assert int(os_[0, 3]) == 0                                   # a square without source rows
+    t = mxfp8.fp4_transpose_dequant(q, sb, 3.0)
+    assert t.shape == (128, 70) and t.dtype == torch.bfloat16
+    ref = (want.float() / torch.tensor(3.0)).t().to(torch.bfloat16)
+    assert torch.equal(t.view(torch.int16), (ref + 0.0).view(torch.int16))
