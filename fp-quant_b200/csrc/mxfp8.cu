@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_fp8_kernel(const uint8_
 __global__ void __launch_bounds__(THREADS) fp4_transpose_bf16_kernel(const uint8_t* __restrict__ codes,
                                                                      const uint8_t* __restrict__ scales, int64_t rows,
                                                                      int64_t cols, const float* __restrict__ alpha,
-                                                                     __nv_bfloat16* __restrict__ out) {
+                                                                     __nv_bfloat16* __restrict__ out, int64_t out_ld) {
   __shared__ __align__(16) __nv_bfloat16 tile[SQ_PER_BLOCK * T16_SQ];      // [square][column of the source][row of the source]
   const int r = threadIdx.x / SQ_PER_BLOCK, c = threadIdx.x % SQ_PER_BLOCK;
   const int64_t row = (int64_t)blockIdx.y * SQ + r;
@@ -231,8 +231,8 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_bf16_kernel(const uint8
   // thread (r, c) owns source column col0 + r: up to 32 contiguous bf16 of the output row
   const int64_t out_row = col0 + r;
   const int64_t m0 = (int64_t)blockIdx.y * SQ;
-  __nv_bfloat16* dst = out + out_row * rows + m0;
-  if (m0 + SQ <= rows && (rows % 8) == 0) {
+  __nv_bfloat16* dst = out + out_row * out_ld + m0;
+  if (m0 + SQ <= rows && (out_ld % 8) == 0) {
     const uint4* t = reinterpret_cast<const uint4*>(&tile[c * T16_SQ + r * T16_ROW]);
 #pragma unroll
     for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(dst)[q] = t[q];
@@ -247,15 +247,16 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_bf16_kernel(const uint8
 using namespace fpq;
 
 extern "C" int fpq_mxfp4_transpose_dequant(const uint8_t* codes, const uint8_t* scales_rowmajor, int64_t rows, int64_t cols,
-                                           const float* alpha, void* out_bf16, fpq_stream_t stream) {
+                                           const float* alpha, void* out_bf16, int64_t out_ld, fpq_stream_t stream) {
   FPQ_CHECK_ARG(codes && scales_rowmajor && alpha && out_bf16, "NULL pointer");
+  FPQ_CHECK_ARG(out_ld >= rows, "out_ld (%lld) must not be below rows (%lld)", (long long)out_ld, (long long)rows);
   FPQ_CHECK_ARG(rows > 0 && cols > 0 && cols % 32 == 0, "cols (%lld) must be a positive multiple of 32", (long long)cols);
   FPQ_CHECK_ARG(rows < (1ll << 31) && cols < (1ll << 31), "shape too large");
   FPQ_CHECK_ARG(((uintptr_t)codes & 15) == 0 && ((uintptr_t)out_bf16 & 15) == 0, "codes and out must be 16-byte aligned");
   const dim3 grid((unsigned)((cols / SQ + SQ_PER_BLOCK - 1) / SQ_PER_BLOCK), (unsigned)((rows + SQ - 1) / SQ));
   FPQ_CHECK_ARG(grid.y < 65536, "too many rows for one launch");
   fp4_transpose_bf16_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(codes, scales_rowmajor, rows, cols, alpha,
-                                                                        reinterpret_cast<__nv_bfloat16*>(out_bf16));
+                                                                        reinterpret_cast<__nv_bfloat16*>(out_bf16), out_ld);
   FPQ_CHECK_LAUNCH();
   return FPQ_OK;
 }

@@ -747,6 +747,86 @@ int launch_silu_mul(const QuantParams& params, const void* up, cudaStream_t stre
   return FPQ_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Quantise the TRANSPOSE of a bf16 matrix: x [t_rows, n] row-major -> MXFP4 of x^T [n, t_pad], rotated and
+// scaled along the t axis (groups of 32 consecutive rows of x), without materialising x^T.  This is what
+// the weight-gradient GEMM of the quantised backward pass needs of the upstream gradient
+// (backward_t_bf16, inference_lib/src/fp_quant/module/qutlass_ops.py:218-245 of IST-DASLab/FP-Quant).
+// A warp takes a 32 x 32 tile of x (32 rows of 64 bytes), turns it round through shared memory, and every
+// lane then owns one output chunk: 32 consecutive t of one column of x, i.e. exactly the chunk
+// process_chunk expects.  Rows of x beyond t_rows read as zero (t_pad may exceed t_rows).  The rotation must
+// stay inside a chunk: group 0, 16 or 32.
+constexpr int TQ_ROW_BYTES = 64 + 16;      // a tile row in shared memory, padded against bank conflicts
+
+template <int GH, int FMT>
+__global__ void __launch_bounds__(256, 2) quant_transposed_kernel(const QuantParams p, int64_t t_rows, int64_t n) {
+  static_assert(GH == 0 || GH == 16 || GH == 32, "the rotation group must fit one 32-element chunk");
+  __shared__ __align__(16) uint8_t tiles[8][32 * TQ_ROW_BYTES];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  uint8_t* tile = tiles[wib];
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  launch_dependents();
+  grid_dependency_wait();
+  const int64_t col_tiles = (n + 31) / 32, t_tiles = p.chunks_per_row;      // tiles along x's columns / rows
+  float unused_max = 0.0f;
+  // tile index = t_tile * col_tiles + col_tile: neighbouring warps read neighbouring 64-byte pieces of the same rows
+  for (int64_t tix = warp; tix < col_tiles * t_tiles; tix += n_warps) {
+    const int64_t tt = tix / col_tiles, ct = tix - tt * col_tiles;
+    const int64_t t0 = tt * 32, j0 = ct * 32;
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int row = q * 8 + (lane >> 2), piece = lane & 3;
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (t0 + row < t_rows && j0 + piece * 8 < n)
+        v = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.x) + (t0 + row) * n + j0 + piece * 8);
+      *reinterpret_cast<uint4*>(tile + row * TQ_ROW_BYTES + piece * 16) = v;
+    }
+    __syncwarp();
+    RawChunk<true> raw;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const uint32_t lo = *reinterpret_cast<const uint16_t*>(tile + (2 * k) * TQ_ROW_BYTES + lane * 2);
+      const uint32_t hi = *reinterpret_cast<const uint16_t*>(tile + (2 * k + 1) * TQ_ROW_BYTES + lane * 2);
+      raw.w[k] = lo | (hi << 16);
+    }
+    const int64_t out_row = j0 + lane;
+    const bool active = out_row < n;
+    process_chunk<GH, FMT, true, MODE_CODES>(p, raw, active ? out_row * p.chunks_per_row + tt : 0, active, lane, 0.0f, 0.0f,
+                                             unused_max);
+  }
+  if (p.pad_rows != 0) {
+    const int64_t n_words = (int64_t)p.pad_rows * p.sf_tiles_per_row_block;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < n_words; w += (int64_t)gridDim.x * blockDim.x) {
+      const uint32_t r = p.rows + (uint32_t)(w / p.sf_tiles_per_row_block);
+      const uint32_t kb = (uint32_t)(w % p.sf_tiles_per_row_block);
+      *reinterpret_cast<uint32_t*>(p.sbytes + swizzled_offset(r, kb * 4u, p.sf_tiles_per_row_block)) = 0u;
+    }
+  }
+}
+
+template <int GH>
+int launch_transposed(const QuantParams& params, int64_t t_rows, int64_t n, cudaStream_t stream) {
+  QuantParams p = params;
+  p.row_magic = (p.chunks_per_row >= 2 && p.n_chunks < (1ll << 32)) ? ~0ull / p.chunks_per_row + 1 : 0;
+  const int64_t tiles = ((n + 31) / 32) * (int64_t)p.chunks_per_row;
+  int64_t blocks = (int64_t)sm_count() * 2;          // persistent: two resident blocks of eight warps per SM
+  if (blocks > ceil_div64(tiles, 8)) blocks = ceil_div64(tiles, 8);
+  if (blocks < 1) blocks = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_dependent_launch() ? 1 : 0;
+  FPQ_CHECK_CUDA(cudaLaunchKernelEx(&cfg, quant_transposed_kernel<GH, FPQ_FMT_MXFP4>, p, t_rows, n));
+  return FPQ_OK;
+}
+
 template <int FMT>
 int launch_silu_mul_gh(int gh, const QuantParams& p, const void* up, cudaStream_t stream) {
   switch (gh) {
@@ -1198,6 +1278,36 @@ extern "C" int fpq_quantize_silu_mul(const void* gate_bf16, const void* up_bf16,
   }
   return format == FPQ_FMT_NVFP4 ? launch_silu_mul_gh<FPQ_FMT_NVFP4>(hadamard_group, p, up_bf16, (cudaStream_t)stream)
                                  : launch_silu_mul_gh<FPQ_FMT_MXFP4>(hadamard_group, p, up_bf16, (cudaStream_t)stream);
+}
+
+extern "C" int fpq_quantize_transposed(const void* x_bf16, int64_t t_rows, int64_t n, int64_t t_pad, int hadamard_group,
+                                       uint8_t* codes, uint8_t* scale_bytes, int scale_layout, fpq_stream_t stream) {
+  FPQ_CHECK_ARG(x_bf16 && codes && scale_bytes, "NULL pointer");
+  FPQ_CHECK_ARG(t_rows > 0 && n > 0 && n % 8 == 0, "n (%lld) must be a positive multiple of 8", (long long)n);
+  FPQ_CHECK_ARG(t_pad >= t_rows && t_pad % 32 == 0, "t_pad (%lld) must be a multiple of 32 not below t_rows", (long long)t_pad);
+  FPQ_CHECK_ARG(hadamard_group == 0 || hadamard_group == 16 || hadamard_group == 32,
+                "the rotation group of the transposing quantiser must be 0, 16 or 32 (got %d)", hadamard_group);
+  FPQ_CHECK_ARG(scale_layout == FPQ_SCALES_ROWMAJOR || scale_layout == FPQ_SCALES_SWIZZLED, "bad scale_layout");
+  FPQ_CHECK_ARG(((uintptr_t)x_bf16 & 15) == 0 && ((uintptr_t)codes & 15) == 0 && ((uintptr_t)scale_bytes & 15) == 0,
+                "pointers must be 16-byte aligned");
+  FPQ_CHECK_ARG(n < ((int64_t)1 << 31) && t_pad < ((int64_t)1 << 31), "shape too large");
+  QuantParams p{};
+  p.x = x_bf16;
+  p.n_chunks = n * t_pad / 32;
+  p.chunks_per_row = (uint32_t)(t_pad / 32);
+  p.codes = codes;
+  p.sbytes = scale_bytes;
+  p.sf_tiles_per_row_block = (uint32_t)ceil_div64(t_pad / 32, 4);
+  p.layout = scale_layout;
+  if (scale_layout == FPQ_SCALES_SWIZZLED) {
+    p.rows = (uint32_t)n;
+    p.pad_rows = (uint32_t)(ceil_div64(n, 128) * 128 - n);
+  }
+  switch (hadamard_group) {
+    case 0: return launch_transposed<0>(p, t_rows, n, (cudaStream_t)stream);
+    case 16: return launch_transposed<16>(p, t_rows, n, (cudaStream_t)stream);
+    default: return launch_transposed<32>(p, t_rows, n, (cudaStream_t)stream);
+  }
 }
 
 extern "C" int fpq_fake_quantize(const void* x, int dtype, int64_t rows, int64_t cols, int hadamard_group,

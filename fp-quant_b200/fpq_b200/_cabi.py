@@ -61,7 +61,8 @@ _SIGNATURES = {
                      c_int64, c_int, c_void_p, c_void_p],
     "fpq_quantize_mxfp8_square": [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "fpq_mxfp4_transpose_mxfp8": [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p],
-    "fpq_mxfp4_transpose_dequant": [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p],
+    "fpq_mxfp4_transpose_dequant": [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p],
+    "fpq_quantize_transposed": [c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "fpq_gemm_mxf8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                       c_void_p, c_void_p],
 }

@@ -265,31 +265,47 @@ class FPQuant4x4MasterFn(Function):
         backward_hadamard_matrix = hadamard_matrix.to(torch.bfloat16)
         g = grad_output.flatten(end_dim=-2).to(torch.bfloat16).contiguous()
         tokens, out_features = g.shape
+        in_features = w_q.size(-1) * 2
         # abs_max MXFP4 carries a factor 3 per operand (the scale is a third of the power of two that is stored)
         ninth = torch.full((1,), 1.0 / 9.0, dtype=torch.float32, device=g.device)
-
-        g_q, g_scales, _ = fused_quantize_mx_op(g, backward_hadamard_matrix, "abs_max", False)
-        wt_q, wt_scales = backward_qt_bf16_op(w_q, w_scales, backward_hadamard_matrix, weight_global_scale.float())
-        grad_input = matmul_mxf4_bf16_tn_op(g_q, wt_q, g_scales, wt_scales, ninth)
+        kind, group = kind_of(0, backward_hadamard_matrix)
+        if kind in ("hadamard", "identity") and group <= 32 and out_features % 8 == 0:
+            # Same data flow as the op sequence below with the re-layouts folded into the producers: scales come
+            # out in the layout the GEMM reads, the transposes happen inside the (de)quantise kernels, and the
+            # token axis is padded to a whole number of K tiles by the kernels that write it.
+            gh = group if kind == "hadamard" else 0
+            w_rm = _row_major_scales(w_scales, out_features, in_features // 32)
+            x_rm = _row_major_scales(x_scales, tokens, in_features // 32)
+            g_q, g_s, _ = ops.quantize(g, "mxfp4", gh, None, swizzled=True)
+            wt = ops.mxfp4_transpose_dequant(w_q.view(torch.uint8), w_rm, weight_global_scale.float())        # [in, out]
+            wt_q, wt_s, _ = ops.quantize(wt, "mxfp4", gh, None, swizzled=True)
+            grad_input = ops.gemm_fp4(g_q, wt_q, g_s, wt_s, ninth, "mxfp4")
+            gt_q, gt_s = ops.quantize_transposed(g, gh, pad_to=128, swizzled=True)                             # [out, tokens_up128]
+            xt = ops.mxfp4_transpose_dequant(x_q.view(torch.uint8), x_rm, act_global_scale.float(), pad_to=128)   # [in, tokens_up128]
+            xt_q, xt_s, _ = ops.quantize(xt, "mxfp4", gh, None, swizzled=True)
+            grad_weight = ops.gemm_fp4(gt_q, xt_q, gt_s, xt_s, ninth, "mxfp4")
+        else:
+            g_q, g_scales, _ = fused_quantize_mx_op(g, backward_hadamard_matrix, "abs_max", False)
+            wt_q, wt_scales = backward_qt_bf16_op(w_q, w_scales, backward_hadamard_matrix, weight_global_scale.float())
+            grad_input = matmul_mxf4_bf16_tn_op(g_q, wt_q, g_scales, wt_scales, ninth)
+            # the weight gradient contracts over the tokens: pad them to a whole number of K tiles with zero rows
+            pad = (-tokens) % 128
+            g_pad = torch.nn.functional.pad(g, (0, 0, 0, pad)) if pad else g
+            gt_q, gt_scales = backward_t_bf16_op(g_pad, backward_hadamard_matrix)
+            if pad:
+                zero_codes = torch.full((pad, x_q.shape[1]), 0x88, dtype=torch.uint8, device=x_q.device)
+                x_q_pad = torch.cat([x_q.view(torch.uint8), zero_codes])
+                xs = x_scales.view(torch.uint8)[:tokens, : x_q.shape[1] // 16]
+                xs_pad = torch.cat([xs, torch.full((pad, xs.shape[1]), 127, dtype=torch.uint8, device=xs.device)])
+            else:
+                x_q_pad, xs_pad = x_q, x_scales
+            xt_q, xt_scales = backward_qt_bf16_op(x_q_pad, xs_pad, backward_hadamard_matrix, act_global_scale.float())
+            grad_weight = matmul_mxf4_bf16_tn_op(gt_q, xt_q, gt_scales, xt_scales, ninth)
         if x_mask is not None:
             grad_input = grad_input * _unpack_mask(x_mask).view_as(grad_input).to(grad_input.dtype)
         grad_input = _unrotate(grad_input, hadamard_matrix).view(ctx.x_shape)
-
-        # the weight gradient contracts over the tokens: pad them to a whole number of K tiles with zero rows
-        pad = (-tokens) % 128
-        g_pad = torch.nn.functional.pad(g, (0, 0, 0, pad)) if pad else g
-        gt_q, gt_scales = backward_t_bf16_op(g_pad, backward_hadamard_matrix)
-        if pad:
-            zero_codes = torch.full((pad, x_q.shape[1]), 0x88, dtype=torch.uint8, device=x_q.device)
-            x_q_pad = torch.cat([x_q.view(torch.uint8), zero_codes])
-            xs = x_scales.view(torch.uint8)[:tokens, : x_q.shape[1] // 16]
-            xs_pad = torch.cat([xs, torch.full((pad, xs.shape[1]), 127, dtype=torch.uint8, device=xs.device)])
-        else:
-            x_q_pad, xs_pad = x_q, x_scales
-        xt_q, xt_scales = backward_qt_bf16_op(x_q_pad, xs_pad, backward_hadamard_matrix, act_global_scale.float())
-        grad_weight = matmul_mxf4_bf16_tn_op(gt_q, xt_q, gt_scales, xt_scales, ninth)
         if w_mask is not None:
             grad_weight = grad_weight * _unpack_mask(w_mask).view_as(grad_weight).to(grad_weight.dtype)
-        grad_weight = _unrotate(grad_weight, hadamard_matrix).view(out_features, w_q.size(-1) * 2)
+        grad_weight = _unrotate(grad_weight, hadamard_matrix).view(out_features, in_features)
         grad_bias = g.sum(dim=0) if ctx.bias_present else None
         return grad_input, grad_weight, None, None, grad_bias, None, None, None

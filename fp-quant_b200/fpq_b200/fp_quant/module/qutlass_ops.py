@@ -299,7 +299,14 @@ def _(x_fp4, scales):
 def backward_t_bf16_op(x: torch.Tensor, hadamard_matrix: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [m, n] -> MXFP4 of its transpose, rotated along m: (codes [n, m/2], row-major e8m0 scales, padded
     like `fused_quantize_mx_op` pads them) (qutlass_ops.py:218-245).  m % 32 == 0."""
-    q, sb = _quantize(x.t().contiguous(), hadamard_matrix, "mxfp4", None, swizzled=False)
+    kind, group = kind_of(0, hadamard_matrix)
+    if kind in ("hadamard", "identity") and group <= 32 and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 \
+            and x.shape[0] % 32 == 0:
+        # one pass: the transpose happens inside the quantise kernel
+        q, sb = ops.quantize_transposed(x, group if kind == "hadamard" else 0)
+        sb = _pad_rowmajor(sb, x.shape[1], x.shape[0] // 32)
+    else:
+        q, sb = _quantize(x.t().contiguous(), hadamard_matrix, "mxfp4", None, swizzled=False)
     return q, sb.view(torch.float8_e8m0fnu)
 
 

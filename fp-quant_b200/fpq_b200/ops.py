@@ -380,8 +380,10 @@ def mxfp4_transpose_mxfp8(codes: torch.Tensor, scales_rowmajor: torch.Tensor, sw
     return out, os_
 
 
-def mxfp4_transpose_dequant(codes: torch.Tensor, scales_rowmajor: torch.Tensor, alpha: torch.Tensor) -> torch.Tensor:
-    """MXFP4 (codes u8 [rows, cols/2], E8M0 bytes [rows, cols/32]) -> bf16 [cols, rows] = dequantised^T / alpha."""
+def mxfp4_transpose_dequant(codes: torch.Tensor, scales_rowmajor: torch.Tensor, alpha: torch.Tensor,
+                            pad_to: int = 1) -> torch.Tensor:
+    """MXFP4 (codes u8 [rows, cols/2], E8M0 bytes [rows, cols/32]) -> bf16 [cols, rows_pad] = dequantised^T / alpha,
+    rows_pad = rows rounded up to a multiple of `pad_to` (the padding columns are zero)."""
     codes = _cuda(codes, "codes").contiguous()
     sc = _cuda(scales_rowmajor, "scales")
     sc = (sc if sc.dtype == torch.uint8 else sc.view(torch.uint8)).contiguous()
@@ -389,11 +391,32 @@ def mxfp4_transpose_dequant(codes: torch.Tensor, scales_rowmajor: torch.Tensor, 
     if tuple(sc.shape) != (rows, cols // 32):
         raise ValueError(f"scales must be [{rows}, {cols // 32}] row-major bytes, got {tuple(sc.shape)}")
     alpha = _cuda(alpha, "alpha").to(torch.float32).reshape(1)
-    out = torch.empty(cols, rows, dtype=torch.bfloat16, device=codes.device)
+    rp = -(-rows // pad_to) * pad_to
+    out = (torch.empty if rp == rows else torch.zeros)(cols, rp, dtype=torch.bfloat16, device=codes.device)
     with _guard(codes.device):
-        C.call("fpq_mxfp4_transpose_dequant", codes.data_ptr(), sc.data_ptr(), rows, cols, alpha.data_ptr(), out.data_ptr(),
+        C.call("fpq_mxfp4_transpose_dequant", codes.data_ptr(), sc.data_ptr(), rows, cols, alpha.data_ptr(), out.data_ptr(), rp,
                _stream(codes))
     return out
+
+
+def quantize_transposed(x: torch.Tensor, hadamard_group: int = 0, pad_to: int = 32, swizzled: bool = False):
+    """MXFP4 of x^T for a bf16 matrix x [t, n] without materialising the transpose: (codes u8 [n, t_pad/2], E8M0 scale
+    bytes [n, t_pad/32] row-major or swizzled); t_pad = t rounded up to a multiple of `pad_to` (a multiple of 32),
+    the padding counts as zeros.  Rotation groups 0, 16 and 32."""
+    x = _cuda(x, "x")
+    if x.dtype != torch.bfloat16 or x.dim() != 2:
+        raise ValueError(f"x must be a 2-D bfloat16 tensor, got {x.dtype} {tuple(x.shape)}")
+    if pad_to % 32 != 0:
+        raise ValueError("pad_to must be a multiple of 32")
+    x = x.contiguous()
+    t, n = x.shape
+    tp = -(-t // pad_to) * pad_to
+    codes = torch.empty(n, tp // 2, dtype=torch.uint8, device=x.device)
+    sb = _scale_buffer(n, tp // 32, swizzled, x.device)
+    with _guard(x.device):
+        C.call("fpq_quantize_transposed", x.data_ptr(), t, n, tp, hadamard_group, codes.data_ptr(), sb.data_ptr(),
+               C.SCALES_SWIZZLED if swizzled else C.SCALES_ROWMAJOR, _stream(x))
+    return codes, sb
 
 
 # --------------------------------------------------------------------------- GPTQ core

@@ -248,10 +248,21 @@ int fpq_mxfp4_transpose_mxfp8(const uint8_t* codes, const uint8_t* scales_rowmaj
  * of the dequantised tensor, every element divided by *alpha (device fp32[1]: the tensor scale the operand
  * was quantised under) and rounded once to bf16.  First half of backward_qt_bf16 (qutlass_ops.py:248-274:
  * dequantise, transpose, rotate, quantise again); the second half is fpq_quantize on the result.
- * cols % 32 == 0.
+ * out_ld: row stride of the output in elements (>= rows; columns [rows, out_ld) are not written, so a caller
+ * that needs the contraction axis padded passes a zeroed buffer).  cols % 32 == 0.
  */
 int fpq_mxfp4_transpose_dequant(const uint8_t* codes, const uint8_t* scales_rowmajor, int64_t rows, int64_t cols,
-                                const float* alpha, void* out_bf16, fpq_stream_t stream);
+                                const float* alpha, void* out_bf16, int64_t out_ld, fpq_stream_t stream);
+
+/*
+ * MXFP4 of the TRANSPOSE of a bf16 matrix without materialising it: x [t_rows, n] row-major -> codes
+ * [n, t_pad/2] and E8M0 scale bytes of x^T, rotated (Hadamard group 0, 16 or 32) and scaled along the t axis;
+ * rows of x beyond t_rows count as zero (t_pad >= t_rows, a multiple of 32).  Same arithmetic as
+ * fpq_quantize on the transposed copy.  Stands for backward_t_bf16 (qutlass_ops.py:218-245): the upstream
+ * gradient as the operand of the weight-gradient GEMM, which contracts over the tokens.  n % 8 == 0.
+ */
+int fpq_quantize_transposed(const void* x_bf16, int64_t t_rows, int64_t n, int64_t t_pad, int hadamard_group,
+                            uint8_t* codes, uint8_t* scale_bytes, int scale_layout, fpq_stream_t stream);
 
 /*
  * Column-parallel form of fpq_gemm_fp4 for tensor parallelism over NVLink (no counterpart in the reference,

@@ -303,3 +303,49 @@ def test_mxfp4_backward_gradients(cuda_device, method):
     print(f"{method}: grad_input {ri:.3f} (cosine {cos_i:.4f}), grad_weight {rw:.3f} relative to the exact products")
     assert ri < 0.3 and rw < 0.3 and cos_i > 0.95
     assert torch.allclose(layer.bias.grad.float().cpu(), g.sum(0).float(), rtol=2e-2, atol=1e-3)
+
+
+@pytest.mark.parametrize("group", [0, 16, 32])
+@pytest.mark.parametrize("shape", [(256, 384), (200, 320), (1000, 1032), (33, 8)])
+def test_transposing_quantiser_equals_quantising_the_transpose(cuda_device, shape, group):
+    """`fpq_quantize_transposed` (the one-pass form of `backward_t_bf16`, qutlass_ops.py:218-245): same codes and
+    scale bytes as zero-padding the token axis, transposing on the host and quantising, in both scale layouts."""
+    from fpq_b200 import ops
+    from tests import inputs
+
+    t, n = shape
+    d = cuda_device
+    x = inputs.outlier_activations(t, n, seed=t + n).to(d)
+    tp = -(-t // 128) * 128
+    xt = torch.zeros(n, tp, dtype=torch.bfloat16, device=d)
+    xt[:, :t] = x.t()
+    want_q, want_s, _ = ops.quantize(xt, "mxfp4", group)
+    got_q, got_s = ops.quantize_transposed(x, group, pad_to=128)
+    assert got_q.shape == (n, tp // 2) and torch.equal(got_q, want_q) and torch.equal(got_s, want_s)
+    want_q2, want_s2, _ = ops.quantize(xt, "mxfp4", group, swizzled=True)
+    got_q2, got_s2 = ops.quantize_transposed(x, group, pad_to=128, swizzled=True)
+    assert torch.equal(got_q2, want_q2) and torch.equal(got_s2.flatten(), want_s2.flatten())
+
+
+def test_backward_t_op_takes_the_one_pass_form_for_the_hadamard_matrix(cuda_device):
+    from fpq_b200.fp_quant.module.qutlass_ops import backward_t_bf16_op, fused_quantize_mx_op
+    from tests import inputs
+
+    d = cuda_device
+    H = fp4_hadamard(32).bfloat16().to(d)
+    x = inputs.outlier_activations(256, 384, seed=9).to(d)
+    q, s = backward_t_bf16_op(x, H)
+    q_ref, s_ref, _ = fused_quantize_mx_op(x.t().contiguous(), H, "abs_max", False)
+    assert torch.equal(q, q_ref) and torch.equal(s.view(torch.uint8), s_ref.view(torch.uint8))
+
+
+def test_transposing_dequantiser_pads_the_contraction_axis(cuda_device):
+    from fpq_b200 import ops
+
+    g = torch.Generator().manual_seed(12)
+    codes = torch.randint(0, 256, (200, 64), generator=g, dtype=torch.uint8)
+    sb = torch.randint(110, 135, (200, 4), generator=g, dtype=torch.uint8)
+    got = ops.mxfp4_transpose_dequant(codes.to(cuda_device), sb.to(cuda_device), torch.tensor([3.0], device=cuda_device), pad_to=128)
+    want = mxfp8.fp4_transpose_dequant(codes, sb, 3.0)
+    assert got.shape == (128, 256)
+    assert torch.equal(got[:, :200].cpu().view(torch.int16), want.view(torch.int16)) and float(got[:, 200:].abs().max()) == 0.0
