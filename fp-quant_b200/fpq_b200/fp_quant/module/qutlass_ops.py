@@ -8,6 +8,10 @@ Two families:
     scale tensors out on every call;
   * the `*_blocked` ops are the fast path: quantise writes the swizzled layout directly and the
     matmul consumes it, so nothing is re-laid out per call.
+The ops of the quantised backward passes (`matmul_mxf8_bf16_tn_op` / `_nn_op`, `backward_t_bf16_op`,
+`backward_qt_bf16_op`, `backward_bf16_square_double_mxfp8_op`, `mxfp4_transpose_mxfp8_op`, qutlass_ops.py:171-330)
+keep the reference's names and shapes too; their arithmetic is defined by this library (QuTLASS is not part of
+the reference tree).
 All are registered as torch custom ops with fake implementations so that torch.compile(fullgraph=True)
 can trace through them.  The reference names live in the reference's own namespace `fp_quant::`
 (qutlass_ops.py:36, :54, :111 register `fp_quant::fused_quantize_mx_op` etc.), so code that reaches
