@@ -162,16 +162,31 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_fp8_kernel(const uint8_
     byte = (uint32_t)(e_sq + 127);
     shift = e_row - e_sq;                              // <= 6 for live rows; very negative rows round to zero
   }
+  // Every code of the row is scaled by the same power of two, so the 32 conversions are table look-ups: the
+  // E4M3 bytes of the eight FP4 magnitudes times 2^shift, once as they are and once with the sign bit (the
+  // zero stays +0 in both, as the code's "-0" must come out), selected four at a time with byte permutes.
+  uint32_t pa = 0, pb = 0, na = 0, nb = 0;
+  if (live) {
+    float m[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) m[i] = scale_pow2(e2m1_magnitude(i), shift);
+    pa = (uint32_t)e4m3x2(m[0], m[1]) | ((uint32_t)e4m3x2(m[2], m[3]) << 16);
+    pb = (uint32_t)e4m3x2(m[4], m[5]) | ((uint32_t)e4m3x2(m[6], m[7]) << 16);
+    na = (pa | 0x80808080u) & 0xffffff00u;
+    nb = pb | 0x80808080u;
+  }
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
 #pragma unroll
-    for (int j = 0; j < 8; j += 2) {
-      float a = live ? scale_pow2(e2m1_value((ws[q] >> (4 * j)) & 15u), shift) : 0.0f;
-      float b = live ? scale_pow2(e2m1_value((ws[q] >> (4 * j + 4)) & 15u), shift) : 0.0f;
-      const uint16_t p = e4m3x2(a + 0.0f, b + 0.0f);                 // "+ 0" turns the code's -0 into +0
-      tile[c * T8_SQ + (8 * q + j) * T8_ROW + r] = (uint8_t)(p & 0xffu);
-      tile[c * T8_SQ + (8 * q + j + 1) * T8_ROW + r] = (uint8_t)(p >> 8);
+    for (int half = 0; half < 2; ++half) {
+      const uint32_t x = half ? ws[q] >> 16 : ws[q];                   // four codes in the low 16 bits
+      const uint32_t sel = x & 0x7777u;                                // their magnitudes as byte selectors
+      const uint32_t pos = __byte_perm(pa, pb, sel), neg = __byte_perm(na, nb, sel);
+      const uint32_t o4 = __byte_perm(pos, neg, ((x & 0x8888u) >> 1) | 0x3210u);   // byte i from neg where code i is negative
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        tile[c * T8_SQ + (8 * q + 4 * half + i) * T8_ROW + r] = (uint8_t)(o4 >> (8 * i));
     }
   }
   __syncthreads();
