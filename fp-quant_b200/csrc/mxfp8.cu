@@ -220,24 +220,51 @@ __global__ void __launch_bounds__(THREADS) fp4_transpose_bf16_kernel(const uint8
     const int e = (int)scales[row * (cols / SQ) + sq_col] - 127;
     const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
     // fl((m 2^e) / a) = fl(m / a) 2^e while nothing leaves the normal range: seven divisions per row instead
-    // of thirty-two.  The bound on e keeps every quotient normal for 2^-20 < |a| < 2^20.
-    const bool table = e > -100 && e < 100 && fabsf(a) > 9.5367e-7f && fabsf(a) < 1.048576e6f;
-    float quot[8];
+    // of thirty-two, and the 32 conversions become table look-ups (low and high bytes of the eight bf16
+    // quotients, the high bytes once more with the sign bit; the zero stays +0), four codes per byte permute.
+    // The bound on e keeps every quotient normal for 2^-20 < a < 2^20.
+    const bool table = e > -100 && e < 100 && a > 9.5367e-7f && a < 1.048576e6f;
+    uint16_t* tile16 = reinterpret_cast<uint16_t*>(tile);
+    if (table) {
+      uint32_t lo_a = 0, lo_b = 0, hi_a = 0, hi_b = 0;
 #pragma unroll
-    for (int m = 0; m < 8; ++m) quot[m] = table ? scale_pow2(__fdiv_rn(e2m1_magnitude(m), a), e) : 0.0f;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t code = (ws[q] >> (4 * j)) & 15u;
-        float v;
-        if (table) {
-          v = quot[code & 7u];
-          v = (code & 8u) ? -v : v;
+      for (int m = 0; m < 8; ++m) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(scale_pow2(__fdiv_rn(e2m1_magnitude(m), a), e));
+        const uint32_t bits = *reinterpret_cast<const uint16_t*>(&h);
+        if (m < 4) {
+          lo_a |= (bits & 0xffu) << (8 * m);
+          hi_a |= (bits >> 8) << (8 * m);
         } else {
-          v = __fdiv_rn(scale_pow2(e2m1_value(code), e), a);
+          lo_b |= (bits & 0xffu) << (8 * (m - 4));
+          hi_b |= (bits >> 8) << (8 * (m - 4));
         }
-        tile[c * T16_SQ + (8 * q + j) * T16_ROW + r] = __float2bfloat16_rn(v + 0.0f);
+      }
+      const uint32_t nhi_a = (hi_a | 0x80808080u) & 0xffffff00u, nhi_b = hi_b | 0x80808080u;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const uint32_t x = half ? ws[q] >> 16 : ws[q];                 // four codes in the low 16 bits
+          const uint32_t sel = x & 0x7777u;
+          const uint32_t lo4 = __byte_perm(lo_a, lo_b, sel);
+          const uint32_t hi4 = __byte_perm(__byte_perm(hi_a, hi_b, sel), __byte_perm(nhi_a, nhi_b, sel),
+                                           ((x & 0x8888u) >> 1) | 0x3210u);
+          const uint32_t w01 = __byte_perm(lo4, hi4, 0x5140), w23 = __byte_perm(lo4, hi4, 0x7362);
+          uint16_t* col = tile16 + c * T16_SQ + (8 * q + 4 * half) * T16_ROW + r;
+          col[0] = (uint16_t)w01;
+          col[T16_ROW] = (uint16_t)(w01 >> 16);
+          col[2 * T16_ROW] = (uint16_t)w23;
+          col[3 * T16_ROW] = (uint16_t)(w23 >> 16);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = __fdiv_rn(scale_pow2(e2m1_value((ws[q] >> (4 * j)) & 15u), e), a);
+          tile[c * T16_SQ + (8 * q + j) * T16_ROW + r] = __float2bfloat16_rn(v + 0.0f);
+        }
       }
     }
   }
