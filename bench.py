@@ -1283,6 +1283,38 @@ def run_qat_step(args):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / args.steps
 
+    def graphed(layer):
+        """The same step replayed from a CUDA graph (forward and backward captured together): what the kernels
+        cost once the Python-level calls of a step are out of the way.  Returns ms per replay, or the reason
+        the capture failed."""
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    x.grad = None
+                    layer.weight.grad = None
+                    layer(x).backward(gy)
+            torch.cuda.current_stream().wait_stream(side)
+            x.grad = None
+            layer.weight.grad = None
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                layer(x).backward(gy)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / args.steps
+        except Exception as exc:      # noqa: BLE001
+            torch.cuda.synchronize()
+            return f"capture failed: {str(exc)[:160]}"
+
     with ClockSampler(0) as clocks:
         for name, bwd in (("bf16", FPQuantDtype.BF16), ("mxfp8", FPQuantDtype.MXFP8), ("mxfp4", FPQuantDtype.MXFP4)):
             layer = FPQuantLinear(K, N, FPQuantConfig(forward_dtype=FPQuantDtype.MXFP4, forward_method="abs_max", backward_dtype=bwd,
@@ -1291,11 +1323,11 @@ def run_qat_step(args):
             layer.weight.data.copy_(w)
             layer.pre_forward()
             ms = timed(layer)
-            results[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+            results[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "graph_replay_ms": graphed(layer)}
         plain = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
         plain.weight.data.copy_(w)
         ms = timed(plain)
-        results["nn.Linear bf16"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+        results["nn.Linear bf16"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12, "graph_replay_ms": graphed(plain)}
     ops.check_device_errors(dev)
     best = results["mxfp8"]
     line = {
