@@ -117,3 +117,27 @@ def test_weighted_bounds_cover_everything_in_order():
         assert len(b) == len(weights) and b[0][0] == 0 and b[-1][1] == n
         assert all(b[i][1] == b[i + 1][0] for i in range(len(b) - 1)) and all(hi >= lo for lo, hi in b)
     assert [hi - lo for lo, hi in fdist.weighted_bounds(128, [0.62] + [7.38 / 7] * 7)][0] == 10     # the tail owner's share
+
+
+@pytest.mark.parametrize("world_size", [1, 2, 3, 4, 5, 6, 7, 8, 16])
+def test_plan_ranks_invariants(world_size):
+    """Every linear of a block gets exactly one rank; the chains of the distinct Hessians go to different ranks
+    while there are enough (widest first, so the widest is rank 0's); a group's first linear stays with the
+    rank that factors its Hessian; the others only move to ranks that run no chain."""
+    from fpq_b200.quantization.driver import plan_ranks
+
+    members = {"qkv": ["q_proj", "k_proj", "v_proj"], "o": ["o_proj"], "gate_up": ["gate_proj", "up_proj"], "down": ["down_proj"]}
+    width = {"qkv": 4096, "o": 4096, "gate_up": 4096, "down": 14336}
+    order, chain_rank, loop_rank = plan_ranks(members, width, world_size)
+    assert order[0] == "down" and chain_rank["down"] == 0
+    assert sorted(loop_rank) == sorted(n for names in members.values() for n in names)
+    assert all(0 <= r < world_size for r in list(chain_rank.values()) + list(loop_rank.values()))
+    if world_size >= 4:
+        assert len(set(chain_rank.values())) == 4
+    chain_ranks = set(chain_rank.values())
+    for grp, names in members.items():
+        assert loop_rank[names[0]] == chain_rank[grp]
+        for n in names[1:]:
+            assert loop_rank[n] == chain_rank[grp] or loop_rank[n] not in chain_ranks
+    moved = [loop_rank[n] for grp, names in members.items() for n in names[1:] if loop_rank[n] != chain_rank[grp]]
+    assert len(moved) == len(set(moved)) == min(3, max(0, world_size - 4))      # one idle rank per moved linear
